@@ -1,0 +1,39 @@
+"""The CPU restatement in oracle/ against the golden outputs of the real reference model."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import bert_oracle
+
+FP32_TOL = 2e-5      # two fp32 evaluations of the same network in a different op order
+FP64_TOL = 1e-9      # fp64 restatement vs fp64 run of the reference module
+
+
+@pytest.mark.parametrize("name", list(cases.CASES.keys()))
+def test_oracle_matches_reference_outputs(name):
+    large, dims = cases.case_dims(name)
+    w = cases.get_weights(cases.CASES[name]["weights"])
+    ids, seg, mask = cases.case_inputs(name)
+    gold = cases.load_golden(name)
+    layers, pooled = bert_oracle.bert_forward(w, ids, seg, mask, dims["heads"], dims["layers"],
+                                              return_all=True)
+    tol = FP32_TOL if name != "edge_zero_row" else 2e-4   # -10000 + score rounds at 1e-3 in fp32
+    assert np.abs(pooled - gold["pooled"]).max() <= tol
+    assert np.abs(layers[0][:, :, :8] - gold["embed8"]).max() <= tol
+    assert np.abs(layers[1][:, :, :8] - gold["layer0_8"]).max() <= tol
+    assert np.abs(layers[-1][:, :, :8] - gold["last8"]).max() <= 10 * tol
+    assert np.abs(layers[-1][:, 0, :] - gold["cls_hidden"]).max() <= 10 * tol
+    probs = bert_oracle.classify(bert_oracle.Weights(w), torch.from_numpy(pooled)).numpy()
+    assert np.abs(probs - gold["probs"]).max() <= tol
+
+
+@pytest.mark.parametrize("name", ["c0", "edge_zero_row", "edge_holes"])
+def test_oracle_fp64_matches_reference_fp64(name):
+    large, dims = cases.case_dims(name)
+    w = cases.get_weights(cases.CASES[name]["weights"])
+    ids, seg, mask = cases.case_inputs(name)
+    gold = cases.load_golden(name)
+    _, pooled = bert_oracle.bert_forward(w, ids, seg, mask, dims["heads"], dims["layers"],
+                                         dtype=torch.float64)
+    assert np.abs(pooled - gold["pooled64"]).max() <= FP64_TOL
