@@ -1,0 +1,313 @@
+// extern "C" surface of libcudaBERT.so; declarations and the reference citations for every
+// entry point are in include/cudabert.h.
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/cudabert.h"
+#include "model.h"
+
+using cb::Model;
+
+namespace {
+
+thread_local std::string g_init_error;
+
+int precision_from_env() {
+  const char* p = std::getenv("CUDABERT_PRECISION");
+  if (!p || !*p) return cb::PREC_BF16;
+  const std::string s(p);
+  if (s == "fp32" || s == "0") return cb::PREC_FP32;
+  if (s == "bf16" || s == "1") return cb::PREC_BF16;
+  if (s == "fp8" || s == "2") return cb::PREC_FP8;
+  return -1;
+}
+
+Model* as_model(void* h) { return static_cast<Model*>(h); }
+
+// Non-CUDA errors (bad arguments, a device-side check) do not poison later calls.
+void begin_call(Model* m) {
+  if (m->status() != 0 && m->status() != 2) m->clear_error();
+}
+
+// The reference's seed input (cuda_bert/cuda_bert.cu:12-22, 94-103): an 11-token sequence whose
+// first 10 entries are cycled up to seq_length - 1 and whose last entry closes the row.
+std::vector<int> tile_seed(const int* seed, int seq_length, int batch) {
+  std::vector<int> out(static_cast<size_t>(seq_length) * batch);
+  for (int i = 0; i < seq_length - 1; ++i) out[i] = seed[i % 10];
+  out[seq_length - 1] = seed[10];
+  for (int b = 1; b < batch; ++b) std::memcpy(&out[static_cast<size_t>(b) * seq_length], &out[0], seq_length * sizeof(int));
+  return out;
+}
+
+struct DevErr {  // scratch error word for the single-kernel entry points
+  int* p = nullptr;
+  bool ok() {
+    if (!p && cudaMalloc(&p, sizeof(int)) != cudaSuccess) return false;
+    return cudaMemset(p, 0, sizeof(int)) == cudaSuccess;
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+void* cudabert_init_ex(bool large, int num_gpu, int max_batchsize, int max_seq_length, const char* dir, int precision,
+                       int num_layers) {
+  g_init_error.clear();
+  if (precision < 0) precision = precision_from_env();
+  if (precision < 0) {
+    g_init_error = "CUDABERT_PRECISION must be fp32, bf16 or fp8";
+    return nullptr;
+  }
+  if (max_batchsize < 0 || max_seq_length < 0) {
+    g_init_error = "max_batchsize and max_seq_length must be >= 0";
+    return nullptr;
+  }
+  Model* m = new Model();
+  if (!m->init(large, num_gpu, max_batchsize, max_seq_length, dir ? dir : "", precision, num_layers)) {
+    g_init_error = m->error();
+    delete m;
+    return nullptr;
+  }
+  return m;
+}
+
+void* init_model(bool large, int num_gpu, int max_batchsize, int max_seq_length, char* dir) {
+  return cudabert_init_ex(large, num_gpu, max_batchsize, max_seq_length, dir, -1, 0);
+}
+
+void release_model(void* model) { delete as_model(model); }
+
+Retval Cuda_Inference(void* model, int* words, int* token_types, int batchsize, int seq_length, int* masks) {
+  Retval r = {nullptr, nullptr};
+  Model* m = as_model(model);
+  if (!m) return r;
+  begin_call(m);
+  // run_host with no host outputs: inputs are staged and copied, results stay on the device
+  if (!m->run_host_keep(words, token_types, masks, batchsize, seq_length)) return r;
+  r.tensor = m->hidden_f32_dev();
+  r.pooled_output = m->pooled_dev();
+  return r;
+}
+
+void Cuda_Bert(void* model, float* output, int* words, int* token_types, int batchsize, int seq_length,
+               int* attention_mask) {
+  Model* m = as_model(model);
+  if (!m) return;
+  begin_call(m);
+  if (!output) {
+    m->set_error(1, "output must not be null");
+    return;
+  }
+  m->run_host(words, token_types, attention_mask, batchsize, seq_length, output, nullptr, 0);
+}
+
+void Cuda_Classify(void* model, float* output, int* words, int* token_types, int batchsize, int seq_length,
+                   int num_classes, int* attention_mask) {
+  Model* m = as_model(model);
+  if (!m) return;
+  begin_call(m);
+  if (!output) {
+    m->set_error(1, "output must not be null");
+    return;
+  }
+  m->run_host(words, token_types, attention_mask, batchsize, seq_length, nullptr, output, num_classes);
+}
+
+void test(int batchsize, int seq_length, int nIter, bool large, int num_gpu) {
+  if (batchsize < 1 || seq_length < 2 || nIter < 1) {
+    std::printf("test: need batchsize >= 1, seq_length >= 2, nIter >= 1\n");
+    return;
+  }
+  void* h = init_model(large, num_gpu, batchsize, seq_length, const_cast<char*>(""));
+  if (!h) {
+    std::printf("test: init_model failed: %s\n", g_init_error.c_str());
+    return;
+  }
+  Model* m = as_model(h);
+  const int word_seed[11] = {2040, 2001, 3958, 27227, 1029, 3958, 103, 2001, 1037, 13997, 11510};
+  const int type_seed[11] = {0, 0, 0, 0, 0, 1, 1, 1, 1, 1, 1};
+  const int mask_seed[11] = {1, 1, 1, 1, 1, 1, 1, 1, 0, 0, 0};
+  std::vector<int> ids = tile_seed(word_seed, seq_length, batchsize);
+  std::vector<int> seg = tile_seed(type_seed, seq_length, batchsize);
+  std::vector<int> msk = tile_seed(mask_seed, seq_length, batchsize);
+  std::vector<float> out(static_cast<size_t>(batchsize) * m->hidden());
+  std::printf(" Seq_length : %d\n Batchsize : %d\n%s\n", seq_length, batchsize,
+              large ? "Using large Model" : "Using Base Model");
+  for (int i = 0; i < 10; ++i) {
+    if (!m->run_host(ids.data(), seg.data(), msk.data(), batchsize, seq_length, out.data(), nullptr, 0)) {
+      std::printf("test: forward failed: %s\n", m->error().c_str());
+      delete m;
+      return;
+    }
+    if (i == 0) {
+      const int step = std::max(batchsize / 10, 1);
+      for (int b = 0; b < batchsize; b += step) {
+        std::printf("unit_test row %d:", b);
+        for (int j = 0; j < 10; ++j) std::printf(" %.6f", out[static_cast<size_t>(b) * m->hidden() + j]);
+        std::printf("\n");
+      }
+    }
+  }
+  cudaEvent_t start, stop;
+  cudaEventCreate(&start);
+  cudaEventCreate(&stop);
+  std::vector<float> latency(nIter);
+  double total = 0;
+  for (int i = 0; i < nIter; ++i) {
+    cudaEventRecord(start, m->stream());
+    m->run_host(ids.data(), seg.data(), msk.data(), batchsize, seq_length, out.data(), nullptr, 0);
+    cudaEventRecord(stop, m->stream());
+    cudaEventSynchronize(stop);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, start, stop);
+    latency[i] = ms;
+    total += ms;
+  }
+  std::sort(latency.begin(), latency.end());
+  std::printf(" 99 Latency : %fms\n", latency[std::min(nIter - 1, static_cast<int>(nIter * 0.99))]);
+  std::printf(" Throughput: %f batches per second (%f sequences per second)\n", nIter * 1000.0 / total,
+              nIter * 1000.0 / total * batchsize);
+  std::printf("Time= %.2f(ms)\n\n", total / nIter);
+  cudaEventDestroy(start);
+  cudaEventDestroy(stop);
+  delete m;
+}
+
+int cudabert_status(void* model) { return model ? as_model(model)->status() : (g_init_error.empty() ? 0 : 3); }
+
+const char* cudabert_last_error(void* model) {
+  if (!model) return g_init_error.c_str();
+  return as_model(model)->error().c_str();
+}
+
+int cudabert_hidden_size(void* model) { return model ? as_model(model)->hidden() : 0; }
+int cudabert_num_classes(void* model) { return model ? as_model(model)->num_classes() : 0; }
+
+int cudabert_forward_dev(void* model, const int* ids_dev, const int* seg_dev, const int* mask_dev, int batchsize,
+                         int seq_length) {
+  Model* m = as_model(model);
+  if (!m) return 1;
+  begin_call(m);
+  return m->forward_device(ids_dev, seg_dev, mask_dev, batchsize, seq_length, false, false) ? 0 : m->status();
+}
+
+int cudabert_sync(void* model) {
+  Model* m = as_model(model);
+  if (!m) return 1;
+  return m->sync() ? 0 : m->status();
+}
+
+float* cudabert_pooled_dev(void* model) { return model ? as_model(model)->pooled_dev() : nullptr; }
+void* cudabert_stream(void* model) { return model ? static_cast<void*>(as_model(model)->stream()) : nullptr; }
+long cudabert_launch_count(void* model) { return model ? as_model(model)->launches_last_forward() : 0; }
+void cudabert_profile_enable(void* model, int on) {
+  if (model) as_model(model)->set_profiling(on != 0);
+}
+void cudabert_profile_reset(void* model) {
+  if (model) as_model(model)->reset_profile();
+}
+int cudabert_profile_get(void* model, int kernel_class, double* total_ms, long* launches) {
+  if (!model || !total_ms || !launches) return 1;
+  as_model(model)->get_profile(kernel_class, total_ms, launches);
+  return 0;
+}
+
+// ------------------------------------------------------------------ single kernels
+int cudabert_k_gemm_bf16(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev, int flags,
+                         const float* bias_dev, const void* residual_dev, const float* colscale_dev, int* err_dev) {
+  if (!A_dev || !W_dev || !out_dev || M <= 0 || N <= 0 || K <= 0 || lda < K) return 1;
+  CUtensorMap tmA, tmW;
+  if (!cb::make_tmap_bf16_kmajor(&tmA, A_dev, M, K, static_cast<uint64_t>(lda) * 2, 128)) return 2;
+  if (!cb::make_tmap_bf16_kmajor(&tmW, W_dev, N, K, static_cast<uint64_t>(K) * 2, cb::gemm_block_n(N))) return 2;
+  static thread_local DevErr scratch;
+  int* err = err_dev;
+  if (!err) {
+    if (!scratch.ok()) return 2;
+    err = scratch.p;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cb::GemmEpilogue epi;
+  epi.flags = flags;
+  epi.bias = bias_dev;
+  epi.residual = residual_dev;
+  epi.colscale = colscale_dev;
+  const int n = cb::gemm_bf16_tcgen05(&tmA, &tmW, M, N, K, out_dev, N, epi, err, sms, nullptr);
+  if (n < 0) return 3;
+  if (cudaDeviceSynchronize() != cudaSuccess) return 4;
+  int herr = 0;
+  if (cudaMemcpy(&herr, err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return 4;
+  return herr ? 5 : 0;
+}
+
+int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, int N, int K, float* out_dev,
+                        int flags, const float* bias_dev, const float* residual_dev) {
+  cb::GemmEpilogue epi;
+  epi.flags = flags;
+  epi.bias = bias_dev;
+  epi.residual = residual_dev;
+  const int n = cb::gemm_f32(A_dev, lda, W_dev, M, N, K, out_dev, N, epi, nullptr);
+  if (n < 0) return 3;
+  return cudaDeviceSynchronize() == cudaSuccess ? 0 : 4;
+}
+
+int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads) {
+  if (!qkv_dev || !ctx_dev || B <= 0 || S <= 0 || heads <= 0) return 1;
+  int* kv = nullptr;
+  if (cudaMalloc(&kv, static_cast<size_t>(B) * sizeof(int)) != cudaSuccess) return 2;
+  int rc = 0;
+  if (cb::mask_to_kv_len(mask_dev, kv, B, S, nullptr) < 0) rc = 3;
+  if (!rc) {
+    const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv,
+                                            static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr)
+                       : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv,
+                                           static_cast<float*>(ctx_dev), B, S, heads, nullptr);
+    if (n < 0) rc = 3;
+  }
+  if (cudaDeviceSynchronize() != cudaSuccess) rc = 4;
+  cudaFree(kv);
+  return rc;
+}
+
+int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev, const void* word_dev,
+                               const void* pos_dev, const void* type_dev, const float* gamma_dev,
+                               const float* beta_dev, void* out_dev, int tokens, int S, int H, int vocab) {
+  static thread_local DevErr scratch;
+  if (!scratch.ok()) return 2;
+  int n;
+  if (bf16)
+    n = cb::embed_layernorm<__nv_bfloat16>(ids_dev, seg_dev, static_cast<const __nv_bfloat16*>(word_dev),
+                                           static_cast<const __nv_bfloat16*>(pos_dev),
+                                           static_cast<const __nv_bfloat16*>(type_dev), gamma_dev, beta_dev,
+                                           static_cast<__nv_bfloat16*>(out_dev), tokens, S, H, vocab, scratch.p, nullptr);
+  else
+    n = cb::embed_layernorm<float>(ids_dev, seg_dev, static_cast<const float*>(word_dev),
+                                   static_cast<const float*>(pos_dev), static_cast<const float*>(type_dev), gamma_dev,
+                                   beta_dev, static_cast<float*>(out_dev), tokens, S, H, vocab, scratch.p, nullptr);
+  if (n < 0) return 3;
+  if (cudaDeviceSynchronize() != cudaSuccess) return 4;
+  int herr = 0;
+  cudaMemcpy(&herr, scratch.p, sizeof(int), cudaMemcpyDeviceToHost);
+  return herr ? 5 : 0;
+}
+
+int cudabert_k_layernorm(int bf16, const void* x_dev, const float* gamma_dev, const float* beta_dev, void* out_dev,
+                         int tokens, int H) {
+  int n;
+  if (bf16)
+    n = cb::layernorm<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(x_dev), gamma_dev, beta_dev,
+                                     static_cast<__nv_bfloat16*>(out_dev), nullptr, tokens, H, nullptr);
+  else
+    n = cb::layernorm<float>(static_cast<const float*>(x_dev), gamma_dev, beta_dev, static_cast<float*>(out_dev),
+                             nullptr, tokens, H, nullptr);
+  if (n < 0) return 3;
+  return cudaDeviceSynchronize() == cudaSuccess ? 0 : 4;
+}
+
+}  // extern "C"

@@ -1,0 +1,320 @@
+// Fused masked scaled-dot-product attention: QK^T, 1/8 scale, additive key mask, softmax and
+// P.V in one kernel, never materialising the [B, S, heads, S] score tensor.  It replaces
+// Query_Key::forward (ops/batch_matmul.cu:24-82), op_SoftMax::forward / cuApplySoftmax
+// (ops/softmax.cu:86-143) and Prob_Value::forward (ops/batch_matmul.cu:85-140) of the
+// reference, and reads Q, K, V straight from the packed projection output [T, 3H].
+//
+// Mask semantics (ops/softmax.cu:97-101, modeling.py:237-240): score/8 + (1-mask[key])*-10000.
+// A masked key's probability is exactly 0 in fp32 whenever the row has at least one valid key,
+// so key tiles at or beyond kv_len[b] (all padding) are skipped.  A row with no valid key
+// gives every key the same -10000, which softmax ignores: the kernels then attend to all keys.
+#include "kernels.h"
+#include "ptx.cuh"
+
+#include <cmath>
+
+namespace cb {
+namespace {
+
+constexpr int HD = 64;     // head size
+constexpr int AQ = 64;     // queries per CTA (4 warps x 16 rows)
+constexpr int AK = 64;     // keys per shared-memory tile
+constexpr int PITCH = 72;  // bf16 elements per smem row: 144 bytes, conflict-free for ldmatrix
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void load_tile_async(__nv_bfloat16 (*dst)[PITCH], const __nv_bfloat16* src_base, int ld,
+                                                int row0, int rows_limit, int tid) {
+  // 64 rows x 8 chunks of 16 bytes; 128 threads x 4 chunks
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = tid + i * 128;
+    const int r = idx >> 3, c = idx & 7;
+    const bool ok = (row0 + r) < rows_limit;
+    const __nv_bfloat16* src = src_base + static_cast<size_t>(ok ? row0 + r : 0) * ld + c * 8;
+    cp_async16(smem_u32(&dst[r][c * 8]), src, ok);
+  }
+}
+
+__global__ void __launch_bounds__(128)
+attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ mask,
+                      const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ ctx, int S, int heads) {
+  __shared__ __align__(16) __nv_bfloat16 sQ[AQ][PITCH];
+  __shared__ __align__(16) __nv_bfloat16 sK[2][AK][PITCH];
+  __shared__ __align__(16) __nv_bfloat16 sV[2][AK][PITCH];
+  __shared__ float sBias[2][AK];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q0 = blockIdx.x * AQ, h = blockIdx.y, b = blockIdx.z;
+  const int H = heads * HD, ld = 3 * H;
+  int klen = kv_len[b];
+  const bool use_mask = (klen > 0) && (mask != nullptr);
+  if (klen <= 0) klen = S;
+  const int ntiles = (klen + AK - 1) / AK;
+  const __nv_bfloat16* base = qkv + static_cast<size_t>(b) * S * ld + h * HD;
+  const int* mrow = mask ? mask + static_cast<size_t>(b) * S : nullptr;
+
+  auto load_bias = [&](int buf, int k0) {
+    if (tid < AK) {
+      const int key = k0 + tid;
+      float v = 0.f;
+      if (key >= klen) v = -INFINITY;
+      else if (use_mask && mrow[key] == 0) v = -10000.0f * LOG2E;
+      sBias[buf][tid] = v;
+    }
+  };
+
+  load_tile_async(sQ, base, ld, q0, S, tid);
+  load_tile_async(sK[0], base + H, ld, 0, S, tid);
+  load_tile_async(sV[0], base + 2 * H, ld, 0, S, tid);
+  cp_async_commit();
+  load_bias(0, 0);
+
+  float o[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  uint32_t qf[4][4];
+  const float scale = 0.125f * LOG2E;
+
+  for (int t = 0; t < ntiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < ntiles) {
+      load_tile_async(sK[buf ^ 1], base + H, ld, (t + 1) * AK, S, tid);
+      load_tile_async(sV[buf ^ 1], base + 2 * H, ld, (t + 1) * AK, S, tid);
+      cp_async_commit();
+      load_bias(buf ^ 1, (t + 1) * AK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    if (t == 0) {
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        ldmatrix_x4(qf[kk], smem_u32(&sQ[warp * 16 + (lane & 15)][kk * 16 + (lane >> 4) * 8]));
+    }
+
+    // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        uint32_t kf[4];
+        const int mid = lane >> 3;
+        ldmatrix_x4(kf, smem_u32(&sK[buf][nb * 16 + (mid >> 1) * 8 + (lane & 7)][kk * 16 + (mid & 1) * 8]));
+        mma_bf16_16816(s[2 * nb], qf[kk], kf[0], kf[1]);
+        mma_bf16_16816(s[2 * nb + 1], qf[kk], kf[2], kf[3]);
+      }
+    }
+
+    // scale + mask bias (log2 domain), running max
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float b0 = sBias[buf][i * 8 + 2 * (lane & 3)];
+      const float b1 = sBias[buf][i * 8 + 2 * (lane & 3) + 1];
+      s[i][0] = fmaf(s[i][0], scale, b0);
+      s[i][1] = fmaf(s[i][1], scale, b1);
+      s[i][2] = fmaf(s[i][2], scale, b0);
+      s[i][3] = fmaf(s[i][3], scale, b1);
+      tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
+      tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+    }
+    float alpha[2], m_new[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      m_new[r] = fmaxf(m_run[r], tmax[r]);
+      // tile 0 always holds key 0 with a finite bias, so m_new is finite from the first tile on
+      alpha[r] = exp2f(m_run[r] - m_new[r]);
+      m_run[r] = m_new[r];
+      l_run[r] *= alpha[r];
+    }
+    uint32_t pf[4][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float p0 = exp2f(s[i][0] - m_new[0]);
+      const float p1 = exp2f(s[i][1] - m_new[0]);
+      const float p2 = exp2f(s[i][2] - m_new[1]);
+      const float p3 = exp2f(s[i][3] - m_new[1]);
+      l_run[0] += p0 + p1;
+      l_run[1] += p2 + p3;
+      pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+    // O += P V : 4 key steps of 16, 4 pairs of 8-wide d tiles
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int db = 0; db < 4; ++db) {
+        uint32_t vf[4];
+        const int mid = lane >> 3;
+        ldmatrix_x4_trans(vf, smem_u32(&sV[buf][j * 16 + (mid & 1) * 8 + (lane & 7)][db * 16 + (mid >> 1) * 8]));
+        mma_bf16_16816(o[2 * db], pf[j], vf[0], vf[1]);
+        mma_bf16_16816(o[2 * db + 1], pf[j], vf[2], vf[3]);
+      }
+    }
+    __syncthreads();  // the next iteration's prefetch overwrites the other buffer
+  }
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
+  const int row0 = q0 + warp * 16 + (lane >> 2);
+  __nv_bfloat16* out_base = ctx + static_cast<size_t>(b) * S * H + h * HD + 2 * (lane & 3);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (row0 < S)
+      *reinterpret_cast<uint32_t*>(out_base + static_cast<size_t>(row0) * H + i * 8) =
+          pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+    if (row0 + 8 < S)
+      *reinterpret_cast<uint32_t*>(out_base + static_cast<size_t>(row0 + 8) * H + i * 8) =
+          pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+  }
+}
+
+// ---------------------------------------------------------------- fp32 path
+constexpr int FQ = 32;  // queries per CTA: 8 warps x 4 queries
+constexpr int FK = 32;  // keys per chunk: one per lane
+
+__global__ void __launch_bounds__(256)
+attention_f32_kernel(const float* __restrict__ qkv, const int* __restrict__ mask, const int* __restrict__ kv_len,
+                     float* __restrict__ ctx, int S, int heads) {
+  __shared__ float sQ[FQ][HD];
+  __shared__ float sK[FK][HD + 1];
+  __shared__ float sV[FK][HD];
+  __shared__ float sBias[FK];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q0 = blockIdx.x * FQ, h = blockIdx.y, b = blockIdx.z;
+  const int H = heads * HD, ld = 3 * H;
+  int klen = kv_len[b];
+  const bool use_mask = (klen > 0) && (mask != nullptr);
+  if (klen <= 0) klen = S;
+  const float* base = qkv + static_cast<size_t>(b) * S * ld + h * HD;
+  const int* mrow = mask ? mask + static_cast<size_t>(b) * S : nullptr;
+
+  for (int i = tid; i < FQ * HD; i += 256) {
+    const int r = i / HD, c = i % HD;
+    sQ[r][c] = (q0 + r < S) ? base[static_cast<size_t>(q0 + r) * ld + c] : 0.f;
+  }
+  float m_run[4], l_run[4], o0[4], o1[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) { m_run[q] = -INFINITY; l_run[q] = 0.f; o0[q] = 0.f; o1[q] = 0.f; }
+
+  for (int k0 = 0; k0 < klen; k0 += FK) {
+    __syncthreads();
+    for (int i = tid; i < FK * HD; i += 256) {
+      const int r = i / HD, c = i % HD;
+      const bool ok = (k0 + r) < S;
+      sK[r][c] = ok ? base[static_cast<size_t>(k0 + r) * ld + H + c] : 0.f;
+      sV[r][c] = ok ? base[static_cast<size_t>(k0 + r) * ld + 2 * H + c] : 0.f;
+    }
+    if (tid < FK) {
+      const int key = k0 + tid;
+      float v = 0.f;
+      if (key >= klen) v = -INFINITY;
+      else if (use_mask && mrow[key] == 0) v = -10000.0f;
+      sBias[tid] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float* qr = sQ[warp * 4 + q];
+      float s = 0.f;
+#pragma unroll 16
+      for (int d = 0; d < HD; ++d) s = fmaf(qr[d], sK[lane][d], s);
+      s = s * 0.125f + sBias[lane];
+      float mx = s;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const float m_new = fmaxf(m_run[q], mx);
+      const float alpha = expf(m_run[q] - m_new);
+      const float p = expf(s - m_new);
+      float ps = p;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+      l_run[q] = l_run[q] * alpha + ps;
+      m_run[q] = m_new;
+      float a0 = o0[q] * alpha, a1 = o1[q] * alpha;
+#pragma unroll
+      for (int j = 0; j < FK; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, p, j);
+        a0 = fmaf(pj, sV[j][lane], a0);
+        a1 = fmaf(pj, sV[j][lane + 32], a1);
+      }
+      o0[q] = a0;
+      o1[q] = a1;
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int row = q0 + warp * 4 + q;
+    if (row < S) {
+      float* dst = ctx + (static_cast<size_t>(b) * S + row) * H + h * HD;
+      dst[lane] = o0[q] / l_run[q];
+      dst[lane + 32] = o1[q] / l_run[q];
+    }
+  }
+}
+
+__global__ void mask_to_kv_len_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int B, int S) {
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= B) return;
+  int last = 0;
+  if (mask == nullptr) {
+    last = S;
+  } else {
+    const int* row = mask + static_cast<size_t>(b) * S;
+    for (int i = lane; i < S; i += 32)
+      if (row[i] != 0) last = i + 1;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, off));
+  }
+  if (lane == 0) kv_len[b] = last;
+}
+
+}  // namespace
+
+int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, __nv_bfloat16* ctx, int B, int S,
+                   int heads, cudaStream_t stream) {
+  if (B <= 0 || S <= 0 || heads <= 0 || B > 65535) return -1;
+  dim3 grid((S + AQ - 1) / AQ, heads, B);
+  attention_bf16_kernel<<<grid, 128, 0, stream>>>(qkv, mask, kv_len, ctx, S, heads);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+int attention_f32(const float* qkv, const int* mask, const int* kv_len, float* ctx, int B, int S, int heads,
+                  cudaStream_t stream) {
+  if (B <= 0 || S <= 0 || heads <= 0 || B > 65535) return -1;
+  dim3 grid((S + FQ - 1) / FQ, heads, B);
+  attention_f32_kernel<<<grid, 256, 0, stream>>>(qkv, mask, kv_len, ctx, S, heads);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+int mask_to_kv_len(const int* mask, int* kv_len, int B, int S, cudaStream_t stream) {
+  if (B <= 0 || S <= 0) return -1;
+  const int warps_per_block = 4;
+  mask_to_kv_len_kernel<<<(B + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, stream>>>(mask, kv_len,
+                                                                                                            B, S);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+}  // namespace cb

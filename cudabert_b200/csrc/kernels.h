@@ -1,0 +1,86 @@
+// Host-side launchers of the hot-path kernels.  Every launcher enqueues on `stream`, never
+// synchronises, never allocates, and returns the number of kernels it launched (>= 1) or a
+// negative value when the arguments are rejected.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace cb {
+
+// Epilogue selection, shared by the tcgen05 and the fp32 GEMM:
+//   out = act( acc * colscale[n] + bias[n] + residual[m, n] )
+enum EpiFlags : int {
+  EPI_BIAS = 1,      // add bias[n] (fp32)
+  EPI_GELU = 2,      // erf GELU (reference: ops/elementwise.cu:38-42)
+  EPI_RESIDUAL = 4,  // add residual[m, n] (same element type and row stride as out)
+  EPI_TANH = 8,      // tanh (pooler, reference: ops/elementwise.cu:57-61)
+  EPI_OUT_F32 = 16,  // write fp32 instead of bf16 (tcgen05 GEMM only; the fp32 GEMM always does)
+  EPI_COLSCALE = 32  // multiply the accumulator by colscale[n] (FP8 weight de-quantisation)
+};
+
+struct GemmEpilogue {
+  int flags = 0;
+  const float* bias = nullptr;
+  const void* residual = nullptr;
+  const float* colscale = nullptr;
+};
+
+// ---- tcgen05 GEMM: out[M, N] = A[M, K] (bf16, K contiguous) x W[N, K]^T (bf16, K contiguous)
+// N must be a multiple of 128 and K of 64; M is arbitrary (tail rows are zero-filled by TMA
+// and never stored).  `tmA` / `tmW` are tiled tensor maps made by make_tmap_bf16_kmajor with
+// box rows 128 (A) and 128 or 256 (W, must equal the block_n that is picked: 256 when N is
+// a multiple of 256, else 128).
+int gemm_bf16_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
+                      const GemmEpilogue& epi, int* err_flag, int num_sms, cudaStream_t stream);
+int gemm_block_n(int N);
+// Encode a 2-D tiled map over a row-major bf16 matrix [rows, cols] with `row_stride_bytes`
+// between rows, box = 64 columns (128 bytes, 128-byte swizzle) x `box_rows` rows.
+bool make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                           uint64_t row_stride_bytes, uint32_t box_rows);
+
+// ---- fp32 CUDA-core GEMM: out[M, N] = A[M, K] (fp32, row stride lda) x W[K, N] (fp32, the
+// on-disk [in, out] layout).  N % 4 == 0, K % 4 == 0.
+int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float* out, int ldo,
+             const GemmEpilogue& epi, cudaStream_t stream);
+
+// ---- masked attention.  qkv is [T, 3H] (Q | K | V column blocks, head h at columns h*64),
+// ctx is [T, H].  kv_len[b] > 0: keys >= kv_len[b] are all masked and are skipped; the
+// int32 key mask (may be null) is applied to the keys below kv_len.  kv_len[b] == 0: the row
+// has no valid key, every key gets the same -10000 so the mask is ignored (softmax is shift
+// invariant).  Head size is 64.
+int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, __nv_bfloat16* ctx, int B, int S,
+                   int heads, cudaStream_t stream);
+int attention_f32(const float* qkv, const int* mask, const int* kv_len, float* ctx, int B, int S, int heads,
+                  cudaStream_t stream);
+// kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none); mask null => S.
+int mask_to_kv_len(const int* mask, int* kv_len, int B, int S, cudaStream_t stream);
+
+// ---- row-wise kernels (T = float or __nv_bfloat16 for tables / activations)
+// out[t] = LayerNorm(word[ids[t]] + pos[t % S] + type[seg[t]]) ; err bit 1 set on a bad id.
+template <typename T>
+int embed_layernorm(const int* ids, const int* seg, const T* word, const T* pos, const T* type,
+                    const float* gamma, const float* beta, T* out, int tokens, int S, int H, int vocab,
+                    int* err_flag, cudaStream_t stream);
+// out[t] = LayerNorm(x[t]) * gamma + beta ; optional fp32 copy of the result.
+template <typename T>
+int layernorm(const T* x, const float* gamma, const float* beta, T* out, float* out_f32, int tokens, int H,
+              cudaStream_t stream);
+// probs[b, :] = softmax(pooled[b, :] . W[H, C] + bias[C]),  C <= 32
+int classify_softmax(const float* pooled, const float* W, const float* bias, float* probs, int B, int H, int C,
+                     cudaStream_t stream);
+
+// ---- weight preparation (load time)
+// dst[n, k] = bf16(src[k, n])  (on-disk [in, out] -> K-contiguous [out, in]); dst row offset lets
+// Q, K, V be packed into one [3H, H] operand.
+int transpose_to_bf16(const float* src, __nv_bfloat16* dst, int K, int N, cudaStream_t stream);
+// FP8 weights: q[n, k] = e4m3(src[k, n] / scale) stored as bytes, and the same values widened
+// exactly to bf16 for the tensor-core operand; scale = maxabs / 448 is computed on the device
+// and written to *scale_out.
+int quantize_fp8_weight(const float* src, uint8_t* dst_q, __nv_bfloat16* dst_op, float* scale_out, int K, int N,
+                        cudaStream_t stream);
+int convert_f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
+int fill_f32(float* dst, float value, size_t n, cudaStream_t stream);
+
+}  // namespace cb

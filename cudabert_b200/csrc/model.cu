@@ -1,0 +1,526 @@
+#include "model.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "npy.h"
+
+namespace cb {
+
+namespace {
+constexpr int MAX_CLASSES = 32;
+constexpr int MAX_SEQ = 512;
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+}  // namespace
+
+bool Model::fail(int code, const std::string& msg) {
+  if (status_ == 0) {
+    status_ = code;
+    error_ = msg;
+  }
+  if (std::getenv("CUDABERT_VERBOSE")) std::fprintf(stderr, "[cudaBERT] error %d: %s\n", code, msg.c_str());
+  return false;
+}
+
+bool Model::check(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return true;
+  return fail(2, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+Model::~Model() {
+  cudaSetDevice(dev_);
+  if (stream_) cudaStreamSynchronize(stream_);
+  for (void* p : owned_) cudaFree(p);
+  if (arena_) cudaFree(arena_);
+  if (hidden_f32_) cudaFree(hidden_f32_);
+  if (stage_f32_) cudaFree(stage_f32_);
+  if (err_dev_) cudaFree(err_dev_);
+  if (h_in_) cudaFreeHost(h_in_);
+  if (h_out_) cudaFreeHost(h_out_);
+  if (h_err_) cudaFreeHost(h_err_);
+  for (cudaEvent_t e : ev_) cudaEventDestroy(e);
+  if (stream_) cudaStreamDestroy(stream_);
+}
+
+bool Model::init(bool large, int gpu, int max_batch, int max_seq, const std::string& dir, int precision,
+                 int num_layers) {
+  if (precision < PREC_FP32 || precision > PREC_FP8) return fail(1, "precision must be 0 (fp32), 1 (bf16) or 2 (fp8)");
+  int ndev = 0;
+  if (!check(cudaGetDeviceCount(&ndev), "cudaGetDeviceCount")) return false;
+  if (gpu < 0 || gpu >= ndev) return fail(1, "gpu id out of range");
+  dev_ = gpu;
+  if (!check(cudaSetDevice(gpu), "cudaSetDevice")) return false;
+  cudaDeviceProp prop;
+  if (!check(cudaGetDeviceProperties(&prop, gpu), "cudaGetDeviceProperties")) return false;
+  if (prop.major != 10) return fail(2, "this library is built for sm_100a (B200) only");
+  num_sms_ = prop.multiProcessorCount;
+  large_ = large;
+  // model dimensions are fixed by the `large` flag, as in utils/manager.cu:8-15
+  if (large) { L_ = 24; H_ = 1024; heads_ = 16; F_ = 4096; }
+  else       { L_ = 12; H_ = 768;  heads_ = 12; F_ = 3072; }
+  if (num_layers > 0) L_ = std::min(L_, num_layers);
+  prec_ = precision;
+  esize_ = (precision == PREC_FP32) ? 4 : 2;
+  if (!check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
+  if (!check(cudaMalloc(&err_dev_, sizeof(int)), "cudaMalloc")) return false;
+  if (!check(cudaMemset(err_dev_, 0, sizeof(int)), "cudaMemset")) return false;
+  if (!check(cudaMallocHost(&h_err_, sizeof(int)), "cudaMallocHost")) return false;
+  *h_err_ = 0;
+  // default directories of the reference (utils/manager.cu:8-17)
+  dir_ = dir.empty() ? (large ? "model_npy/large_uncased" : "model_npy/base_uncased") : dir;
+  if (!load_weights(dir_)) return false;
+  if (max_batch > 0 && max_seq > 0) {
+    if (max_seq > MAX_SEQ) return fail(1, "max_seq_length exceeds the 512 positions of the position table");
+    if (!ensure_capacity(max_batch, max_seq, false)) return false;
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------ weight loading
+const std::string* Model::find_file(const std::vector<std::string>& keys) const {
+  // first file (sorted by name) whose NAME contains every key -- the reference matches the
+  // same way on the full path in directory order (utils/load_model.cc:15-37)
+  for (const std::string& f : files_) {
+    bool all = true;
+    for (const std::string& k : keys)
+      if (f.find(k) == std::string::npos) { all = false; break; }
+    if (all) return &f;
+  }
+  return nullptr;
+}
+
+bool Model::read_tensor(const std::vector<std::string>& keys, size_t expect, NpyArray* arr) {
+  const std::string* f = find_file(keys);
+  if (!f) {
+    std::string k;
+    for (const auto& s : keys) k += " " + s;
+    return fail(3, "no weight file in " + dir_ + " matches keys:" + k);
+  }
+  std::string err;
+  if (!load_npy_f32(dir_ + "/" + *f, arr, &err)) return fail(3, err);
+  if (expect && arr->numel() != expect)
+    return fail(3, *f + ": has " + std::to_string(arr->numel()) + " elements, expected " + std::to_string(expect));
+  if (arr->numel() > stage_elems_) {
+    if (stage_f32_) cudaFree(stage_f32_);
+    stage_f32_ = nullptr;
+    stage_elems_ = 0;
+    if (!check(cudaMalloc(&stage_f32_, arr->numel() * sizeof(float)), "cudaMalloc(staging)")) return false;
+    stage_elems_ = arr->numel();
+  }
+  if (!check(cudaMemcpyAsync(stage_f32_, arr->data.data(), arr->numel() * sizeof(float), cudaMemcpyHostToDevice,
+                             stream_), "weight upload"))
+    return false;
+  return check(cudaStreamSynchronize(stream_), "weight upload");
+}
+
+bool Model::upload_vec(const std::vector<std::string>& keys, size_t n, float** dst) {
+  NpyArray a;
+  if (!read_tensor(keys, n, &a)) return false;
+  if (!*dst) {
+    if (!check(cudaMalloc(dst, n * sizeof(float)), "cudaMalloc")) return false;
+    owned_.push_back(*dst);
+  }
+  if (!check(cudaMemcpyAsync(*dst, stage_f32_, n * sizeof(float), cudaMemcpyDeviceToDevice, stream_), "copy"))
+    return false;
+  return check(cudaStreamSynchronize(stream_), "copy");
+}
+
+bool Model::upload_table(const std::vector<std::string>& keys, size_t min_rows, void** dst, int* rows_out) {
+  NpyArray a;
+  if (!read_tensor(keys, 0, &a)) return false;
+  if (a.shape.size() != 2 || a.shape[1] != static_cast<size_t>(H_) || a.shape[0] < min_rows)
+    return fail(3, "embedding table has the wrong shape");
+  if (rows_out) *rows_out = static_cast<int>(a.shape[0]);
+  const size_t n = a.numel();
+  if (!check(cudaMalloc(dst, n * esize_), "cudaMalloc")) return false;
+  owned_.push_back(*dst);
+  if (prec_ == PREC_FP32) {
+    if (!check(cudaMemcpyAsync(*dst, stage_f32_, n * 4, cudaMemcpyDeviceToDevice, stream_), "copy")) return false;
+  } else if (convert_f32_to_bf16(stage_f32_, static_cast<__nv_bfloat16*>(*dst), n, stream_) < 0) {
+    return fail(2, "convert launch failed");
+  }
+  return check(cudaStreamSynchronize(stream_), "table conversion");
+}
+
+bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::vector<std::string>& keys_bias, int K,
+                       int N, DenseWeight* d, int n_off, int n_total) {
+  if (n_off == 0) {
+    d->K = K;
+    d->N = n_total;
+    const size_t elems = static_cast<size_t>(K) * n_total;
+    if (!check(cudaMalloc(&d->w, elems * esize_), "cudaMalloc")) return false;
+    owned_.push_back(d->w);
+    if (!check(cudaMalloc(&d->bias, n_total * sizeof(float)), "cudaMalloc")) return false;
+    owned_.push_back(d->bias);
+    if (prec_ == PREC_FP8) {
+      if (!check(cudaMalloc(&d->w_fp8, elems), "cudaMalloc")) return false;
+      owned_.push_back(d->w_fp8);
+      if (!check(cudaMalloc(&d->colscale, n_total * sizeof(float)), "cudaMalloc")) return false;
+      owned_.push_back(d->colscale);
+    }
+  }
+  NpyArray a;
+  if (!read_tensor(keys_kernel, static_cast<size_t>(K) * N, &a)) return false;
+  if (a.shape.size() != 2 || a.shape[0] != static_cast<size_t>(K) || a.shape[1] != static_cast<size_t>(N))
+    return fail(3, "dense kernel is not stored [in, out]");
+  if (prec_ == PREC_FP32) {
+    // keep [K, N]; Q, K, V are packed side by side into [K, 3H]
+    float* base = static_cast<float*>(d->w) + n_off;
+    if (!check(cudaMemcpy2DAsync(base, static_cast<size_t>(n_total) * 4, stage_f32_, static_cast<size_t>(N) * 4,
+                                 static_cast<size_t>(N) * 4, K, cudaMemcpyDeviceToDevice, stream_), "pack"))
+      return false;
+  } else if (prec_ == PREC_BF16) {
+    if (transpose_to_bf16(stage_f32_, static_cast<__nv_bfloat16*>(d->w) + static_cast<size_t>(n_off) * K, K, N,
+                          stream_) < 0)
+      return fail(2, "transpose launch failed");
+  } else {
+    float* scale_dev = d->colscale + n_off;  // first element of the segment doubles as the scalar slot
+    if (quantize_fp8_weight(stage_f32_, d->w_fp8 + static_cast<size_t>(n_off) * K,
+                            static_cast<__nv_bfloat16*>(d->w) + static_cast<size_t>(n_off) * K, scale_dev, K, N,
+                            stream_) < 0)
+      return fail(2, "quantise launch failed");
+    float scale = 0.f;
+    if (!check(cudaMemcpyAsync(&scale, scale_dev, sizeof(float), cudaMemcpyDeviceToHost, stream_), "scale")) return false;
+    if (!check(cudaStreamSynchronize(stream_), "scale")) return false;
+    if (fill_f32(scale_dev, scale, N, stream_) < 0) return fail(2, "fill launch failed");
+  }
+  if (!check(cudaStreamSynchronize(stream_), "weight conversion")) return false;
+  NpyArray b;
+  if (!read_tensor(keys_bias, N, &b)) return false;
+  if (!check(cudaMemcpyAsync(d->bias + n_off, stage_f32_, N * sizeof(float), cudaMemcpyDeviceToDevice, stream_),
+             "bias"))
+    return false;
+  return check(cudaStreamSynchronize(stream_), "bias");
+}
+
+bool Model::finish_dense(DenseWeight* d) {
+  if (prec_ == PREC_FP32) return true;
+  if (!make_tmap_bf16_kmajor(&d->tmap, d->w, d->N, d->K, static_cast<uint64_t>(d->K) * 2, gemm_block_n(d->N)))
+    return fail(2, "cuTensorMapEncodeTiled failed for a weight matrix");
+  return true;
+}
+
+bool Model::load_weights(const std::string& dir) {
+  std::string err;
+  if (!list_npy_files(dir, &files_, &err)) return fail(3, err);
+  if (files_.empty()) return fail(3, "no .npy files in " + dir);
+  const size_t H = H_;
+  // embeddings: key pairs as in ops/embedding.cuh:12-20
+  if (!upload_table({"embeddings", "word"}, 2, &word_, &vocab_rows_)) return false;
+  if (!upload_table({"embeddings", "position"}, MAX_SEQ, &pos_, nullptr)) return false;
+  if (!upload_table({"embeddings", "token_type"}, 2, &type_, nullptr)) return false;
+  if (!upload_vec({"embeddings_LayerNorm_gamma"}, H, &emb_g_)) return false;
+  if (!upload_vec({"embeddings_LayerNorm_beta"}, H, &emb_b_)) return false;
+  layer_.resize(L_);
+  for (int i = 0; i < L_; ++i) {
+    // per-layer keys "_<i>_" + suffix, as in utils/bert.cu:17-61
+    const std::string p = "_" + std::to_string(i) + "_";
+    LayerWeights& lw = layer_[i];
+    const char* qkv_names[3] = {"query", "key", "value"};
+    for (int j = 0; j < 3; ++j) {
+      const std::string s = p + "attention_self_" + qkv_names[j];
+      if (!load_dense({s + "_kernel"}, {s + "_bias"}, H_, H_, &lw.qkv, j * H_, 3 * H_)) return false;
+    }
+    if (!finish_dense(&lw.qkv)) return false;
+    if (!load_dense({p + "attention_output_dense_kernel"}, {p + "attention_output_dense_bias"}, H_, H_, &lw.attn_out,
+                    0, H_) || !finish_dense(&lw.attn_out))
+      return false;
+    if (!upload_vec({p + "attention_output_LayerNorm_gamma"}, H, &lw.ln1_g)) return false;
+    if (!upload_vec({p + "attention_output_LayerNorm_beta"}, H, &lw.ln1_b)) return false;
+    if (!load_dense({p + "intermediate_dense_kernel"}, {p + "intermediate_dense_bias"}, H_, F_, &lw.ffn1, 0, F_) ||
+        !finish_dense(&lw.ffn1))
+      return false;
+    if (!load_dense({p + "output_dense_kernel"}, {p + "output_dense_bias"}, F_, H_, &lw.ffn2, 0, H_) ||
+        !finish_dense(&lw.ffn2))
+      return false;
+    if (!upload_vec({p + "output_LayerNorm_gamma"}, H, &lw.ln2_g)) return false;
+    if (!upload_vec({p + "output_LayerNorm_beta"}, H, &lw.ln2_b)) return false;
+  }
+  // the pooler is needed by the encoder although name.txt does not list it (utils/bert.cu:67-69)
+  if (!load_dense({"pooler_dense_kernel"}, {"pooler_dense_bias"}, H_, H_, &pooler_, 0, H_) || !finish_dense(&pooler_))
+    return false;
+  // optional fine-tune head (apps/finetune.py:33-34)
+  if (find_file({"classifier_kernel"}) && find_file({"classifier_bias"})) {
+    NpyArray k;
+    if (!read_tensor({"classifier_kernel"}, 0, &k)) return false;
+    if (k.shape.size() == 2 && k.shape[0] == H && k.shape[1] >= 1 && k.shape[1] <= MAX_CLASSES) {
+      classes_ = static_cast<int>(k.shape[1]);
+      if (!check(cudaMalloc(&cls_w_, k.numel() * sizeof(float)), "cudaMalloc")) return false;
+      owned_.push_back(cls_w_);
+      if (!check(cudaMemcpy(cls_w_, stage_f32_, k.numel() * sizeof(float), cudaMemcpyDeviceToDevice), "copy"))
+        return false;
+      if (!upload_vec({"classifier_bias"}, classes_, &cls_b_)) return false;
+    }
+  }
+  if (stage_f32_) {
+    cudaFree(stage_f32_);
+    stage_f32_ = nullptr;
+    stage_elems_ = 0;
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------ arena
+bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
+  const size_t T = static_cast<size_t>(B) * S;
+  if (T > cap_tokens_ || B > cap_batch_) {
+    if (!check(cudaStreamSynchronize(stream_), "sync before arena growth")) return false;
+    const size_t ct = std::max(T, cap_tokens_);
+    const int cbatch = std::max(B, cap_batch_);
+    if (arena_) cudaFree(arena_);
+    arena_ = nullptr;
+    cap_tokens_ = 0;
+    cap_batch_ = 0;
+    size_t off = 0;
+    auto slot = [&](size_t bytes) { const size_t o = off; off = align_up(off + bytes, 1024); return o; };
+    const size_t o_ints = slot(3 * ct * sizeof(int));
+    const size_t o_kv = slot(static_cast<size_t>(cbatch) * sizeof(int));
+    const size_t o_x = slot(ct * H_ * esize_);
+    const size_t o_x1 = slot(ct * H_ * esize_);
+    const size_t o_y = slot(ct * H_ * esize_);
+    const size_t o_ctx = slot(ct * H_ * esize_);
+    const size_t o_qkv = slot(ct * 3 * H_ * esize_);
+    const size_t o_z = slot(ct * F_ * esize_);
+    const size_t o_pool = slot(static_cast<size_t>(cbatch) * H_ * sizeof(float));
+    const size_t o_probs = slot(static_cast<size_t>(cbatch) * MAX_CLASSES * sizeof(float));
+    if (!check(cudaMalloc(&arena_, off), "cudaMalloc(activation arena)")) return false;
+    char* base = static_cast<char*>(arena_);
+    ids_ = reinterpret_cast<int*>(base + o_ints);
+    kv_len_ = reinterpret_cast<int*>(base + o_kv);
+    x_ = base + o_x; x1_ = base + o_x1; y_ = base + o_y; ctx_ = base + o_ctx; qkv_ = base + o_qkv; z_ = base + o_z;
+    pooled_ = reinterpret_cast<float*>(base + o_pool);
+    probs_ = reinterpret_cast<float*>(base + o_probs);
+    // zero once so that tile rows beyond the live token count never hold NaN patterns
+    if (!check(cudaMemsetAsync(arena_, 0, off, stream_), "cudaMemset(arena)")) return false;
+    if (prec_ != PREC_FP32) {
+      const uint64_t rows = ct;
+      bool ok = make_tmap_bf16_kmajor(&tm_x_, x_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
+                make_tmap_bf16_kmajor(&tm_x1_, x1_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
+                make_tmap_bf16_kmajor(&tm_ctx_, ctx_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
+                make_tmap_bf16_kmajor(&tm_z_, z_, rows, F_, static_cast<uint64_t>(F_) * 2, 128);
+      if (!ok) return fail(2, "cuTensorMapEncodeTiled failed for an activation buffer");
+    }
+    if (h_in_) cudaFreeHost(h_in_);
+    if (h_out_) cudaFreeHost(h_out_);
+    h_in_ = nullptr; h_out_ = nullptr;
+    if (!check(cudaMallocHost(&h_in_, 3 * ct * sizeof(int)), "cudaMallocHost")) return false;
+    h_out_elems_ = static_cast<size_t>(cbatch) * (H_ + MAX_CLASSES);
+    if (!check(cudaMallocHost(&h_out_, h_out_elems_ * sizeof(float)), "cudaMallocHost")) return false;
+    cap_tokens_ = ct;
+    cap_batch_ = cbatch;
+  }
+  if (want_hidden_f32 && prec_ != PREC_FP32 && hidden_f32_tokens_ < T) {
+    if (!check(cudaStreamSynchronize(stream_), "sync")) return false;
+    if (hidden_f32_) cudaFree(hidden_f32_);
+    hidden_f32_ = nullptr;
+    hidden_f32_tokens_ = 0;
+    const size_t tok = std::max(T, cap_tokens_);
+    if (!check(cudaMalloc(&hidden_f32_, tok * H_ * sizeof(float)), "cudaMalloc(hidden fp32)")) return false;
+    hidden_f32_tokens_ = tok;
+  }
+  return true;
+}
+
+float* Model::hidden_f32_dev() const { return prec_ == PREC_FP32 ? static_cast<float*>(x_) : hidden_f32_; }
+
+// ------------------------------------------------------------------ profiling
+void Model::count(int kclass, int n) {
+  if (n > 0) {
+    launches_ += n;
+    prof_n_[kclass] += profiling_ ? n : 0;
+  }
+}
+void Model::prof_begin(int kclass) {
+  if (!profiling_) return;
+  if (ev_used_ + 2 > ev_.size()) {
+    for (int i = 0; i < 64; ++i) {
+      cudaEvent_t e;
+      cudaEventCreate(&e);
+      ev_.push_back(e);
+    }
+  }
+  ev_class_.push_back(kclass);
+  cudaEventRecord(ev_[ev_used_], stream_);
+}
+void Model::prof_end(int) {
+  if (!profiling_) return;
+  cudaEventRecord(ev_[ev_used_ + 1], stream_);
+  ev_used_ += 2;
+}
+bool Model::collect_profile() {
+  for (size_t p = 0; p < ev_class_.size() && 2 * p + 1 < ev_.size(); ++p) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, ev_[2 * p], ev_[2 * p + 1]) == cudaSuccess) prof_ms_[ev_class_[p]] += ms;
+  }
+  ev_used_ = 0;
+  ev_class_.clear();
+  return true;
+}
+void Model::reset_profile() {
+  for (int i = 0; i < KC_COUNT; ++i) { prof_ms_[i] = 0; prof_n_[i] = 0; }
+  ev_used_ = 0;
+  ev_class_.clear();
+}
+void Model::get_profile(int kclass, double* ms, long* launches) const {
+  if (kclass < 0 || kclass >= KC_COUNT) { *ms = 0; *launches = 0; return; }
+  *ms = prof_ms_[kclass];
+  *launches = prof_n_[kclass];
+}
+
+// ------------------------------------------------------------------ forward
+bool Model::dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, int lda, int M, void* out, int flags,
+                  const void* residual, int kclass) {
+  GemmEpilogue epi;
+  epi.flags = flags;
+  epi.bias = w.bias;
+  epi.residual = residual;
+  int n;
+  prof_begin(kclass);
+  if (prec_ == PREC_FP32) {
+    n = gemm_f32(static_cast<const float*>(A), lda, static_cast<const float*>(w.w), M, w.N, w.K,
+                 static_cast<float*>(out), w.N, epi, stream_);
+  } else {
+    if (prec_ == PREC_FP8) {
+      epi.flags |= EPI_COLSCALE;
+      epi.colscale = w.colscale;
+    }
+    n = gemm_bf16_tcgen05(tmA, &w.tmap, M, w.N, w.K, out, w.N, epi, err_dev_, num_sms_, stream_);
+  }
+  prof_end(kclass);
+  if (n < 0) return fail(2, "GEMM launch rejected (code " + std::to_string(n) + ")");
+  count(kclass, n);
+  return true;
+}
+
+bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask, int B, int S, bool want_hidden_f32,
+                           bool want_probs) {
+  if (status_ != 0) return false;
+  if (B < 1 || S < 1) return fail(1, "batch size and sequence length must be positive");
+  if (S > MAX_SEQ) return fail(1, "sequence length exceeds the 512 positions of the position table");
+  if (static_cast<long long>(B) * S > (1ll << 24)) return fail(1, "batch * seq too large");
+  if (want_probs && classes_ == 0) return fail(1, "the model directory has no classifier_kernel/bias");
+  if (!check(cudaSetDevice(dev_), "cudaSetDevice")) return false;
+  if (!ensure_capacity(B, S, want_hidden_f32)) return false;
+  const int T = B * S;
+  launches_ = 0;
+  int n;
+
+#define CB_LAUNCH(kclass, call)                                         \
+  do {                                                                  \
+    prof_begin(kclass);                                                 \
+    n = (call);                                                         \
+    prof_end(kclass);                                                   \
+    if (n < 0) return fail(2, "kernel launch rejected: " #call);        \
+    count(kclass, n);                                                   \
+  } while (0)
+
+  CB_LAUNCH(KC_OTHER, mask_to_kv_len(d_mask, kv_len_, B, S, stream_));
+  if (prec_ == PREC_FP32) {
+    CB_LAUNCH(KC_EMBED, embed_layernorm<float>(d_ids, d_seg, static_cast<const float*>(word_),
+                                               static_cast<const float*>(pos_), static_cast<const float*>(type_),
+                                               emb_g_, emb_b_, static_cast<float*>(x_), T, S, H_, vocab_rows_,
+                                               err_dev_, stream_));
+  } else {
+    CB_LAUNCH(KC_EMBED, embed_layernorm<__nv_bfloat16>(
+                            d_ids, d_seg, static_cast<const __nv_bfloat16*>(word_),
+                            static_cast<const __nv_bfloat16*>(pos_), static_cast<const __nv_bfloat16*>(type_), emb_g_,
+                            emb_b_, static_cast<__nv_bfloat16*>(x_), T, S, H_, vocab_rows_, err_dev_, stream_));
+  }
+  for (int l = 0; l < L_; ++l) {
+    const LayerWeights& w = layer_[l];
+    const bool last = (l == L_ - 1);
+    if (!dense(w.qkv, x_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) return false;
+    if (prec_ == PREC_FP32) {
+      CB_LAUNCH(KC_ATTENTION, attention_f32(static_cast<const float*>(qkv_), d_mask, kv_len_,
+                                            static_cast<float*>(ctx_), B, S, heads_, stream_));
+    } else {
+      CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_,
+                                             static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, stream_));
+    }
+    if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, T, y_, EPI_BIAS | EPI_RESIDUAL, x_, KC_GEMM_ATTN_OUT)) return false;
+    if (prec_ == PREC_FP32) {
+      CB_LAUNCH(KC_LAYERNORM, layernorm<float>(static_cast<const float*>(y_), w.ln1_g, w.ln1_b,
+                                               static_cast<float*>(x1_), nullptr, T, H_, stream_));
+    } else {
+      CB_LAUNCH(KC_LAYERNORM, layernorm<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(y_), w.ln1_g, w.ln1_b,
+                                                       static_cast<__nv_bfloat16*>(x1_), nullptr, T, H_, stream_));
+    }
+    if (!dense(w.ffn1, x1_, &tm_x1_, H_, T, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
+    if (!dense(w.ffn2, z_, &tm_z_, F_, T, y_, EPI_BIAS | EPI_RESIDUAL, x1_, KC_GEMM_FFN2)) return false;
+    if (prec_ == PREC_FP32) {
+      CB_LAUNCH(KC_LAYERNORM, layernorm<float>(static_cast<const float*>(y_), w.ln2_g, w.ln2_b,
+                                               static_cast<float*>(x_), nullptr, T, H_, stream_));
+    } else {
+      CB_LAUNCH(KC_LAYERNORM, layernorm<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(y_), w.ln2_g, w.ln2_b,
+                                                       static_cast<__nv_bfloat16*>(x_),
+                                                       (last && want_hidden_f32) ? hidden_f32_ : nullptr, T, H_,
+                                                       stream_));
+    }
+  }
+  // pooler: rows b*S of the final hidden states, tanh(dense) -> fp32 [B, H] (utils/bert.cu:239-247)
+  if (prec_ == PREC_FP32) {
+    if (!dense(pooler_, x_, nullptr, S * H_, B, pooled_, EPI_BIAS | EPI_TANH, nullptr, KC_POOLER)) return false;
+  } else {
+    CUtensorMap tm_cls;
+    if (!make_tmap_bf16_kmajor(&tm_cls, x_, B, H_, static_cast<uint64_t>(S) * H_ * 2, 128))
+      return fail(2, "cuTensorMapEncodeTiled failed for the pooler input");
+    if (!dense(pooler_, x_, &tm_cls, 0, B, pooled_, EPI_BIAS | EPI_TANH | EPI_OUT_F32, nullptr, KC_POOLER))
+      return false;
+  }
+  if (want_probs)
+    CB_LAUNCH(KC_OTHER, classify_softmax(pooled_, cls_w_, cls_b_, probs_, B, H_, classes_, stream_));
+#undef CB_LAUNCH
+  return true;
+}
+
+bool Model::sync() {
+  if (!check(cudaSetDevice(dev_), "cudaSetDevice")) return false;
+  if (!check(cudaMemcpyAsync(h_err_, err_dev_, sizeof(int), cudaMemcpyDeviceToHost, stream_), "error flag copy"))
+    return false;
+  if (!check(cudaStreamSynchronize(stream_), "stream synchronize")) return false;
+  if (profiling_) collect_profile();
+  if (*h_err_ != 0) {
+    const int e = *h_err_;
+    cudaMemsetAsync(err_dev_, 0, sizeof(int), stream_);
+    if (e & 1)
+      return fail(4, "a device-side wait in the GEMM pipeline timed out (site " + std::to_string(e >> 8) +
+                         "); results of this call are invalid");
+    return fail(4, "input ids or segment ids out of range (clamped); results of this call are suspect");
+  }
+  return true;
+}
+
+bool Model::run_host(const int* ids, const int* seg, const int* mask, int B, int S, float* pooled_out,
+                     float* probs_out, int num_classes, bool want_hidden_f32) {
+  if (status_ != 0) return false;
+  if (!ids || !seg) return fail(1, "ids and segment ids must not be null");
+  if (B < 1 || S < 1 || S > MAX_SEQ) return fail(1, "need batch >= 1 and 1 <= seq_length <= 512");
+  if (probs_out && num_classes != classes_) return fail(1, "num_classes does not match classifier_kernel");
+  if (!check(cudaSetDevice(dev_), "cudaSetDevice")) return false;
+  if (!ensure_capacity(B, S, want_hidden_f32)) return false;
+  const size_t T = static_cast<size_t>(B) * S;
+  std::memcpy(h_in_, ids, T * sizeof(int));
+  std::memcpy(h_in_ + T, seg, T * sizeof(int));
+  if (mask) std::memcpy(h_in_ + 2 * T, mask, T * sizeof(int));
+  if (!check(cudaMemcpyAsync(ids_, h_in_, (mask ? 3 : 2) * T * sizeof(int), cudaMemcpyHostToDevice, stream_),
+             "input copy"))
+    return false;
+  if (!forward_device(ids_, ids_ + T, mask ? ids_ + 2 * T : nullptr, B, S, want_hidden_f32, probs_out != nullptr))
+    return false;
+  const size_t nh = static_cast<size_t>(B) * H_;
+  if (pooled_out &&
+      !check(cudaMemcpyAsync(h_out_, pooled_, nh * sizeof(float), cudaMemcpyDeviceToHost, stream_), "output copy"))
+    return false;
+  if (probs_out && !check(cudaMemcpyAsync(h_out_ + nh, probs_, static_cast<size_t>(B) * classes_ * sizeof(float),
+                                          cudaMemcpyDeviceToHost, stream_), "output copy"))
+    return false;
+  if (!sync()) return false;
+  if (pooled_out) std::memcpy(pooled_out, h_out_, nh * sizeof(float));
+  if (probs_out) std::memcpy(probs_out, h_out_ + nh, static_cast<size_t>(B) * classes_ * sizeof(float));
+  return true;
+}
+
+}  // namespace cb

@@ -1,0 +1,149 @@
+// One encoder replica on one GPU: weights, activation arena, stream, pinned staging and the
+// per-call schedule.  It takes the place of the reference's `class bert`
+// (utils/bert.cu:4-252), `global_handle` (utils/manager.cu:4-109) and the weight loader
+// (utils/load_model.cc:15-98), with these differences by design:
+//   * one stream, no per-layer host synchronisation (the reference synchronises once per layer
+//     to rewind its bump arena, utils/bert.cu:232-234): buffers are fixed slots of one arena;
+//   * persistent pinned staging instead of cudaMallocHost / cudaFreeHost per call
+//     (utils/bert.cu:100,123); positions are t % S computed on the device;
+//   * the arena is sized from max_batch * max_seq and grows on demand; it never takes "all free
+//     memory" (utils/manager.cu:42-47);
+//   * errors are recorded on the handle and reported, the process is never terminated
+//     (the reference exits, utils/common.h:58-65).
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "kernels.h"
+
+namespace cb {
+
+enum Precision : int { PREC_FP32 = 0, PREC_BF16 = 1, PREC_FP8 = 2 };
+
+enum KernelClass : int {
+  KC_EMBED = 0, KC_GEMM_QKV, KC_ATTENTION, KC_GEMM_ATTN_OUT, KC_LAYERNORM, KC_GEMM_FFN1, KC_GEMM_FFN2,
+  KC_POOLER, KC_OTHER, KC_COUNT
+};
+
+struct DenseWeight {      // one projection
+  void* w = nullptr;      // fp32 [K, N] (fp32 mode) or bf16 [N, K] (bf16 / fp8 modes)
+  uint8_t* w_fp8 = nullptr;  // fp8 mode: e4m3 bytes [N, K] (the stored quantised weights)
+  float* bias = nullptr;     // [N]
+  float* colscale = nullptr; // fp8 mode: [N] de-quantisation scale per output column
+  int K = 0, N = 0;
+  CUtensorMap tmap;          // bf16 / fp8 modes
+};
+
+struct LayerWeights {
+  DenseWeight qkv, attn_out, ffn1, ffn2;
+  float *ln1_g = nullptr, *ln1_b = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
+};
+
+class Model {
+ public:
+  Model() = default;
+  ~Model();
+  // Returns false and fills error() on failure.  num_layers <= 0 means the model's own depth.
+  bool init(bool large, int gpu, int max_batch, int max_seq, const std::string& dir, int precision, int num_layers);
+
+  // Host arrays in (int32 [B, S]; mask may be null), pooler out (fp32 [B, H]) -- blocking.
+  bool run_host(const int* ids, const int* seg, const int* mask, int B, int S, float* pooled_out,
+                float* probs_out, int num_classes, bool want_hidden_f32 = false);
+  // Same, but the results (pooler and fp32 final hidden states) stay on the device.
+  bool run_host_keep(const int* ids, const int* seg, const int* mask, int B, int S) {
+    return run_host(ids, seg, mask, B, S, nullptr, nullptr, 0, true);
+  }
+  void set_error(int code, const std::string& msg) { fail(code, msg); }
+  // Device arrays in; asynchronous on stream(); results stay on the device.
+  bool forward_device(const int* d_ids, const int* d_seg, const int* d_mask, int B, int S, bool want_hidden_f32,
+                      bool want_probs);
+  bool sync();
+
+  float* pooled_dev() const { return pooled_; }
+  float* hidden_f32_dev() const;
+  float* probs_dev() const { return probs_; }
+  int hidden() const { return H_; }
+  int layers() const { return L_; }
+  int heads() const { return heads_; }
+  int ffn() const { return F_; }
+  int precision() const { return prec_; }
+  int num_classes() const { return classes_; }
+  cudaStream_t stream() const { return stream_; }
+  int status() const { return status_; }
+  const std::string& error() const { return error_; }
+  void clear_error() { status_ = 0; error_.clear(); }
+
+  long launches_last_forward() const { return launches_; }
+  void set_profiling(bool on) { profiling_ = on; }
+  void reset_profile();
+  void get_profile(int kclass, double* ms, long* launches) const;
+
+ private:
+  bool fail(int code, const std::string& msg);
+  bool check(cudaError_t e, const char* what);
+  bool ensure_capacity(int B, int S, bool want_hidden_f32);
+  bool load_weights(const std::string& dir);
+  bool load_dense(const std::vector<std::string>& keys_kernel, const std::vector<std::string>& keys_bias,
+                  int K, int N, DenseWeight* dst, int n_off, int n_total);
+  bool finish_dense(DenseWeight* d);
+  bool upload_vec(const std::vector<std::string>& keys, size_t n, float** dst);
+  bool upload_table(const std::vector<std::string>& keys, size_t min_rows, void** dst, int* rows_out);
+  const std::string* find_file(const std::vector<std::string>& keys) const;
+  bool read_tensor(const std::vector<std::string>& keys, size_t expect, struct NpyArray* arr);
+  void count(int kclass, int n);
+  void prof_begin(int kclass);
+  void prof_end(int kclass);
+  bool collect_profile();
+  bool dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, int lda, int M, void* out, int flags,
+             const void* residual, int kclass);
+
+  int dev_ = 0, num_sms_ = 148;
+  bool large_ = false;
+  int L_ = 0, H_ = 0, heads_ = 0, F_ = 0, prec_ = PREC_BF16, classes_ = 0, vocab_rows_ = 0;
+  size_t esize_ = 2;
+  cudaStream_t stream_ = nullptr;
+  std::string dir_;
+  std::vector<std::string> files_;
+
+  // weights
+  void *word_ = nullptr, *pos_ = nullptr, *type_ = nullptr;
+  float *emb_g_ = nullptr, *emb_b_ = nullptr;
+  std::vector<LayerWeights> layer_;
+  DenseWeight pooler_;
+  float *cls_w_ = nullptr, *cls_b_ = nullptr;
+  float* stage_f32_ = nullptr;  // device staging for load-time conversion
+  size_t stage_elems_ = 0;
+  std::vector<void*> owned_;    // every cudaMalloc'ed weight pointer
+
+  // activation arena
+  size_t cap_tokens_ = 0;
+  int cap_batch_ = 0;
+  void* arena_ = nullptr;
+  int *ids_ = nullptr, *kv_len_ = nullptr, *err_dev_ = nullptr;  // ids_: 3 * cap_tokens ints (ids | seg | mask)
+  void *x_ = nullptr, *x1_ = nullptr, *y_ = nullptr, *ctx_ = nullptr, *qkv_ = nullptr, *z_ = nullptr;
+  float *pooled_ = nullptr, *probs_ = nullptr, *hidden_f32_ = nullptr;
+  size_t hidden_f32_tokens_ = 0;
+  CUtensorMap tm_x_, tm_x1_, tm_ctx_, tm_z_;
+  int tm_rows_ = 0;
+
+  // pinned staging
+  int* h_in_ = nullptr;
+  size_t h_in_elems_ = 0;
+  float* h_out_ = nullptr;
+  size_t h_out_elems_ = 0;
+  int* h_err_ = nullptr;
+
+  // bookkeeping
+  int status_ = 0;
+  std::string error_;
+  long launches_ = 0;
+  bool profiling_ = false;
+  std::vector<cudaEvent_t> ev_;
+  std::vector<int> ev_class_;
+  size_t ev_used_ = 0;
+  double prof_ms_[KC_COUNT] = {};
+  long prof_n_[KC_COUNT] = {};
+};
+
+}  // namespace cb

@@ -1,0 +1,319 @@
+// Memory-bound row kernels: embedding gather + LayerNorm, LayerNorm, classifier head, and the
+// load-time weight conversions.  One warp owns one row; 16-byte loads and stores; mean and
+// variance by warp shuffles; variance as mean((x-u)^2) over values held in registers, the
+// form the reference model uses (modeling.py:168-172; the CUDA reference reaches the same
+// population variance by Welford, ops/layernorm.cu:52-134); eps 1e-12 inside the sqrt
+// (ops/layernorm.cuh:43).
+//
+//   embed_layernorm  replaces DeviceApplyEmbeddings (ops/embedding.cu:3-20) + the LayerNorm
+//                    that follows it (ops/embedding.cu:39-58): one pass instead of three.
+//   layernorm        replaces cuApplyLayerNorm (ops/layernorm.cu:136-182); the residual add
+//                    it did in place now happens in the producing GEMM's epilogue.
+//   classify_softmax the sample app's fine-tune head (apps/finetune.py:16-24) on the device.
+#include "kernels.h"
+#include "ptx.cuh"
+
+#include <cuda_fp8.h>
+
+namespace cb {
+namespace {
+
+constexpr float LN_EPS = 1e-12f;
+constexpr int ROWS_PER_BLOCK = 4;
+
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+  static constexpr int N = 4;
+  using Raw = float4;
+  __device__ static void load(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+  __device__ static void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+      v[2 * i] = __low2float(h);
+      v[2 * i + 1] = __high2float(h);
+    }
+  }
+  __device__ static void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 t;
+    t.x = pack_bf16(v[0], v[1]); t.y = pack_bf16(v[2], v[3]);
+    t.z = pack_bf16(v[4], v[5]); t.w = pack_bf16(v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = t;
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+// MAXV: vectors per lane; H <= 32 * MAXV * Vec<T>::N  (H = 768 or 1024 -> 4 vectors of 8 bf16 / 8 of 4 fp32)
+template <typename T, int MAXV>
+__device__ __forceinline__ void normalise_and_store(float (&x)[MAXV][Vec<T>::N], int nvec, int lane, int H,
+                                                    const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                    T* __restrict__ out_row, float* __restrict__ out_f32_row) {
+  constexpr int VN = Vec<T>::N;
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+    if (i < nvec)
+#pragma unroll
+      for (int j = 0; j < VN; ++j) sum += x[i][j];
+  const float mean = warp_sum(sum) / static_cast<float>(H);
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+    if (i < nvec)
+#pragma unroll
+      for (int j = 0; j < VN; ++j) {
+        const float d = x[i][j] - mean;
+        sq += d * d;
+      }
+  const float var = warp_sum(sq) / static_cast<float>(H);
+  const float rstd = 1.0f / sqrtf(var + LN_EPS);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    if (i < nvec) {
+      const int col = (i * 32 + lane) * VN;
+      float y[VN];
+#pragma unroll
+      for (int j = 0; j < VN; j += 4) {
+        const float4 g = __ldg(reinterpret_cast<const float4*>(gamma + col + j));
+        const float4 bt = __ldg(reinterpret_cast<const float4*>(beta + col + j));
+        y[j] = g.x * ((x[i][j] - mean) * rstd) + bt.x;
+        y[j + 1] = g.y * ((x[i][j + 1] - mean) * rstd) + bt.y;
+        y[j + 2] = g.z * ((x[i][j + 2] - mean) * rstd) + bt.z;
+        y[j + 3] = g.w * ((x[i][j + 3] - mean) * rstd) + bt.w;
+      }
+      Vec<T>::store(out_row + col, y);
+      if (out_f32_row) {
+#pragma unroll
+        for (int j = 0; j < VN; j += 4)
+          *reinterpret_cast<float4*>(out_f32_row + col + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
+embed_layernorm_kernel(const int* __restrict__ ids, const int* __restrict__ seg, const T* __restrict__ word,
+                       const T* __restrict__ pos, const T* __restrict__ type, const float* __restrict__ gamma,
+                       const float* __restrict__ beta, T* __restrict__ out, int tokens, int S, int H, int vocab,
+                       int* err) {
+  constexpr int VN = Vec<T>::N;
+  constexpr int MAXV = 32 / VN;  // 1024 / (32 * VN)
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  int id = ids[t], sg = seg[t];
+  if (id < 0 || id >= vocab || sg < 0 || sg > 1) {
+    if (lane == 0) atomicOr(err, 2);  // bad token or segment id: clamp, report
+    id = min(max(id, 0), vocab - 1);
+    sg = min(max(sg, 0), 1);
+  }
+  const T* wr = word + static_cast<size_t>(id) * H;
+  const T* pr = pos + static_cast<size_t>(t % S) * H;
+  const T* tr = type + static_cast<size_t>(sg) * H;
+  const int nvec = H / (32 * VN);
+  float x[MAXV][VN];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    if (i < nvec) {
+      const int col = (i * 32 + lane) * VN;
+      float a[VN], b[VN], c[VN];
+      Vec<T>::load(wr + col, a);
+      Vec<T>::load(pr + col, b);
+      Vec<T>::load(tr + col, c);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) x[i][j] = a[j] + b[j] + c[j];
+    }
+  }
+  normalise_and_store<T, MAXV>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H, nullptr);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
+layernorm_kernel(const T* __restrict__ in, const float* __restrict__ gamma, const float* __restrict__ beta,
+                 T* __restrict__ out, float* __restrict__ out_f32, int tokens, int H) {
+  constexpr int VN = Vec<T>::N;
+  constexpr int MAXV = 32 / VN;
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const T* row = in + static_cast<size_t>(t) * H;
+  const int nvec = H / (32 * VN);
+  float x[MAXV][VN];
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i)
+    if (i < nvec) Vec<T>::load(row + (i * 32 + lane) * VN, x[i]);
+  normalise_and_store<T, MAXV>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H,
+                               out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr);
+}
+
+__global__ void classify_softmax_kernel(const float* __restrict__ pooled, const float* __restrict__ W,
+                                        const float* __restrict__ bias, float* __restrict__ probs, int B, int H,
+                                        int C) {
+  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= B) return;
+  const float* x = pooled + static_cast<size_t>(b) * H;
+  float logit = -INFINITY;  // lane c keeps class c
+  for (int c = 0; c < C; ++c) {
+    float s = 0.f;
+    for (int k = lane; k < H; k += 32) s = fmaf(x[k], W[static_cast<size_t>(k) * C + c], s);
+    s = warp_sum(s) + bias[c];
+    if (lane == c) logit = s;
+  }
+  float mx = logit;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  const float e = (lane < C) ? expf(logit - mx) : 0.f;
+  const float den = warp_sum(e);
+  if (lane < C) probs[static_cast<size_t>(b) * C + lane] = e / den;
+}
+
+// dst[n, k] = bf16(src[k, n]) through a 32x33 shared tile
+__global__ void transpose_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int K, int N) {
+  __shared__ float tile[32][33];
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int k = k0 + r, n = n0 + threadIdx.x;
+    tile[r][threadIdx.x] = (k < K && n < N) ? src[static_cast<size_t>(k) * N + n] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < K) dst[static_cast<size_t>(n) * K + k] = __float2bfloat16_rn(tile[threadIdx.x][r]);
+  }
+}
+
+__global__ void maxabs_kernel(const float* __restrict__ src, size_t n, unsigned int* __restrict__ out_bits) {
+  float m = 0.f;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    m = fmaxf(m, fabsf(src[i]));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+  if ((threadIdx.x & 31) == 0) atomicMax(out_bits, __float_as_uint(m));  // non-negative floats order as uints
+}
+
+__global__ void finish_scale_kernel(float* scale_io) {
+  const float m = *scale_io;
+  *scale_io = (m > 0.f) ? m / 448.0f : 1.0f;
+}
+
+__global__ void quantize_fp8_kernel(const float* __restrict__ src, uint8_t* __restrict__ dst_q,
+                                    __nv_bfloat16* __restrict__ dst_op, const float* __restrict__ scale, int K, int N) {
+  __shared__ float tile[32][33];
+  const float inv = 1.0f / *scale;
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int k = k0 + r, n = n0 + threadIdx.x;
+    tile[r][threadIdx.x] = (k < K && n < N) ? src[static_cast<size_t>(k) * N + n] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < K) {
+      const __nv_fp8_e4m3 q(tile[threadIdx.x][r] * inv);
+      const size_t o = static_cast<size_t>(n) * K + k;
+      dst_q[o] = q.__x;
+      dst_op[o] = __float2bfloat16_rn(static_cast<float>(q));  // e4m3 is exactly representable in bf16
+    }
+  }
+}
+
+__global__ void convert_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+__global__ void fill_f32_kernel(float* dst, float v, size_t n) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    dst[i] = v;
+}
+
+inline bool ln_shape_ok(int H, int vn) { return H > 0 && H % (32 * vn) == 0 && H <= 1024; }
+
+}  // namespace
+
+template <typename T>
+int embed_layernorm(const int* ids, const int* seg, const T* word, const T* pos, const T* type,
+                    const float* gamma, const float* beta, T* out, int tokens, int S, int H, int vocab,
+                    int* err_flag, cudaStream_t stream) {
+  if (tokens <= 0 || S <= 0 || !ln_shape_ok(H, Vec<T>::N)) return -1;
+  const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
+  embed_layernorm_kernel<T><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(ids, seg, word, pos, type, gamma, beta, out,
+                                                                        tokens, S, H, vocab, err_flag);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+template <typename T>
+int layernorm(const T* x, const float* gamma, const float* beta, T* out, float* out_f32, int tokens, int H,
+              cudaStream_t stream) {
+  if (tokens <= 0 || !ln_shape_ok(H, Vec<T>::N)) return -1;
+  const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
+  layernorm_kernel<T><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(x, gamma, beta, out, out_f32, tokens, H);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+template int embed_layernorm<float>(const int*, const int*, const float*, const float*, const float*, const float*,
+                                    const float*, float*, int, int, int, int, int*, cudaStream_t);
+template int embed_layernorm<__nv_bfloat16>(const int*, const int*, const __nv_bfloat16*, const __nv_bfloat16*,
+                                            const __nv_bfloat16*, const float*, const float*, __nv_bfloat16*, int, int,
+                                            int, int, int*, cudaStream_t);
+template int layernorm<float>(const float*, const float*, const float*, float*, float*, int, int, cudaStream_t);
+template int layernorm<__nv_bfloat16>(const __nv_bfloat16*, const float*, const float*, __nv_bfloat16*, float*, int,
+                                      int, cudaStream_t);
+
+int classify_softmax(const float* pooled, const float* W, const float* bias, float* probs, int B, int H, int C,
+                     cudaStream_t stream) {
+  if (B <= 0 || H <= 0 || C <= 0 || C > 32) return -1;
+  classify_softmax_kernel<<<(B + 3) / 4, 128, 0, stream>>>(pooled, W, bias, probs, B, H, C);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+int transpose_to_bf16(const float* src, __nv_bfloat16* dst, int K, int N, cudaStream_t stream) {
+  dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
+  transpose_to_bf16_kernel<<<grid, block, 0, stream>>>(src, dst, K, N);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+int quantize_fp8_weight(const float* src, uint8_t* dst_q, __nv_bfloat16* dst_op, float* scale_out, int K, int N,
+                        cudaStream_t stream) {
+  if (cudaMemsetAsync(scale_out, 0, sizeof(float), stream) != cudaSuccess) return -3;
+  maxabs_kernel<<<296, 256, 0, stream>>>(src, static_cast<size_t>(K) * N, reinterpret_cast<unsigned int*>(scale_out));
+  finish_scale_kernel<<<1, 1, 0, stream>>>(scale_out);
+  dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
+  quantize_fp8_kernel<<<grid, block, 0, stream>>>(src, dst_q, dst_op, scale_out, K, N);
+  return cudaGetLastError() == cudaSuccess ? 3 : -3;
+}
+
+int convert_f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  convert_f32_to_bf16_kernel<<<592, 256, 0, stream>>>(src, dst, n);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+int fill_f32(float* dst, float value, size_t n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  fill_f32_kernel<<<296, 256, 0, stream>>>(dst, value, n);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+}  // namespace cb

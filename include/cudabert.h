@@ -1,0 +1,128 @@
+/* C ABI of libcudaBERT.so -- a B200 (sm_100a) BERT-encoder inference backend that is a drop-in
+ * for the shared library of qsyao/cudaBERT.  The first five entry points have the reference's
+ * names, argument order and meaning, so the reference's ctypes binding (cuda_bert/pybert.py:12-38)
+ * and its unit_test program (cuda_bert/test/test.cpp) work against this library unchanged.
+ *
+ * All array arguments are caller-owned, C-contiguous host memory unless a name says "_dev".
+ * No entry point terminates the process: failures are recorded on the handle
+ * (cudabert_status / cudabert_last_error); init_model returns NULL on failure.
+ * A handle is not re-entrant; distinct handles (one per GPU) may be used from distinct threads.
+ */
+#ifndef CUDABERT_H_
+#define CUDABERT_H_
+
+#include <stdbool.h>
+#include <stddef.h>
+
+#if defined(__GNUC__)
+#define CUDABERT_API __attribute__((visibility("default")))
+#else
+#define CUDABERT_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Reference: `Retval` (cuda_bert/utils/common.h:174-177).  Both fields are DEVICE pointers
+ * (fp32) owned by the handle and valid until its next call:
+ *   tensor         final hidden states [batch, seq, hidden]
+ *   pooled_output  pooler output       [batch, hidden]                                   */
+typedef struct Retval {
+  float* tensor;
+  float* pooled_output;
+} Retval;
+
+/* Reference: init_model (cuda_bert/cuda_bert.cu:26-33; ctypes cuda_bert/pybert.py:14-16).
+ * `large` picks the hard-coded dimensions (base 12/768/12/3072, large 24/1024/16/4096,
+ * utils/manager.cu:8-15); `dir` is a directory of float32 .npy files (name.txt layout), "" means
+ * "model_npy/base_uncased" or "model_npy/large_uncased"; max_batchsize == max_seq_length == 0
+ * sizes the activation arena lazily at the first call.  The precision mode comes from the
+ * environment variable CUDABERT_PRECISION = fp32 | bf16 (default) | fp8.                    */
+CUDABERT_API void* init_model(bool large, int num_gpu, int max_batchsize, int max_seq_length, char* dir);
+
+/* Reference: release_model (cuda_bert/cuda_bert.cu:34-37). */
+CUDABERT_API void release_model(void* model);
+
+/* Reference: Cuda_Inference (cuda_bert/cuda_bert.cu:40-53).  Runs the forward pass on host
+ * int32 arrays [batchsize, seq_length] (`masks` may be NULL = all valid) and returns device
+ * pointers; the call returns after the work has been enqueued AND completed.              */
+CUDABERT_API Retval Cuda_Inference(void* model, int* words, int* token_types, int batchsize, int seq_length, int* masks);
+
+/* Reference: Cuda_Bert (cuda_bert/cuda_bert.cu:55-70).  Forward pass + copy of the pooler
+ * output into `output` (host fp32 [batchsize, hidden]); blocking.  On failure `output` is
+ * left untouched and the handle's status is set.                                           */
+CUDABERT_API void Cuda_Bert(void* model, float* output, int* words, int* token_types, int batchsize, int seq_length,
+               int* attention_mask);
+
+/* Reference: test (cuda_bert/cuda_bert.cu:91-180, cuda_bert/cuda_bert.cuh:4-5).  Built-in
+ * latency / throughput loop on the reference's 11-token seed input tiled to seq_length:
+ * 10 warm-up calls, nIter timed calls, prints the p99 latency and batches per second.       */
+CUDABERT_API void test(int batchsize, int seq_length, int nIter, bool large, int num_gpu);
+
+/* Reference: Cuda_Classify, present but commented out (cuda_bert/cuda_bert.cu:72-89,
+ * cuda_bert/pybert.py:40-42).  Pooler followed by Linear(hidden -> num_classes) + Softmax on
+ * the device, with classifier_kernel.npy [hidden, num_classes] / classifier_bias.npy from the
+ * model directory (the sample app's head, apps/finetune.py:16-44).  `output` is host fp32
+ * [batchsize, num_classes].                                                                 */
+CUDABERT_API void Cuda_Classify(void* model, float* output, int* words, int* token_types, int batchsize, int seq_length,
+                   int num_classes, int* attention_mask);
+
+/* ---- additions (no counterpart in the reference, which exits the process on any error) ---- */
+
+/* init_model with an explicit precision (0 fp32, 1 bf16, 2 fp8-e4m3 weights; -1 = environment /
+ * default) and an optional cap on the number of encoder layers (<= 0: all).                  */
+CUDABERT_API void* cudabert_init_ex(bool large, int num_gpu, int max_batchsize, int max_seq_length, const char* dir,
+                       int precision, int num_layers);
+/* 0 = ok, 1 = bad argument, 2 = CUDA error (sticky), 3 = weight loading, 4 = device-side check. */
+CUDABERT_API int cudabert_status(void* model);
+/* Message of the first error since the last successful call; model == NULL: why the last
+ * init_model on this thread failed.                                                          */
+CUDABERT_API const char* cudabert_last_error(void* model);
+CUDABERT_API int cudabert_hidden_size(void* model);
+CUDABERT_API int cudabert_num_classes(void* model);
+
+/* Forward pass on inputs that already live in device memory (int32 [batchsize, seq_length];
+ * mask_dev may be NULL).  Enqueues on the handle's stream and returns; cudabert_sync waits.
+ * Results: cudabert_pooled_dev (fp32 [batchsize, hidden]).  Returns 0 on success.            */
+CUDABERT_API int cudabert_forward_dev(void* model, const int* ids_dev, const int* seg_dev, const int* mask_dev, int batchsize,
+                         int seq_length);
+CUDABERT_API int cudabert_sync(void* model);
+CUDABERT_API float* cudabert_pooled_dev(void* model);
+/* The handle's CUDA stream (a cudaStream_t), for event timing on the launching stream. */
+CUDABERT_API void* cudabert_stream(void* model);
+
+/* Kernels launched by the last forward pass of this handle. */
+CUDABERT_API long cudabert_launch_count(void* model);
+/* Per-kernel-class device timing with CUDA events on the handle's stream.  Classes: 0 embedding+LN,
+ * 1 QKV GEMM, 2 attention, 3 attention-output GEMM, 4 LayerNorm, 5 FFN1 GEMM, 6 FFN2 GEMM,
+ * 7 pooler GEMM, 8 other.  Enable, run forwards + sync, then read accumulated ms and launches. */
+CUDABERT_API void cudabert_profile_enable(void* model, int on);
+CUDABERT_API void cudabert_profile_reset(void* model);
+CUDABERT_API int cudabert_profile_get(void* model, int kernel_class, double* total_ms, long* launches);
+
+/* ---- single kernels on device buffers (stream 0, synchronous), for per-kernel parity tests ---- */
+
+/* out[M,N] = epilogue(A[M,K] bf16 (row stride lda elements) x W[N,K]^T bf16); flags: 1 bias, 2 GELU,
+ * 4 residual, 8 tanh, 16 fp32 output, 32 per-column scale.  err_dev: device int, set non-zero if a
+ * pipeline wait timed out.  N % 128 == 0, K % 64 == 0.                                        */
+CUDABERT_API int cudabert_k_gemm_bf16(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev,
+                         int flags, const float* bias_dev, const void* residual_dev, const float* colscale_dev,
+                         int* err_dev);
+/* out[M,N] = epilogue(A[M,K] fp32 (row stride lda) x W[K,N] fp32). */
+CUDABERT_API int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, int N, int K, float* out_dev,
+                        int flags, const float* bias_dev, const float* residual_dev);
+/* ctx[T,H] = attention(qkv[T,3H]); mask_dev int32 [B,S] or NULL; bf16 != 0 selects the bf16 kernel. */
+CUDABERT_API int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads);
+/* out[T,H] = LayerNorm(word[ids] + pos[t % S] + type[seg]); tables and out bf16 or fp32. */
+CUDABERT_API int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev, const void* word_dev,
+                               const void* pos_dev, const void* type_dev, const float* gamma_dev,
+                               const float* beta_dev, void* out_dev, int tokens, int S, int H, int vocab);
+/* out[T,H] = LayerNorm(x[T,H]) * gamma + beta. */
+CUDABERT_API int cudabert_k_layernorm(int bf16, const void* x_dev, const float* gamma_dev, const float* beta_dev, void* out_dev,
+                         int tokens, int H);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUDABERT_H_ */

@@ -1,0 +1,179 @@
+"""Per-kernel parity on the GPU, through the C ABI (cudabert_k_* entry points), against the
+oracle's functions evaluated in fp32 on the same seeded inputs."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import bert_oracle
+
+pytestmark = pytest.mark.gpu
+
+EPI_BIAS, EPI_GELU, EPI_RESIDUAL, EPI_TANH, EPI_OUT_F32, EPI_COLSCALE = 1, 2, 4, 8, 16, 32
+
+# bf16 has 8 significand bits: one rounding is 2^-9 relative; outputs here see two (input and
+# output rounding) on top of fp32 accumulation order differences.
+BF16_REL_TOL = 1.0e-2
+FP32_ABS_TOL = 2.0e-4
+
+
+@pytest.fixture(scope="module")
+def pybert():
+    from cudabert_b200.cuda_bert import pybert as pb
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return pb
+
+
+def _ref_epilogue(acc, flags, bias, resid, colscale):
+    if flags & EPI_COLSCALE:
+        acc = acc * colscale
+    if flags & EPI_BIAS:
+        acc = acc + bias
+    if flags & EPI_RESIDUAL:
+        acc = acc + resid.float()
+    if flags & EPI_GELU:
+        acc = bert_oracle.gelu(acc)
+    if flags & EPI_TANH:
+        acc = torch.tanh(acc)
+    return acc
+
+
+GEMM_SHAPES = [(128, 256, 64), (128, 128, 64), (1, 256, 128), (300, 768, 768), (1000, 2304, 768),
+               (515, 3072, 768), (2048, 1024, 4096), (4100, 4096, 1024), (77, 384, 192)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("flags", [0, EPI_BIAS, EPI_BIAS | EPI_GELU, EPI_BIAS | EPI_RESIDUAL,
+                                   EPI_BIAS | EPI_TANH | EPI_OUT_F32, EPI_BIAS | EPI_COLSCALE])
+def test_gemm_bf16_tcgen05(pybert, M, N, K, flags):
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K + flags)
+    A = (torch.randn(M, K, device="cuda", generator=g) * 0.5).bfloat16()
+    W = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    bias = torch.randn(N, device="cuda", generator=g) * 0.1
+    colscale = torch.rand(N, device="cuda", generator=g) + 0.5
+    out_f32 = bool(flags & EPI_OUT_F32)
+    resid = (torch.randn(M, N, device="cuda", generator=g)).bfloat16()
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float32 if out_f32 else torch.bfloat16)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc = pybert.k_gemm_bf16(A.data_ptr(), K, W.data_ptr(), M, N, K, out.data_ptr(), flags, bias.data_ptr(),
+                            resid.data_ptr(), colscale.data_ptr(), err.data_ptr())
+    assert rc == 0, "k_gemm_bf16 rc=%d err=%d" % (rc, int(err.item()))
+    ref = _ref_epilogue(A.float() @ W.float().t(), flags, bias, resid, colscale)
+    got = out.float()
+    assert torch.isfinite(got).all()
+    rel = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+    assert rel <= BF16_REL_TOL, "rel err %.3g" % rel
+
+
+def test_gemm_bf16_strided_rows(pybert):
+    """The pooler reads row b*S of the hidden states: A rows with a stride larger than K."""
+    B, S, H = 37, 13, 768
+    g = torch.Generator(device="cuda").manual_seed(5)
+    hidden = torch.randn(B * S, H, device="cuda", generator=g).bfloat16()
+    W = (torch.randn(H, H, device="cuda", generator=g) * 0.05).bfloat16()
+    bias = torch.randn(H, device="cuda", generator=g) * 0.1
+    out = torch.empty(B, H, device="cuda", dtype=torch.float32)
+    rc = pybert.k_gemm_bf16(hidden.data_ptr(), S * H, W.data_ptr(), B, H, H, out.data_ptr(),
+                            EPI_BIAS | EPI_TANH | EPI_OUT_F32, bias.data_ptr(), None, None, None)
+    assert rc == 0
+    ref = torch.tanh(hidden.view(B, S, H)[:, 0].float() @ W.float().t() + bias)
+    assert (out - ref).abs().max().item() <= 5e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 768, 768), (1024, 2304, 768), (333, 3072, 768), (130, 1024, 4096)])
+@pytest.mark.parametrize("flags", [EPI_BIAS, EPI_BIAS | EPI_GELU, EPI_BIAS | EPI_RESIDUAL, EPI_BIAS | EPI_TANH])
+def test_gemm_f32(pybert, M, N, K, flags):
+    g = torch.Generator(device="cuda").manual_seed(M + N + K + flags)
+    A = torch.randn(M, K, device="cuda", generator=g) * 0.5
+    W = torch.randn(K, N, device="cuda", generator=g) * 0.05
+    bias = torch.randn(N, device="cuda", generator=g) * 0.1
+    resid = torch.randn(M, N, device="cuda", generator=g)
+    out = torch.full((M, N), float("nan"), device="cuda")
+    rc = pybert.k_gemm_f32(A.data_ptr(), K, W.data_ptr(), M, N, K, out.data_ptr(), flags, bias.data_ptr(),
+                           resid.data_ptr())
+    assert rc == 0
+    ref = _ref_epilogue((A.double() @ W.double()).float(), flags, bias, resid, None)
+    assert (out - ref).abs().max().item() <= FP32_ABS_TOL
+
+
+def _attention_ref(qkv, mask, B, S, heads):
+    H = heads * 64
+    q, k, v = [t.view(B, S, heads, 64).permute(0, 2, 1, 3).float() for t in qkv.view(B * S, 3, H).unbind(1)]
+    scores = q @ k.transpose(-1, -2) / math.sqrt(64)
+    if mask is not None:
+        scores = scores + (1.0 - mask.view(B, 1, 1, S).float()) * -10000.0
+    ctx = torch.softmax(scores, -1) @ v
+    return ctx.permute(0, 2, 1, 3).reshape(B * S, H)
+
+
+def _mask(B, S, mode, g):
+    if mode == "none":
+        return None
+    lens = torch.randint(1, S + 1, (B,), device="cuda", generator=g)
+    m = (torch.arange(S, device="cuda")[None, :] < lens[:, None]).int()
+    if mode == "full":
+        m[:] = 1
+    if mode == "holes":
+        m = m * (torch.rand(B, S, device="cuda", generator=g) > 0.3).int()
+        m[:, 0] = 1
+    if mode == "zero_row":
+        m[0, :] = 0
+    return m.contiguous()
+
+
+@pytest.mark.parametrize("bf16", [1, 0])
+@pytest.mark.parametrize("B,S,heads", [(2, 128, 12), (3, 200, 16), (1, 512, 16), (4, 17, 12), (2, 1, 12), (5, 64, 16),
+                                       (2, 65, 12)])
+@pytest.mark.parametrize("mode", ["prefix", "none", "holes", "zero_row", "full"])
+def test_attention(pybert, bf16, B, S, heads, mode):
+    g = torch.Generator(device="cuda").manual_seed(B * 1000 + S + heads)
+    H = heads * 64
+    qkv = torch.randn(B * S, 3 * H, device="cuda", generator=g)
+    mask = _mask(B, S, mode, g)
+    x = qkv.bfloat16() if bf16 else qkv
+    ctx = torch.full((B * S, H), float("nan"), device="cuda", dtype=x.dtype)
+    rc = pybert.k_attention(bf16, x.data_ptr(), None if mask is None else mask.data_ptr(), ctx.data_ptr(), B, S, heads)
+    assert rc == 0
+    ref = _attention_ref(x.float(), mask, B, S, heads)
+    got = ctx.float()
+    assert torch.isfinite(got).all()
+    err = (got - ref).abs().max().item()
+    assert err <= (2.5e-2 if bf16 else 1e-4), "max abs err %.3g" % err
+
+
+@pytest.mark.parametrize("bf16", [1, 0])
+@pytest.mark.parametrize("H", [768, 1024])
+def test_embed_layernorm_and_layernorm(pybert, bf16, H):
+    g = torch.Generator(device="cuda").manual_seed(H + bf16)
+    B, S, vocab = 5, 37, 4000
+    T = B * S
+    dt = torch.bfloat16 if bf16 else torch.float32
+    word = (torch.randn(vocab, H, device="cuda", generator=g) * 0.02).to(dt)
+    pos = (torch.randn(512, H, device="cuda", generator=g) * 0.02).to(dt)
+    typ = (torch.randn(2, H, device="cuda", generator=g) * 0.02).to(dt)
+    gamma = 1 + torch.randn(H, device="cuda", generator=g) * 0.1
+    beta = torch.randn(H, device="cuda", generator=g) * 0.1
+    ids = torch.randint(0, vocab, (T,), device="cuda", generator=g, dtype=torch.int32)
+    seg = torch.randint(0, 2, (T,), device="cuda", generator=g, dtype=torch.int32)
+    out = torch.empty(T, H, device="cuda", dtype=dt)
+    rc = pybert.k_embed_layernorm(bf16, ids.data_ptr(), seg.data_ptr(), word.data_ptr(), pos.data_ptr(),
+                                  typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), T, S, H, vocab)
+    assert rc == 0
+    p = torch.arange(T, device="cuda") % S
+    e = word.float()[ids.long()] + pos.float()[p] + typ.float()[seg.long()]
+    ref = bert_oracle.layer_norm(e, gamma, beta)
+    tol = 3e-2 if bf16 else 2e-5
+    assert (out.float() - ref).abs().max().item() <= tol
+
+    x = torch.randn(T, H, device="cuda", generator=g).to(dt)
+    out2 = torch.empty_like(x)
+    assert pybert.k_layernorm(bf16, x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out2.data_ptr(), T, H) == 0
+    ref2 = bert_oracle.layer_norm(x.float(), gamma, beta)
+    assert (out2.float() - ref2).abs().max().item() <= tol
+
+    # an out-of-range id is clamped and reported, it never reads outside the table
+    ids[3] = vocab + 5
+    rc = pybert.k_embed_layernorm(bf16, ids.data_ptr(), seg.data_ptr(), word.data_ptr(), pos.data_ptr(),
+                                  typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), T, S, H, vocab)
+    assert rc == 5

@@ -1,0 +1,141 @@
+"""End-to-end parity of the CUDA path, called through the reference-facing API
+(Cuda_BERT.encode -> ctypes -> Cuda_Bert), against the golden outputs of the real reference
+model and against the CPU oracle.
+
+Tolerances are the ones the benchmark specification states:
+  fp32 mode   max-abs pooler error <= 1e-3
+  bf16 mode   max|a-b| / max|b|    <= 2e-2
+  fp8 mode    max|a-b| / max|b|    <= 5e-2   (against the fp32 path on identical inputs)
+"""
+import numpy as np
+import pytest
+
+import cases
+from cudabert_b200 import synth
+from oracle import bert_oracle
+
+pytestmark = pytest.mark.gpu
+
+FP32_MAXABS = 1e-3
+BF16_REL = 2e-2
+FP8_REL = 5e-2
+
+
+@pytest.mark.parametrize("name", list(cases.CASES.keys()))
+def test_fp32_mode_matches_reference(models, name):
+    m = models(cases.CASES[name]["weights"], "fp32")
+    ids, seg, mask = cases.case_inputs(name)
+    gold = cases.load_golden(name)
+    pooled = m.encode([ids, seg, mask])
+    assert pooled.shape == gold["pooled"].shape and pooled.dtype == np.float32
+    assert np.abs(pooled - gold["pooled"]).max() <= FP32_MAXABS
+    assert np.abs(pooled - gold["pooled64"]).max() <= FP32_MAXABS
+
+
+@pytest.mark.parametrize("name", list(cases.CASES.keys()))
+def test_bf16_mode_matches_reference(models, name):
+    m = models(cases.CASES[name]["weights"], "bf16")
+    ids, seg, mask = cases.case_inputs(name)
+    gold = cases.load_golden(name)
+    pooled = m.encode([ids, seg, mask])
+    assert np.isfinite(pooled).all()
+    assert bert_oracle.rel_err(pooled, gold["pooled"]) <= BF16_REL
+
+
+@pytest.mark.parametrize("name", ["c4_small", "c1_small", "c0_affine", "edge_s17"])
+def test_fp8_mode_matches_fp32_path(models, name):
+    wname = cases.CASES[name]["weights"]
+    ids, seg, mask = cases.case_inputs(name)
+    p8 = models(wname, "fp8").encode([ids, seg, mask])
+    p32 = models(wname, "fp32").encode([ids, seg, mask])
+    assert np.isfinite(p8).all()
+    assert bert_oracle.rel_err(p8, p32) <= FP8_REL
+
+
+@pytest.mark.parametrize("name,precision", [("c1_small", "bf16"), ("c0", "fp32"), ("c4_small", "fp8")])
+def test_classifier_head(models, name, precision):
+    m = models(cases.CASES[name]["weights"], precision)
+    ids, seg, mask = cases.case_inputs(name)
+    gold = cases.load_golden(name)
+    probs = m.classify([ids, seg, mask])
+    assert probs.shape == gold["probs"].shape
+    assert np.abs(probs.sum(-1) - 1).max() <= 1e-5
+    assert np.abs(probs - gold["probs"]).max() <= (1e-3 if precision == "fp32" else 2e-2)
+
+
+def test_cuda_inference_returns_device_hidden_states(models):
+    """Cuda_Inference hands back device pointers {hidden [B,S,H] fp32, pooled [B,H] fp32}."""
+    import torch
+    from cudabert_b200.cuda_bert import pybert
+    name = "edge_s17"
+    m = models(cases.CASES[name]["weights"], "fp32")
+    ids, seg, mask = cases.case_inputs(name)
+    gold = cases.load_golden(name)
+    B, S = ids.shape
+    H = m.hidden_size
+    ret = pybert.inference(m.model, ids, seg, B, S, mask)
+    pybert.check(m.model)
+    assert ret.tensor and ret.Pooled_Output
+    hidden = np.empty((B, S, H), np.float32)
+    pooled = np.empty((B, H), np.float32)
+    rt = torch.cuda.cudart()
+    assert int(rt.cudaMemcpy(hidden.ctypes.data, ret.tensor, hidden.nbytes, 2)) == 0
+    assert int(rt.cudaMemcpy(pooled.ctypes.data, ret.Pooled_Output, pooled.nbytes, 2)) == 0
+    assert np.abs(pooled - gold["pooled"]).max() <= FP32_MAXABS
+    assert np.abs(hidden[:, 0, :] - gold["cls_hidden"]).max() <= 2e-3
+
+
+# ---------------------------------------------------------------- full-size workloads
+def _full_inputs(cfg):
+    c = synth.CONFIGS[cfg]
+    return synth.make_inputs(synth.input_seed(cfg), c["batch"], c["seq"], c["dist"])
+
+
+@pytest.mark.parametrize("cfg,wname,precision", [(1, "large_affine", "bf16"), (2, "base_affine", "bf16"),
+                                                 (3, "large_affine", "bf16"), (4, "large_affine", "fp8")])
+def test_full_size_properties(models, cfg, wname, precision):
+    """At the specification's full batch shapes the CPU oracle is too slow, so check properties
+    that do not depend on size:
+      * a row's pooler output does not depend on which other rows share the batch (bit-exact);
+      * token ids under masked positions do not influence the output (bit-exact);
+      * trimming the padded tail that no row uses (the engine's right-trim, utils.py:3-13)
+        does not change the output (bit-exact);
+      * the first rows agree with the CPU oracle within the mode's tolerance."""
+    m = models(wname, precision)
+    ids, seg, mask = _full_inputs(cfg)
+    full = m.encode([ids, seg, mask])
+    assert np.isfinite(full).all()
+    sub = m.encode([ids[:3], seg[:3], mask[:3]])
+    assert np.array_equal(full[:3], sub)
+    ids2 = ids.copy()
+    ids2[mask == 0] = 1234
+    assert np.array_equal(m.encode([ids2, seg, mask]), full)
+    maxlen = int(mask.sum(1).max())
+    if maxlen < ids.shape[1]:
+        trimmed = m.encode([ids[:, :maxlen].copy(), seg[:, :maxlen].copy(), mask[:, :maxlen].copy()])
+        assert np.array_equal(trimmed, full)
+    large, dims = cases.WEIGHT_SETS[wname][0], synth.model_dims(cases.WEIGHT_SETS[wname][0])
+    _, ref = bert_oracle.bert_forward(cases.get_weights(wname), ids[:2], seg[:2], mask[:2], dims["heads"],
+                                      dims["layers"])
+    tol = FP8_REL if precision == "fp8" else BF16_REL
+    assert bert_oracle.rel_err(full[:2], ref) <= tol
+
+
+def test_errors_do_not_kill_the_process(models, weight_dirs):
+    from cudabert_b200.cuda_bert import pybert
+    m = models("base_affine", "bf16")
+    ids, seg, mask = cases.case_inputs("edge_s17")
+    # sequence longer than the position table
+    big = np.zeros((1, 600), np.int32)
+    out = np.zeros((1, m.hidden_size), np.float32)
+    pybert.bert(m.model, out, big, big, 1, 600, None)
+    assert pybert.status(m.model) == 1 and "512" in pybert.last_error(m.model)
+    # an out-of-vocabulary id is reported, and the handle keeps working afterwards
+    bad = ids.copy()
+    bad[0, 1] = 40000
+    pybert.bert(m.model, np.zeros((ids.shape[0], m.hidden_size), np.float32), bad, seg, ids.shape[0], ids.shape[1], mask)
+    assert pybert.status(m.model) == 4
+    good = m.encode([ids, seg, mask])
+    assert np.isfinite(good).all()
+    with pytest.raises(RuntimeError):
+        pybert.load_model(False, "/nonexistent/dir")
