@@ -196,6 +196,21 @@ int cudabert_forward_dev(void* model, const int* ids_dev, const int* seg_dev, co
   return m->forward_device(ids_dev, seg_dev, mask_dev, batchsize, seq_length, false, false) ? 0 : m->status();
 }
 
+int cudabert_classify_dev(void* model, const int* ids_dev, const int* seg_dev, const int* mask_dev, int batchsize,
+                          int seq_length) {
+  Model* m = as_model(model);
+  if (!m) return 1;
+  begin_call(m);
+  return m->forward_device(ids_dev, seg_dev, mask_dev, batchsize, seq_length, false, true) ? 0 : m->status();
+}
+
+int cudabert_copy_to_host(void* dst_host, const void* src_dev, size_t bytes) {
+  if (!dst_host || !src_dev) return 1;
+  return cudaMemcpy(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 2;
+}
+
+float* cudabert_probs_dev(void* model) { return model ? as_model(model)->probs_dev() : nullptr; }
+
 int cudabert_sync(void* model) {
   Model* m = as_model(model);
   if (!m) return 1;
@@ -275,21 +290,20 @@ int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, voi
   return rc;
 }
 
-int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev, const void* word_dev,
-                               const void* pos_dev, const void* type_dev, const float* gamma_dev,
-                               const float* beta_dev, void* out_dev, int tokens, int S, int H, int vocab) {
+int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev, const float* word_dev,
+                               const float* pos_dev, const float* type_dev, const float* gamma_dev,
+                               const float* beta_dev, void* out_dev, float* out_f32_dev, int tokens, int S, int H,
+                               int vocab) {
   static thread_local DevErr scratch;
   if (!scratch.ok()) return 2;
   int n;
   if (bf16)
-    n = cb::embed_layernorm<__nv_bfloat16>(ids_dev, seg_dev, static_cast<const __nv_bfloat16*>(word_dev),
-                                           static_cast<const __nv_bfloat16*>(pos_dev),
-                                           static_cast<const __nv_bfloat16*>(type_dev), gamma_dev, beta_dev,
-                                           static_cast<__nv_bfloat16*>(out_dev), tokens, S, H, vocab, scratch.p, nullptr);
+    n = cb::embed_layernorm<__nv_bfloat16>(ids_dev, seg_dev, word_dev, pos_dev, type_dev, gamma_dev, beta_dev,
+                                           static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, S, H, vocab,
+                                           scratch.p, nullptr);
   else
-    n = cb::embed_layernorm<float>(ids_dev, seg_dev, static_cast<const float*>(word_dev),
-                                   static_cast<const float*>(pos_dev), static_cast<const float*>(type_dev), gamma_dev,
-                                   beta_dev, static_cast<float*>(out_dev), tokens, S, H, vocab, scratch.p, nullptr);
+    n = cb::embed_layernorm<float>(ids_dev, seg_dev, word_dev, pos_dev, type_dev, gamma_dev, beta_dev,
+                                   static_cast<float*>(out_dev), out_f32_dev, tokens, S, H, vocab, scratch.p, nullptr);
   if (n < 0) return 3;
   if (cudaDeviceSynchronize() != cudaSuccess) return 4;
   int herr = 0;
@@ -297,15 +311,14 @@ int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev,
   return herr ? 5 : 0;
 }
 
-int cudabert_k_layernorm(int bf16, const void* x_dev, const float* gamma_dev, const float* beta_dev, void* out_dev,
-                         int tokens, int H) {
+int cudabert_k_layernorm(int bf16, const float* x_dev, const float* gamma_dev, const float* beta_dev, void* out_dev,
+                         float* out_f32_dev, int tokens, int H) {
   int n;
   if (bf16)
-    n = cb::layernorm<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(x_dev), gamma_dev, beta_dev,
-                                     static_cast<__nv_bfloat16*>(out_dev), nullptr, tokens, H, nullptr);
+    n = cb::layernorm<__nv_bfloat16>(x_dev, gamma_dev, beta_dev, static_cast<__nv_bfloat16*>(out_dev), out_f32_dev,
+                                     tokens, H, nullptr);
   else
-    n = cb::layernorm<float>(static_cast<const float*>(x_dev), gamma_dev, beta_dev, static_cast<float*>(out_dev),
-                             nullptr, tokens, H, nullptr);
+    n = cb::layernorm<float>(x_dev, gamma_dev, beta_dev, static_cast<float*>(out_dev), out_f32_dev, tokens, H, nullptr);
   if (n < 0) return 3;
   return cudaDeviceSynchronize() == cudaSuccess ? 0 : 4;
 }

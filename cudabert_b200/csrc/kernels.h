@@ -57,15 +57,16 @@ int attention_f32(const float* qkv, const int* mask, const int* kv_len, float* c
 // kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none); mask null => S.
 int mask_to_kv_len(const int* mask, int* kv_len, int B, int S, cudaStream_t stream);
 
-// ---- row-wise kernels (T = float or __nv_bfloat16 for tables / activations)
+// ---- row-wise kernels.  The residual stream is kept in fp32; TOut (float or __nv_bfloat16) is
+// the copy that feeds the next GEMM.  out_f32 (may be null) receives the same values in fp32.
 // out[t] = LayerNorm(word[ids[t]] + pos[t % S] + type[seg[t]]) ; err bit 1 set on a bad id.
-template <typename T>
-int embed_layernorm(const int* ids, const int* seg, const T* word, const T* pos, const T* type,
-                    const float* gamma, const float* beta, T* out, int tokens, int S, int H, int vocab,
-                    int* err_flag, cudaStream_t stream);
-// out[t] = LayerNorm(x[t]) * gamma + beta ; optional fp32 copy of the result.
-template <typename T>
-int layernorm(const T* x, const float* gamma, const float* beta, T* out, float* out_f32, int tokens, int H,
+template <typename TOut>
+int embed_layernorm(const int* ids, const int* seg, const float* word, const float* pos, const float* type,
+                    const float* gamma, const float* beta, TOut* out, float* out_f32, int tokens, int S, int H,
+                    int vocab, int* err_flag, cudaStream_t stream);
+// out[t] = LayerNorm(x[t]) * gamma + beta.
+template <typename TOut>
+int layernorm(const float* x, const float* gamma, const float* beta, TOut* out, float* out_f32, int tokens, int H,
               cudaStream_t stream);
 // probs[b, :] = softmax(pooled[b, :] . W[H, C] + bias[C]),  C <= 32
 int classify_softmax(const float* pooled, const float* W, const float* bias, float* probs, int B, int H, int C,

@@ -35,7 +35,6 @@ Model::~Model() {
   if (stream_) cudaStreamSynchronize(stream_);
   for (void* p : owned_) cudaFree(p);
   if (arena_) cudaFree(arena_);
-  if (hidden_f32_) cudaFree(hidden_f32_);
   if (stage_f32_) cudaFree(stage_f32_);
   if (err_dev_) cudaFree(err_dev_);
   if (h_in_) cudaFreeHost(h_in_);
@@ -128,34 +127,31 @@ bool Model::upload_vec(const std::vector<std::string>& keys, size_t n, float** d
   return check(cudaStreamSynchronize(stream_), "copy");
 }
 
-bool Model::upload_table(const std::vector<std::string>& keys, size_t min_rows, void** dst, int* rows_out) {
+bool Model::upload_table(const std::vector<std::string>& keys, size_t min_rows, float** dst, int* rows_out) {
   NpyArray a;
   if (!read_tensor(keys, 0, &a)) return false;
   if (a.shape.size() != 2 || a.shape[1] != static_cast<size_t>(H_) || a.shape[0] < min_rows)
     return fail(3, "embedding table has the wrong shape");
   if (rows_out) *rows_out = static_cast<int>(a.shape[0]);
   const size_t n = a.numel();
-  if (!check(cudaMalloc(dst, n * esize_), "cudaMalloc")) return false;
+  if (!check(cudaMalloc(dst, n * sizeof(float)), "cudaMalloc")) return false;
   owned_.push_back(*dst);
-  if (prec_ == PREC_FP32) {
-    if (!check(cudaMemcpyAsync(*dst, stage_f32_, n * 4, cudaMemcpyDeviceToDevice, stream_), "copy")) return false;
-  } else if (convert_f32_to_bf16(stage_f32_, static_cast<__nv_bfloat16*>(*dst), n, stream_) < 0) {
-    return fail(2, "convert launch failed");
-  }
-  return check(cudaStreamSynchronize(stream_), "table conversion");
+  if (!check(cudaMemcpyAsync(*dst, stage_f32_, n * 4, cudaMemcpyDeviceToDevice, stream_), "copy")) return false;
+  return check(cudaStreamSynchronize(stream_), "table copy");
 }
 
 bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::vector<std::string>& keys_bias, int K,
-                       int N, DenseWeight* d, int n_off, int n_total) {
+                       int N, DenseWeight* d, int n_off, int n_total, int prec) {
+  const size_t esize = (prec == PREC_FP32) ? 4 : 2;
   if (n_off == 0) {
     d->K = K;
     d->N = n_total;
     const size_t elems = static_cast<size_t>(K) * n_total;
-    if (!check(cudaMalloc(&d->w, elems * esize_), "cudaMalloc")) return false;
+    if (!check(cudaMalloc(&d->w, elems * esize), "cudaMalloc")) return false;
     owned_.push_back(d->w);
     if (!check(cudaMalloc(&d->bias, n_total * sizeof(float)), "cudaMalloc")) return false;
     owned_.push_back(d->bias);
-    if (prec_ == PREC_FP8) {
+    if (prec == PREC_FP8) {
       if (!check(cudaMalloc(&d->w_fp8, elems), "cudaMalloc")) return false;
       owned_.push_back(d->w_fp8);
       if (!check(cudaMalloc(&d->colscale, n_total * sizeof(float)), "cudaMalloc")) return false;
@@ -166,13 +162,13 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
   if (!read_tensor(keys_kernel, static_cast<size_t>(K) * N, &a)) return false;
   if (a.shape.size() != 2 || a.shape[0] != static_cast<size_t>(K) || a.shape[1] != static_cast<size_t>(N))
     return fail(3, "dense kernel is not stored [in, out]");
-  if (prec_ == PREC_FP32) {
+  if (prec == PREC_FP32) {
     // keep [K, N]; Q, K, V are packed side by side into [K, 3H]
     float* base = static_cast<float*>(d->w) + n_off;
     if (!check(cudaMemcpy2DAsync(base, static_cast<size_t>(n_total) * 4, stage_f32_, static_cast<size_t>(N) * 4,
                                  static_cast<size_t>(N) * 4, K, cudaMemcpyDeviceToDevice, stream_), "pack"))
       return false;
-  } else if (prec_ == PREC_BF16) {
+  } else if (prec == PREC_BF16) {
     if (transpose_to_bf16(stage_f32_, static_cast<__nv_bfloat16*>(d->w) + static_cast<size_t>(n_off) * K, K, N,
                           stream_) < 0)
       return fail(2, "transpose launch failed");
@@ -196,8 +192,8 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
   return check(cudaStreamSynchronize(stream_), "bias");
 }
 
-bool Model::finish_dense(DenseWeight* d) {
-  if (prec_ == PREC_FP32) return true;
+bool Model::finish_dense(DenseWeight* d, int prec) {
+  if (prec == PREC_FP32) return true;
   if (!make_tmap_bf16_kmajor(&d->tmap, d->w, d->N, d->K, static_cast<uint64_t>(d->K) * 2, gemm_block_n(d->N)))
     return fail(2, "cuTensorMapEncodeTiled failed for a weight matrix");
   return true;
@@ -222,26 +218,26 @@ bool Model::load_weights(const std::string& dir) {
     const char* qkv_names[3] = {"query", "key", "value"};
     for (int j = 0; j < 3; ++j) {
       const std::string s = p + "attention_self_" + qkv_names[j];
-      if (!load_dense({s + "_kernel"}, {s + "_bias"}, H_, H_, &lw.qkv, j * H_, 3 * H_)) return false;
+      if (!load_dense({s + "_kernel"}, {s + "_bias"}, H_, H_, &lw.qkv, j * H_, 3 * H_, prec_)) return false;
     }
-    if (!finish_dense(&lw.qkv)) return false;
+    if (!finish_dense(&lw.qkv, prec_)) return false;
     if (!load_dense({p + "attention_output_dense_kernel"}, {p + "attention_output_dense_bias"}, H_, H_, &lw.attn_out,
-                    0, H_) || !finish_dense(&lw.attn_out))
+                    0, H_, prec_) || !finish_dense(&lw.attn_out, prec_))
       return false;
     if (!upload_vec({p + "attention_output_LayerNorm_gamma"}, H, &lw.ln1_g)) return false;
     if (!upload_vec({p + "attention_output_LayerNorm_beta"}, H, &lw.ln1_b)) return false;
-    if (!load_dense({p + "intermediate_dense_kernel"}, {p + "intermediate_dense_bias"}, H_, F_, &lw.ffn1, 0, F_) ||
-        !finish_dense(&lw.ffn1))
+    if (!load_dense({p + "intermediate_dense_kernel"}, {p + "intermediate_dense_bias"}, H_, F_, &lw.ffn1, 0, F_, prec_) ||
+        !finish_dense(&lw.ffn1, prec_))
       return false;
-    if (!load_dense({p + "output_dense_kernel"}, {p + "output_dense_bias"}, F_, H_, &lw.ffn2, 0, H_) ||
-        !finish_dense(&lw.ffn2))
+    if (!load_dense({p + "output_dense_kernel"}, {p + "output_dense_bias"}, F_, H_, &lw.ffn2, 0, H_, prec_) ||
+        !finish_dense(&lw.ffn2, prec_))
       return false;
     if (!upload_vec({p + "output_LayerNorm_gamma"}, H, &lw.ln2_g)) return false;
     if (!upload_vec({p + "output_LayerNorm_beta"}, H, &lw.ln2_b)) return false;
   }
   // the pooler is needed by the encoder although name.txt does not list it (utils/bert.cu:67-69)
-  if (!load_dense({"pooler_dense_kernel"}, {"pooler_dense_bias"}, H_, H_, &pooler_, 0, H_) || !finish_dense(&pooler_))
-    return false;
+  // (kept in fp32 in every mode: it is 2 H^2 FLOPs per sequence and reads the fp32 residual stream)
+  if (!load_dense({"pooler_dense_kernel"}, {"pooler_dense_bias"}, H_, H_, &pooler_, 0, H_, PREC_FP32)) return false;
   // optional fine-tune head (apps/finetune.py:33-34)
   if (find_file({"classifier_kernel"}) && find_file({"classifier_bias"})) {
     NpyArray k;
@@ -264,67 +260,61 @@ bool Model::load_weights(const std::string& dir) {
 }
 
 // ------------------------------------------------------------------ arena
-bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
+bool Model::ensure_capacity(int B, int S, bool) {
   const size_t T = static_cast<size_t>(B) * S;
-  if (T > cap_tokens_ || B > cap_batch_) {
-    if (!check(cudaStreamSynchronize(stream_), "sync before arena growth")) return false;
-    const size_t ct = std::max(T, cap_tokens_);
-    const int cbatch = std::max(B, cap_batch_);
-    if (arena_) cudaFree(arena_);
-    arena_ = nullptr;
-    cap_tokens_ = 0;
-    cap_batch_ = 0;
-    size_t off = 0;
-    auto slot = [&](size_t bytes) { const size_t o = off; off = align_up(off + bytes, 1024); return o; };
-    const size_t o_ints = slot(3 * ct * sizeof(int));
-    const size_t o_kv = slot(static_cast<size_t>(cbatch) * sizeof(int));
-    const size_t o_x = slot(ct * H_ * esize_);
-    const size_t o_x1 = slot(ct * H_ * esize_);
-    const size_t o_y = slot(ct * H_ * esize_);
-    const size_t o_ctx = slot(ct * H_ * esize_);
-    const size_t o_qkv = slot(ct * 3 * H_ * esize_);
-    const size_t o_z = slot(ct * F_ * esize_);
-    const size_t o_pool = slot(static_cast<size_t>(cbatch) * H_ * sizeof(float));
-    const size_t o_probs = slot(static_cast<size_t>(cbatch) * MAX_CLASSES * sizeof(float));
-    if (!check(cudaMalloc(&arena_, off), "cudaMalloc(activation arena)")) return false;
-    char* base = static_cast<char*>(arena_);
-    ids_ = reinterpret_cast<int*>(base + o_ints);
-    kv_len_ = reinterpret_cast<int*>(base + o_kv);
-    x_ = base + o_x; x1_ = base + o_x1; y_ = base + o_y; ctx_ = base + o_ctx; qkv_ = base + o_qkv; z_ = base + o_z;
-    pooled_ = reinterpret_cast<float*>(base + o_pool);
-    probs_ = reinterpret_cast<float*>(base + o_probs);
-    // zero once so that tile rows beyond the live token count never hold NaN patterns
-    if (!check(cudaMemsetAsync(arena_, 0, off, stream_), "cudaMemset(arena)")) return false;
-    if (prec_ != PREC_FP32) {
-      const uint64_t rows = ct;
-      bool ok = make_tmap_bf16_kmajor(&tm_x_, x_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
-                make_tmap_bf16_kmajor(&tm_x1_, x1_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
-                make_tmap_bf16_kmajor(&tm_ctx_, ctx_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
-                make_tmap_bf16_kmajor(&tm_z_, z_, rows, F_, static_cast<uint64_t>(F_) * 2, 128);
-      if (!ok) return fail(2, "cuTensorMapEncodeTiled failed for an activation buffer");
-    }
-    if (h_in_) cudaFreeHost(h_in_);
-    if (h_out_) cudaFreeHost(h_out_);
-    h_in_ = nullptr; h_out_ = nullptr;
-    if (!check(cudaMallocHost(&h_in_, 3 * ct * sizeof(int)), "cudaMallocHost")) return false;
-    h_out_elems_ = static_cast<size_t>(cbatch) * (H_ + MAX_CLASSES);
-    if (!check(cudaMallocHost(&h_out_, h_out_elems_ * sizeof(float)), "cudaMallocHost")) return false;
-    cap_tokens_ = ct;
-    cap_batch_ = cbatch;
+  if (T <= cap_tokens_ && B <= cap_batch_) return true;
+  if (!check(cudaStreamSynchronize(stream_), "sync before arena growth")) return false;
+  const size_t ct = std::max(T, cap_tokens_);
+  const int cbatch = std::max(B, cap_batch_);
+  if (arena_) cudaFree(arena_);
+  arena_ = nullptr;
+  cap_tokens_ = 0;
+  cap_batch_ = 0;
+  const bool lowp = prec_ != PREC_FP32;
+  size_t off = 0;
+  auto slot = [&](size_t bytes) { const size_t o = off; off = align_up(off + bytes, 1024); return o; };
+  const size_t o_ints = slot(3 * ct * sizeof(int));
+  const size_t o_kv = slot(static_cast<size_t>(cbatch) * sizeof(int));
+  const size_t o_xf = slot(ct * H_ * sizeof(float));
+  const size_t o_x1f = slot(ct * H_ * sizeof(float));
+  const size_t o_y = slot(ct * H_ * sizeof(float));
+  const size_t o_xa = lowp ? slot(ct * H_ * 2) : o_xf;
+  const size_t o_x1a = lowp ? slot(ct * H_ * 2) : o_x1f;
+  const size_t o_ctx = slot(ct * H_ * esize_);
+  const size_t o_qkv = slot(ct * 3 * H_ * esize_);
+  const size_t o_z = slot(ct * F_ * esize_);
+  const size_t o_pool = slot(static_cast<size_t>(cbatch) * H_ * sizeof(float));
+  const size_t o_probs = slot(static_cast<size_t>(cbatch) * MAX_CLASSES * sizeof(float));
+  if (!check(cudaMalloc(&arena_, off), "cudaMalloc(activation arena)")) return false;
+  char* base = static_cast<char*>(arena_);
+  ids_ = reinterpret_cast<int*>(base + o_ints);
+  kv_len_ = reinterpret_cast<int*>(base + o_kv);
+  xf_ = reinterpret_cast<float*>(base + o_xf);
+  x1f_ = reinterpret_cast<float*>(base + o_x1f);
+  y_ = reinterpret_cast<float*>(base + o_y);
+  xa_ = base + o_xa; x1a_ = base + o_x1a; ctx_ = base + o_ctx; qkv_ = base + o_qkv; z_ = base + o_z;
+  pooled_ = reinterpret_cast<float*>(base + o_pool);
+  probs_ = reinterpret_cast<float*>(base + o_probs);
+  // zero once so that tile rows beyond the live token count never hold NaN patterns
+  if (!check(cudaMemsetAsync(arena_, 0, off, stream_), "cudaMemset(arena)")) return false;
+  if (lowp) {
+    const uint64_t rows = ct;
+    bool ok = make_tmap_bf16_kmajor(&tm_x_, xa_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
+              make_tmap_bf16_kmajor(&tm_x1_, x1a_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
+              make_tmap_bf16_kmajor(&tm_ctx_, ctx_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
+              make_tmap_bf16_kmajor(&tm_z_, z_, rows, F_, static_cast<uint64_t>(F_) * 2, 128);
+    if (!ok) return fail(2, "cuTensorMapEncodeTiled failed for an activation buffer");
   }
-  if (want_hidden_f32 && prec_ != PREC_FP32 && hidden_f32_tokens_ < T) {
-    if (!check(cudaStreamSynchronize(stream_), "sync")) return false;
-    if (hidden_f32_) cudaFree(hidden_f32_);
-    hidden_f32_ = nullptr;
-    hidden_f32_tokens_ = 0;
-    const size_t tok = std::max(T, cap_tokens_);
-    if (!check(cudaMalloc(&hidden_f32_, tok * H_ * sizeof(float)), "cudaMalloc(hidden fp32)")) return false;
-    hidden_f32_tokens_ = tok;
-  }
+  if (h_in_) cudaFreeHost(h_in_);
+  if (h_out_) cudaFreeHost(h_out_);
+  h_in_ = nullptr; h_out_ = nullptr;
+  if (!check(cudaMallocHost(&h_in_, 3 * ct * sizeof(int)), "cudaMallocHost")) return false;
+  h_out_elems_ = static_cast<size_t>(cbatch) * (H_ + MAX_CLASSES);
+  if (!check(cudaMallocHost(&h_out_, h_out_elems_ * sizeof(float)), "cudaMallocHost")) return false;
+  cap_tokens_ = ct;
+  cap_batch_ = cbatch;
   return true;
 }
-
-float* Model::hidden_f32_dev() const { return prec_ == PREC_FP32 ? static_cast<float*>(x_) : hidden_f32_; }
 
 // ------------------------------------------------------------------ profiling
 void Model::count(int kclass, int n) {
@@ -418,57 +408,52 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
   } while (0)
 
   CB_LAUNCH(KC_OTHER, mask_to_kv_len(d_mask, kv_len_, B, S, stream_));
-  if (prec_ == PREC_FP32) {
-    CB_LAUNCH(KC_EMBED, embed_layernorm<float>(d_ids, d_seg, static_cast<const float*>(word_),
-                                               static_cast<const float*>(pos_), static_cast<const float*>(type_),
-                                               emb_g_, emb_b_, static_cast<float*>(x_), T, S, H_, vocab_rows_,
-                                               err_dev_, stream_));
+  const bool lowp = prec_ != PREC_FP32;
+  __nv_bfloat16* xa = static_cast<__nv_bfloat16*>(xa_);
+  __nv_bfloat16* x1a = static_cast<__nv_bfloat16*>(x1a_);
+  if (lowp) {
+    CB_LAUNCH(KC_EMBED, embed_layernorm<__nv_bfloat16>(d_ids, d_seg, word_, pos_, type_, emb_g_, emb_b_, xa, xf_, T, S,
+                                                       H_, vocab_rows_, err_dev_, stream_));
   } else {
-    CB_LAUNCH(KC_EMBED, embed_layernorm<__nv_bfloat16>(
-                            d_ids, d_seg, static_cast<const __nv_bfloat16*>(word_),
-                            static_cast<const __nv_bfloat16*>(pos_), static_cast<const __nv_bfloat16*>(type_), emb_g_,
-                            emb_b_, static_cast<__nv_bfloat16*>(x_), T, S, H_, vocab_rows_, err_dev_, stream_));
+    CB_LAUNCH(KC_EMBED, embed_layernorm<float>(d_ids, d_seg, word_, pos_, type_, emb_g_, emb_b_, xf_, nullptr, T, S, H_,
+                                               vocab_rows_, err_dev_, stream_));
   }
+  const int f32out = lowp ? EPI_OUT_F32 : 0;  // the fp32 GEMM always writes fp32
   for (int l = 0; l < L_; ++l) {
     const LayerWeights& w = layer_[l];
-    const bool last = (l == L_ - 1);
-    if (!dense(w.qkv, x_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) return false;
-    if (prec_ == PREC_FP32) {
-      CB_LAUNCH(KC_ATTENTION, attention_f32(static_cast<const float*>(qkv_), d_mask, kv_len_,
-                                            static_cast<float*>(ctx_), B, S, heads_, stream_));
-    } else {
+    if (!dense(w.qkv, xa_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) return false;
+    if (lowp) {
       CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_,
                                              static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, stream_));
-    }
-    if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, T, y_, EPI_BIAS | EPI_RESIDUAL, x_, KC_GEMM_ATTN_OUT)) return false;
-    if (prec_ == PREC_FP32) {
-      CB_LAUNCH(KC_LAYERNORM, layernorm<float>(static_cast<const float*>(y_), w.ln1_g, w.ln1_b,
-                                               static_cast<float*>(x1_), nullptr, T, H_, stream_));
     } else {
-      CB_LAUNCH(KC_LAYERNORM, layernorm<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(y_), w.ln1_g, w.ln1_b,
-                                                       static_cast<__nv_bfloat16*>(x1_), nullptr, T, H_, stream_));
+      CB_LAUNCH(KC_ATTENTION, attention_f32(static_cast<const float*>(qkv_), d_mask, kv_len_,
+                                            static_cast<float*>(ctx_), B, S, heads_, stream_));
     }
-    if (!dense(w.ffn1, x1_, &tm_x1_, H_, T, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
-    if (!dense(w.ffn2, z_, &tm_z_, F_, T, y_, EPI_BIAS | EPI_RESIDUAL, x1_, KC_GEMM_FFN2)) return false;
-    if (prec_ == PREC_FP32) {
-      CB_LAUNCH(KC_LAYERNORM, layernorm<float>(static_cast<const float*>(y_), w.ln2_g, w.ln2_b,
-                                               static_cast<float*>(x_), nullptr, T, H_, stream_));
+    // y = ctx.Wo + bo + x  (fp32), x1 = LN(y)
+    if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, T, y_, EPI_BIAS | EPI_RESIDUAL | f32out, xf_, KC_GEMM_ATTN_OUT))
+      return false;
+    if (lowp) {
+      CB_LAUNCH(KC_LAYERNORM, layernorm<__nv_bfloat16>(y_, w.ln1_g, w.ln1_b, x1a, x1f_, T, H_, stream_));
     } else {
-      CB_LAUNCH(KC_LAYERNORM, layernorm<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(y_), w.ln2_g, w.ln2_b,
-                                                       static_cast<__nv_bfloat16*>(x_),
-                                                       (last && want_hidden_f32) ? hidden_f32_ : nullptr, T, H_,
-                                                       stream_));
+      CB_LAUNCH(KC_LAYERNORM, layernorm<float>(y_, w.ln1_g, w.ln1_b, x1f_, nullptr, T, H_, stream_));
+    }
+    if (!dense(w.ffn1, x1a_, &tm_x1_, H_, T, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
+    // y = z.W2 + b2 + x1 (fp32), x = LN(y)
+    if (!dense(w.ffn2, z_, &tm_z_, F_, T, y_, EPI_BIAS | EPI_RESIDUAL | f32out, x1f_, KC_GEMM_FFN2)) return false;
+    if (lowp) {
+      CB_LAUNCH(KC_LAYERNORM, layernorm<__nv_bfloat16>(y_, w.ln2_g, w.ln2_b, xa, xf_, T, H_, stream_));
+    } else {
+      CB_LAUNCH(KC_LAYERNORM, layernorm<float>(y_, w.ln2_g, w.ln2_b, xf_, nullptr, T, H_, stream_));
     }
   }
-  // pooler: rows b*S of the final hidden states, tanh(dense) -> fp32 [B, H] (utils/bert.cu:239-247)
-  if (prec_ == PREC_FP32) {
-    if (!dense(pooler_, x_, nullptr, S * H_, B, pooled_, EPI_BIAS | EPI_TANH, nullptr, KC_POOLER)) return false;
-  } else {
-    CUtensorMap tm_cls;
-    if (!make_tmap_bf16_kmajor(&tm_cls, x_, B, H_, static_cast<uint64_t>(S) * H_ * 2, 128))
-      return fail(2, "cuTensorMapEncodeTiled failed for the pooler input");
-    if (!dense(pooler_, x_, &tm_cls, 0, B, pooled_, EPI_BIAS | EPI_TANH | EPI_OUT_F32, nullptr, KC_POOLER))
-      return false;
+  // pooler: rows b*S of the fp32 final hidden states, tanh(dense) -> fp32 [B, H]
+  // (utils/bert.cu:239-247); always the fp32 kernel, it is 2 H^2 FLOPs per sequence
+  {
+    GemmEpilogue epi;
+    epi.flags = EPI_BIAS | EPI_TANH;
+    epi.bias = pooler_.bias;
+    CB_LAUNCH(KC_POOLER, gemm_f32(xf_, S * H_, static_cast<const float*>(pooler_.w), B, H_, H_, pooled_, H_, epi,
+                                  stream_));
   }
   if (want_probs)
     CB_LAUNCH(KC_OTHER, classify_softmax(pooled_, cls_w_, cls_b_, probs_, B, H_, classes_, stream_));

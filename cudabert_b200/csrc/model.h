@@ -61,7 +61,7 @@ class Model {
   bool sync();
 
   float* pooled_dev() const { return pooled_; }
-  float* hidden_f32_dev() const;
+  float* hidden_f32_dev() const { return xf_; }
   float* probs_dev() const { return probs_; }
   int hidden() const { return H_; }
   int layers() const { return L_; }
@@ -85,10 +85,10 @@ class Model {
   bool ensure_capacity(int B, int S, bool want_hidden_f32);
   bool load_weights(const std::string& dir);
   bool load_dense(const std::vector<std::string>& keys_kernel, const std::vector<std::string>& keys_bias,
-                  int K, int N, DenseWeight* dst, int n_off, int n_total);
-  bool finish_dense(DenseWeight* d);
+                  int K, int N, DenseWeight* dst, int n_off, int n_total, int prec);
+  bool finish_dense(DenseWeight* d, int prec);
   bool upload_vec(const std::vector<std::string>& keys, size_t n, float** dst);
-  bool upload_table(const std::vector<std::string>& keys, size_t min_rows, void** dst, int* rows_out);
+  bool upload_table(const std::vector<std::string>& keys, size_t min_rows, float** dst, int* rows_out);
   const std::string* find_file(const std::vector<std::string>& keys) const;
   bool read_tensor(const std::vector<std::string>& keys, size_t expect, struct NpyArray* arr);
   void count(int kclass, int n);
@@ -107,7 +107,7 @@ class Model {
   std::vector<std::string> files_;
 
   // weights
-  void *word_ = nullptr, *pos_ = nullptr, *type_ = nullptr;
+  float *word_ = nullptr, *pos_ = nullptr, *type_ = nullptr;  // embedding tables stay fp32 in every mode
   float *emb_g_ = nullptr, *emb_b_ = nullptr;
   std::vector<LayerWeights> layer_;
   DenseWeight pooler_;
@@ -121,11 +121,13 @@ class Model {
   int cap_batch_ = 0;
   void* arena_ = nullptr;
   int *ids_ = nullptr, *kv_len_ = nullptr, *err_dev_ = nullptr;  // ids_: 3 * cap_tokens ints (ids | seg | mask)
-  void *x_ = nullptr, *x1_ = nullptr, *y_ = nullptr, *ctx_ = nullptr, *qkv_ = nullptr, *z_ = nullptr;
-  float *pooled_ = nullptr, *probs_ = nullptr, *hidden_f32_ = nullptr;
-  size_t hidden_f32_tokens_ = 0;
+  // residual stream in fp32: xf_ (layer input / output), x1f_ (after the attention block),
+  // y_ (pre-LayerNorm sums).  xa_ / x1a_ are the copies that feed the GEMMs (bf16 in the bf16 and
+  // fp8 modes; in fp32 mode they alias xf_ / x1f_).  ctx_, qkv_, z_ are in the GEMM element type.
+  float *xf_ = nullptr, *x1f_ = nullptr, *y_ = nullptr;
+  void *xa_ = nullptr, *x1a_ = nullptr, *ctx_ = nullptr, *qkv_ = nullptr, *z_ = nullptr;
+  float *pooled_ = nullptr, *probs_ = nullptr;
   CUtensorMap tm_x_, tm_x1_, tm_ctx_, tm_z_;
-  int tm_rows_ = 0;
 
   // pinned staging
   int* h_in_ = nullptr;

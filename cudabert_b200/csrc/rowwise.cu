@@ -21,63 +21,45 @@ namespace {
 constexpr float LN_EPS = 1e-12f;
 constexpr int ROWS_PER_BLOCK = 4;
 
-template <typename T> struct Vec;
-template <> struct Vec<float> {
-  static constexpr int N = 4;
-  using Raw = float4;
-  __device__ static void load(const float* p, float (&v)[4]) {
-    const float4 t = *reinterpret_cast<const float4*>(p);
-    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-  }
-  __device__ static void store(float* p, const float (&v)[4]) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-  }
-};
-template <> struct Vec<__nv_bfloat16> {
-  static constexpr int N = 8;
-  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
-    const uint4 t = *reinterpret_cast<const uint4*>(p);
-    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
-      v[2 * i] = __low2float(h);
-      v[2 * i + 1] = __high2float(h);
-    }
-  }
-  __device__ static void store(__nv_bfloat16* p, const float (&v)[8]) {
-    uint4 t;
-    t.x = pack_bf16(v[0], v[1]); t.y = pack_bf16(v[2], v[3]);
-    t.z = pack_bf16(v[4], v[5]); t.w = pack_bf16(v[6], v[7]);
-    *reinterpret_cast<uint4*>(p) = t;
-  }
-};
-
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
   return v;
 }
 
-// MAXV: vectors per lane; H <= 32 * MAXV * Vec<T>::N  (H = 768 or 1024 -> 4 vectors of 8 bf16 / 8 of 4 fp32)
-template <typename T, int MAXV>
-__device__ __forceinline__ void normalise_and_store(float (&x)[MAXV][Vec<T>::N], int nvec, int lane, int H,
+// Each lane holds NV float4 vectors of its row: columns (i * 32 + lane) * 4 .. + 3, i < nvec.
+// H <= 1024 -> at most 8 vectors per lane.
+constexpr int MAXV = 8;
+
+template <typename TOut>
+__device__ __forceinline__ void store4(TOut* p, const float (&y)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&y)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(y[0], y[1], y[2], y[3]);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&y)[4]) {
+  uint2 t;
+  t.x = pack_bf16(y[0], y[1]);
+  t.y = pack_bf16(y[2], y[3]);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+template <typename TOut>
+__device__ __forceinline__ void normalise_and_store(float (&x)[MAXV][4], int nvec, int lane, int H,
                                                     const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                    T* __restrict__ out_row, float* __restrict__ out_f32_row) {
-  constexpr int VN = Vec<T>::N;
+                                                    TOut* __restrict__ out_row, float* __restrict__ out_f32_row) {
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i)
-    if (i < nvec)
-#pragma unroll
-      for (int j = 0; j < VN; ++j) sum += x[i][j];
+    if (i < nvec) sum += (x[i][0] + x[i][1]) + (x[i][2] + x[i][3]);
   const float mean = warp_sum(sum) / static_cast<float>(H);
   float sq = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i)
     if (i < nvec)
 #pragma unroll
-      for (int j = 0; j < VN; ++j) {
+      for (int j = 0; j < 4; ++j) {
         const float d = x[i][j] - mean;
         sq += d * d;
       }
@@ -86,35 +68,26 @@ __device__ __forceinline__ void normalise_and_store(float (&x)[MAXV][Vec<T>::N],
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     if (i < nvec) {
-      const int col = (i * 32 + lane) * VN;
-      float y[VN];
-#pragma unroll
-      for (int j = 0; j < VN; j += 4) {
-        const float4 g = __ldg(reinterpret_cast<const float4*>(gamma + col + j));
-        const float4 bt = __ldg(reinterpret_cast<const float4*>(beta + col + j));
-        y[j] = g.x * ((x[i][j] - mean) * rstd) + bt.x;
-        y[j + 1] = g.y * ((x[i][j + 1] - mean) * rstd) + bt.y;
-        y[j + 2] = g.z * ((x[i][j + 2] - mean) * rstd) + bt.z;
-        y[j + 3] = g.w * ((x[i][j + 3] - mean) * rstd) + bt.w;
-      }
-      Vec<T>::store(out_row + col, y);
-      if (out_f32_row) {
-#pragma unroll
-        for (int j = 0; j < VN; j += 4)
-          *reinterpret_cast<float4*>(out_f32_row + col + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
-      }
+      const int col = (i * 32 + lane) * 4;
+      const float4 g = __ldg(reinterpret_cast<const float4*>(gamma + col));
+      const float4 bt = __ldg(reinterpret_cast<const float4*>(beta + col));
+      float y[4];
+      y[0] = g.x * ((x[i][0] - mean) * rstd) + bt.x;
+      y[1] = g.y * ((x[i][1] - mean) * rstd) + bt.y;
+      y[2] = g.z * ((x[i][2] - mean) * rstd) + bt.z;
+      y[3] = g.w * ((x[i][3] - mean) * rstd) + bt.w;
+      store4<TOut>(out_row + col, y);
+      if (out_f32_row) store4<float>(out_f32_row + col, y);
     }
   }
 }
 
-template <typename T>
+template <typename TOut>
 __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
-embed_layernorm_kernel(const int* __restrict__ ids, const int* __restrict__ seg, const T* __restrict__ word,
-                       const T* __restrict__ pos, const T* __restrict__ type, const float* __restrict__ gamma,
-                       const float* __restrict__ beta, T* __restrict__ out, int tokens, int S, int H, int vocab,
-                       int* err) {
-  constexpr int VN = Vec<T>::N;
-  constexpr int MAXV = 32 / VN;  // 1024 / (32 * VN)
+embed_layernorm_kernel(const int* __restrict__ ids, const int* __restrict__ seg, const float* __restrict__ word,
+                       const float* __restrict__ pos, const float* __restrict__ type, const float* __restrict__ gamma,
+                       const float* __restrict__ beta, TOut* __restrict__ out, float* __restrict__ out_f32, int tokens,
+                       int S, int H, int vocab, int* err) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
   if (t >= tokens) return;
@@ -124,43 +97,44 @@ embed_layernorm_kernel(const int* __restrict__ ids, const int* __restrict__ seg,
     id = min(max(id, 0), vocab - 1);
     sg = min(max(sg, 0), 1);
   }
-  const T* wr = word + static_cast<size_t>(id) * H;
-  const T* pr = pos + static_cast<size_t>(t % S) * H;
-  const T* tr = type + static_cast<size_t>(sg) * H;
-  const int nvec = H / (32 * VN);
-  float x[MAXV][VN];
+  const float* wr = word + static_cast<size_t>(id) * H;
+  const float* pr = pos + static_cast<size_t>(t % S) * H;
+  const float* tr = type + static_cast<size_t>(sg) * H;
+  const int nvec = H / 128;
+  float x[MAXV][4];
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     if (i < nvec) {
-      const int col = (i * 32 + lane) * VN;
-      float a[VN], b[VN], c[VN];
-      Vec<T>::load(wr + col, a);
-      Vec<T>::load(pr + col, b);
-      Vec<T>::load(tr + col, c);
-#pragma unroll
-      for (int j = 0; j < VN; ++j) x[i][j] = a[j] + b[j] + c[j];
+      const int col = (i * 32 + lane) * 4;
+      const float4 a = __ldg(reinterpret_cast<const float4*>(wr + col));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(pr + col));
+      const float4 c = __ldg(reinterpret_cast<const float4*>(tr + col));
+      x[i][0] = a.x + b.x + c.x; x[i][1] = a.y + b.y + c.y;
+      x[i][2] = a.z + b.z + c.z; x[i][3] = a.w + b.w + c.w;
     }
   }
-  normalise_and_store<T, MAXV>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H, nullptr);
+  normalise_and_store<TOut>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H,
+                            out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr);
 }
 
-template <typename T>
+template <typename TOut>
 __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
-layernorm_kernel(const T* __restrict__ in, const float* __restrict__ gamma, const float* __restrict__ beta,
-                 T* __restrict__ out, float* __restrict__ out_f32, int tokens, int H) {
-  constexpr int VN = Vec<T>::N;
-  constexpr int MAXV = 32 / VN;
+layernorm_kernel(const float* __restrict__ in, const float* __restrict__ gamma, const float* __restrict__ beta,
+                 TOut* __restrict__ out, float* __restrict__ out_f32, int tokens, int H) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
   if (t >= tokens) return;
-  const T* row = in + static_cast<size_t>(t) * H;
-  const int nvec = H / (32 * VN);
-  float x[MAXV][VN];
+  const float* row = in + static_cast<size_t>(t) * H;
+  const int nvec = H / 128;
+  float x[MAXV][4];
 #pragma unroll
   for (int i = 0; i < MAXV; ++i)
-    if (i < nvec) Vec<T>::load(row + (i * 32 + lane) * VN, x[i]);
-  normalise_and_store<T, MAXV>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H,
-                               out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr);
+    if (i < nvec) {
+      const float4 v = *reinterpret_cast<const float4*>(row + (i * 32 + lane) * 4);
+      x[i][0] = v.x; x[i][1] = v.y; x[i][2] = v.z; x[i][3] = v.w;
+    }
+  normalise_and_store<TOut>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H,
+                            out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr);
 }
 
 __global__ void classify_softmax_kernel(const float* __restrict__ pooled, const float* __restrict__ W,
@@ -248,38 +222,38 @@ __global__ void fill_f32_kernel(float* dst, float v, size_t n) {
     dst[i] = v;
 }
 
-inline bool ln_shape_ok(int H, int vn) { return H > 0 && H % (32 * vn) == 0 && H <= 1024; }
+inline bool ln_shape_ok(int H) { return H > 0 && H % 128 == 0 && H <= 1024; }
 
 }  // namespace
 
-template <typename T>
-int embed_layernorm(const int* ids, const int* seg, const T* word, const T* pos, const T* type,
-                    const float* gamma, const float* beta, T* out, int tokens, int S, int H, int vocab,
-                    int* err_flag, cudaStream_t stream) {
-  if (tokens <= 0 || S <= 0 || !ln_shape_ok(H, Vec<T>::N)) return -1;
+template <typename TOut>
+int embed_layernorm(const int* ids, const int* seg, const float* word, const float* pos, const float* type,
+                    const float* gamma, const float* beta, TOut* out, float* out_f32, int tokens, int S, int H,
+                    int vocab, int* err_flag, cudaStream_t stream) {
+  if (tokens <= 0 || S <= 0 || !ln_shape_ok(H)) return -1;
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
-  embed_layernorm_kernel<T><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(ids, seg, word, pos, type, gamma, beta, out,
-                                                                        tokens, S, H, vocab, err_flag);
+  embed_layernorm_kernel<TOut><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(ids, seg, word, pos, type, gamma, beta, out,
+                                                                           out_f32, tokens, S, H, vocab, err_flag);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
-template <typename T>
-int layernorm(const T* x, const float* gamma, const float* beta, T* out, float* out_f32, int tokens, int H,
+template <typename TOut>
+int layernorm(const float* x, const float* gamma, const float* beta, TOut* out, float* out_f32, int tokens, int H,
               cudaStream_t stream) {
-  if (tokens <= 0 || !ln_shape_ok(H, Vec<T>::N)) return -1;
+  if (tokens <= 0 || !ln_shape_ok(H)) return -1;
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
-  layernorm_kernel<T><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(x, gamma, beta, out, out_f32, tokens, H);
+  layernorm_kernel<TOut><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(x, gamma, beta, out, out_f32, tokens, H);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
 template int embed_layernorm<float>(const int*, const int*, const float*, const float*, const float*, const float*,
-                                    const float*, float*, int, int, int, int, int*, cudaStream_t);
-template int embed_layernorm<__nv_bfloat16>(const int*, const int*, const __nv_bfloat16*, const __nv_bfloat16*,
-                                            const __nv_bfloat16*, const float*, const float*, __nv_bfloat16*, int, int,
-                                            int, int, int*, cudaStream_t);
+                                    const float*, float*, float*, int, int, int, int, int*, cudaStream_t);
+template int embed_layernorm<__nv_bfloat16>(const int*, const int*, const float*, const float*, const float*,
+                                            const float*, const float*, __nv_bfloat16*, float*, int, int, int, int,
+                                            int*, cudaStream_t);
 template int layernorm<float>(const float*, const float*, const float*, float*, float*, int, int, cudaStream_t);
-template int layernorm<__nv_bfloat16>(const __nv_bfloat16*, const float*, const float*, __nv_bfloat16*, float*, int,
-                                      int, cudaStream_t);
+template int layernorm<__nv_bfloat16>(const float*, const float*, const float*, __nv_bfloat16*, float*, int, int,
+                                      cudaStream_t);
 
 int classify_softmax(const float* pooled, const float* W, const float* bias, float* probs, int B, int H, int C,
                      cudaStream_t stream) {

@@ -13,7 +13,7 @@ Differences, on purpose:
   message, ``status`` / ``last_error`` report per-handle errors, ``check`` raises on them.
 """
 from ctypes import (CDLL, RTLD_GLOBAL, POINTER, Structure, byref, c_bool, c_char_p, c_double, c_float, c_int,
-                    c_long, c_void_p)
+                    c_long, c_size_t, c_void_p)
 import os
 
 import numpy
@@ -123,6 +123,14 @@ forward_dev = lib.cudabert_forward_dev
 forward_dev.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]
 forward_dev.restype = c_int
 
+classify_dev = lib.cudabert_classify_dev
+classify_dev.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]
+classify_dev.restype = c_int
+
+probs_dev = lib.cudabert_probs_dev
+probs_dev.argtypes = [c_void_p]
+probs_dev.restype = c_void_p
+
 sync = lib.cudabert_sync
 sync.argtypes = [c_void_p]
 sync.restype = c_int
@@ -130,6 +138,10 @@ sync.restype = c_int
 pooled_dev = lib.cudabert_pooled_dev
 pooled_dev.argtypes = [c_void_p]
 pooled_dev.restype = c_void_p
+
+copy_to_host = lib.cudabert_copy_to_host
+copy_to_host.argtypes = [c_void_p, c_void_p, c_size_t]
+copy_to_host.restype = c_int
 
 stream = lib.cudabert_stream
 stream.argtypes = [c_void_p]
@@ -176,10 +188,10 @@ k_attention.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int
 k_attention.restype = c_int
 k_embed_layernorm = lib.cudabert_k_embed_layernorm
 k_embed_layernorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                              c_void_p, c_int, c_int, c_int, c_int]
+                              c_void_p, c_void_p, c_int, c_int, c_int, c_int]
 k_embed_layernorm.restype = c_int
 k_layernorm = lib.cudabert_k_layernorm
-k_layernorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]
+k_layernorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]
 k_layernorm.restype = c_int
 
 

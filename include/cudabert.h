@@ -87,8 +87,15 @@ CUDABERT_API int cudabert_num_classes(void* model);
  * Results: cudabert_pooled_dev (fp32 [batchsize, hidden]).  Returns 0 on success.            */
 CUDABERT_API int cudabert_forward_dev(void* model, const int* ids_dev, const int* seg_dev, const int* mask_dev, int batchsize,
                          int seq_length);
+/* Same with the classifier head appended (Cuda_Classify on device-resident inputs); results:
+ * cudabert_probs_dev (fp32 [batchsize, num_classes]).                                          */
+CUDABERT_API int cudabert_classify_dev(void* model, const int* ids_dev, const int* seg_dev, const int* mask_dev,
+                                       int batchsize, int seq_length);
 CUDABERT_API int cudabert_sync(void* model);
 CUDABERT_API float* cudabert_pooled_dev(void* model);
+CUDABERT_API float* cudabert_probs_dev(void* model);
+/* Blocking device-to-host copy, so that a ctypes caller can read what Retval points to. */
+CUDABERT_API int cudabert_copy_to_host(void* dst_host, const void* src_dev, size_t bytes);
 /* The handle's CUDA stream (a cudaStream_t), for event timing on the launching stream. */
 CUDABERT_API void* cudabert_stream(void* model);
 
@@ -114,13 +121,16 @@ CUDABERT_API int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W
                         int flags, const float* bias_dev, const float* residual_dev);
 /* ctx[T,H] = attention(qkv[T,3H]); mask_dev int32 [B,S] or NULL; bf16 != 0 selects the bf16 kernel. */
 CUDABERT_API int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads);
-/* out[T,H] = LayerNorm(word[ids] + pos[t % S] + type[seg]); tables and out bf16 or fp32. */
-CUDABERT_API int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev, const void* word_dev,
-                               const void* pos_dev, const void* type_dev, const float* gamma_dev,
-                               const float* beta_dev, void* out_dev, int tokens, int S, int H, int vocab);
-/* out[T,H] = LayerNorm(x[T,H]) * gamma + beta. */
-CUDABERT_API int cudabert_k_layernorm(int bf16, const void* x_dev, const float* gamma_dev, const float* beta_dev, void* out_dev,
-                         int tokens, int H);
+/* out[T,H] = LayerNorm(word[ids] + pos[t % S] + type[seg]); tables fp32; out is bf16 (bf16 != 0) or
+ * fp32; out_f32_dev (may be NULL) receives the same values in fp32.  Returns 5 after clamping an
+ * id outside [0, vocab) or a segment id outside {0, 1}.                                        */
+CUDABERT_API int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev, const float* word_dev,
+                                            const float* pos_dev, const float* type_dev, const float* gamma_dev,
+                                            const float* beta_dev, void* out_dev, float* out_f32_dev, int tokens,
+                                            int S, int H, int vocab);
+/* out[T,H] = LayerNorm(x[T,H] fp32) * gamma + beta; out bf16 or fp32, optional fp32 copy. */
+CUDABERT_API int cudabert_k_layernorm(int bf16, const float* x_dev, const float* gamma_dev, const float* beta_dev,
+                                      void* out_dev, float* out_f32_dev, int tokens, int H);
 
 #ifdef __cplusplus
 }

@@ -98,13 +98,14 @@ def test_gemm_f32(pybert, M, N, K, flags):
 
 
 def _attention_ref(qkv, mask, B, S, heads):
+    # float64: in fp32 a row whose keys are all masked loses score bits to the -10000 offset
     H = heads * 64
-    q, k, v = [t.view(B, S, heads, 64).permute(0, 2, 1, 3).float() for t in qkv.view(B * S, 3, H).unbind(1)]
+    q, k, v = [t.view(B, S, heads, 64).permute(0, 2, 1, 3).double() for t in qkv.view(B * S, 3, H).unbind(1)]
     scores = q @ k.transpose(-1, -2) / math.sqrt(64)
     if mask is not None:
-        scores = scores + (1.0 - mask.view(B, 1, 1, S).float()) * -10000.0
+        scores = scores + (1.0 - mask.view(B, 1, 1, S).double()) * -10000.0
     ctx = torch.softmax(scores, -1) @ v
-    return ctx.permute(0, 2, 1, 3).reshape(B * S, H)
+    return ctx.permute(0, 2, 1, 3).reshape(B * S, H).float()
 
 
 def _mask(B, S, mode, g):
@@ -149,31 +150,39 @@ def test_embed_layernorm_and_layernorm(pybert, bf16, H):
     B, S, vocab = 5, 37, 4000
     T = B * S
     dt = torch.bfloat16 if bf16 else torch.float32
-    word = (torch.randn(vocab, H, device="cuda", generator=g) * 0.02).to(dt)
-    pos = (torch.randn(512, H, device="cuda", generator=g) * 0.02).to(dt)
-    typ = (torch.randn(2, H, device="cuda", generator=g) * 0.02).to(dt)
+    word = torch.randn(vocab, H, device="cuda", generator=g) * 0.02
+    pos = torch.randn(512, H, device="cuda", generator=g) * 0.02
+    typ = torch.randn(2, H, device="cuda", generator=g) * 0.02
     gamma = 1 + torch.randn(H, device="cuda", generator=g) * 0.1
     beta = torch.randn(H, device="cuda", generator=g) * 0.1
     ids = torch.randint(0, vocab, (T,), device="cuda", generator=g, dtype=torch.int32)
     seg = torch.randint(0, 2, (T,), device="cuda", generator=g, dtype=torch.int32)
     out = torch.empty(T, H, device="cuda", dtype=dt)
+    out32 = torch.empty(T, H, device="cuda", dtype=torch.float32)
     rc = pybert.k_embed_layernorm(bf16, ids.data_ptr(), seg.data_ptr(), word.data_ptr(), pos.data_ptr(),
-                                  typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), T, S, H, vocab)
+                                  typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(),
+                                  out32.data_ptr(), T, S, H, vocab)
     assert rc == 0
     p = torch.arange(T, device="cuda") % S
-    e = word.float()[ids.long()] + pos.float()[p] + typ.float()[seg.long()]
+    e = word[ids.long()] + pos[p] + typ[seg.long()]
     ref = bert_oracle.layer_norm(e, gamma, beta)
     tol = 3e-2 if bf16 else 2e-5
     assert (out.float() - ref).abs().max().item() <= tol
+    assert (out32 - ref).abs().max().item() <= 2e-5
 
-    x = torch.randn(T, H, device="cuda", generator=g).to(dt)
-    out2 = torch.empty_like(x)
-    assert pybert.k_layernorm(bf16, x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out2.data_ptr(), T, H) == 0
-    ref2 = bert_oracle.layer_norm(x.float(), gamma, beta)
+    x = torch.randn(T, H, device="cuda", generator=g)
+    out2 = torch.empty(T, H, device="cuda", dtype=dt)
+    out2_32 = torch.empty(T, H, device="cuda", dtype=torch.float32)
+    assert pybert.k_layernorm(bf16, x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out2.data_ptr(),
+                              out2_32.data_ptr(), T, H) == 0
+    ref2 = bert_oracle.layer_norm(x, gamma, beta)
     assert (out2.float() - ref2).abs().max().item() <= tol
+    assert (out2_32 - ref2).abs().max().item() <= 2e-5
+    assert pybert.k_layernorm(bf16, x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out2.data_ptr(), None, T, H) == 0
 
     # an out-of-range id is clamped and reported, it never reads outside the table
     ids[3] = vocab + 5
     rc = pybert.k_embed_layernorm(bf16, ids.data_ptr(), seg.data_ptr(), word.data_ptr(), pos.data_ptr(),
-                                  typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), T, S, H, vocab)
+                                  typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), None, T, S, H,
+                                  vocab)
     assert rc == 5
