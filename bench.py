@@ -207,7 +207,9 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     dims = synth.model_dims(True)
     B, S = WL["batch"], WL["seq"]
     wdir = weights_dir(local_rank, barrier)
-    model = pybert.load_model(True, wdir, dev, B, S, precision="bf16")
+    model = pybert.load_model(True, wdir, dev, B, S, precision="bf16", num_layers=args.layers)
+    if args.layers:
+        dims = dict(dims, layers=min(args.layers, dims["layers"]))
     C = pybert.num_classes(model)
     stream = torch.cuda.ExternalStream(pybert.stream(model), device=dev)
 
@@ -287,7 +289,7 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
                    "share": (v[0] / total_ms if total_ms else 0)} for k, v in prof.items()}
     attn_ms = prof["attention"][0]
     ln_ms, ln_n = prof["layernorm"]
-    ln_bytes = 2 * B * S * dims["hidden"] * 2  # read x, write out (bf16)
+    ln_bytes = B * S * dims["hidden"] * 10  # read fp32 sums, write the bf16 GEMM copy and the fp32 residual copy
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -320,6 +322,8 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
         "layernorm_gbs": (ln_bytes * ln_n / (ln_ms / 1e3) / 1e9) if ln_ms else None,
         "cpu_baseline": cpu,
     }
+    if args.layers:
+        line["profiling_only"] = "first %d encoder layers only: not a benchmark result" % dims["layers"]
     print(json.dumps(line), flush=True)
     pybert.unload_model(model)
 
@@ -331,6 +335,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="profiling only: run the first N encoder layers (the printed line is then not a "
+                         "benchmark result and says so)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 

@@ -1,0 +1,289 @@
+"""File-to-file inference pipeline with the reference's ``Engine`` API (engine.py:169-403):
+
+    engine = Engine(config)
+    engine.set_cuda_model(Cuda_BERT)            # class: (id_gpu, config) -> .encode(tensor)
+    engine.set_finetune_layer(Finetune_Layer)   # class: (is_large) -> .init_finetune_layer(gpu), .run(np[B,H])
+    engine.set_tokenlizer_function(fn)          # (max_seq_length, line, index) -> (idx, raw, ids, mask, seg)
+    engine.set_output_function(fn)              # (raw_line, output) -> str
+    engine.run(input_file, output_file)
+
+Stages, one OS process each as in the reference (engine.py:385-397): a reader that tokenises,
+buckets lines by valid length (boundaries [0, start_split, start_split+split_size, ..., end_split,
+max_seq_length], engine.py:225-232) and right-trims every batch to its own longest line
+(utils.py:3-13); one worker per GPU id in ``config.gpu`` holding an independent replica (batch
+sharding, no collective: workers pull whole batches from a shared queue); a writer that restores
+the input order in a sliding window and applies back-pressure through ``alert_size``
+(engine.py:303-375).
+
+Differences from the reference, on purpose: workers block on the queue instead of busy-polling
+``empty()`` (engine.py:253-264); every stage is joined and a stage that dies is detected by the
+parent, which stops the others and raises instead of waiting forever on a sentinel count
+(engine.py:312, 401); the standard ``logging`` module replaces the reference's colour logger.
+"""
+import copy
+import logging
+import multiprocessing as mp
+import queue as pyqueue
+import sys
+import time
+
+from .utils import optimize_batch, Batch_Packed, Tagged_line
+
+_DONE = "__stage_done__"
+
+
+def get_mylogger():
+    logger = logging.getLogger("cuda_bert.engine")
+    if not logger.handlers:
+        h = logging.StreamHandler()
+        h.setFormatter(logging.Formatter("%(asctime)s %(levelname)s %(message)s"))
+        logger.addHandler(h)
+        logger.setLevel(logging.INFO)
+    return logger
+
+
+class batch_container(object):
+    """ Bucket of lines whose valid length lies in (base_length, top_length]. """
+    def __init__(self, base_length, top_length, batchsize):
+        self.base_length = base_length
+        self.top_length = top_length
+        self.prepare = []
+        self.temp = []
+        self.min_index = sys.maxsize
+        self.batchsize = batchsize
+
+    def put(self, tg_line):
+        self.temp.append(tg_line)
+        if len(self.temp) == self.batchsize:
+            self._batch()
+
+    def _batch(self):
+        """ Batch the collected lines and keep the batch ready for the input queue """
+        if len(self.temp) == 0:
+            return
+        batch_tensor = optimize_batch(self.temp)
+        self.prepare.append(Batch_Packed(list(self.temp), batch_tensor))
+        self.temp.clear()
+        self.reset_min_index()
+
+    def force_enqueue(self):
+        """ Flush a partly filled bucket: memory pressure in the writer, or end of file """
+        self._batch()
+
+    def pop(self):
+        ret = self.prepare.pop(0)
+        self.reset_min_index()
+        return ret
+
+    def reset_min_index(self):
+        if len(self.prepare) != 0:
+            self.min_index = self.prepare[0].lines_list[0].num_line
+        else:
+            self.min_index = sys.maxsize
+        return self.min_index
+
+
+class queue_manager(object):
+    """ Buckets for every length range plus the queues between the stages """
+    def __init__(self, seq_length_split, list_gpu, logger, batchsize, ctx=None):
+        ctx = ctx or mp.get_context()
+        self.num_containers = len(seq_length_split) - 1
+        self.boardlines = seq_length_split
+        self.output_queue = ctx.Queue()
+        self.force_queue = ctx.Queue(1)
+        self.input_queue = ctx.Queue(10)
+        self.logger = logger
+        self.containers = [batch_container(self.boardlines[i], self.boardlines[i + 1], batchsize)
+                           for i in range(self.num_containers)]
+
+    def put(self, line):
+        """ Find the bucket of the line's length and add it; ship batches that became ready """
+        num_queue = 0
+        while num_queue < self.num_containers - 1 and line.length > self.boardlines[num_queue + 1]:
+            num_queue += 1
+        self.containers[num_queue].put(line)
+        self.enqueue(False)
+
+    def force_enqueue(self):
+        for container in self.containers:
+            container.force_enqueue()
+        while self.enqueue(True) != -1:
+            pass
+
+    def enqueue(self, is_force):
+        """ Ship the ready batch that starts at the smallest line number (keeps the writer's
+        window short); returns -1 when no bucket holds a ready batch """
+        target = None
+        for container in self.containers:
+            if container.prepare and (target is None or container.reset_min_index() < target.min_index):
+                target = container
+        if target is None:
+            return -1
+        min_index = target.min_index
+        self.input_queue.put(target.pop())   # bounded queue: blocks while the GPUs are busy
+        return min_index
+
+    def get(self, timeout=None):
+        return self.input_queue.get(timeout=timeout)
+
+
+class Engine(object):
+    def __init__(self, config):
+        self.handle = None
+        self.finetune_layer = None
+        self.cuda_model = None
+        self.tokenlizer_line = None
+        self.output_line = None
+        self.input_file = None
+        self.output_file = None
+        self.config = config
+        self.logger = get_mylogger()
+        self.poll_seconds = 0.2
+
+    def _init(self):
+        self.generate_splits()
+        assert(self.cuda_model is not None)
+        assert(self.finetune_layer is not None)
+        assert(self.tokenlizer_line is not None)
+        assert(self.output_line is not None)
+        assert(self.config.gpu != [])
+        self._ctx = mp.get_context(getattr(self.config, "mp_start_method", None))
+        self.handle = queue_manager(self.seq_length_split, self.config.gpu,
+                                    self.logger, self.config.batch_size, self._ctx)
+
+    def set_cuda_model(self, cuda_model):
+        self.cuda_model = cuda_model
+
+    def set_finetune_layer(self, finetune_layer):
+        self.finetune_layer = finetune_layer
+
+    def set_tokenlizer_function(self, tokenlizer_line):
+        self.tokenlizer_line = tokenlizer_line
+
+    def set_output_function(self, output_line):
+        self.output_line = output_line
+
+    def generate_splits(self):
+        '''
+        Boundaries of the length buckets over [0, max_length].
+        Too sparse : wasted computation on padding.  Too dense : more lines wait in the writer.
+        '''
+        ret = [0]
+        for i in range(self.config.start_split,
+                       self.config.end_split + self.config.split_size,
+                       self.config.split_size):
+            ret.append(i)
+        ret.append(self.config.max_seq_length)
+        self.seq_length_split = ret
+
+    # ------------------------------------------------------------------ stages
+    def _engine_model(self, id_gpu):
+        config = self.config
+        handle = self.handle
+        user_layer = self.finetune_layer(config.is_large)
+        user_layer.init_finetune_layer(id_gpu)
+        model = self.cuda_model(id_gpu, config)
+        start = time.time()
+        total_length = 0
+        while True:
+            packed_batch = handle.get()
+            if packed_batch == _DONE:
+                break
+            output = model.encode(packed_batch.tensor)
+            packed_batch.output = user_layer.run(output)
+            handle.output_queue.put(packed_batch)
+            total_length += packed_batch.tensor[0].shape[0]
+        handle.output_queue.put(_DONE)
+        self.logger.info("engine_model on gpu %s done: %d lines in %.2f s", id_gpu, total_length, time.time() - start)
+
+    def _generate_tagged_line(self, user_output):
+        return Tagged_line(
+                num_line=user_output[0],
+                line_data=user_output[1],
+                input_ids=user_output[2],
+                input_mask=user_output[3],
+                segment_ids=user_output[4])
+
+    def _engine_preprocess(self, input_file):
+        config = self.config
+        handle = self.handle
+        with open(input_file, 'r', encoding='utf-8') as f:
+            if self.config.skip_first_line:
+                f.readline()
+            index = 0
+            for line in f:
+                handle.put(self._generate_tagged_line(self.tokenlizer_line(config.max_seq_length, line, index)))
+                index += 1
+                try:
+                    handle.force_queue.get_nowait()
+                    handle.force_enqueue()
+                except pyqueue.Empty:
+                    pass
+            handle.force_enqueue()
+        for _ in self.config.gpu:
+            handle.input_queue.put(_DONE)
+        self.logger.info("engine_preprocess done: %d lines", index)
+
+    def _engine_postprocess(self, output_file):
+        handle = self.handle
+        done = 0
+        window = {}            # line number -> formatted text, for lines that arrived early
+        next_line = 0
+        with open(output_file, 'w', encoding='utf-8') as f:
+            while done < len(self.config.gpu):
+                packed_batch = handle.output_queue.get()
+                if packed_batch == _DONE:
+                    done += 1
+                    continue
+                packed_batch.write_line()
+                for tl in packed_batch.lines_list:
+                    if tl.num_line in window or tl.num_line < next_line:
+                        raise RuntimeError("Line Index {} is written twice!".format(tl.num_line))
+                    window[tl.num_line] = self.output_line(tl.line_data, tl.output)
+                while next_line in window:
+                    f.write(window.pop(next_line) + '\n')
+                    next_line += 1
+                if len(window) > self.config.alert_size:
+                    # too many lines wait for a slow bucket: make the reader flush its partial buckets
+                    try:
+                        handle.force_queue.put_nowait("force_enqueue Now")
+                    except pyqueue.Full:
+                        pass
+            if window:
+                raise RuntimeError("%d lines never received their predecessors" % len(window))
+        self.logger.info("engine_postprocess done: %d lines", next_line)
+
+    # ------------------------------------------------------------------ driver
+    def run(self, input_file, output_file):
+        assert(type(output_file) == str)
+        assert(type(input_file) == str)
+        self._init()
+        self.config.input_file = input_file
+        self.config.output_file = output_file
+        ctx = self._ctx
+        procs = [("reader", ctx.Process(target=self._engine_preprocess, args=(input_file,), daemon=True))]
+        for num_gpu in self.config.gpu:
+            procs.append(("gpu%s" % num_gpu, ctx.Process(target=self._engine_model, args=(num_gpu,), daemon=True)))
+        procs.append(("writer", ctx.Process(target=self._engine_postprocess, args=(output_file,), daemon=True)))
+        for _, p in procs:
+            p.start()
+        failed = None
+        while failed is None and any(p.is_alive() for _, p in procs):
+            for name, p in procs:
+                if not p.is_alive() and p.exitcode not in (0, None):
+                    failed = (name, p.exitcode)
+                    break
+            time.sleep(self.poll_seconds)
+        for name, p in procs:
+            if failed is None and p.exitcode not in (0, None):
+                failed = (name, p.exitcode)
+        if failed is not None:
+            for _, p in procs:
+                if p.is_alive():
+                    p.terminate()
+            for _, p in procs:
+                p.join(5)
+            raise RuntimeError("engine stage %s died with exit code %s; the run was stopped" % failed)
+        for _, p in procs:
+            p.join()
+        self.logger.info("ALL JOBS DONE")
