@@ -53,6 +53,10 @@ struct DevErr {  // scratch error word for the single-kernel entry points
 
 }  // namespace
 
+namespace cb {
+void set_thread_error(const std::string& msg) { g_init_error = msg; }
+}  // namespace cb
+
 extern "C" {
 
 void* cudabert_init_ex(bool large, int num_gpu, int max_batchsize, int max_seq_length, const char* dir, int precision,

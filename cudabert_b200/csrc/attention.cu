@@ -10,8 +10,10 @@
 // gives every key the same -10000, which softmax ignores: the kernels then attend to all keys.
 #include "kernels.h"
 #include "ptx.cuh"
+#include "../../include/cudabert.h"
 
 #include <cmath>
+#include <mutex>
 
 namespace cb {
 namespace {
@@ -318,3 +320,59 @@ int mask_to_kv_len(const int* mask, int* kv_len, int B, int S, cudaStream_t stre
 }
 
 }  // namespace cb
+
+// ---------------------------------------------------------------- entry point without allocation
+// Scratch of cudabert_k_attention_noalloc: the per-row key counts that cudabert_k_attention keeps
+// in a buffer it allocates per call.  It lives in the library image, so every GPU that loads the
+// library holds CUDABERT_NOALLOC_MAX_BATCH * 4 bytes (16 KiB) of it until the process exits.
+static __device__ __align__(256) int g_noalloc_kv_len[CUDABERT_NOALLOC_MAX_BATCH];
+
+extern "C" int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B,
+                                            int S, int heads) {
+  if (!qkv_dev || !ctx_dev || B <= 0 || S <= 0 || heads <= 0) {
+    cb::set_thread_error("cudabert_k_attention_noalloc: null buffer or non-positive size");
+    return 1;
+  }
+  if (B > CUDABERT_NOALLOC_MAX_BATCH) {
+    cb::set_thread_error("cudabert_k_attention_noalloc: batch exceeds CUDABERT_NOALLOC_MAX_BATCH (4096), the size "
+                         "of the built-in scratch; use cudabert_k_attention or split the batch");
+    return 6;
+  }
+  // In host code the array's name is only a handle for the runtime, not an address a kernel can
+  // use; the device address is looked up once per device, with that device current.
+  static std::mutex mu;
+  static int* scratch_of_device[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cb::set_thread_error("cudabert_k_attention_noalloc: no current CUDA device");
+    return 2;
+  }
+  int* kv = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratch_of_device[dev]) {
+      void* p = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_kv_len);
+      if (e != cudaSuccess || !p) {
+        cb::set_thread_error(std::string("cudabert_k_attention_noalloc: cudaGetSymbolAddress failed: ") +
+                             cudaGetErrorString(e));
+        return 2;
+      }
+      scratch_of_device[dev] = static_cast<int*>(p);
+    }
+    kv = scratch_of_device[dev];
+  }
+  // every entry [0, B) is rewritten before it is read, so nothing left by an earlier call matters
+  if (cb::mask_to_kv_len(mask_dev, kv, B, S, nullptr) < 0) return 3;
+  const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv,
+                                          static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr)
+                     : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv,
+                                         static_cast<float*>(ctx_dev), B, S, heads, nullptr);
+  if (n < 0) return 3;
+  const cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    cb::set_thread_error(std::string("cudabert_k_attention_noalloc: ") + cudaGetErrorString(e));
+    return 4;
+  }
+  return 0;
+}

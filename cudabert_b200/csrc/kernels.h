@@ -3,6 +3,7 @@
 // negative value when the arguments are rejected.
 #pragma once
 #include <cstdint>
+#include <string>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -83,5 +84,8 @@ int quantize_fp8_weight(const float* src, uint8_t* dst_q, __nv_bfloat16* dst_op,
                         cudaStream_t stream);
 int convert_f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
 int fill_f32(float* dst, float value, size_t n, cudaStream_t stream);
+
+// Message that cudabert_last_error(NULL) returns on the calling thread.
+void set_thread_error(const std::string& msg);
 
 }  // namespace cb

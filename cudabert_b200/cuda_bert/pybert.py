@@ -186,6 +186,10 @@ k_gemm_f32.restype = c_int
 k_attention = lib.cudabert_k_attention
 k_attention.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]
 k_attention.restype = c_int
+k_attention_noalloc = lib.cudabert_k_attention_noalloc
+k_attention_noalloc.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]
+k_attention_noalloc.restype = c_int
+NOALLOC_MAX_BATCH = 4096
 k_embed_layernorm = lib.cudabert_k_embed_layernorm
 k_embed_layernorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_int, c_int, c_int, c_int]

@@ -121,6 +121,22 @@ CUDABERT_API int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W
                         int flags, const float* bias_dev, const float* residual_dev);
 /* ctx[T,H] = attention(qkv[T,3H]); mask_dev int32 [B,S] or NULL; bf16 != 0 selects the bf16 kernel. */
 CUDABERT_API int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads);
+/* No counterpart in the reference.  cudabert_k_attention for callers that must not allocate device
+ * memory: code that runs where cudaMalloc is not allowed (inside another framework's memory pool
+ * or allocator callback, in a process whose device memory is fully pre-partitioned, or in a
+ * latency-critical loop that must not take the allocator's lock).  The per-row key counts, which
+ * cudabert_k_attention keeps in a buffer it allocates and frees per call, live in a fixed array
+ * inside the library image instead, so batch is limited to CUDABERT_NOALLOC_MAX_BATCH rows
+ * (return code 6 and a message in cudabert_last_error(NULL) beyond that) and every GPU that loads
+ * the library holds those 16 KiB until the process exits.  Inputs and outputs are the caller's, as
+ * for cudabert_k_attention; no cudaMalloc / cudaFree or allocating library routine is called.
+ * The first call on each device looks up the array's device address; make that first call before
+ * starting any stream capture.  All calls share the one array: it is fully rewritten by each call
+ * before use, and two calls of one process that overlap on the same GPU (for example from two
+ * host threads) race on it -- serialise them.  Separate processes have separate copies.        */
+#define CUDABERT_NOALLOC_MAX_BATCH 4096
+CUDABERT_API int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev,
+                                              int B, int S, int heads);
 /* out[T,H] = LayerNorm(word[ids] + pos[t % S] + type[seg]); tables fp32; out is bf16 (bf16 != 0) or
  * fp32; out_f32_dev (may be NULL) receives the same values in fp32.  Returns 5 after clamping an
  * id outside [0, vocab) or a segment id outside {0, 1}.                                        */
