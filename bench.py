@@ -289,7 +289,8 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
                    "share": (v[0] / total_ms if total_ms else 0)} for k, v in prof.items()}
     attn_ms = prof["attention"][0]
     ln_ms, ln_n = prof["layernorm"]
-    ln_bytes = B * S * dims["hidden"] * 10  # read fp32 sums, write the bf16 GEMM copy and the fp32 residual copy
+    # LayerNorm: read fp16 dense output + fp32 residual, write the bf16 GEMM copy + the fp32 residual copy
+    ln_bytes = B * S * dims["hidden"] * 12
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:

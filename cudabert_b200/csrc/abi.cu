@@ -242,7 +242,7 @@ int cudabert_k_gemm_bf16(const void* A_dev, long lda, const void* W_dev, int M, 
   if (!A_dev || !W_dev || !out_dev || M <= 0 || N <= 0 || K <= 0 || lda < K) return 1;
   CUtensorMap tmA, tmW;
   if (!cb::make_tmap_bf16_kmajor(&tmA, A_dev, M, K, static_cast<uint64_t>(lda) * 2, 128)) return 2;
-  if (!cb::make_tmap_bf16_kmajor(&tmW, W_dev, N, K, static_cast<uint64_t>(K) * 2, cb::gemm_block_n(N))) return 2;
+  if (!cb::make_tmap_bf16_kmajor(&tmW, W_dev, N, K, static_cast<uint64_t>(K) * 2, cb::gemm_w_box_rows(N))) return 2;
   static thread_local DevErr scratch;
   int* err = err_dev;
   if (!err) {
@@ -315,14 +315,24 @@ int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev,
   return herr ? 5 : 0;
 }
 
-int cudabert_k_layernorm(int bf16, const float* x_dev, const float* gamma_dev, const float* beta_dev, void* out_dev,
-                         float* out_f32_dev, int tokens, int H) {
+int cudabert_k_layernorm(int out_bf16, int in_f16, const void* x_dev, const float* residual_dev,
+                         const float* gamma_dev, const float* beta_dev, void* out_dev, float* out_f32_dev, int tokens,
+                         int H) {
   int n;
-  if (bf16)
-    n = cb::layernorm<__nv_bfloat16>(x_dev, gamma_dev, beta_dev, static_cast<__nv_bfloat16*>(out_dev), out_f32_dev,
+  const __half* xh = static_cast<const __half*>(x_dev);
+  const float* xf = static_cast<const float*>(x_dev);
+  if (out_bf16 && in_f16)
+    n = cb::layernorm<__half, __nv_bfloat16>(xh, residual_dev, gamma_dev, beta_dev,
+                                             static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, H, nullptr);
+  else if (out_bf16)
+    n = cb::layernorm<float, __nv_bfloat16>(xf, residual_dev, gamma_dev, beta_dev,
+                                            static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, H, nullptr);
+  else if (in_f16)
+    n = cb::layernorm<__half, float>(xh, residual_dev, gamma_dev, beta_dev, static_cast<float*>(out_dev), out_f32_dev,
                                      tokens, H, nullptr);
   else
-    n = cb::layernorm<float>(x_dev, gamma_dev, beta_dev, static_cast<float*>(out_dev), out_f32_dev, tokens, H, nullptr);
+    n = cb::layernorm<float, float>(xf, residual_dev, gamma_dev, beta_dev, static_cast<float*>(out_dev), out_f32_dev,
+                                    tokens, H, nullptr);
   if (n < 0) return 3;
   return cudaDeviceSynchronize() == cudaSuccess ? 0 : 4;
 }

@@ -7,7 +7,13 @@
 // `cuApplyLayerNorm` does in place (ops/layernorm.cu:152-158) and the pooler's tanh
 // (ops/elementwise.cu:57-70).
 //
-// Structure (one persistent CTA per SM, 192 threads, no clusters, no multicast):
+// Two variants share the epilogue.  `gemm_tcgen05_pair_kernel` (default when N is a multiple of
+// 256) runs CTA pairs: a 256 x 256 tile per pair, `tcgen05.mma.cta_group::2`, each CTA loading its
+// own 128 rows of A and its own half (128 rows) of the W tile, so an SM fills 32 KB of shared
+// memory per k-block instead of 48 KB; the operand feed is what bounds the single-CTA variant.
+// Loads are never shared between CTAs.  `gemm_tcgen05_kernel` is the single-CTA variant:
+//
+// Structure (one persistent CTA per SM, 192 threads):
 //   warp 0, one lane   TMA producer: per k-block one 128x64 tile of A and one BNx64 tile of W
 //                      (128-byte swizzle) into a ring of shared-memory stages guarded by
 //                      full/empty mbarriers.
@@ -22,6 +28,7 @@
 #include "ptx.cuh"
 
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace cb {
@@ -32,6 +39,9 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARP_BYTES = 32 * 128;           // one 32-row x 128-byte piece per epilogue warp
+constexpr int EPI_VEC_BYTES = 2 * 256 * 4;           // bias and column scale of one tile
+constexpr int EPI_STAGE_BYTES = 4 * EPI_WARP_BYTES + EPI_VEC_BYTES;
 
 template <int BN>
 struct Cfg {
@@ -41,85 +51,184 @@ struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // 1024: alignment slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + BAR_BYTES + 1024;  // 1024: alignment slack
 };
 
+// erf-GELU x * 0.5 * (1 + erf(x / sqrt 2)) evaluated as 0.5 x (1 + tanh(x (c0 + c1 x^2 + c2 x^4))) with
+// coefficients fitted to the erf form (max abs deviation 2.5e-5 over the reals, below one bf16
+// rounding of the result everywhere) and the hardware tanh (relative error 2^-11): 9 instructions
+// per element instead of ~45 for erff, which otherwise makes the FFN1 epilogue slower than its
+// main loop.  |x| is clamped to 8 inside the polynomial (tanh is +-1 to fp32 precision beyond 6).
 __device__ __forceinline__ float gelu_erf(float x) {
-  return x * 0.5f * (1.0f + erff(x * 0.70710678118654752f));
+  const float xc = fminf(fmaxf(x, -8.0f), 8.0f);
+  const float x2 = xc * xc;
+  float p = fmaf(x2, -0.000351516789798119f, 0.03700564602858787f);
+  p = fmaf(x2, p, 0.7975078842834395f);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(xc * p));
+  const float hx = 0.5f * x;
+  return fmaf(hx, t, hx);
 }
 
-// 32 consecutive output columns of one row: scale, bias, residual, activation, store.
-template <bool OUT_F32>
-__device__ __forceinline__ void epilogue_row32(const uint32_t (&v)[32], int flags, const float* __restrict__ bias,
-                                               const float* __restrict__ colscale, const void* __restrict__ residual,
-                                               void* __restrict__ out, size_t row_off, int col) {
-  float f[32];
+// Epilogue of one accumulator (128 TMEM lanes x BN columns at `t_acc`), run by the four epilogue
+// warps; each owns the lane quarter warp % 4.  `m0` is the first output row of THIS CTA's 128 rows.
+//
+// FLAGS >= 0 fixes the epilogue at compile time (the combinations the model uses); FLAGS < 0 takes
+// the run-time `flags`.  A thread reads one accumulator ROW from TMEM, but 32 threads storing to 32
+// different rows touch 32 cache lines per instruction, so each warp transposes 32-column chunks
+// through its own 4 KB of shared memory: phase 1, thread = row, writes 16-byte pieces at a swizzled
+// position (conflict-free); phase 2, consecutive lanes cover consecutive bytes of a row, so global
+// stores are full-sector, row-contiguous accesses.  Bias and column scale of the tile are staged
+// in shared memory once per tile.  A residual (tests only: the model adds its residual in the
+// LayerNorm kernel) is read by the row's own thread in phase 1.
+template <int BN, int FLAGS>
+__device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restrict__ stage, const float* __restrict__ sbias,
+                                              const float* __restrict__ sscale, int warp, int lane, int m0, int n0,
+                                              int M, void* __restrict__ out, int ldo, int flags,
+                                              const void* __restrict__ residual) {
+  const int fl = (FLAGS >= 0) ? FLAGS : flags;
+  tc_fence_after();
+  const int quarter = warp & 3;
+  const int row_base = m0 + quarter * 32;
+  const int my_grow = row_base + lane;
+  const uint32_t t_row = t_acc + (static_cast<uint32_t>(quarter * 32) << 16);
+  const bool has_res = (fl & EPI_RESIDUAL) != 0 && my_grow < M;
+
+  // acc * scale + bias (+ residual) -> activation, for the 32 columns starting at n0 + col
+  auto finish32 = [&](const uint32_t (&v)[32], float (&f)[32], int col) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-  if (flags & EPI_COLSCALE) {
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      const float4 s = __ldg(reinterpret_cast<const float4*>(colscale + col + j));
-      f[j] *= s.x; f[j + 1] *= s.y; f[j + 2] *= s.z; f[j + 3] *= s.w;
+    for (int j = 0; j < 32; ++j) {
+      f[j] = __uint_as_float(v[j]);
+      if (fl & EPI_COLSCALE) f[j] *= sscale[col + j];
+      if (fl & EPI_BIAS) f[j] += sbias[col + j];
     }
-  }
-  if (flags & EPI_BIAS) {
+    if (fl & EPI_RESIDUAL) {
+      if (has_res) {
+        if (fl & EPI_OUT_F32) {
+          const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(residual) +
+                                                            static_cast<size_t>(my_grow) * ldo + n0 + col);
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      const float4 b = __ldg(reinterpret_cast<const float4*>(bias + col + j));
-      f[j] += b.x; f[j + 1] += b.y; f[j + 2] += b.z; f[j + 3] += b.w;
-    }
-  }
-  if (flags & EPI_RESIDUAL) {
-    if (OUT_F32) {
-      const float4* r = reinterpret_cast<const float4*>(static_cast<const float*>(residual) + row_off + col);
+          for (int j = 0; j < 8; ++j) {
+            const float4 t = __ldg(r + j);
+            f[4 * j] += t.x; f[4 * j + 1] += t.y; f[4 * j + 2] += t.z; f[4 * j + 3] += t.w;
+          }
+        } else {
+          const uint4* r = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(residual) +
+                                                          static_cast<size_t>(my_grow) * ldo + n0 + col);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 t = __ldg(r + j);
-        f[4 * j] += t.x; f[4 * j + 1] += t.y; f[4 * j + 2] += t.z; f[4 * j + 3] += t.w;
-      }
-    } else {
-      const uint4* r = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(residual) + row_off + col);
+          for (int j = 0; j < 4; ++j) {
+            const uint4 t = __ldg(r + j);
+            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 t = __ldg(r + j);
-        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[q]);
-          f[8 * j + 2 * q] += __low2float(h);
-          f[8 * j + 2 * q + 1] += __high2float(h);
+            for (int q = 0; q < 4; ++q) {
+              const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[q]);
+              f[8 * j + 2 * q] += __low2float(h);
+              f[8 * j + 2 * q + 1] += __high2float(h);
+            }
+          }
         }
       }
     }
-  }
-  if (flags & EPI_GELU) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
-  }
-  if (flags & EPI_TANH) {
+    for (int j = 0; j < 32; ++j) {
+      if (fl & EPI_GELU) f[j] = gelu_erf(f[j]);
+      if (fl & EPI_TANH) f[j] = tanhf(f[j]);
+    }
+  };
+
+  if (fl & EPI_OUT_F32) {
+    // 32 fp32 columns = 128 bytes per row; phase 2: 8 lanes per row, 4 rows per instruction
+    float* outf = static_cast<float*>(out);
+    uint8_t* my_row = stage + lane * 128;
+    const int r2 = lane >> 3, p2 = lane & 7;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) f[j] = tanhf(f[j]);
-  }
-  if (OUT_F32) {
-    float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + row_off + col);
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col = c * 32;
+      uint32_t v[32];
+      tmem_ld32(t_row + col, v);
+      tmem_ld_wait();
+      float f[32];
+      finish32(v, f, col);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(my_row + ((j ^ (lane & 7)) << 4)) =
+            make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = i * 4 + r2;
+        const int row = row_base + r;
+        const float4 t = *reinterpret_cast<const float4*>(stage + r * 128 + (p2 << 4));
+        if (row < M)
+          *reinterpret_cast<float4*>(outf + static_cast<size_t>(row) * ldo + n0 + col + ((p2 ^ (r & 7)) << 2)) = t;
+      }
+      __syncwarp();
+    }
   } else {
-    uint4* o = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + row_off + col);
+    // 32 16-bit columns (bf16, or fp16 with EPI_OUT_F16) = 64 bytes per row; phase 2: 4 lanes per
+    // row, 8 rows per instruction
+    uint16_t* outh = static_cast<uint16_t*>(out);
+    uint8_t* my_row = stage + lane * 64;
+    const int r2 = lane >> 2, p2 = lane & 3;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint4 t;
-      t.x = pack_bf16(f[8 * j], f[8 * j + 1]);
-      t.y = pack_bf16(f[8 * j + 2], f[8 * j + 3]);
-      t.z = pack_bf16(f[8 * j + 4], f[8 * j + 5]);
-      t.w = pack_bf16(f[8 * j + 6], f[8 * j + 7]);
-      o[j] = t;
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col = c * 32;
+      uint32_t v[32];
+      tmem_ld32(t_row + col, v);
+      tmem_ld_wait();
+      float f[32];
+      finish32(v, f, col);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 t;
+        if (fl & EPI_OUT_F16) {
+          t.x = pack_f16(f[8 * j], f[8 * j + 1]);
+          t.y = pack_f16(f[8 * j + 2], f[8 * j + 3]);
+          t.z = pack_f16(f[8 * j + 4], f[8 * j + 5]);
+          t.w = pack_f16(f[8 * j + 6], f[8 * j + 7]);
+        } else {
+          t.x = pack_bf16(f[8 * j], f[8 * j + 1]);
+          t.y = pack_bf16(f[8 * j + 2], f[8 * j + 3]);
+          t.z = pack_bf16(f[8 * j + 4], f[8 * j + 5]);
+          t.w = pack_bf16(f[8 * j + 6], f[8 * j + 7]);
+        }
+        *reinterpret_cast<uint4*>(my_row + ((j ^ ((lane >> 1) & 3)) << 4)) = t;
+      }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = i * 8 + r2;
+        const int row = row_base + r;
+        const uint4 t = *reinterpret_cast<const uint4*>(stage + r * 64 + (p2 << 4));
+        if (row < M)
+          *reinterpret_cast<uint4*>(outh + static_cast<size_t>(row) * ldo + n0 + col + ((p2 ^ ((r >> 1) & 3)) << 3)) = t;
+      }
+      __syncwarp();
     }
   }
+  tc_fence_before();
+  __syncwarp();
 }
 
-template <int BN>
+// The four epilogue warps (128 threads, named barrier 1) stage bias / column scale of the tile's BN
+// columns in shared memory.  The first barrier keeps a fast warp from overwriting values a slow
+// warp still reads for the previous tile.
+template <int BN, int FLAGS>
+__device__ __forceinline__ void stage_tile_vectors(float* __restrict__ sbias, float* __restrict__ sscale, int flags,
+                                                   const float* __restrict__ bias, const float* __restrict__ colscale,
+                                                   int n0) {
+  const int fl = (FLAGS >= 0) ? FLAGS : flags;
+  if (!(fl & (EPI_BIAS | EPI_COLSCALE))) return;
+  const int t = threadIdx.x - 64;  // 0..127
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  for (int i = t; i < BN; i += 128) {
+    if (fl & EPI_BIAS) sbias[i] = __ldg(bias + n0 + i);
+    if (fl & EPI_COLSCALE) sscale[i] = __ldg(colscale + n0 + i);
+  }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+template <int BN, int FLAGS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, int M, int N,
                     int K, void* __restrict__ out, int ldo, int flags, const float* __restrict__ bias,
@@ -127,7 +236,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;
+  float* sbias = reinterpret_cast<float*>(epi_stage + 4 * EPI_WARP_BYTES);
+  float* sscale = sbias + 256;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + EPI_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + C::STAGES;
   uint64_t* tfull_bar = empty_bar + C::STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
@@ -212,34 +324,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else {
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
-    const int row_in_tile = quarter * 32 + lane;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (tile / tiles_n) * BM;
       const int n0 = (tile % tiles_n) * BN;
+      const int m0 = (tile / tiles_n) * BM;
+      stage_tile_vectors<BN, FLAGS>(sbias, sscale, flags, bias, colscale, n0);
       mbar_wait(tfull_bar + acc, acc_phase, abort_flag, err, SITE_TMEM_FULL);
-      tc_fence_after();
-      const int row = m0 + row_in_tile;
-      const bool valid = row < M;
-      const size_t row_off = static_cast<size_t>(row) * ldo;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(t_row + c * 32, v);
-        tmem_ld_wait();
-        if (valid) {
-          if (flags & EPI_OUT_F32)
-            epilogue_row32<true>(v, flags, bias, colscale, residual, out, row_off, n0 + c * 32);
-          else
-            epilogue_row32<false>(v, flags, bias, colscale, residual, out, row_off, n0 + c * 32);
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
+      epilogue_tile<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp & 3) * EPI_WARP_BYTES, sbias, sscale, warp, lane,
+                               m0, n0, M, out, ldo, flags, residual);
       if (lane == 0) mbar_arrive(tempty_bar + acc);
     }
   }
@@ -260,6 +354,155 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant: cluster of 2, tile 256 (M) x BN (N) per pair, 6 stages of 32 KB per CTA.
+//   both CTAs   warp 0 / one lane: TMA producer for the CTA's own A rows and W half; completion
+//               bytes of both CTAs are counted on the LEADER's full barrier.
+//   leader      warp 1 / one lane: tcgen05.mma.cta_group::2 for the pair; tcgen05.commit arrives
+//               on the empty barrier (and, per tile, the accumulator-full barrier) of BOTH CTAs.
+//   both CTAs   warps 2-5: epilogue of the CTA's own 128 accumulator rows; every epilogue warp
+//               of the pair arrives on the leader's accumulator-empty barrier (count 8).
+template <int BN>
+struct PairCfg {
+  static constexpr int STAGES = 6;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + BAR_BYTES + 1024;
+};
+
+template <int BN, int FLAGS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, int M,
+                         int N, int K, void* __restrict__ out, int ldo, int flags, const float* __restrict__ bias,
+                         const void* __restrict__ residual, const float* __restrict__ colscale, int* err) {
+  using C = PairCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;
+  float* sbias = reinterpret_cast<float*>(epi_stage + 4 * EPI_WARP_BYTES);
+  float* sscale = sbias + 256;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + EPI_STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + C::STAGES;
+  uint64_t* tfull_bar = empty_bar + C::STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar + s, 1);   // the leader's producer arrives; only the leader's copy is used
+      mbar_init(empty_bar + s, 1);  // one commit arrival from the leader's MMA thread, in each CTA
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar + a, 1);
+      mbar_init(tempty_bar + a, 8);  // 4 epilogue warps of each CTA; only the leader's copy is used
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_n = N / BN;
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  const int num_tiles = tiles_m * tiles_n;
+  const int kblocks = K / BK;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = pair_id; tile < num_tiles; tile += num_pairs) {
+        const int m0 = (tile / tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
+        const int n0 = (tile % tiles_n) * BN + static_cast<int>(rank) * (BN / 2);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, err, SITE_EMPTY);
+          uint8_t* sa = smem + stage * C::STAGE_BYTES;
+          if (leader) mbar_arrive_expect_tx(full_bar + stage, 2 * C::STAGE_BYTES);
+          const uint32_t leader_full = mapa_u32(smem_u32(full_bar + stage), 0);
+          tma_load_2d_pair(sa, &tmA, leader_full, kb * BK, m0);
+          tma_load_2d_pair(sa + C::A_BYTES, &tmW, leader_full, kb * BK, n0);
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        mbar_wait(tempty_bar + acc, acc_phase ^ 1, abort_flag, err, SITE_TMEM_EMPTY);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          mbar_wait(full_bar + stage, phase, abort_flag, err, SITE_FULL);
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint64_t da = umma_desc_sw128(sa);
+          const uint64_t db = umma_desc_sw128(sa + C::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          umma_commit_pair(empty_bar + stage, 3);
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit_pair(tfull_bar + acc, 3);
+      }
+    }
+  } else {
+    int it = 0;
+    for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int n0 = (tile % tiles_n) * BN;
+      const int m0 = (tile / tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
+      stage_tile_vectors<BN, FLAGS>(sbias, sscale, flags, bias, colscale, n0);
+      mbar_wait(tfull_bar + acc, acc_phase, abort_flag, err, SITE_TMEM_FULL);
+      epilogue_tile<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp & 3) * EPI_WARP_BYTES, sbias, sscale, warp, lane,
+                               m0, n0, M, out, ldo, flags, residual);
+      if (lane == 0) {
+        if (leader) mbar_arrive(tempty_bar + acc);
+        else mbar_arrive_cluster(mapa_u32(smem_u32(tempty_bar + acc), 0));
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  cluster_sync_all();  // neither CTA leaves while its peer may still signal its barriers or read its tiles
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -277,29 +520,120 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-template <int BN>
-int launch(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
-           const GemmEpilogue& epi, int* err_flag, int num_sms, cudaStream_t stream) {
+// Epilogue combinations compiled with the flags fixed (the ones the encoder uses; for CTA pairs
+// also with the FP8 column scale); everything else runs the FLAGS = -1 instantiation.
+constexpr int F_QKV = EPI_BIAS;
+constexpr int F_FFN1 = EPI_BIAS | EPI_GELU;
+constexpr int F_H16 = EPI_BIAS | EPI_OUT_F16;
+
+template <int BN, int FLAGS>
+int launch_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
+               const GemmEpilogue& epi, int* err_flag, int num_sms, cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, FLAGS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::SMEM_BYTES) != cudaSuccess)
       return -2;
     attr_set[dev] = true;
   }
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  gemm_tcgen05_kernel<BN><<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(
+  gemm_tcgen05_kernel<BN, FLAGS><<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(
       *tmA, *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+template <int BN>
+int launch(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
+           const GemmEpilogue& epi, int* err_flag, int num_sms, cudaStream_t stream) {
+  switch (epi.flags) {
+    case F_QKV: return launch_one<BN, F_QKV>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
+    case F_FFN1: return launch_one<BN, F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
+    case F_H16: return launch_one<BN, F_H16>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
+    default: return launch_one<BN, -1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
+  }
+}
+
+// Number of CTA pairs that can be resident at once on this device (pairs need two SMs of one
+// GPC); a persistent grid larger than that would run its last pairs after all the others.
+template <int FLAGS>
+int max_resident_pairs(int dev) {
+  static int cached[64] = {};
+  if (dev < 64 && cached[dev] > 0) return cached[dev];
+  using C = PairCfg<256>;
+  if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<256, FLAGS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           C::SMEM_BYTES) != cudaSuccess)
+    return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 148, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<256, FLAGS>, &cfg) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (dev < 64) cached[dev] = n;
+  return n;
+}
+
+template <int FLAGS>
+int launch_pair_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
+                    const GemmEpilogue& epi, int* err_flag, cudaStream_t stream) {
+  using C = PairCfg<256>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int pairs = max_resident_pairs<FLAGS>(dev);
+  if (pairs <= 0) return -2;
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * (N / 256);
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  gemm_tcgen05_pair_kernel<256, FLAGS><<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(
+      *tmA, *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+int launch_pair(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
+                const GemmEpilogue& epi, int* err_flag, cudaStream_t stream) {
+  switch (epi.flags) {
+    case F_QKV: return launch_pair_one<F_QKV>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+    case F_FFN1: return launch_pair_one<F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+    case F_H16: return launch_pair_one<F_H16>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+    case F_QKV | EPI_COLSCALE:
+      return launch_pair_one<F_QKV | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+    case F_FFN1 | EPI_COLSCALE:
+      return launch_pair_one<F_FFN1 | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+    case F_H16 | EPI_COLSCALE:
+      return launch_pair_one<F_H16 | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+    default: return launch_pair_one<-1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+  }
+}
+
+bool pair_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("CUDABERT_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 }  // namespace
 
 int gemm_block_n(int N) { return (N % 256 == 0) ? 256 : 128; }
+
+bool gemm_uses_pairs(int N) { return pair_enabled() && (N % 256 == 0); }
+
+// Rows of the W tensor map's box: a CTA of a pair loads half of the 256-row tile.
+int gemm_w_box_rows(int N) { return gemm_uses_pairs(N) ? 128 : gemm_block_n(N); }
 
 bool make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                            uint64_t row_stride_bytes, uint32_t box_rows) {
@@ -323,6 +657,7 @@ int gemm_bf16_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int
   if ((epi.flags & EPI_BIAS) && !epi.bias) return -1;
   if ((epi.flags & EPI_RESIDUAL) && !epi.residual) return -1;
   if ((epi.flags & EPI_COLSCALE) && !epi.colscale) return -1;
+  if (gemm_uses_pairs(N)) return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
   if (gemm_block_n(N) == 256) return launch<256>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
   return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
 }

@@ -6,6 +6,7 @@
 #include <string>
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 namespace cb {
@@ -18,7 +19,9 @@ enum EpiFlags : int {
   EPI_RESIDUAL = 4,  // add residual[m, n] (same element type and row stride as out)
   EPI_TANH = 8,      // tanh (pooler, reference: ops/elementwise.cu:57-61)
   EPI_OUT_F32 = 16,  // write fp32 instead of bf16 (tcgen05 GEMM only; the fp32 GEMM always does)
-  EPI_COLSCALE = 32  // multiply the accumulator by colscale[n] (FP8 weight de-quantisation)
+  EPI_COLSCALE = 32, // multiply the accumulator by colscale[n] (FP8 weight de-quantisation)
+  EPI_OUT_F16 = 64   // write fp16 instead of bf16 (tcgen05 GEMM only): the dense outputs that the
+                     // LayerNorm kernel adds to the fp32 residual stream
 };
 
 struct GemmEpilogue {
@@ -31,11 +34,13 @@ struct GemmEpilogue {
 // ---- tcgen05 GEMM: out[M, N] = A[M, K] (bf16, K contiguous) x W[N, K]^T (bf16, K contiguous)
 // N must be a multiple of 128 and K of 64; M is arbitrary (tail rows are zero-filled by TMA
 // and never stored).  `tmA` / `tmW` are tiled tensor maps made by make_tmap_bf16_kmajor with
-// box rows 128 (A) and 128 or 256 (W, must equal the block_n that is picked: 256 when N is
-// a multiple of 256, else 128).
+// box rows 128 (A) and gemm_w_box_rows(N) (W).
 int gemm_bf16_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
                       const GemmEpilogue& epi, int* err_flag, int num_sms, cudaStream_t stream);
 int gemm_block_n(int N);
+// Box rows the W tensor map must be encoded with for the kernel variant that gemm_bf16_tcgen05
+// will pick for this N (128 when CTA pairs each load half of a 256-row tile, else gemm_block_n).
+int gemm_w_box_rows(int N);
 // Encode a 2-D tiled map over a row-major bf16 matrix [rows, cols] with `row_stride_bytes`
 // between rows, box = 64 columns (128 bytes, 128-byte swizzle) x `box_rows` rows.
 bool make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
@@ -65,10 +70,11 @@ template <typename TOut>
 int embed_layernorm(const int* ids, const int* seg, const float* word, const float* pos, const float* type,
                     const float* gamma, const float* beta, TOut* out, float* out_f32, int tokens, int S, int H,
                     int vocab, int* err_flag, cudaStream_t stream);
-// out[t] = LayerNorm(x[t]) * gamma + beta.
-template <typename TOut>
-int layernorm(const float* x, const float* gamma, const float* beta, TOut* out, float* out_f32, int tokens, int H,
-              cudaStream_t stream);
+// out[t] = LayerNorm(x[t] + residual[t]) * gamma + beta; x is fp32 or fp16 (the tensor-core GEMM's
+// dense output), residual (may be null) is the fp32 residual stream.
+template <typename TIn, typename TOut>
+int layernorm(const TIn* x, const float* residual, const float* gamma, const float* beta, TOut* out, float* out_f32,
+              int tokens, int H, cudaStream_t stream);
 // probs[b, :] = softmax(pooled[b, :] . W[H, C] + bias[C]),  C <= 32
 int classify_softmax(const float* pooled, const float* W, const float* bias, float* probs, int B, int H, int C,
                      cudaStream_t stream);

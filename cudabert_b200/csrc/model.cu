@@ -194,7 +194,7 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
 
 bool Model::finish_dense(DenseWeight* d, int prec) {
   if (prec == PREC_FP32) return true;
-  if (!make_tmap_bf16_kmajor(&d->tmap, d->w, d->N, d->K, static_cast<uint64_t>(d->K) * 2, gemm_block_n(d->N)))
+  if (!make_tmap_bf16_kmajor(&d->tmap, d->w, d->N, d->K, static_cast<uint64_t>(d->K) * 2, gemm_w_box_rows(d->N)))
     return fail(2, "cuTensorMapEncodeTiled failed for a weight matrix");
   return true;
 }
@@ -277,7 +277,7 @@ bool Model::ensure_capacity(int B, int S, bool) {
   const size_t o_kv = slot(static_cast<size_t>(cbatch) * sizeof(int));
   const size_t o_xf = slot(ct * H_ * sizeof(float));
   const size_t o_x1f = slot(ct * H_ * sizeof(float));
-  const size_t o_y = slot(ct * H_ * sizeof(float));
+  const size_t o_y = slot(ct * H_ * (lowp ? 2 : 4));
   const size_t o_xa = lowp ? slot(ct * H_ * 2) : o_xf;
   const size_t o_x1a = lowp ? slot(ct * H_ * 2) : o_x1f;
   const size_t o_ctx = slot(ct * H_ * esize_);
@@ -291,7 +291,7 @@ bool Model::ensure_capacity(int B, int S, bool) {
   kv_len_ = reinterpret_cast<int*>(base + o_kv);
   xf_ = reinterpret_cast<float*>(base + o_xf);
   x1f_ = reinterpret_cast<float*>(base + o_x1f);
-  y_ = reinterpret_cast<float*>(base + o_y);
+  y_ = base + o_y;
   xa_ = base + o_xa; x1a_ = base + o_x1a; ctx_ = base + o_ctx; qkv_ = base + o_qkv; z_ = base + o_z;
   pooled_ = reinterpret_cast<float*>(base + o_pool);
   probs_ = reinterpret_cast<float*>(base + o_probs);
@@ -418,32 +418,32 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
     CB_LAUNCH(KC_EMBED, embed_layernorm<float>(d_ids, d_seg, word_, pos_, type_, emb_g_, emb_b_, xf_, nullptr, T, S, H_,
                                                vocab_rows_, err_dev_, stream_));
   }
-  const int f32out = lowp ? EPI_OUT_F32 : 0;  // the fp32 GEMM always writes fp32
   for (int l = 0; l < L_; ++l) {
     const LayerWeights& w = layer_[l];
     if (!dense(w.qkv, xa_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) return false;
     if (lowp) {
       CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_,
                                              static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, stream_));
+      // y = ctx.Wo + bo in fp16; x1 = LN(y + x) with the add in fp32 inside the LayerNorm kernel
+      if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, T, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_ATTN_OUT))
+        return false;
+      CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __nv_bfloat16>(static_cast<const __half*>(y_), xf_, w.ln1_g, w.ln1_b,
+                                                                x1a, x1f_, T, H_, stream_)));
+      if (!dense(w.ffn1, x1a_, &tm_x1_, H_, T, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
+      if (!dense(w.ffn2, z_, &tm_z_, F_, T, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_FFN2)) return false;
+      CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __nv_bfloat16>(static_cast<const __half*>(y_), x1f_, w.ln2_g, w.ln2_b,
+                                                                xa, xf_, T, H_, stream_)));
     } else {
       CB_LAUNCH(KC_ATTENTION, attention_f32(static_cast<const float*>(qkv_), d_mask, kv_len_,
                                             static_cast<float*>(ctx_), B, S, heads_, stream_));
-    }
-    // y = ctx.Wo + bo + x  (fp32), x1 = LN(y)
-    if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, T, y_, EPI_BIAS | EPI_RESIDUAL | f32out, xf_, KC_GEMM_ATTN_OUT))
-      return false;
-    if (lowp) {
-      CB_LAUNCH(KC_LAYERNORM, layernorm<__nv_bfloat16>(y_, w.ln1_g, w.ln1_b, x1a, x1f_, T, H_, stream_));
-    } else {
-      CB_LAUNCH(KC_LAYERNORM, layernorm<float>(y_, w.ln1_g, w.ln1_b, x1f_, nullptr, T, H_, stream_));
-    }
-    if (!dense(w.ffn1, x1a_, &tm_x1_, H_, T, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
-    // y = z.W2 + b2 + x1 (fp32), x = LN(y)
-    if (!dense(w.ffn2, z_, &tm_z_, F_, T, y_, EPI_BIAS | EPI_RESIDUAL | f32out, x1f_, KC_GEMM_FFN2)) return false;
-    if (lowp) {
-      CB_LAUNCH(KC_LAYERNORM, layernorm<__nv_bfloat16>(y_, w.ln2_g, w.ln2_b, xa, xf_, T, H_, stream_));
-    } else {
-      CB_LAUNCH(KC_LAYERNORM, layernorm<float>(y_, w.ln2_g, w.ln2_b, xf_, nullptr, T, H_, stream_));
+      // fp32 mode: the GEMM epilogue adds the residual, y = ctx.Wo + bo + x
+      if (!dense(w.attn_out, ctx_, nullptr, H_, T, y_, EPI_BIAS | EPI_RESIDUAL, xf_, KC_GEMM_ATTN_OUT)) return false;
+      CB_LAUNCH(KC_LAYERNORM, (layernorm<float, float>(static_cast<const float*>(y_), nullptr, w.ln1_g, w.ln1_b, x1f_,
+                                                       nullptr, T, H_, stream_)));
+      if (!dense(w.ffn1, x1a_, nullptr, H_, T, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
+      if (!dense(w.ffn2, z_, nullptr, F_, T, y_, EPI_BIAS | EPI_RESIDUAL, x1f_, KC_GEMM_FFN2)) return false;
+      CB_LAUNCH(KC_LAYERNORM, (layernorm<float, float>(static_cast<const float*>(y_), nullptr, w.ln2_g, w.ln2_b, xf_,
+                                                       nullptr, T, H_, stream_)));
     }
   }
   // pooler: rows b*S of the fp32 final hidden states, tanh(dense) -> fp32 [B, H]

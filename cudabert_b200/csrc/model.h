@@ -122,9 +122,10 @@ class Model {
   void* arena_ = nullptr;
   int *ids_ = nullptr, *kv_len_ = nullptr, *err_dev_ = nullptr;  // ids_: 3 * cap_tokens ints (ids | seg | mask)
   // residual stream in fp32: xf_ (layer input / output), x1f_ (after the attention block),
-  // y_ (pre-LayerNorm sums).  xa_ / x1a_ are the copies that feed the GEMMs (bf16 in the bf16 and
+  // y_ (dense outputs, added to the stream by the LayerNorm kernel).  xa_ / x1a_ are the copies that feed the GEMMs (bf16 in the bf16 and
   // fp8 modes; in fp32 mode they alias xf_ / x1f_).  ctx_, qkv_, z_ are in the GEMM element type.
-  float *xf_ = nullptr, *x1f_ = nullptr, *y_ = nullptr;
+  float *xf_ = nullptr, *x1f_ = nullptr;
+  void* y_ = nullptr;  // dense outputs before the residual add: fp16 (bf16 / fp8 modes) or fp32 sums (fp32 mode)
   void *xa_ = nullptr, *x1a_ = nullptr, *ctx_ = nullptr, *qkv_ = nullptr, *z_ = nullptr;
   float *pooled_ = nullptr, *probs_ = nullptr;
   CUtensorMap tm_x_, tm_x1_, tm_ctx_, tm_z_;

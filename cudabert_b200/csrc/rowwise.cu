@@ -13,6 +13,7 @@
 #include "kernels.h"
 #include "ptx.cuh"
 
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
 namespace cb {
@@ -117,21 +118,43 @@ embed_layernorm_kernel(const int* __restrict__ ids, const int* __restrict__ seg,
                             out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr);
 }
 
-template <typename TOut>
+template <typename TIn>
+__device__ __forceinline__ void load4(const TIn* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void load4<__half>(const __half* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+// out = LayerNorm(in + residual): `in` is the dense projection's output (fp32, or fp16 from the
+// tensor-core GEMM), `residual` (may be null) the fp32 residual stream.
+template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
-layernorm_kernel(const float* __restrict__ in, const float* __restrict__ gamma, const float* __restrict__ beta,
-                 TOut* __restrict__ out, float* __restrict__ out_f32, int tokens, int H) {
+layernorm_kernel(const TIn* __restrict__ in, const float* __restrict__ residual, const float* __restrict__ gamma,
+                 const float* __restrict__ beta, TOut* __restrict__ out, float* __restrict__ out_f32, int tokens,
+                 int H) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
   if (t >= tokens) return;
-  const float* row = in + static_cast<size_t>(t) * H;
+  const TIn* row = in + static_cast<size_t>(t) * H;
+  const float* res = residual ? residual + static_cast<size_t>(t) * H : nullptr;
   const int nvec = H / 128;
   float x[MAXV][4];
 #pragma unroll
   for (int i = 0; i < MAXV; ++i)
     if (i < nvec) {
-      const float4 v = *reinterpret_cast<const float4*>(row + (i * 32 + lane) * 4);
-      x[i][0] = v.x; x[i][1] = v.y; x[i][2] = v.z; x[i][3] = v.w;
+      load4<TIn>(row + (i * 32 + lane) * 4, x[i]);
+      if (res) {
+        const float4 r = *reinterpret_cast<const float4*>(res + (i * 32 + lane) * 4);
+        x[i][0] += r.x; x[i][1] += r.y; x[i][2] += r.z; x[i][3] += r.w;
+      }
     }
   normalise_and_store<TOut>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H,
                             out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr);
@@ -237,12 +260,13 @@ int embed_layernorm(const int* ids, const int* seg, const float* word, const flo
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
-template <typename TOut>
-int layernorm(const float* x, const float* gamma, const float* beta, TOut* out, float* out_f32, int tokens, int H,
-              cudaStream_t stream) {
+template <typename TIn, typename TOut>
+int layernorm(const TIn* x, const float* residual, const float* gamma, const float* beta, TOut* out, float* out_f32,
+              int tokens, int H, cudaStream_t stream) {
   if (tokens <= 0 || !ln_shape_ok(H)) return -1;
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
-  layernorm_kernel<TOut><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(x, gamma, beta, out, out_f32, tokens, H);
+  layernorm_kernel<TIn, TOut><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(x, residual, gamma, beta, out, out_f32,
+                                                                          tokens, H);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
@@ -251,9 +275,14 @@ template int embed_layernorm<float>(const int*, const int*, const float*, const 
 template int embed_layernorm<__nv_bfloat16>(const int*, const int*, const float*, const float*, const float*,
                                             const float*, const float*, __nv_bfloat16*, float*, int, int, int, int,
                                             int*, cudaStream_t);
-template int layernorm<float>(const float*, const float*, const float*, float*, float*, int, int, cudaStream_t);
-template int layernorm<__nv_bfloat16>(const float*, const float*, const float*, __nv_bfloat16*, float*, int, int,
+template int layernorm<float, float>(const float*, const float*, const float*, const float*, float*, float*, int, int,
+                                     cudaStream_t);
+template int layernorm<float, __nv_bfloat16>(const float*, const float*, const float*, const float*, __nv_bfloat16*,
+                                             float*, int, int, cudaStream_t);
+template int layernorm<__half, float>(const __half*, const float*, const float*, const float*, float*, float*, int, int,
                                       cudaStream_t);
+template int layernorm<__half, __nv_bfloat16>(const __half*, const float*, const float*, const float*, __nv_bfloat16*,
+                                              float*, int, int, cudaStream_t);
 
 int classify_softmax(const float* pooled, const float* W, const float* bias, float* probs, int B, int H, int C,
                      cudaStream_t stream) {

@@ -195,7 +195,7 @@ k_embed_layernorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_v
                               c_void_p, c_void_p, c_int, c_int, c_int, c_int]
 k_embed_layernorm.restype = c_int
 k_layernorm = lib.cudabert_k_layernorm
-k_layernorm.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]
+k_layernorm.argtypes = [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int]
 k_layernorm.restype = c_int
 
 

@@ -111,7 +111,7 @@ CUDABERT_API int cudabert_profile_get(void* model, int kernel_class, double* tot
 /* ---- single kernels on device buffers (stream 0, synchronous), for per-kernel parity tests ---- */
 
 /* out[M,N] = epilogue(A[M,K] bf16 (row stride lda elements) x W[N,K]^T bf16); flags: 1 bias, 2 GELU,
- * 4 residual, 8 tanh, 16 fp32 output, 32 per-column scale.  err_dev: device int, set non-zero if a
+ * 4 residual, 8 tanh, 16 fp32 output, 32 per-column scale, 64 fp16 output.  err_dev: device int, set non-zero if a
  * pipeline wait timed out.  N % 128 == 0, K % 64 == 0.                                        */
 CUDABERT_API int cudabert_k_gemm_bf16(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev,
                          int flags, const float* bias_dev, const void* residual_dev, const float* colscale_dev,
@@ -144,9 +144,12 @@ CUDABERT_API int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const 
                                             const float* pos_dev, const float* type_dev, const float* gamma_dev,
                                             const float* beta_dev, void* out_dev, float* out_f32_dev, int tokens,
                                             int S, int H, int vocab);
-/* out[T,H] = LayerNorm(x[T,H] fp32) * gamma + beta; out bf16 or fp32, optional fp32 copy. */
-CUDABERT_API int cudabert_k_layernorm(int bf16, const float* x_dev, const float* gamma_dev, const float* beta_dev,
-                                      void* out_dev, float* out_f32_dev, int tokens, int H);
+/* out[T,H] = LayerNorm(x[T,H] + residual[T,H]) * gamma + beta.  x is fp32, or fp16 when in_f16 != 0;
+ * residual is fp32 or NULL; out is bf16 when out_bf16 != 0, else fp32; out_f32_dev (may be NULL)
+ * receives the same values in fp32.                                                          */
+CUDABERT_API int cudabert_k_layernorm(int out_bf16, int in_f16, const void* x_dev, const float* residual_dev,
+                                      const float* gamma_dev, const float* beta_dev, void* out_dev,
+                                      float* out_f32_dev, int tokens, int H);
 
 #ifdef __cplusplus
 }

@@ -10,7 +10,7 @@ from oracle import bert_oracle
 
 pytestmark = pytest.mark.gpu
 
-EPI_BIAS, EPI_GELU, EPI_RESIDUAL, EPI_TANH, EPI_OUT_F32, EPI_COLSCALE = 1, 2, 4, 8, 16, 32
+EPI_BIAS, EPI_GELU, EPI_RESIDUAL, EPI_TANH, EPI_OUT_F32, EPI_COLSCALE, EPI_OUT_F16 = 1, 2, 4, 8, 16, 32, 64
 
 # bf16 has 8 significand bits: one rounding is 2^-9 relative; outputs here see two (input and
 # output rounding) on top of fp32 accumulation order differences.
@@ -45,7 +45,8 @@ GEMM_SHAPES = [(128, 256, 64), (128, 128, 64), (1, 256, 128), (300, 768, 768), (
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
 @pytest.mark.parametrize("flags", [0, EPI_BIAS, EPI_BIAS | EPI_GELU, EPI_BIAS | EPI_RESIDUAL,
-                                   EPI_BIAS | EPI_TANH | EPI_OUT_F32, EPI_BIAS | EPI_COLSCALE])
+                                   EPI_BIAS | EPI_TANH | EPI_OUT_F32, EPI_BIAS | EPI_COLSCALE, EPI_BIAS | EPI_OUT_F16,
+                                   EPI_BIAS | EPI_GELU | EPI_COLSCALE, EPI_BIAS | EPI_RESIDUAL | EPI_OUT_F32])
 def test_gemm_bf16_tcgen05(pybert, M, N, K, flags):
     g = torch.Generator(device="cuda").manual_seed(M * 7 + N * 3 + K + flags)
     A = (torch.randn(M, K, device="cuda", generator=g) * 0.5).bfloat16()
@@ -53,8 +54,10 @@ def test_gemm_bf16_tcgen05(pybert, M, N, K, flags):
     bias = torch.randn(N, device="cuda", generator=g) * 0.1
     colscale = torch.rand(N, device="cuda", generator=g) + 0.5
     out_f32 = bool(flags & EPI_OUT_F32)
-    resid = (torch.randn(M, N, device="cuda", generator=g)).bfloat16()
-    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.float32 if out_f32 else torch.bfloat16)
+    resid = torch.randn(M, N, device="cuda", generator=g)
+    resid = resid if out_f32 else resid.bfloat16()
+    odt = torch.float32 if out_f32 else (torch.float16 if flags & EPI_OUT_F16 else torch.bfloat16)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=odt)
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
     rc = pybert.k_gemm_bf16(A.data_ptr(), K, W.data_ptr(), M, N, K, out.data_ptr(), flags, bias.data_ptr(),
                             resid.data_ptr(), colscale.data_ptr(), err.data_ptr())
@@ -171,14 +174,19 @@ def test_embed_layernorm_and_layernorm(pybert, bf16, H):
     assert (out32 - ref).abs().max().item() <= 2e-5
 
     x = torch.randn(T, H, device="cuda", generator=g)
+    res = torch.randn(T, H, device="cuda", generator=g)
     out2 = torch.empty(T, H, device="cuda", dtype=dt)
     out2_32 = torch.empty(T, H, device="cuda", dtype=torch.float32)
-    assert pybert.k_layernorm(bf16, x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out2.data_ptr(),
-                              out2_32.data_ptr(), T, H) == 0
-    ref2 = bert_oracle.layer_norm(x, gamma, beta)
-    assert (out2.float() - ref2).abs().max().item() <= tol
-    assert (out2_32 - ref2).abs().max().item() <= 2e-5
-    assert pybert.k_layernorm(bf16, x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out2.data_ptr(), None, T, H) == 0
+    for in_f16 in (0, 1):
+        xin = x.half() if in_f16 else x
+        for r in (None, res):
+            assert pybert.k_layernorm(bf16, in_f16, xin.data_ptr(), None if r is None else r.data_ptr(),
+                                      gamma.data_ptr(), beta.data_ptr(), out2.data_ptr(), out2_32.data_ptr(), T, H) == 0
+            ref2 = bert_oracle.layer_norm(xin.float() + (0 if r is None else r), gamma, beta)
+            assert (out2.float() - ref2).abs().max().item() <= tol
+            assert (out2_32 - ref2).abs().max().item() <= 2e-5
+    assert pybert.k_layernorm(bf16, 0, x.data_ptr(), None, gamma.data_ptr(), beta.data_ptr(), out2.data_ptr(), None,
+                              T, H) == 0
 
     # an out-of-range id is clamped and reported, it never reads outside the table
     ids[3] = vocab + 5
