@@ -18,177 +18,182 @@
 namespace cb {
 namespace {
 
-constexpr int HD = 64;     // head size
-constexpr int AQ = 64;     // queries per CTA (4 warps x 16 rows)
-constexpr int AK = 64;     // keys per shared-memory tile
-constexpr int PITCH = 72;  // bf16 elements per smem row: 144 bytes, conflict-free for ldmatrix
+constexpr int HD = 64;  // head size
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr int ATT_MAX_WARPS = 8;
 
-__device__ __forceinline__ void load_tile_async(__nv_bfloat16 (*dst)[PITCH], const __nv_bfloat16* src_base, int ld,
-                                                int row0, int rows_limit, int tid) {
-  // 64 rows x 8 chunks of 16 bytes; 128 threads x 4 chunks
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int idx = tid + i * 128;
-    const int r = idx >> 3, c = idx & 7;
-    const bool ok = (row0 + r) < rows_limit;
-    const __nv_bfloat16* src = src_base + static_cast<size_t>(ok ? row0 + r : 0) * ld + c * 8;
-    cp_async16(smem_u32(&dst[r][c * 8]), src, ok);
-  }
+// Shared-memory rows are 128 bytes (64 bf16); the 16-byte chunk c of row r lives at position
+// c ^ (r & 7), which makes ldmatrix (8 consecutive rows, one chunk column) conflict-free without
+// padding.
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+  return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-__global__ void __launch_bounds__(128)
+// One CTA per (batch row, head).  All keys and values the row can attend to (kv_len[b], rounded
+// up to 16) are loaded into shared memory once; then every warp takes 16-query blocks
+// (warp, warp + nwarps, ...) and runs QK^T -> scale + mask bias -> online softmax -> P.V over 64-key
+// tiles entirely out of shared memory, with no further block-wide synchronisation.
+//   smem: K [R][64] | V [R][64] | per-warp Q / O staging [16][64] | bias [R]   (R = keys rounded to 64)
+__global__ void __launch_bounds__(ATT_MAX_WARPS * 32, 2)
 attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ mask,
-                      const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ ctx, int S, int heads) {
-  __shared__ __align__(16) __nv_bfloat16 sQ[AQ][PITCH];
-  __shared__ __align__(16) __nv_bfloat16 sK[2][AK][PITCH];
-  __shared__ __align__(16) __nv_bfloat16 sV[2][AK][PITCH];
-  __shared__ float sBias[2][AK];
+                      const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ ctx, int S, int heads, int R) {
+  extern __shared__ __align__(1024) uint8_t att_smem[];
+  uint8_t* sK = att_smem;
+  uint8_t* sV = sK + static_cast<size_t>(R) * 128;
+  uint8_t* sQ = sV + static_cast<size_t>(R) * 128;
+  const int nwarps = blockDim.x >> 5;
+  float* sBias = reinterpret_cast<float*>(sQ + nwarps * 2048);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q0 = blockIdx.x * AQ, h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int H = heads * HD, ld = 3 * H;
   int klen = kv_len[b];
   const bool use_mask = (klen > 0) && (mask != nullptr);
   if (klen <= 0) klen = S;
-  const int ntiles = (klen + AK - 1) / AK;
+  const int ktiles = (klen + 63) >> 6;
+  const int krows = ktiles << 6;  // rows of K / V the tiles touch; rows >= klen are zero-filled
   const __nv_bfloat16* base = qkv + static_cast<size_t>(b) * S * ld + h * HD;
-  const int* mrow = mask ? mask + static_cast<size_t>(b) * S : nullptr;
 
-  auto load_bias = [&](int buf, int k0) {
-    if (tid < AK) {
-      const int key = k0 + tid;
-      float v = 0.f;
-      if (key >= klen) v = -INFINITY;
-      else if (use_mask && mrow[key] == 0) v = -10000.0f * LOG2E;
-      sBias[buf][tid] = v;
-    }
-  };
-
-  load_tile_async(sQ, base, ld, q0, S, tid);
-  load_tile_async(sK[0], base + H, ld, 0, S, tid);
-  load_tile_async(sV[0], base + 2 * H, ld, 0, S, tid);
+  for (int i = tid; i < krows * 8; i += blockDim.x) {
+    const int r = i >> 3, c = i & 7;
+    const bool ok = r < klen;
+    const __nv_bfloat16* src = base + static_cast<size_t>(ok ? r : 0) * ld + c * 8;
+    cp_async16(smem_u32(sK + swz(r, c)), src + H, ok);
+    cp_async16(smem_u32(sV + swz(r, c)), src + 2 * H, ok);
+  }
   cp_async_commit();
-  load_bias(0, 0);
+  const int* mrow = mask ? mask + static_cast<size_t>(b) * S : nullptr;
+  for (int key = tid; key < krows; key += blockDim.x) {
+    float v = 0.f;
+    if (key >= klen) v = -INFINITY;
+    else if (use_mask && mrow[key] == 0) v = -10000.0f * LOG2E;
+    sBias[key] = v;
+  }
+  cp_async_wait<0>();
+  __syncthreads();
 
-  float o[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY};
-  float l_run[2] = {0.f, 0.f};
-  uint32_t qf[4][4];
+  uint8_t* myQ = sQ + warp * 2048;
   const float scale = 0.125f * LOG2E;
-
-  for (int t = 0; t < ntiles; ++t) {
-    const int buf = t & 1;
-    if (t + 1 < ntiles) {
-      load_tile_async(sK[buf ^ 1], base + H, ld, (t + 1) * AK, S, tid);
-      load_tile_async(sV[buf ^ 1], base + 2 * H, ld, (t + 1) * AK, S, tid);
-      cp_async_commit();
-      load_bias(buf ^ 1, (t + 1) * AK);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+  const int qblocks = (S + 15) >> 4;
+  for (int qb = warp; qb < qblocks; qb += nwarps) {
+    const int q0 = qb * 16;
+    // stage the 16 x 64 Q block: lane l moves chunk l % 8 of rows l / 8 + 4 i
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = (lane >> 3) + 4 * i, c = lane & 7;
+      uint4 t = make_uint4(0u, 0u, 0u, 0u);
+      if (q0 + r < S) t = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + r) * ld + c * 8));
+      *reinterpret_cast<uint4*>(myQ + swz(r, c)) = t;
     }
-    __syncthreads();
+    __syncwarp();
+    uint32_t qf[4][4];
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(myQ + swz(lane & 15, kk * 2 + (lane >> 4))));
 
-    if (t == 0) {
+    float o[8][4];
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        ldmatrix_x4(qf[kk], smem_u32(&sQ[warp * 16 + (lane & 15)][kk * 16 + (lane >> 4) * 8]));
-    }
+    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
 
-    // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
-    float s[8][4];
+    for (int t = 0; t < ktiles; ++t) {
+      const int k0 = t << 6;
+      // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
+      float s[8][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      const int mid = lane >> 3;
 #pragma unroll
-    for (int nb = 0; nb < 4; ++nb) {
+      for (int nb = 0; nb < 4; ++nb) {
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        uint32_t kf[4];
-        const int mid = lane >> 3;
-        ldmatrix_x4(kf, smem_u32(&sK[buf][nb * 16 + (mid >> 1) * 8 + (lane & 7)][kk * 16 + (mid & 1) * 8]));
-        mma_bf16_16816(s[2 * nb], qf[kk], kf[0], kf[1]);
-        mma_bf16_16816(s[2 * nb + 1], qf[kk], kf[2], kf[3]);
+        for (int kk = 0; kk < 4; ++kk) {
+          uint32_t kf[4];
+          ldmatrix_x4(kf, smem_u32(sK + swz(k0 + nb * 16 + (mid >> 1) * 8 + (lane & 7), kk * 2 + (mid & 1))));
+          mma_bf16_16816(s[2 * nb], qf[kk], kf[0], kf[1]);
+          mma_bf16_16816(s[2 * nb + 1], qf[kk], kf[2], kf[3]);
+        }
+      }
+      // scale + mask bias (log2 domain), running max
+      float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 bb = *reinterpret_cast<const float2*>(sBias + k0 + i * 8 + 2 * (lane & 3));
+        s[i][0] = fmaf(s[i][0], scale, bb.x);
+        s[i][1] = fmaf(s[i][1], scale, bb.y);
+        s[i][2] = fmaf(s[i][2], scale, bb.x);
+        s[i][3] = fmaf(s[i][3], scale, bb.y);
+        tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
+        tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+      }
+      float alpha[2], m_new[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        m_new[r] = fmaxf(m_run[r], tmax[r]);
+        // tile 0 always holds key 0 with a finite bias, so m_new is finite from the first tile on
+        alpha[r] = exp2f(m_run[r] - m_new[r]);
+        m_run[r] = m_new[r];
+        l_run[r] *= alpha[r];
+      }
+      uint32_t pf[4][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p0 = exp2f(s[i][0] - m_new[0]);
+        const float p1 = exp2f(s[i][1] - m_new[0]);
+        const float p2 = exp2f(s[i][2] - m_new[1]);
+        const float p3 = exp2f(s[i][3] - m_new[1]);
+        l_run[0] += p0 + p1;
+        l_run[1] += p2 + p3;
+        pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+        pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+      }
+      // O += P V : 4 key steps of 16, 4 pairs of 8-wide d tiles
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int db = 0; db < 4; ++db) {
+          uint32_t vf[4];
+          ldmatrix_x4_trans(vf, smem_u32(sV + swz(k0 + j * 16 + (mid & 1) * 8 + (lane & 7), db * 2 + (mid >> 1))));
+          mma_bf16_16816(o[2 * db], pf[j], vf[0], vf[1]);
+          mma_bf16_16816(o[2 * db + 1], pf[j], vf[2], vf[3]);
+        }
       }
     }
 
-    // scale + mask bias (log2 domain), running max
-    float tmax[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float b0 = sBias[buf][i * 8 + 2 * (lane & 3)];
-      const float b1 = sBias[buf][i * 8 + 2 * (lane & 3) + 1];
-      s[i][0] = fmaf(s[i][0], scale, b0);
-      s[i][1] = fmaf(s[i][1], scale, b1);
-      s[i][2] = fmaf(s[i][2], scale, b0);
-      s[i][3] = fmaf(s[i][3], scale, b1);
-      tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
-      tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
-    }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
-      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
-    float alpha[2], m_new[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      m_new[r] = fmaxf(m_run[r], tmax[r]);
-      // tile 0 always holds key 0 with a finite bias, so m_new is finite from the first tile on
-      alpha[r] = exp2f(m_run[r] - m_new[r]);
-      m_run[r] = m_new[r];
-      l_run[r] *= alpha[r];
-    }
-    uint32_t pf[4][4];
+    const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
+    // stage the 16 x 64 output block in the Q buffer, then store it with 16-byte row-contiguous pieces
+    __syncwarp();
+    const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float p0 = exp2f(s[i][0] - m_new[0]);
-      const float p1 = exp2f(s[i][1] - m_new[0]);
-      const float p2 = exp2f(s[i][2] - m_new[1]);
-      const float p3 = exp2f(s[i][3] - m_new[1]);
-      l_run[0] += p0 + p1;
-      l_run[1] += p2 + p3;
-      pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
-      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+      // columns i*8 + 2*t4, +1 of rows g and g + 8: chunk i, byte offset 4 * t4 inside the chunk
+      *reinterpret_cast<uint32_t*>(myQ + swz(g, i) + 4 * t4) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+      *reinterpret_cast<uint32_t*>(myQ + swz(g + 8, i) + 4 * t4) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
     }
+    __syncwarp();
+    __nv_bfloat16* out_base = ctx + static_cast<size_t>(b) * S * H + h * HD;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    for (int i = 0; i < 4; ++i) {
+      const int r = (lane >> 3) + 4 * i, c = lane & 7;
+      if (q0 + r < S)
+        *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(q0 + r) * H + c * 8) =
+            *reinterpret_cast<const uint4*>(myQ + swz(r, c));
     }
-    // O += P V : 4 key steps of 16, 4 pairs of 8-wide d tiles
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-#pragma unroll
-      for (int db = 0; db < 4; ++db) {
-        uint32_t vf[4];
-        const int mid = lane >> 3;
-        ldmatrix_x4_trans(vf, smem_u32(&sV[buf][j * 16 + (mid & 1) * 8 + (lane & 7)][db * 16 + (mid >> 1) * 8]));
-        mma_bf16_16816(o[2 * db], pf[j], vf[0], vf[1]);
-        mma_bf16_16816(o[2 * db + 1], pf[j], vf[2], vf[3]);
-      }
-    }
-    __syncthreads();  // the next iteration's prefetch overwrites the other buffer
-  }
-
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-  }
-  const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
-  const int row0 = q0 + warp * 16 + (lane >> 2);
-  __nv_bfloat16* out_base = ctx + static_cast<size_t>(b) * S * H + h * HD + 2 * (lane & 3);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    if (row0 < S)
-      *reinterpret_cast<uint32_t*>(out_base + static_cast<size_t>(row0) * H + i * 8) =
-          pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
-    if (row0 + 8 < S)
-      *reinterpret_cast<uint32_t*>(out_base + static_cast<size_t>(row0 + 8) * H + i * 8) =
-          pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
   }
 }
 
@@ -297,9 +302,23 @@ __global__ void mask_to_kv_len_kernel(const int* __restrict__ mask, int* __restr
 
 int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, __nv_bfloat16* ctx, int B, int S,
                    int heads, cudaStream_t stream) {
-  if (B <= 0 || S <= 0 || heads <= 0 || B > 65535) return -1;
-  dim3 grid((S + AQ - 1) / AQ, heads, B);
-  attention_bf16_kernel<<<grid, 128, 0, stream>>>(qkv, mask, kv_len, ctx, S, heads);
+  if (B <= 0 || S <= 0 || S > 512 || heads <= 0 || B > 65535) return -1;
+  const int R = ((S + 63) / 64) * 64;
+  const int qblocks = (S + 15) / 16;
+  const int nwarps = qblocks < ATT_MAX_WARPS ? qblocks : ATT_MAX_WARPS;
+  const size_t smem = static_cast<size_t>(R) * 256 + nwarps * 2048 + static_cast<size_t>(R) * 4;
+  static size_t attr_max[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && smem > attr_max[dev]) {
+    const size_t want = 512 * 256 + ATT_MAX_WARPS * 2048 + 512 * 4;
+    if (cudaFuncSetAttribute(attention_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(want)) != cudaSuccess)
+      return -2;
+    attr_max[dev] = want;
+  }
+  dim3 grid(heads, B);
+  attention_bf16_kernel<<<grid, nwarps * 32, smem, stream>>>(qkv, mask, kv_len, ctx, S, heads, R);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 

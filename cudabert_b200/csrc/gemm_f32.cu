@@ -109,7 +109,56 @@ gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
   }
 }
 
+// Pooler: out[b, :] = tanh(x[b * ldx + 0..H) . W[H, H] + bias), fp32, for the few rows of a batch
+// (reference: copy_pooler + op_Linear + op_Tanh, ops/elementwise.cu:6-32, 57-70, utils/bert.cu:239-247).
+// 16 rows x 64 columns per CTA so that a batch of 128 fills 128 CTAs; thread = 1 row x 4 columns.
+constexpr int PM = 16, PN = 64, PK = 32;
+
+__global__ void __launch_bounds__(256)
+pooler_f32_kernel(const float* __restrict__ x, size_t ldx, const float* __restrict__ W, const float* __restrict__ bias,
+                  float* __restrict__ out, int B, int H) {
+  __shared__ float xs[PM][PK + 1];
+  __shared__ __align__(16) float ws[PK][PN];
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * PN, b0 = blockIdx.y * PM;
+  const int row = tid >> 4, c4 = (tid & 15) * 4;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < H; k0 += PK) {
+    for (int i = tid; i < PM * PK; i += 256) {
+      const int r = i / PK, k = i % PK;
+      xs[r][k] = (b0 + r < B) ? x[static_cast<size_t>(b0 + r) * ldx + k0 + k] : 0.f;
+    }
+    for (int i = tid; i < PK * PN / 4; i += 256) {
+      const int k = i / (PN / 4), c = (i % (PN / 4)) * 4;
+      *reinterpret_cast<float4*>(&ws[k][c]) = __ldg(reinterpret_cast<const float4*>(W + static_cast<size_t>(k0 + k) * H + n0 + c));
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < PK; ++k) {
+      const float a = xs[row][k];
+      const float4 w = *reinterpret_cast<const float4*>(&ws[k][c4]);
+      acc[0] = fmaf(a, w.x, acc[0]); acc[1] = fmaf(a, w.y, acc[1]);
+      acc[2] = fmaf(a, w.z, acc[2]); acc[3] = fmaf(a, w.w, acc[3]);
+    }
+    __syncthreads();
+  }
+  if (b0 + row < B) {
+    const float4 bv = __ldg(reinterpret_cast<const float4*>(bias + n0 + c4));
+    *reinterpret_cast<float4*>(out + static_cast<size_t>(b0 + row) * H + n0 + c4) =
+        make_float4(tanhf(acc[0] + bv.x), tanhf(acc[1] + bv.y), tanhf(acc[2] + bv.z), tanhf(acc[3] + bv.w));
+  }
+}
+
 }  // namespace
+
+int pooler_f32(const float* x, size_t ldx, const float* W, const float* bias, float* out, int B, int H,
+               cudaStream_t stream) {
+  if (B <= 0 || H <= 0 || (H % PN) != 0 || (H % PK) != 0) return -1;
+  dim3 grid(H / PN, (B + PM - 1) / PM);
+  if (grid.y > 65535) return -1;
+  pooler_f32_kernel<<<grid, 256, 0, stream>>>(x, ldx, W, bias, out, B, H);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
 
 int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float* out, int ldo,
              const GemmEpilogue& epi, cudaStream_t stream) {

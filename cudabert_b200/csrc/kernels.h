@@ -51,6 +51,10 @@ bool make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, ui
 int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float* out, int ldo,
              const GemmEpilogue& epi, cudaStream_t stream);
 
+// Pooler: out[b, :] = tanh(x[b * ldx ...] . W[H, H] + bias[H]) in fp32; H % 64 == 0.
+int pooler_f32(const float* x, size_t ldx, const float* W, const float* bias, float* out, int B, int H,
+               cudaStream_t stream);
+
 // ---- masked attention.  qkv is [T, 3H] (Q | K | V column blocks, head h at columns h*64),
 // ctx is [T, H].  kv_len[b] > 0: keys >= kv_len[b] are all masked and are skipped; the
 // int32 key mask (may be null) is applied to the keys below kv_len.  kv_len[b] == 0: the row

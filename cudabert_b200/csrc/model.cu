@@ -448,13 +448,8 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
   }
   // pooler: rows b*S of the fp32 final hidden states, tanh(dense) -> fp32 [B, H]
   // (utils/bert.cu:239-247); always the fp32 kernel, it is 2 H^2 FLOPs per sequence
-  {
-    GemmEpilogue epi;
-    epi.flags = EPI_BIAS | EPI_TANH;
-    epi.bias = pooler_.bias;
-    CB_LAUNCH(KC_POOLER, gemm_f32(xf_, S * H_, static_cast<const float*>(pooler_.w), B, H_, H_, pooled_, H_, epi,
-                                  stream_));
-  }
+  CB_LAUNCH(KC_POOLER, pooler_f32(xf_, static_cast<size_t>(S) * H_, static_cast<const float*>(pooler_.w), pooler_.bias,
+                                  pooled_, B, H_, stream_));
   if (want_probs)
     CB_LAUNCH(KC_OTHER, classify_softmax(pooled_, cls_w_, cls_b_, probs_, B, H_, classes_, stream_));
 #undef CB_LAUNCH
