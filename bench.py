@@ -58,11 +58,19 @@ def flops_per_step(batch, seq, dims):
     return dense, attn, batch * 2 * H * H
 
 
-def gemm_flops_per_step(batch, seq, dims):
+def gemm_flops(tokens, dims):
+    """FLOPs the tensor-core GEMMs execute for `tokens` rows (QKV, attention-output, FFN1, FFN2 of
+    every layer).  With the packed layout only the valid tokens of a batch are rows."""
     H, L, F = dims["hidden"], dims["layers"], dims["ffn"]
-    T = batch * seq
-    per_layer = 2 * T * (3 * H * H + H * H + 2 * H * F)
-    return L * per_layer + 2 * batch * H * H
+    return L * 2 * tokens * (3 * H * H + H * H + 2 * H * F)
+
+
+def live_tokens(mask):
+    """Rows the packed layout computes for a batch: per line 1 + index of its last valid position
+    (a line with no valid position counts as the full padded length)."""
+    S = mask.shape[1]
+    last = np.where(mask.any(1), S - np.argmax(mask[:, ::-1] != 0, axis=1), S)
+    return last
 
 
 def load_peaks():
@@ -281,7 +289,12 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     peaks = load_peaks()
     gemm_ms = sum(prof[k][0] for k in prof if k.startswith("gemm"))
     gemm_n = sum(prof[k][1] for k in prof if k.startswith("gemm"))
-    gflops = gemm_flops_per_step(B, S, dims) * prof_steps
+    packed = os.environ.get("CUDABERT_PACK", "1") != "0"
+    lens = [live_tokens(hb[2]) if packed else np.full(B, S) for hb in host]
+    prof_lens = [lens[i % n_pool] for i in range(prof_steps)]
+    gflops = sum(gemm_flops(int(l.sum()), dims) for l in prof_lens)
+    attn_exec = sum(dims["layers"] * 4 * dims["hidden"] * float((l.astype(np.float64) ** 2).sum()) for l in prof_lens)
+    ln_rows = sum(int(l.sum()) for l in prof_lens) / prof_steps
     achieved = gflops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
     dense, attn, pool = flops_per_step(B, S, dims)
     total_ms = sum(v[0] for v in prof.values())
@@ -290,7 +303,7 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     attn_ms = prof["attention"][0]
     ln_ms, ln_n = prof["layernorm"]
     # LayerNorm: read fp16 dense output + fp32 residual, write the bf16 GEMM copy + the fp32 residual copy
-    ln_bytes = B * S * dims["hidden"] * 12
+    ln_bytes = ln_rows * dims["hidden"] * 12
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -308,7 +321,10 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
         "config": {"workload": WORKLOAD, "batch_per_gpu": B, "seq_len": S, "global_batch": B * world,
                    "parallelism": "replicas x%d (batch sharding, no collective)" % world,
                    "l2": "working set per step (577 MB of activations, 604 MB of weights) is larger than L2",
-                   "tflops_per_step_padded": (dense + attn + pool) / 1e12},
+                   "tflops_per_step_padded": (dense + attn + pool) / 1e12,
+                   "layout": ("packed: padding tokens are not computed (%.0f live of %d token slots per step)"
+                              % (ln_rows, B * S)) if packed else "padded",
+                   "tflops_per_step_executed_gemm": gflops / prof_steps / 1e12},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": 3 * B * S * 4, "d2h_bytes_per_step": B * C * 4 + 4},
@@ -319,7 +335,7 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
                      "launches": gemm_n / prof_steps, "avg_launch_ms": gemm_ms / gemm_n if gemm_n else None,
                      "traffic": None},
         "kernels": kernels,
-        "attention_tflops": (attn * prof_steps / (attn_ms / 1e3) / 1e12) if attn_ms else None,
+        "attention_tflops": (attn_exec / (attn_ms / 1e3) / 1e12) if attn_ms else None,
         "layernorm_gbs": (ln_bytes * ln_n / (ln_ms / 1e3) / 1e9) if ln_ms else None,
         "cpu_baseline": cpu,
     }

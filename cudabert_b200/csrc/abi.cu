@@ -257,7 +257,7 @@ int cudabert_k_gemm_bf16(const void* A_dev, long lda, const void* W_dev, int M, 
   epi.bias = bias_dev;
   epi.residual = residual_dev;
   epi.colscale = colscale_dev;
-  const int n = cb::gemm_bf16_tcgen05(&tmA, &tmW, M, N, K, out_dev, N, epi, err, sms, nullptr);
+  const int n = cb::gemm_bf16_tcgen05(&tmA, &tmW, M, N, K, out_dev, N, epi, err, sms, nullptr, nullptr);
   if (n < 0) return 3;
   if (cudaDeviceSynchronize() != cudaSuccess) return 4;
   int herr = 0;
@@ -271,7 +271,7 @@ int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, 
   epi.flags = flags;
   epi.bias = bias_dev;
   epi.residual = residual_dev;
-  const int n = cb::gemm_f32(A_dev, lda, W_dev, M, N, K, out_dev, N, epi, nullptr);
+  const int n = cb::gemm_f32(A_dev, lda, W_dev, M, N, K, out_dev, N, epi, nullptr, nullptr);
   if (n < 0) return 3;
   return cudaDeviceSynchronize() == cudaSuccess ? 0 : 4;
 }
@@ -281,11 +281,11 @@ int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, voi
   int* kv = nullptr;
   if (cudaMalloc(&kv, static_cast<size_t>(B) * sizeof(int)) != cudaSuccess) return 2;
   int rc = 0;
-  if (cb::mask_to_kv_len(mask_dev, kv, B, S, nullptr) < 0) rc = 3;
+  if (cb::row_layout(mask_dev, kv, nullptr, B, S, nullptr) < 0) rc = 3;
   if (!rc) {
-    const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv,
+    const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
                                             static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr)
-                       : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv,
+                       : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr,
                                            static_cast<float*>(ctx_dev), B, S, heads, nullptr);
     if (n < 0) rc = 3;
   }
@@ -304,10 +304,11 @@ int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev,
   if (bf16)
     n = cb::embed_layernorm<__nv_bfloat16>(ids_dev, seg_dev, word_dev, pos_dev, type_dev, gamma_dev, beta_dev,
                                            static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, S, H, vocab,
-                                           scratch.p, nullptr);
+                                           scratch.p, nullptr, nullptr);
   else
     n = cb::embed_layernorm<float>(ids_dev, seg_dev, word_dev, pos_dev, type_dev, gamma_dev, beta_dev,
-                                   static_cast<float*>(out_dev), out_f32_dev, tokens, S, H, vocab, scratch.p, nullptr);
+                                   static_cast<float*>(out_dev), out_f32_dev, tokens, S, H, vocab, scratch.p, nullptr,
+                                   nullptr);
   if (n < 0) return 3;
   if (cudaDeviceSynchronize() != cudaSuccess) return 4;
   int herr = 0;
@@ -323,16 +324,16 @@ int cudabert_k_layernorm(int out_bf16, int in_f16, const void* x_dev, const floa
   const float* xf = static_cast<const float*>(x_dev);
   if (out_bf16 && in_f16)
     n = cb::layernorm<__half, __nv_bfloat16>(xh, residual_dev, gamma_dev, beta_dev,
-                                             static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, H, nullptr);
+                                             static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, H, nullptr, nullptr);
   else if (out_bf16)
     n = cb::layernorm<float, __nv_bfloat16>(xf, residual_dev, gamma_dev, beta_dev,
-                                            static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, H, nullptr);
+                                            static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, H, nullptr, nullptr);
   else if (in_f16)
     n = cb::layernorm<__half, float>(xh, residual_dev, gamma_dev, beta_dev, static_cast<float*>(out_dev), out_f32_dev,
-                                     tokens, H, nullptr);
+                                     tokens, H, nullptr, nullptr);
   else
     n = cb::layernorm<float, float>(xf, residual_dev, gamma_dev, beta_dev, static_cast<float*>(out_dev), out_f32_dev,
-                                    tokens, H, nullptr);
+                                    tokens, H, nullptr, nullptr);
   if (n < 0) return 3;
   return cudaDeviceSynchronize() == cudaSuccess ? 0 : 4;
 }

@@ -36,7 +36,8 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 //   smem: K [R][64] | V [R][64] | per-warp Q / O staging [16][64] | bias [R]   (R = keys rounded to 64)
 __global__ void __launch_bounds__(ATT_MAX_WARPS * 32, 2)
 attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ mask,
-                      const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ ctx, int S, int heads, int R) {
+                      const int* __restrict__ kv_len, const int* __restrict__ row_start,
+                      __nv_bfloat16* __restrict__ ctx, int S, int heads, int R) {
   extern __shared__ __align__(1024) uint8_t att_smem[];
   uint8_t* sK = att_smem;
   uint8_t* sV = sK + static_cast<size_t>(R) * 128;
@@ -50,9 +51,12 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   int klen = kv_len[b];
   const bool use_mask = (klen > 0) && (mask != nullptr);
   if (klen <= 0) klen = S;
+  // rows of this sequence: [first, first + nq).  Packed: only the klen rows that exist; else all S.
+  const int first = row_start ? row_start[b] : b * S;
+  const int nq = row_start ? klen : S;
   const int ktiles = (klen + 63) >> 6;
   const int krows = ktiles << 6;  // rows of K / V the tiles touch; rows >= klen are zero-filled
-  const __nv_bfloat16* base = qkv + static_cast<size_t>(b) * S * ld + h * HD;
+  const __nv_bfloat16* base = qkv + static_cast<size_t>(first) * ld + h * HD;
 
   for (int i = tid; i < krows * 8; i += blockDim.x) {
     const int r = i >> 3, c = i & 7;
@@ -74,7 +78,7 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
 
   uint8_t* myQ = sQ + warp * 2048;
   const float scale = 0.125f * LOG2E;
-  const int qblocks = (S + 15) >> 4;
+  const int qblocks = (nq + 15) >> 4;
   for (int qb = warp; qb < qblocks; qb += nwarps) {
     const int q0 = qb * 16;
     // stage the 16 x 64 Q block: lane l moves chunk l % 8 of rows l / 8 + 4 i
@@ -83,7 +87,7 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
     for (int i = 0; i < 4; ++i) {
       const int r = (lane >> 3) + 4 * i, c = lane & 7;
       uint4 t = make_uint4(0u, 0u, 0u, 0u);
-      if (q0 + r < S) t = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + r) * ld + c * 8));
+      if (q0 + r < nq) t = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + r) * ld + c * 8));
       *reinterpret_cast<uint4*>(myQ + swz(r, c)) = t;
     }
     __syncwarp();
@@ -186,11 +190,11 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
       *reinterpret_cast<uint32_t*>(myQ + swz(g + 8, i) + 4 * t4) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
     }
     __syncwarp();
-    __nv_bfloat16* out_base = ctx + static_cast<size_t>(b) * S * H + h * HD;
+    __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = (lane >> 3) + 4 * i, c = lane & 7;
-      if (q0 + r < S)
+      if (q0 + r < nq)
         *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(q0 + r) * H + c * 8) =
             *reinterpret_cast<const uint4*>(myQ + swz(r, c));
     }
@@ -203,7 +207,7 @@ constexpr int FK = 32;  // keys per chunk: one per lane
 
 __global__ void __launch_bounds__(256)
 attention_f32_kernel(const float* __restrict__ qkv, const int* __restrict__ mask, const int* __restrict__ kv_len,
-                     float* __restrict__ ctx, int S, int heads) {
+                     const int* __restrict__ row_start, float* __restrict__ ctx, int S, int heads) {
   __shared__ float sQ[FQ][HD];
   __shared__ float sK[FK][HD + 1];
   __shared__ float sV[FK][HD];
@@ -214,12 +218,15 @@ attention_f32_kernel(const float* __restrict__ qkv, const int* __restrict__ mask
   int klen = kv_len[b];
   const bool use_mask = (klen > 0) && (mask != nullptr);
   if (klen <= 0) klen = S;
-  const float* base = qkv + static_cast<size_t>(b) * S * ld + h * HD;
+  const int first = row_start ? row_start[b] : b * S;
+  const int nq = row_start ? klen : S;
+  if (q0 >= nq) return;
+  const float* base = qkv + static_cast<size_t>(first) * ld + h * HD;
   const int* mrow = mask ? mask + static_cast<size_t>(b) * S : nullptr;
 
   for (int i = tid; i < FQ * HD; i += 256) {
     const int r = i / HD, c = i % HD;
-    sQ[r][c] = (q0 + r < S) ? base[static_cast<size_t>(q0 + r) * ld + c] : 0.f;
+    sQ[r][c] = (q0 + r < nq) ? base[static_cast<size_t>(q0 + r) * ld + c] : 0.f;
   }
   float m_run[4], l_run[4], o0[4], o1[4];
 #pragma unroll
@@ -229,7 +236,7 @@ attention_f32_kernel(const float* __restrict__ qkv, const int* __restrict__ mask
     __syncthreads();
     for (int i = tid; i < FK * HD; i += 256) {
       const int r = i / HD, c = i % HD;
-      const bool ok = (k0 + r) < S;
+      const bool ok = (k0 + r) < klen;
       sK[r][c] = ok ? base[static_cast<size_t>(k0 + r) * ld + H + c] : 0.f;
       sV[r][c] = ok ? base[static_cast<size_t>(k0 + r) * ld + 2 * H + c] : 0.f;
     }
@@ -273,35 +280,77 @@ attention_f32_kernel(const float* __restrict__ qkv, const int* __restrict__ mask
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     const int row = q0 + warp * 4 + q;
-    if (row < S) {
-      float* dst = ctx + (static_cast<size_t>(b) * S + row) * H + h * HD;
+    if (row < nq) {
+      float* dst = ctx + (static_cast<size_t>(first) + row) * H + h * HD;
       dst[lane] = o0[q] / l_run[q];
       dst[lane + 32] = o1[q] / l_run[q];
     }
   }
 }
 
-__global__ void mask_to_kv_len_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int B, int S) {
-  const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (b >= B) return;
-  int last = 0;
-  if (mask == nullptr) {
-    last = S;
-  } else {
-    const int* row = mask + static_cast<size_t>(b) * S;
-    for (int i = lane; i < S; i += 32)
-      if (row[i] != 0) last = i + 1;
+// One block.  kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none; S if
+// mask is null).  With `row_start` (B + 1 entries) it also lays the sequences out back to back:
+// row_start[b] = sum of the lengths of the rows before b, a row of length 0 (no valid key: it
+// attends to everything) counting as S; row_start[B] is the number of packed rows.
+__global__ void __launch_bounds__(1024)
+row_layout_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int* __restrict__ row_start, int B, int S) {
+  __shared__ int warp_tot[32];
+  __shared__ int carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int b = warp; b < B; b += 32) {
+    int last = 0;
+    if (mask == nullptr) {
+      last = S;
+    } else {
+      const int* row = mask + static_cast<size_t>(b) * S;
+      for (int i = lane; i < S; i += 32)
+        if (row[i] != 0) last = i + 1;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, off));
+      for (int off = 16; off > 0; off >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, off));
+    }
+    if (lane == 0) kv_len[b] = last;
   }
-  if (lane == 0) kv_len[b] = last;
+  if (row_start == nullptr) return;
+  if (tid == 0) carry = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < B; b0 += 1024) {
+    const int b = b0 + tid;
+    int v = 0;
+    if (b < B) {
+      v = kv_len[b];
+      if (v <= 0) v = S;
+    }
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += n;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_tot[lane];
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, w, off);
+        if (lane >= off) w += n;
+      }
+      warp_tot[lane] = w;  // inclusive totals of the warps
+    }
+    __syncthreads();
+    const int before = carry + (warp > 0 ? warp_tot[warp - 1] : 0) + incl - v;
+    if (b < B) row_start[b] = before;
+    __syncthreads();
+    if (tid == 1023) carry = before + v;
+    __syncthreads();
+  }
+  if (tid == 0) row_start[B] = carry;
 }
 
 }  // namespace
 
-int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, __nv_bfloat16* ctx, int B, int S,
-                   int heads, cudaStream_t stream) {
+int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, const int* row_start,
+                   __nv_bfloat16* ctx, int B, int S, int heads, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || S > 512 || heads <= 0 || B > 65535) return -1;
   const int R = ((S + 63) / 64) * 64;
   const int qblocks = (S + 15) / 16;
@@ -318,23 +367,21 @@ int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
     attr_max[dev] = want;
   }
   dim3 grid(heads, B);
-  attention_bf16_kernel<<<grid, nwarps * 32, smem, stream>>>(qkv, mask, kv_len, ctx, S, heads, R);
+  attention_bf16_kernel<<<grid, nwarps * 32, smem, stream>>>(qkv, mask, kv_len, row_start, ctx, S, heads, R);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
-int attention_f32(const float* qkv, const int* mask, const int* kv_len, float* ctx, int B, int S, int heads,
-                  cudaStream_t stream) {
+int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,
+                  int S, int heads, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || heads <= 0 || B > 65535) return -1;
   dim3 grid((S + FQ - 1) / FQ, heads, B);
-  attention_f32_kernel<<<grid, 256, 0, stream>>>(qkv, mask, kv_len, ctx, S, heads);
+  attention_f32_kernel<<<grid, 256, 0, stream>>>(qkv, mask, kv_len, row_start, ctx, S, heads);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
-int mask_to_kv_len(const int* mask, int* kv_len, int B, int S, cudaStream_t stream) {
+int row_layout(const int* mask, int* kv_len, int* row_start, int B, int S, cudaStream_t stream) {
   if (B <= 0 || S <= 0) return -1;
-  const int warps_per_block = 4;
-  mask_to_kv_len_kernel<<<(B + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, stream>>>(mask, kv_len,
-                                                                                                            B, S);
+  row_layout_kernel<<<1, 1024, 0, stream>>>(mask, kv_len, row_start, B, S);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
@@ -382,10 +429,10 @@ extern "C" int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const
     kv = scratch_of_device[dev];
   }
   // every entry [0, B) is rewritten before it is read, so nothing left by an earlier call matters
-  if (cb::mask_to_kv_len(mask_dev, kv, B, S, nullptr) < 0) return 3;
-  const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv,
+  if (cb::row_layout(mask_dev, kv, nullptr, B, S, nullptr) < 0) return 3;
+  const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
                                           static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr)
-                     : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv,
+                     : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr,
                                          static_cast<float*>(ctx_dev), B, S, heads, nullptr);
   if (n < 0) return 3;
   const cudaError_t e = cudaDeviceSynchronize();

@@ -18,7 +18,10 @@ __device__ __forceinline__ float gelu_erf_f32(float x) { return x * 0.5f * (1.0f
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int M, int N, int K,
                 float* __restrict__ out, int ldo, int flags, const float* __restrict__ bias,
-                const float* __restrict__ residual, const float* __restrict__ colscale) {
+                const float* __restrict__ residual, const float* __restrict__ colscale,
+                const int* __restrict__ m_dev) {
+  if (m_dev) M = min(M, __ldg(m_dev));
+  if (static_cast<int>(blockIdx.y) * TM >= M) return;
   __shared__ float As[2][TK][TM + 4];
   __shared__ float Bs[2][TK][TN];
   const int tid = threadIdx.x;
@@ -115,8 +118,8 @@ gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
 constexpr int PM = 16, PN = 64, PK = 32;
 
 __global__ void __launch_bounds__(256)
-pooler_f32_kernel(const float* __restrict__ x, size_t ldx, const float* __restrict__ W, const float* __restrict__ bias,
-                  float* __restrict__ out, int B, int H) {
+pooler_f32_kernel(const float* __restrict__ x, int rows_per_seq, const int* __restrict__ row_start,
+                  const float* __restrict__ W, const float* __restrict__ bias, float* __restrict__ out, int B, int H) {
   __shared__ float xs[PM][PK + 1];
   __shared__ __align__(16) float ws[PK][PN];
   const int tid = threadIdx.x;
@@ -126,7 +129,9 @@ pooler_f32_kernel(const float* __restrict__ x, size_t ldx, const float* __restri
   for (int k0 = 0; k0 < H; k0 += PK) {
     for (int i = tid; i < PM * PK; i += 256) {
       const int r = i / PK, k = i % PK;
-      xs[r][k] = (b0 + r < B) ? x[static_cast<size_t>(b0 + r) * ldx + k0 + k] : 0.f;
+      const int bb = b0 + r;
+      const size_t xrow = bb < B ? (row_start ? static_cast<size_t>(row_start[bb]) : static_cast<size_t>(bb) * rows_per_seq) : 0;
+      xs[r][k] = (bb < B) ? x[xrow * H + k0 + k] : 0.f;
     }
     for (int i = tid; i < PK * PN / 4; i += 256) {
       const int k = i / (PN / 4), c = (i % (PN / 4)) * 4;
@@ -151,17 +156,17 @@ pooler_f32_kernel(const float* __restrict__ x, size_t ldx, const float* __restri
 
 }  // namespace
 
-int pooler_f32(const float* x, size_t ldx, const float* W, const float* bias, float* out, int B, int H,
-               cudaStream_t stream) {
+int pooler_f32(const float* x, int rows_per_seq, const int* row_start, const float* W, const float* bias, float* out,
+               int B, int H, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || (H % PN) != 0 || (H % PK) != 0) return -1;
   dim3 grid(H / PN, (B + PM - 1) / PM);
   if (grid.y > 65535) return -1;
-  pooler_f32_kernel<<<grid, 256, 0, stream>>>(x, ldx, W, bias, out, B, H);
+  pooler_f32_kernel<<<grid, 256, 0, stream>>>(x, rows_per_seq, row_start, W, bias, out, B, H);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
 int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float* out, int ldo,
-             const GemmEpilogue& epi, cudaStream_t stream) {
+             const GemmEpilogue& epi, const int* m_dev, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (N % 4) != 0 || (K % TK) != 0 || (lda % 4) != 0 || (ldo % 4) != 0) return -1;
   if ((epi.flags & EPI_BIAS) && !epi.bias) return -1;
   if ((epi.flags & EPI_RESIDUAL) && !epi.residual) return -1;
@@ -169,7 +174,7 @@ int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float
   dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
   if (grid.y > 65535) return -1;
   gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, lda, W, M, N, K, out, ldo, epi.flags, epi.bias,
-                                             static_cast<const float*>(epi.residual), epi.colscale);
+                                             static_cast<const float*>(epi.residual), epi.colscale, m_dev);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 

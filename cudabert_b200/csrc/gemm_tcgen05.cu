@@ -232,8 +232,10 @@ template <int BN, int FLAGS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, int M, int N,
                     int K, void* __restrict__ out, int ldo, int flags, const float* __restrict__ bias,
-                    const void* __restrict__ residual, const float* __restrict__ colscale, int* err) {
+                    const void* __restrict__ residual, const float* __restrict__ colscale, int* err,
+                    const int* __restrict__ m_dev) {
   using C = Cfg<BN>;
+  if (m_dev) M = min(M, __ldg(m_dev));
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;
@@ -378,8 +380,10 @@ template <int BN, int FLAGS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, int M,
                          int N, int K, void* __restrict__ out, int ldo, int flags, const float* __restrict__ bias,
-                         const void* __restrict__ residual, const float* __restrict__ colscale, int* err) {
+                         const void* __restrict__ residual, const float* __restrict__ colscale, int* err,
+                         const int* __restrict__ m_dev) {
   using C = PairCfg<BN>;
+  if (m_dev) M = min(M, __ldg(m_dev));
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;
@@ -528,7 +532,7 @@ constexpr int F_H16 = EPI_BIAS | EPI_OUT_F16;
 
 template <int BN, int FLAGS>
 int launch_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
-               const GemmEpilogue& epi, int* err_flag, int num_sms, cudaStream_t stream) {
+               const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream) {
   using C = Cfg<BN>;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -542,18 +546,18 @@ int launch_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   gemm_tcgen05_kernel<BN, FLAGS><<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(
-      *tmA, *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag);
+      *tmA, *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
 template <int BN>
 int launch(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
-           const GemmEpilogue& epi, int* err_flag, int num_sms, cudaStream_t stream) {
+           const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream) {
   switch (epi.flags) {
-    case F_QKV: return launch_one<BN, F_QKV>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
-    case F_FFN1: return launch_one<BN, F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
-    case F_H16: return launch_one<BN, F_H16>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
-    default: return launch_one<BN, -1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
+    case F_QKV: return launch_one<BN, F_QKV>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
+    case F_FFN1: return launch_one<BN, F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
+    case F_H16: return launch_one<BN, F_H16>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
+    default: return launch_one<BN, -1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
   }
 }
 
@@ -589,7 +593,7 @@ int max_resident_pairs(int dev) {
 
 template <int FLAGS>
 int launch_pair_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
-                    const GemmEpilogue& epi, int* err_flag, cudaStream_t stream) {
+                    const GemmEpilogue& epi, int* err_flag, const int* m_dev, cudaStream_t stream) {
   using C = PairCfg<256>;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -598,23 +602,23 @@ int launch_pair_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * (N / 256);
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
   gemm_tcgen05_pair_kernel<256, FLAGS><<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(
-      *tmA, *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag);
+      *tmA, *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
 int launch_pair(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
-                const GemmEpilogue& epi, int* err_flag, cudaStream_t stream) {
+                const GemmEpilogue& epi, int* err_flag, const int* m_dev, cudaStream_t stream) {
   switch (epi.flags) {
-    case F_QKV: return launch_pair_one<F_QKV>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
-    case F_FFN1: return launch_pair_one<F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
-    case F_H16: return launch_pair_one<F_H16>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+    case F_QKV: return launch_pair_one<F_QKV>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_FFN1: return launch_pair_one<F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_H16: return launch_pair_one<F_H16>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_QKV | EPI_COLSCALE:
-      return launch_pair_one<F_QKV | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+      return launch_pair_one<F_QKV | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_FFN1 | EPI_COLSCALE:
-      return launch_pair_one<F_FFN1 | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+      return launch_pair_one<F_FFN1 | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_H16 | EPI_COLSCALE:
-      return launch_pair_one<F_H16 | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
-    default: return launch_pair_one<-1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
+      return launch_pair_one<F_H16 | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    default: return launch_pair_one<-1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   }
 }
 
@@ -652,14 +656,14 @@ bool make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, ui
 }
 
 int gemm_bf16_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
-                      const GemmEpilogue& epi, int* err_flag, int num_sms, cudaStream_t stream) {
+                      const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (N % 128) != 0 || (K % BK) != 0 || (ldo % 8) != 0) return -1;
   if ((epi.flags & EPI_BIAS) && !epi.bias) return -1;
   if ((epi.flags & EPI_RESIDUAL) && !epi.residual) return -1;
   if ((epi.flags & EPI_COLSCALE) && !epi.colscale) return -1;
-  if (gemm_uses_pairs(N)) return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, stream);
-  if (gemm_block_n(N) == 256) return launch<256>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
-  return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, stream);
+  if (gemm_uses_pairs(N)) return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+  if (gemm_block_n(N) == 256) return launch<256>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
+  return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
 }
 
 }  // namespace cb

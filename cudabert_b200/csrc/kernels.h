@@ -35,8 +35,10 @@ struct GemmEpilogue {
 // N must be a multiple of 128 and K of 64; M is arbitrary (tail rows are zero-filled by TMA
 // and never stored).  `tmA` / `tmW` are tiled tensor maps made by make_tmap_bf16_kmajor with
 // box rows 128 (A) and gemm_w_box_rows(N) (W).
+// m_dev (device int, may be null): the live row count; the kernel then computes rows
+// [0, min(M, *m_dev)) while the launch is sized for M.
 int gemm_bf16_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
-                      const GemmEpilogue& epi, int* err_flag, int num_sms, cudaStream_t stream);
+                      const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream);
 int gemm_block_n(int N);
 // Box rows the W tensor map must be encoded with for the kernel variant that gemm_bf16_tcgen05
 // will pick for this N (128 when CTA pairs each load half of a 256-row tile, else gemm_block_n).
@@ -49,36 +51,47 @@ bool make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, ui
 // ---- fp32 CUDA-core GEMM: out[M, N] = A[M, K] (fp32, row stride lda) x W[K, N] (fp32, the
 // on-disk [in, out] layout).  N % 4 == 0, K % 4 == 0.
 int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float* out, int ldo,
-             const GemmEpilogue& epi, cudaStream_t stream);
+             const GemmEpilogue& epi, const int* m_dev, cudaStream_t stream);
 
-// Pooler: out[b, :] = tanh(x[b * ldx ...] . W[H, H] + bias[H]) in fp32; H % 64 == 0.
-int pooler_f32(const float* x, size_t ldx, const float* W, const float* bias, float* out, int B, int H,
-               cudaStream_t stream);
+// Pooler: out[b, :] = tanh(x[row(b)] . W[H, H] + bias[H]) in fp32; H % 64 == 0.  row(b) = b * rows_per_seq,
+// or row_start[b] when row_start != null (packed layout).
+int pooler_f32(const float* x, int rows_per_seq, const int* row_start, const float* W, const float* bias, float* out,
+               int B, int H, cudaStream_t stream);
 
-// ---- masked attention.  qkv is [T, 3H] (Q | K | V column blocks, head h at columns h*64),
-// ctx is [T, H].  kv_len[b] > 0: keys >= kv_len[b] are all masked and are skipped; the
-// int32 key mask (may be null) is applied to the keys below kv_len.  kv_len[b] == 0: the row
+// ---- masked attention.  qkv is [rows, 3H] (Q | K | V column blocks, head h at columns h*64),
+// ctx is [rows, H].  kv_len[b] > 0: keys >= kv_len[b] are all masked and are skipped; the
+// int32 key mask [B, S] (may be null) is applied to the keys below kv_len.  kv_len[b] == 0: the row
 // has no valid key, every key gets the same -10000 so the mask is ignored (softmax is shift
-// invariant).  Head size is 64.
-int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, __nv_bfloat16* ctx, int B, int S,
-                   int heads, cudaStream_t stream);
-int attention_f32(const float* qkv, const int* mask, const int* kv_len, float* ctx, int B, int S, int heads,
-                  cudaStream_t stream);
+// invariant) and the row counts as S long.  Head size is 64.
+// row_start == null: sequence b occupies rows [b*S, (b+1)*S) (padded layout).  row_start != null
+// (B + 1 entries from row_layout): sequences are packed back to back, sequence b occupies rows
+// [row_start[b], row_start[b+1]) and has no rows for its padding.
+int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, const int* row_start,
+                   __nv_bfloat16* ctx, int B, int S, int heads, cudaStream_t stream);
+int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,
+                  int S, int heads, cudaStream_t stream);
 // kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none); mask null => S.
-int mask_to_kv_len(const int* mask, int* kv_len, int B, int S, cudaStream_t stream);
+// row_start (may be null): exclusive prefix sum of the sequence lengths (a length of 0 counts as S),
+// B + 1 entries, the last one being the number of packed rows.
+int row_layout(const int* mask, int* kv_len, int* row_start, int B, int S, cudaStream_t stream);
 
 // ---- row-wise kernels.  The residual stream is kept in fp32; TOut (float or __nv_bfloat16) is
 // the copy that feeds the next GEMM.  out_f32 (may be null) receives the same values in fp32.
-// out[t] = LayerNorm(word[ids[t]] + pos[t % S] + type[seg[t]]) ; err bit 1 set on a bad id.
+// out[row(t)] = LayerNorm(word[ids[t]] + pos[t % S] + type[seg[t]]) for t < tokens = B*S; err bit 1
+// set on a bad id.  row_start == null: row(t) = t.  Packed (row_start from row_layout): token
+// (b, s) goes to row row_start[b] + s, tokens beyond a sequence's length are skipped.
 template <typename TOut>
 int embed_layernorm(const int* ids, const int* seg, const float* word, const float* pos, const float* type,
                     const float* gamma, const float* beta, TOut* out, float* out_f32, int tokens, int S, int H,
-                    int vocab, int* err_flag, cudaStream_t stream);
+                    int vocab, int* err_flag, const int* row_start, cudaStream_t stream);
 // out[t] = LayerNorm(x[t] + residual[t]) * gamma + beta; x is fp32 or fp16 (the tensor-core GEMM's
-// dense output), residual (may be null) is the fp32 residual stream.
+// dense output), residual (may be null) is the fp32 residual stream.  Rows t < min(tokens, *rows_dev)
+// (rows_dev: device int, may be null) are processed.
 template <typename TIn, typename TOut>
 int layernorm(const TIn* x, const float* residual, const float* gamma, const float* beta, TOut* out, float* out_f32,
-              int tokens, int H, cudaStream_t stream);
+              int tokens, int H, const int* rows_dev, cudaStream_t stream);
+// dst[B*S, H] (fp32) = packed src rows scattered back to the padded layout, zeros for padding.
+int unpack_rows(const float* src, const int* row_start, float* dst, int tokens, int S, int H, cudaStream_t stream);
 // probs[b, :] = softmax(pooled[b, :] . W[H, C] + bias[C]),  C <= 32
 int classify_softmax(const float* pooled, const float* W, const float* bias, float* probs, int B, int H, int C,
                      cudaStream_t stream);

@@ -36,6 +36,7 @@ Model::~Model() {
   for (void* p : owned_) cudaFree(p);
   if (arena_) cudaFree(arena_);
   if (stage_f32_) cudaFree(stage_f32_);
+  if (hidden_unpacked_) cudaFree(hidden_unpacked_);
   if (err_dev_) cudaFree(err_dev_);
   if (h_in_) cudaFreeHost(h_in_);
   if (h_out_) cudaFreeHost(h_out_);
@@ -62,6 +63,11 @@ bool Model::init(bool large, int gpu, int max_batch, int max_seq, const std::str
   else       { L_ = 12; H_ = 768;  heads_ = 12; F_ = 3072; }
   if (num_layers > 0) L_ = std::min(L_, num_layers);
   prec_ = precision;
+  {
+    // CUDABERT_PACK=0 keeps the padded layout (hidden states are then computed for padding tokens too)
+    const char* e = std::getenv("CUDABERT_PACK");
+    packed_ = !(e && e[0] == '0');
+  }
   esize_ = (precision == PREC_FP32) ? 4 : 2;
   if (!check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
   if (!check(cudaMalloc(&err_dev_, sizeof(int)), "cudaMalloc")) return false;
@@ -260,8 +266,17 @@ bool Model::load_weights(const std::string& dir) {
 }
 
 // ------------------------------------------------------------------ arena
-bool Model::ensure_capacity(int B, int S, bool) {
+bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   const size_t T = static_cast<size_t>(B) * S;
+  if (want_hidden_f32 && packed_ && hidden_unpacked_tokens_ < T) {
+    if (!check(cudaStreamSynchronize(stream_), "sync")) return false;
+    if (hidden_unpacked_) cudaFree(hidden_unpacked_);
+    hidden_unpacked_ = nullptr;
+    hidden_unpacked_tokens_ = 0;
+    const size_t tok = std::max(T, cap_tokens_);
+    if (!check(cudaMalloc(&hidden_unpacked_, tok * H_ * sizeof(float)), "cudaMalloc(hidden states)")) return false;
+    hidden_unpacked_tokens_ = tok;
+  }
   if (T <= cap_tokens_ && B <= cap_batch_) return true;
   if (!check(cudaStreamSynchronize(stream_), "sync before arena growth")) return false;
   const size_t ct = std::max(T, cap_tokens_);
@@ -275,6 +290,7 @@ bool Model::ensure_capacity(int B, int S, bool) {
   auto slot = [&](size_t bytes) { const size_t o = off; off = align_up(off + bytes, 1024); return o; };
   const size_t o_ints = slot(3 * ct * sizeof(int));
   const size_t o_kv = slot(static_cast<size_t>(cbatch) * sizeof(int));
+  const size_t o_rs = slot((static_cast<size_t>(cbatch) + 1) * sizeof(int));
   const size_t o_xf = slot(ct * H_ * sizeof(float));
   const size_t o_x1f = slot(ct * H_ * sizeof(float));
   const size_t o_y = slot(ct * H_ * (lowp ? 2 : 4));
@@ -289,6 +305,7 @@ bool Model::ensure_capacity(int B, int S, bool) {
   char* base = static_cast<char*>(arena_);
   ids_ = reinterpret_cast<int*>(base + o_ints);
   kv_len_ = reinterpret_cast<int*>(base + o_kv);
+  row_start_ = reinterpret_cast<int*>(base + o_rs);
   xf_ = reinterpret_cast<float*>(base + o_xf);
   x1f_ = reinterpret_cast<float*>(base + o_x1f);
   y_ = base + o_y;
@@ -371,13 +388,13 @@ bool Model::dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, i
   prof_begin(kclass);
   if (prec_ == PREC_FP32) {
     n = gemm_f32(static_cast<const float*>(A), lda, static_cast<const float*>(w.w), M, w.N, w.K,
-                 static_cast<float*>(out), w.N, epi, stream_);
+                 static_cast<float*>(out), w.N, epi, m_dev_cur_, stream_);
   } else {
     if (prec_ == PREC_FP8) {
       epi.flags |= EPI_COLSCALE;
       epi.colscale = w.colscale;
     }
-    n = gemm_bf16_tcgen05(tmA, &w.tmap, M, w.N, w.K, out, w.N, epi, err_dev_, num_sms_, stream_);
+    n = gemm_bf16_tcgen05(tmA, &w.tmap, M, w.N, w.K, out, w.N, epi, err_dev_, num_sms_, m_dev_cur_, stream_);
   }
   prof_end(kclass);
   if (n < 0) return fail(2, "GEMM launch rejected (code " + std::to_string(n) + ")");
@@ -407,49 +424,54 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
     count(kclass, n);                                                   \
   } while (0)
 
-  CB_LAUNCH(KC_OTHER, mask_to_kv_len(d_mask, kv_len_, B, S, stream_));
+  m_dev_cur_ = packed_ ? row_start_ + B : nullptr;
+  const int* rs = packed_ ? row_start_ : nullptr;          // first row of every sequence
+  const int* live = packed_ ? row_start_ + B : nullptr;     // live row count (device)
+  CB_LAUNCH(KC_OTHER, row_layout(d_mask, kv_len_, packed_ ? row_start_ : nullptr, B, S, stream_));
   const bool lowp = prec_ != PREC_FP32;
   __nv_bfloat16* xa = static_cast<__nv_bfloat16*>(xa_);
   __nv_bfloat16* x1a = static_cast<__nv_bfloat16*>(x1a_);
   if (lowp) {
     CB_LAUNCH(KC_EMBED, embed_layernorm<__nv_bfloat16>(d_ids, d_seg, word_, pos_, type_, emb_g_, emb_b_, xa, xf_, T, S,
-                                                       H_, vocab_rows_, err_dev_, stream_));
+                                                       H_, vocab_rows_, err_dev_, rs, stream_));
   } else {
     CB_LAUNCH(KC_EMBED, embed_layernorm<float>(d_ids, d_seg, word_, pos_, type_, emb_g_, emb_b_, xf_, nullptr, T, S, H_,
-                                               vocab_rows_, err_dev_, stream_));
+                                               vocab_rows_, err_dev_, rs, stream_));
   }
   for (int l = 0; l < L_; ++l) {
     const LayerWeights& w = layer_[l];
     if (!dense(w.qkv, xa_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) return false;
     if (lowp) {
-      CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_,
+      CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_, rs,
                                              static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, stream_));
       // y = ctx.Wo + bo in fp16; x1 = LN(y + x) with the add in fp32 inside the LayerNorm kernel
       if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, T, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_ATTN_OUT))
         return false;
       CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __nv_bfloat16>(static_cast<const __half*>(y_), xf_, w.ln1_g, w.ln1_b,
-                                                                x1a, x1f_, T, H_, stream_)));
+                                                                x1a, x1f_, T, H_, live, stream_)));
       if (!dense(w.ffn1, x1a_, &tm_x1_, H_, T, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
       if (!dense(w.ffn2, z_, &tm_z_, F_, T, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_FFN2)) return false;
       CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __nv_bfloat16>(static_cast<const __half*>(y_), x1f_, w.ln2_g, w.ln2_b,
-                                                                xa, xf_, T, H_, stream_)));
+                                                                xa, xf_, T, H_, live, stream_)));
     } else {
-      CB_LAUNCH(KC_ATTENTION, attention_f32(static_cast<const float*>(qkv_), d_mask, kv_len_,
+      CB_LAUNCH(KC_ATTENTION, attention_f32(static_cast<const float*>(qkv_), d_mask, kv_len_, rs,
                                             static_cast<float*>(ctx_), B, S, heads_, stream_));
       // fp32 mode: the GEMM epilogue adds the residual, y = ctx.Wo + bo + x
       if (!dense(w.attn_out, ctx_, nullptr, H_, T, y_, EPI_BIAS | EPI_RESIDUAL, xf_, KC_GEMM_ATTN_OUT)) return false;
       CB_LAUNCH(KC_LAYERNORM, (layernorm<float, float>(static_cast<const float*>(y_), nullptr, w.ln1_g, w.ln1_b, x1f_,
-                                                       nullptr, T, H_, stream_)));
+                                                       nullptr, T, H_, live, stream_)));
       if (!dense(w.ffn1, x1a_, nullptr, H_, T, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
       if (!dense(w.ffn2, z_, nullptr, F_, T, y_, EPI_BIAS | EPI_RESIDUAL, x1f_, KC_GEMM_FFN2)) return false;
       CB_LAUNCH(KC_LAYERNORM, (layernorm<float, float>(static_cast<const float*>(y_), nullptr, w.ln2_g, w.ln2_b, xf_,
-                                                       nullptr, T, H_, stream_)));
+                                                       nullptr, T, H_, live, stream_)));
     }
   }
   // pooler: rows b*S of the fp32 final hidden states, tanh(dense) -> fp32 [B, H]
   // (utils/bert.cu:239-247); always the fp32 kernel, it is 2 H^2 FLOPs per sequence
-  CB_LAUNCH(KC_POOLER, pooler_f32(xf_, static_cast<size_t>(S) * H_, static_cast<const float*>(pooler_.w), pooler_.bias,
-                                  pooled_, B, H_, stream_));
+  CB_LAUNCH(KC_POOLER, pooler_f32(xf_, S, rs, static_cast<const float*>(pooler_.w), pooler_.bias, pooled_, B, H_,
+                                  stream_));
+  if (want_hidden_f32 && packed_)
+    CB_LAUNCH(KC_OTHER, unpack_rows(xf_, row_start_, hidden_unpacked_, T, S, H_, stream_));
   if (want_probs)
     CB_LAUNCH(KC_OTHER, classify_softmax(pooled_, cls_w_, cls_b_, probs_, B, H_, classes_, stream_));
 #undef CB_LAUNCH

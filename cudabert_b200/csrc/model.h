@@ -61,7 +61,8 @@ class Model {
   bool sync();
 
   float* pooled_dev() const { return pooled_; }
-  float* hidden_f32_dev() const { return xf_; }
+  // fp32 final hidden states [B, S, H] of the last call that asked for them (Cuda_Inference)
+  float* hidden_f32_dev() const { return packed_ ? hidden_unpacked_ : xf_; }
   float* probs_dev() const { return probs_; }
   int hidden() const { return H_; }
   int layers() const { return L_; }
@@ -121,6 +122,13 @@ class Model {
   int cap_batch_ = 0;
   void* arena_ = nullptr;
   int *ids_ = nullptr, *kv_len_ = nullptr, *err_dev_ = nullptr;  // ids_: 3 * cap_tokens ints (ids | seg | mask)
+  // packed layout: padding tokens get no rows; row_start_[b] is the first row of sequence b and
+  // row_start_[B] the live row count, all computed on the device (no host round trip)
+  bool packed_ = true;
+  int* row_start_ = nullptr;
+  const int* m_dev_cur_ = nullptr;  // live row count of the forward being enqueued
+  float* hidden_unpacked_ = nullptr;
+  size_t hidden_unpacked_tokens_ = 0;
   // residual stream in fp32: xf_ (layer input / output), x1f_ (after the attention block),
   // y_ (dense outputs, added to the stream by the LayerNorm kernel).  xa_ / x1a_ are the copies that feed the GEMMs (bf16 in the bf16 and
   // fp8 modes; in fp32 mode they alias xf_ / x1f_).  ctx_, qkv_, z_ are in the GEMM element type.

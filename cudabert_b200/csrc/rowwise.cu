@@ -88,10 +88,18 @@ __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
 embed_layernorm_kernel(const int* __restrict__ ids, const int* __restrict__ seg, const float* __restrict__ word,
                        const float* __restrict__ pos, const float* __restrict__ type, const float* __restrict__ gamma,
                        const float* __restrict__ beta, TOut* __restrict__ out, float* __restrict__ out_f32, int tokens,
-                       int S, int H, int vocab, int* err) {
+                       int S, int H, int vocab, int* err, const int* __restrict__ row_start) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
   if (t >= tokens) return;
+  // packed layout: token (b, s) goes to row row_start[b] + s; padding tokens have no row
+  size_t orow = static_cast<size_t>(t);
+  if (row_start) {
+    const int b = t / S, sidx = t % S;
+    const int first = row_start[b];
+    if (sidx >= row_start[b + 1] - first) return;
+    orow = static_cast<size_t>(first) + sidx;
+  }
   int id = ids[t], sg = seg[t];
   if (id < 0 || id >= vocab || sg < 0 || sg > 1) {
     if (lane == 0) atomicOr(err, 2);  // bad token or segment id: clamp, report
@@ -114,8 +122,7 @@ embed_layernorm_kernel(const int* __restrict__ ids, const int* __restrict__ seg,
       x[i][2] = a.z + b.z + c.z; x[i][3] = a.w + b.w + c.w;
     }
   }
-  normalise_and_store<TOut>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H,
-                            out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr);
+  normalise_and_store<TOut>(x, nvec, lane, H, gamma, beta, out + orow * H, out_f32 ? out_f32 + orow * H : nullptr);
 }
 
 template <typename TIn>
@@ -139,10 +146,10 @@ template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
 layernorm_kernel(const TIn* __restrict__ in, const float* __restrict__ residual, const float* __restrict__ gamma,
                  const float* __restrict__ beta, TOut* __restrict__ out, float* __restrict__ out_f32, int tokens,
-                 int H) {
+                 int H, const int* __restrict__ rows_dev) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
-  if (t >= tokens) return;
+  if (t >= tokens || (rows_dev && t >= __ldg(rows_dev))) return;
   const TIn* row = in + static_cast<size_t>(t) * H;
   const float* res = residual ? residual + static_cast<size_t>(t) * H : nullptr;
   const int nvec = H / 128;
@@ -158,6 +165,20 @@ layernorm_kernel(const TIn* __restrict__ in, const float* __restrict__ residual,
     }
   normalise_and_store<TOut>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H,
                             out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr);
+}
+
+// dst[b, s, :] = src[row_start[b] + s, :] for the rows a sequence has, 0 for its padding.
+__global__ void unpack_rows_kernel(const float* __restrict__ src, const int* __restrict__ row_start,
+                                   float* __restrict__ dst, int tokens, int S, int H) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const int b = t / S, sidx = t % S;
+  const int first = row_start[b];
+  const bool live = sidx < row_start[b + 1] - first;
+  const float4* s4 = reinterpret_cast<const float4*>(src + (static_cast<size_t>(first) + sidx) * H);
+  float4* d4 = reinterpret_cast<float4*>(dst + static_cast<size_t>(t) * H);
+  for (int i = lane; i < H / 4; i += 32) d4[i] = live ? s4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
 __global__ void classify_softmax_kernel(const float* __restrict__ pooled, const float* __restrict__ W,
@@ -252,37 +273,44 @@ inline bool ln_shape_ok(int H) { return H > 0 && H % 128 == 0 && H <= 1024; }
 template <typename TOut>
 int embed_layernorm(const int* ids, const int* seg, const float* word, const float* pos, const float* type,
                     const float* gamma, const float* beta, TOut* out, float* out_f32, int tokens, int S, int H,
-                    int vocab, int* err_flag, cudaStream_t stream) {
+                    int vocab, int* err_flag, const int* row_start, cudaStream_t stream) {
   if (tokens <= 0 || S <= 0 || !ln_shape_ok(H)) return -1;
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
-  embed_layernorm_kernel<TOut><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(ids, seg, word, pos, type, gamma, beta, out,
-                                                                           out_f32, tokens, S, H, vocab, err_flag);
+  embed_layernorm_kernel<TOut><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(
+      ids, seg, word, pos, type, gamma, beta, out, out_f32, tokens, S, H, vocab, err_flag, row_start);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
 template <typename TIn, typename TOut>
 int layernorm(const TIn* x, const float* residual, const float* gamma, const float* beta, TOut* out, float* out_f32,
-              int tokens, int H, cudaStream_t stream) {
+              int tokens, int H, const int* rows_dev, cudaStream_t stream) {
   if (tokens <= 0 || !ln_shape_ok(H)) return -1;
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
   layernorm_kernel<TIn, TOut><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(x, residual, gamma, beta, out, out_f32,
-                                                                          tokens, H);
+                                                                          tokens, H, rows_dev);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
 template int embed_layernorm<float>(const int*, const int*, const float*, const float*, const float*, const float*,
-                                    const float*, float*, float*, int, int, int, int, int*, cudaStream_t);
+                                    const float*, float*, float*, int, int, int, int, int*, const int*, cudaStream_t);
 template int embed_layernorm<__nv_bfloat16>(const int*, const int*, const float*, const float*, const float*,
                                             const float*, const float*, __nv_bfloat16*, float*, int, int, int, int,
-                                            int*, cudaStream_t);
+                                            int*, const int*, cudaStream_t);
 template int layernorm<float, float>(const float*, const float*, const float*, const float*, float*, float*, int, int,
-                                     cudaStream_t);
+                                     const int*, cudaStream_t);
 template int layernorm<float, __nv_bfloat16>(const float*, const float*, const float*, const float*, __nv_bfloat16*,
-                                             float*, int, int, cudaStream_t);
+                                             float*, int, int, const int*, cudaStream_t);
 template int layernorm<__half, float>(const __half*, const float*, const float*, const float*, float*, float*, int, int,
-                                      cudaStream_t);
+                                      const int*, cudaStream_t);
 template int layernorm<__half, __nv_bfloat16>(const __half*, const float*, const float*, const float*, __nv_bfloat16*,
-                                              float*, int, int, cudaStream_t);
+                                              float*, int, int, const int*, cudaStream_t);
+
+int unpack_rows(const float* src, const int* row_start, float* dst, int tokens, int S, int H, cudaStream_t stream) {
+  if (tokens <= 0 || S <= 0 || H % 4 != 0) return -1;
+  const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
+  unpack_rows_kernel<<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(src, row_start, dst, tokens, S, H);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
 
 int classify_softmax(const float* pooled, const float* W, const float* bias, float* probs, int B, int H, int C,
                      cudaStream_t stream) {
