@@ -241,8 +241,10 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
         torch.cuda.synchronize(dev)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
+        t_host = time.perf_counter()
         for i in range(steps):
             fn(i)
+        timed.host_ms = (time.perf_counter() - t_host) * 1e3 / steps
         e1.record(stream)
         if sync_after:
             rc = pybert.sync(model)
@@ -260,6 +262,13 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     sampler = ClockSampler(dev)
     if rank == 0:
         sampler.start()
+    # host cost of enqueueing one step into an empty stream (the timed loop below can block on a
+    # full launch queue, so it cannot show this)
+    torch.cuda.synchronize(dev)
+    t_host = time.perf_counter()
+    step_dev(0)
+    host_enqueue_ms = (time.perf_counter() - t_host) * 1e3
+    pybert.sync(model)
     ms_total = timed(step_dev, args.steps, True)
     launches = pybert.launch_count(model) * args.steps
     # end to end through the reference-facing call, host buffers in and out
@@ -316,7 +325,7 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_total / args.steps, "host_enqueue_ms_per_step": host_enqueue_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "batch_per_gpu": B, "seq_len": S, "global_batch": B * world,
                    "parallelism": "replicas x%d (batch sharding, no collective)" % world,

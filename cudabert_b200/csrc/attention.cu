@@ -48,6 +48,8 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x, b = blockIdx.y;
   const int H = heads * HD, ld = 3 * H;
+  griddep_wait();
+  griddep_launch();
   int klen = kv_len[b];
   const bool use_mask = (klen > 0) && (mask != nullptr);
   if (klen <= 0) klen = S;
@@ -215,6 +217,8 @@ attention_f32_kernel(const float* __restrict__ qkv, const int* __restrict__ mask
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q0 = blockIdx.x * FQ, h = blockIdx.y, b = blockIdx.z;
   const int H = heads * HD, ld = 3 * H;
+  griddep_wait();
+  griddep_launch();
   int klen = kv_len[b];
   const bool use_mask = (klen > 0) && (mask != nullptr);
   if (klen <= 0) klen = S;
@@ -297,6 +301,8 @@ row_layout_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int* _
   __shared__ int warp_tot[32];
   __shared__ int carry;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  griddep_wait();
+  griddep_launch();
   for (int b = warp; b < B; b += 32) {
     int last = 0;
     if (mask == nullptr) {
@@ -367,22 +373,22 @@ int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
     attr_max[dev] = want;
   }
   dim3 grid(heads, B);
-  attention_bf16_kernel<<<grid, nwarps * 32, smem, stream>>>(qkv, mask, kv_len, row_start, ctx, S, heads, R);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(attention_bf16_kernel, grid, dim3(nwarps * 32), smem, stream, qkv, mask, kv_len, row_start, ctx, S,
+                    heads, R) == cudaSuccess ? 1 : -3;
 }
 
 int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,
                   int S, int heads, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || heads <= 0 || B > 65535) return -1;
   dim3 grid((S + FQ - 1) / FQ, heads, B);
-  attention_f32_kernel<<<grid, 256, 0, stream>>>(qkv, mask, kv_len, row_start, ctx, S, heads);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(attention_f32_kernel, grid, dim3(256), 0, stream, qkv, mask, kv_len, row_start, ctx, S, heads) ==
+                 cudaSuccess ? 1 : -3;
 }
 
 int row_layout(const int* mask, int* kv_len, int* row_start, int B, int S, cudaStream_t stream) {
   if (B <= 0 || S <= 0) return -1;
-  row_layout_kernel<<<1, 1024, 0, stream>>>(mask, kv_len, row_start, B, S);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(row_layout_kernel, dim3(1), dim3(1024), 0, stream, mask, kv_len, row_start, B, S) == cudaSuccess
+             ? 1 : -3;
 }
 
 }  // namespace cb

@@ -7,6 +7,7 @@
 // 128x128 tile, k-step 8, 256 threads, 8x8 outputs per thread, register-prefetched next
 // k-step.  Rows beyond M are loaded as zero and not stored.
 #include "kernels.h"
+#include "ptx.cuh"
 
 namespace cb {
 namespace {
@@ -20,6 +21,8 @@ gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
                 float* __restrict__ out, int ldo, int flags, const float* __restrict__ bias,
                 const float* __restrict__ residual, const float* __restrict__ colscale,
                 const int* __restrict__ m_dev) {
+  griddep_wait();
+  griddep_launch();
   if (m_dev) M = min(M, __ldg(m_dev));
   if (static_cast<int>(blockIdx.y) * TM >= M) return;
   __shared__ float As[2][TK][TM + 4];
@@ -126,6 +129,8 @@ pooler_f32_kernel(const float* __restrict__ x, int rows_per_seq, const int* __re
   const int n0 = blockIdx.x * PN, b0 = blockIdx.y * PM;
   const int row = tid >> 4, c4 = (tid & 15) * 4;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  griddep_wait();
+  griddep_launch();
   for (int k0 = 0; k0 < H; k0 += PK) {
     for (int i = tid; i < PM * PK; i += 256) {
       const int r = i / PK, k = i % PK;
@@ -161,8 +166,8 @@ int pooler_f32(const float* x, int rows_per_seq, const int* row_start, const flo
   if (B <= 0 || H <= 0 || (H % PN) != 0 || (H % PK) != 0) return -1;
   dim3 grid(H / PN, (B + PM - 1) / PM);
   if (grid.y > 65535) return -1;
-  pooler_f32_kernel<<<grid, 256, 0, stream>>>(x, rows_per_seq, row_start, W, bias, out, B, H);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(pooler_f32_kernel, grid, dim3(256), 0, stream, x, rows_per_seq, row_start, W, bias, out, B, H) ==
+                 cudaSuccess ? 1 : -3;
 }
 
 int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float* out, int ldo,
@@ -173,9 +178,8 @@ int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float
   if ((epi.flags & EPI_COLSCALE) && !epi.colscale) return -1;
   dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
   if (grid.y > 65535) return -1;
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, lda, W, M, N, K, out, ldo, epi.flags, epi.bias,
-                                             static_cast<const float*>(epi.residual), epi.colscale, m_dev);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(gemm_f32_kernel, grid, dim3(256), 0, stream, A, lda, W, M, N, K, out, ldo, epi.flags, epi.bias,
+                    static_cast<const float*>(epi.residual), epi.colscale, m_dev) == cudaSuccess ? 1 : -3;
 }
 
 }  // namespace cb

@@ -235,7 +235,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const void* __restrict__ residual, const float* __restrict__ colscale, int* err,
                     const int* __restrict__ m_dev) {
   using C = Cfg<BN>;
-  if (m_dev) M = min(M, __ldg(m_dev));
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;
@@ -273,6 +272,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above is private to this CTA; from here on it touches the predecessor's output
+  griddep_wait();
+  griddep_launch();
+  if (m_dev) M = min(M, __ldg(m_dev));
 
   const int tiles_n = N / BN;
   const int tiles_m = (M + BM - 1) / BM;
@@ -383,7 +386,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                          const void* __restrict__ residual, const float* __restrict__ colscale, int* err,
                          const int* __restrict__ m_dev) {
   using C = PairCfg<BN>;
-  if (m_dev) M = min(M, __ldg(m_dev));
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;
@@ -423,6 +425,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   cluster_sync_all();  // barriers of both CTAs are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above is private to this pair; from here on it touches the predecessor's output
+  griddep_wait();
+  griddep_launch();
+  if (m_dev) M = min(M, __ldg(m_dev));
 
   const int tiles_n = N / BN;
   const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
@@ -545,9 +551,9 @@ int launch_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int
   }
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  gemm_tcgen05_kernel<BN, FLAGS><<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(
-      *tmA, *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(gemm_tcgen05_kernel<BN, FLAGS>, dim3(grid), dim3(GEMM_THREADS), C::SMEM_BYTES, stream, *tmA, *tmW, M,
+                    N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev) == cudaSuccess
+             ? 1 : -3;
 }
 
 template <int BN>
@@ -601,9 +607,9 @@ int launch_pair_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N
   if (pairs <= 0) return -2;
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * (N / 256);
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  gemm_tcgen05_pair_kernel<256, FLAGS><<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(
-      *tmA, *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(gemm_tcgen05_pair_kernel<256, FLAGS>, dim3(grid), dim3(GEMM_THREADS), C::SMEM_BYTES, stream, *tmA,
+                    *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev) ==
+                 cudaSuccess ? 1 : -3;
 }
 
 int launch_pair(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,

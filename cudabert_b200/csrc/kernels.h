@@ -11,6 +11,26 @@
 
 namespace cb {
 
+// Launch `kernel` so that it may start while the previous kernel of the stream is still draining
+// (programmatic dependent launch).  Every kernel launched this way executes griddep_wait() before
+// it reads or writes anything a predecessor produces or still reads; until then it only does work
+// that is private to it (barrier set-up, TMEM allocation, descriptor prefetch).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Epilogue selection, shared by the tcgen05 and the fp32 GEMM:
 //   out = act( acc * colscale[n] + bias[n] + residual[m, n] )
 enum EpiFlags : int {

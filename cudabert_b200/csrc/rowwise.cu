@@ -91,6 +91,8 @@ embed_layernorm_kernel(const int* __restrict__ ids, const int* __restrict__ seg,
                        int S, int H, int vocab, int* err, const int* __restrict__ row_start) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  griddep_wait();
+  griddep_launch();
   if (t >= tokens) return;
   // packed layout: token (b, s) goes to row row_start[b] + s; padding tokens have no row
   size_t orow = static_cast<size_t>(t);
@@ -149,6 +151,8 @@ layernorm_kernel(const TIn* __restrict__ in, const float* __restrict__ residual,
                  int H, const int* __restrict__ rows_dev) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  griddep_wait();
+  griddep_launch();
   if (t >= tokens || (rows_dev && t >= __ldg(rows_dev))) return;
   const TIn* row = in + static_cast<size_t>(t) * H;
   const float* res = residual ? residual + static_cast<size_t>(t) * H : nullptr;
@@ -172,6 +176,8 @@ __global__ void unpack_rows_kernel(const float* __restrict__ src, const int* __r
                                    float* __restrict__ dst, int tokens, int S, int H) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
+  griddep_wait();
+  griddep_launch();
   if (t >= tokens) return;
   const int b = t / S, sidx = t % S;
   const int first = row_start[b];
@@ -186,6 +192,8 @@ __global__ void classify_softmax_kernel(const float* __restrict__ pooled, const 
                                         int C) {
   const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
+  griddep_wait();
+  griddep_launch();
   if (b >= B) return;
   const float* x = pooled + static_cast<size_t>(b) * H;
   float logit = -INFINITY;  // lane c keeps class c
@@ -276,9 +284,8 @@ int embed_layernorm(const int* ids, const int* seg, const float* word, const flo
                     int vocab, int* err_flag, const int* row_start, cudaStream_t stream) {
   if (tokens <= 0 || S <= 0 || !ln_shape_ok(H)) return -1;
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
-  embed_layernorm_kernel<TOut><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(
-      ids, seg, word, pos, type, gamma, beta, out, out_f32, tokens, S, H, vocab, err_flag, row_start);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(embed_layernorm_kernel<TOut>, dim3(blocks), dim3(ROWS_PER_BLOCK * 32), 0, stream, ids, seg, word, pos,
+                    type, gamma, beta, out, out_f32, tokens, S, H, vocab, err_flag, row_start) == cudaSuccess ? 1 : -3;
 }
 
 template <typename TIn, typename TOut>
@@ -286,9 +293,8 @@ int layernorm(const TIn* x, const float* residual, const float* gamma, const flo
               int tokens, int H, const int* rows_dev, cudaStream_t stream) {
   if (tokens <= 0 || !ln_shape_ok(H)) return -1;
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
-  layernorm_kernel<TIn, TOut><<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(x, residual, gamma, beta, out, out_f32,
-                                                                          tokens, H, rows_dev);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(layernorm_kernel<TIn, TOut>, dim3(blocks), dim3(ROWS_PER_BLOCK * 32), 0, stream, x, residual, gamma,
+                    beta, out, out_f32, tokens, H, rows_dev) == cudaSuccess ? 1 : -3;
 }
 
 template int embed_layernorm<float>(const int*, const int*, const float*, const float*, const float*, const float*,
@@ -308,15 +314,15 @@ template int layernorm<__half, __nv_bfloat16>(const __half*, const float*, const
 int unpack_rows(const float* src, const int* row_start, float* dst, int tokens, int S, int H, cudaStream_t stream) {
   if (tokens <= 0 || S <= 0 || H % 4 != 0) return -1;
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
-  unpack_rows_kernel<<<blocks, ROWS_PER_BLOCK * 32, 0, stream>>>(src, row_start, dst, tokens, S, H);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(unpack_rows_kernel, dim3(blocks), dim3(ROWS_PER_BLOCK * 32), 0, stream, src, row_start, dst, tokens,
+                    S, H) == cudaSuccess ? 1 : -3;
 }
 
 int classify_softmax(const float* pooled, const float* W, const float* bias, float* probs, int B, int H, int C,
                      cudaStream_t stream) {
   if (B <= 0 || H <= 0 || C <= 0 || C > 32) return -1;
-  classify_softmax_kernel<<<(B + 3) / 4, 128, 0, stream>>>(pooled, W, bias, probs, B, H, C);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+  return launch_pdl(classify_softmax_kernel, dim3((B + 3) / 4), dim3(128), 0, stream, pooled, W, bias, probs, B, H, C) ==
+                 cudaSuccess ? 1 : -3;
 }
 
 int transpose_to_bf16(const float* src, __nv_bfloat16* dst, int K, int N, cudaStream_t stream) {
