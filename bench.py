@@ -338,11 +338,13 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": 3 * B * S * 4, "d2h_bytes_per_step": B * C * 4 + 4},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (QKV, attention-output, FFN1, FFN2, pooler)",
+        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel (QKV, attention-output, FFN1, FFN2)",
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tensor"] if peaks["tensor"] else None, "peak_source": peaks["source"],
                      "launches": gemm_n / prof_steps, "avg_launch_ms": gemm_ms / gemm_n if gemm_n else None,
-                     "traffic": None},
+                     # mean DRAM bytes (read + write) per GEMM launch from the ncu capture summarised in
+                     # profiles/gemm_tcgen05_c1_2layers.md (QKV 70, attention-output 32, FFN1 99, FFN2 139 MB)
+                     "traffic": 85.0e6 if not args.layers else None, "traffic_unit": "bytes per launch (ncu, mean of the four GEMMs of a layer)"},
         "kernels": kernels,
         "attention_tflops": (attn_exec / (attn_ms / 1e3) / 1e12) if attn_ms else None,
         "layernorm_gbs": (ln_bytes * ln_n / (ln_ms / 1e3) / 1e9) if ln_ms else None,
