@@ -279,17 +279,36 @@ int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, 
 int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads) {
   if (!qkv_dev || !ctx_dev || B <= 0 || S <= 0 || heads <= 0) return 1;
   int* kv = nullptr;
-  if (cudaMalloc(&kv, static_cast<size_t>(B) * sizeof(int)) != cudaSuccess) return 2;
+  if (cudaMalloc(&kv, (static_cast<size_t>(B) + 1) * sizeof(int)) != cudaSuccess) return 2;
+  int* err = kv + B;
+  cudaMemset(err, 0, sizeof(int));
   int rc = 0;
   if (cb::row_layout(mask_dev, kv, nullptr, B, S, nullptr) < 0) rc = 3;
   if (!rc) {
-    const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
-                                            static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr)
-                       : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr,
-                                           static_cast<float*>(ctx_dev), B, S, heads, nullptr);
+    int n;
+    if (bf16 == 2) {  // tcgen05 kernel
+      CUtensorMap tm;
+      int dev = 0, sms = 148;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (!cb::make_tmap_qkv(&tm, qkv_dev, static_cast<uint64_t>(B) * S, heads * 64)) {
+        cudaFree(kv);
+        return 2;
+      }
+      n = cb::attention_bf16_tc(&tm, mask_dev, kv, nullptr, static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, sms, err,
+                                nullptr);
+    } else if (bf16) {
+      n = cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
+                             static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr);
+    } else {
+      n = cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr, static_cast<float*>(ctx_dev), B,
+                            S, heads, nullptr);
+    }
     if (n < 0) rc = 3;
   }
   if (cudaDeviceSynchronize() != cudaSuccess) rc = 4;
+  int herr = 0;
+  if (!rc && cudaMemcpy(&herr, err, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && herr) rc = 5;
   cudaFree(kv);
   return rc;
 }

@@ -1,0 +1,464 @@
+// Fused masked attention on the tcgen05 tensor cores (bf16 / fp8 modes).  Same contract as
+// attention_bf16 in attention.cu (which stays as the `mma.sync` variant): QK^T, 1/8 scale, additive
+// key mask, softmax, P.V in one kernel, keys at or beyond kv_len[b] never touched.  Replaces
+// Query_Key::forward (ops/batch_matmul.cu:24-82), cuApplySoftmax (ops/softmax.cu:86-143) and
+// Prob_Value::forward (ops/batch_matmul.cu:85-140) of the reference.
+//
+// Persistent CTAs (two per SM) walk over work items (sequence b, head h, 128-query tile).  Per
+// item, for every block of 64 keys:
+//   warp 4, one lane   TMA: Q tile (once per item), K block, V block -> shared memory (128-byte
+//                      swizzle), two buffers each; a buffer is re-filled as soon as the MMAs that
+//                      read it have completed (tcgen05.commit on its "empty" barrier).
+//   warp 5, one lane   S = Q K^T   tcgen05.mma 128 x 64 x 16 (x4 over d = 64) into one of two S
+//                      buffers in TMEM, issued one block AHEAD so that it runs while the softmax
+//                      warps work; after they have written P: O (+)= P V, 128 x 64 x 16 (x4 over
+//                      the 64 keys), V used as an MN-major operand straight from its [key][d]
+//                      rows, O in TMEM columns [128, 192).
+//   warps 0-3          thread = query row = TMEM lane: scale + mask bias, row max (no shuffles: the
+//                      whole row belongs to the thread), online-softmax correction of O in TMEM
+//                      when a later key block raises the max, P = exp2(x - max) as bf16 into the
+//                      swizzled A-operand tile in shared memory; at the end O / sum -> bf16 ->
+//                      coalesced stores.
+// Every wait is bounded (ptx.cuh): a broken pipeline ends with an error flag, not a hang.
+#include "kernels.h"
+#include "ptx.cuh"
+
+#include <cstdlib>
+
+namespace cb {
+namespace {
+
+constexpr int HD = 64;
+constexpr int TQ = 128;  // queries per item
+constexpr int TK = 64;   // keys per block
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr int ATC_THREADS = 192;
+constexpr int Q_BYTES = TQ * 128;   // 128 query rows x 128 bytes (64 bf16)
+constexpr int KV_BYTES = TK * 128;  // 64 key rows x 128 bytes
+constexpr int P_BYTES = TQ * 128;   // 128 query rows x 64 keys (bf16)
+// Q, K and V are double-buffered so that the loads and the QK^T of the next block (or item) run
+// while the softmax warps work on the current one.
+constexpr int SMEM_Q = 0, SMEM_K = 2 * Q_BYTES, SMEM_V = SMEM_K + 2 * KV_BYTES, SMEM_P = SMEM_V + 2 * KV_BYTES;
+constexpr int SMEM_BIAS = SMEM_P + P_BYTES;
+constexpr int SMEM_BAR = SMEM_BIAS + 512 * 4 + 16;  // bias of up to 512 keys + one flag word
+constexpr int ATC_SMEM = SMEM_BAR + 256 + 1024;  // + barriers + alignment slack: 83 KB, two CTAs per SM
+constexpr uint32_t TMEM_COLS = 256;  // S buffers in columns [0, 64) and [64, 128), O in [128, 192)
+constexpr uint32_t S_COL = 0, O_COL = 128;
+
+enum { SITE_ATT_Q = 10, SITE_ATT_K, SITE_ATT_V, SITE_ATT_S, SITE_ATT_P, SITE_ATT_O, SITE_ATT_E };
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+        "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+        "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory descriptor of an MN-major bf16 operand stored as rows of 64 elements (128 bytes,
+// 128-byte swizzle), one row per K index: 8-row groups are 1024 bytes apart (stride byte offset);
+// the leading byte offset (distance between 64-element groups along MN) is unused for N = 64.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr >> 4) & 0x3fff) | (64ull << 16) | (64ull << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// Instruction descriptor: D fp32, A bf16 K-major, B bf16 MN-major, shape M x N (x 16).
+__host__ __device__ constexpr uint32_t umma_idesc_bf16_bmn(int m, int n) {
+  return umma_idesc_bf16(m, n) | (1u << 16);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct ItemInfo {
+  int b, h, q0, first, nq, klen, nblocks;
+  bool use_mask, live;
+};
+
+__device__ __forceinline__ ItemInfo decode_item(int item, int QT, int heads, int S, const int* __restrict__ kv_len,
+                                                const int* __restrict__ row_start, const int* __restrict__ mask) {
+  ItemInfo it;
+  const int qt = item % QT;
+  it.h = (item / QT) % heads;
+  it.b = item / (QT * heads);
+  int klen = kv_len[it.b];
+  it.use_mask = (klen > 0) && (mask != nullptr);
+  if (klen <= 0) klen = S;
+  it.klen = klen;
+  it.first = row_start ? row_start[it.b] : it.b * S;
+  it.nq = row_start ? klen : S;
+  it.q0 = qt * TQ;
+  it.live = it.q0 < it.nq;
+  it.nblocks = (klen + TK - 1) / TK;
+  return it;
+}
+
+__global__ void __launch_bounds__(ATC_THREADS, 2)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __restrict__ mask,
+                    const int* __restrict__ kv_len, const int* __restrict__ row_start,
+                    __nv_bfloat16* __restrict__ ctx, int B, int S, int heads, int* err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* sBias = reinterpret_cast<float*>(smem + SMEM_BIAS);
+  unsigned int* sFlags = reinterpret_cast<unsigned int*>(smem + SMEM_BIAS + 512 * 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BAR);
+  uint64_t *q_full = bars, *q_empty = bars + 2, *k_full = bars + 4, *k_empty = bars + 6, *v_full = bars + 8,
+           *v_empty = bars + 10, *s_full = bars + 12, *p_full = bars + 14, *o_full = bars + 15;  // [2] each but the last two
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 14; ++i) mbar_init(bars + i, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQKV);
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  griddep_wait();
+  griddep_launch();
+
+  const int H = heads * HD;
+  const int QT = (S + TQ - 1) / TQ;
+  const int num_items = B * heads * QT;
+
+  // Walks the key blocks of this CTA's live items in order: (item, block j), counting items and
+  // blocks so that every role derives buffer indices and barrier parities the same way.
+  struct Cursor {
+    int item, j, items_done, blocks_done;
+    ItemInfo it;
+    bool valid;
+  };
+  auto cursor_seek = [&](Cursor& c) {  // position on the first live item at or after c.item
+    c.valid = false;
+    while (c.item < num_items) {
+      c.it = decode_item(c.item, QT, heads, S, kv_len, row_start, mask);
+      if (c.it.live) { c.valid = true; break; }
+      c.item += gridDim.x;
+    }
+    c.j = 0;
+  };
+  auto cursor_next = [&](Cursor& c) {
+    ++c.blocks_done;
+    if (++c.j < c.it.nblocks) return;
+    ++c.items_done;
+    c.item += gridDim.x;
+    cursor_seek(c);
+  };
+
+  if (warp == 4) {
+    if (lane == 0) {
+      Cursor c{};
+      c.item = static_cast<int>(blockIdx.x);
+      for (cursor_seek(c); c.valid; cursor_next(c)) {
+        if (c.j == 0) {
+          const int qb = c.items_done & 1;
+          mbar_wait(q_empty + qb, ((c.items_done >> 1) & 1) ^ 1, abort_flag, err, SITE_ATT_E);
+          mbar_arrive_expect_tx(q_full + qb, Q_BYTES);  // two 64-row boxes
+          tma_load_2d(smem + SMEM_Q + qb * Q_BYTES, &tmQKV, q_full + qb, c.it.h * HD, c.it.first + c.it.q0);
+          tma_load_2d(smem + SMEM_Q + qb * Q_BYTES + Q_BYTES / 2, &tmQKV, q_full + qb, c.it.h * HD,
+                      c.it.first + c.it.q0 + 64);
+        }
+        const int kb = c.blocks_done & 1;
+        const uint32_t par = ((c.blocks_done >> 1) & 1) ^ 1;
+        mbar_wait(k_empty + kb, par, abort_flag, err, SITE_ATT_E);
+        mbar_arrive_expect_tx(k_full + kb, KV_BYTES);
+        tma_load_2d(smem + SMEM_K + kb * KV_BYTES, &tmQKV, k_full + kb, H + c.it.h * HD, c.it.first + c.j * TK);
+        mbar_wait(v_empty + kb, par, abort_flag, err, SITE_ATT_E);
+        mbar_arrive_expect_tx(v_full + kb, KV_BYTES);
+        tma_load_2d(smem + SMEM_V + kb * KV_BYTES, &tmQKV, v_full + kb, 2 * H + c.it.h * HD, c.it.first + c.j * TK);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(TQ, TK);
+      constexpr uint32_t idesc_o = umma_idesc_bf16_bmn(TQ, HD);
+      const uint32_t sq = smem_u32(smem + SMEM_Q), sk = smem_u32(smem + SMEM_K), sv = smem_u32(smem + SMEM_V),
+                     sp = smem_u32(smem + SMEM_P);
+      // S = Q K^T of the block under `c` into S buffer blocks_done & 1.  That buffer was last read by
+      // the softmax of block blocks_done - 2, whose p_full this thread has already waited for.
+      auto issue_s = [&](const Cursor& c) {
+        const int qb = c.items_done & 1, kb = c.blocks_done & 1;
+        if (c.j == 0) mbar_wait(q_full + qb, (c.items_done >> 1) & 1, abort_flag, err, SITE_ATT_Q);
+        mbar_wait(k_full + kb, (c.blocks_done >> 1) & 1, abort_flag, err, SITE_ATT_K);
+        tc_fence_after();
+        const uint64_t da = umma_desc_sw128(sq + qb * Q_BYTES), db = umma_desc_sw128(sk + kb * KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) umma_bf16(tmem_base + S_COL + kb * TK, da + 2 * k, db + 2 * k, idesc_s, k != 0);
+        umma_commit(s_full + kb);
+        umma_commit(k_empty + kb);
+        if (c.j == c.it.nblocks - 1) umma_commit(q_empty + qb);
+      };
+      // O (+)= P V over the block's 64 keys: A = P (K-major over the keys), B = V rows (MN-major)
+      auto issue_pv = [&](const Cursor& c) {
+        const int vb = c.blocks_done & 1;
+        mbar_wait(v_full + vb, (c.blocks_done >> 1) & 1, abort_flag, err, SITE_ATT_V);
+        mbar_wait(p_full, c.blocks_done & 1, abort_flag, err, SITE_ATT_P);
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < TK / 16; ++k) {
+          const uint64_t da = umma_desc_sw128(sp) + 2 * k;
+          const uint64_t db = umma_desc_sw128_mn(sv + vb * KV_BYTES) + static_cast<uint64_t>(k) * (2048 >> 4);
+          umma_bf16(tmem_base + O_COL, da, db, idesc_o, (c.j | k) != 0);
+        }
+        umma_commit(o_full);
+        umma_commit(v_empty + vb);
+      };
+      Cursor cs{};
+      cs.item = static_cast<int>(blockIdx.x);
+      cursor_seek(cs);
+      Cursor cp = cs;
+      if (cs.valid) {
+        issue_s(cs);
+        cursor_next(cs);
+      }
+      while (cp.valid) {
+        if (cs.valid) {  // the next block's QK^T runs while the softmax warps work on this one
+          issue_s(cs);
+          cursor_next(cs);
+        }
+        issue_pv(cp);
+        cursor_next(cp);
+      }
+    }
+  } else {
+    // softmax warps 0-3: thread r owns query row r of the tile and TMEM lane r
+    const int r = threadIdx.x;  // 0..127
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    uint8_t* my_p = smem + SMEM_P + r * 128;       // this row's 64 probabilities of the block
+    uint8_t* stage = smem + SMEM_P + warp * 4096;  // output staging: this warp's 32 rows x 128 B
+    const float scale = 0.125f * LOG2E;
+    uint32_t o_waits = 0;  // completions of o_full consumed so far
+    float m_run = -INFINITY, l_run = 0.f;
+    Cursor c{};
+    c.item = static_cast<int>(blockIdx.x);
+    for (cursor_seek(c); c.valid; cursor_next(c)) {
+      const ItemInfo& it = c.it;
+      const int j = c.j;
+      const int* mrow = mask ? mask + static_cast<size_t>(it.b) * S : nullptr;
+      if (j == 0) { m_run = -INFINITY; l_run = 0.f; }
+      const uint32_t t_s = t_lane + S_COL + (c.blocks_done & 1) * TK;
+      if (j == 0) {
+        // once per item: additive bias (log2 domain) of every key of the sequence, and one flag bit
+        // per 64-key block that has any non-zero bias (masked key or tail beyond the last key)
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone is done with the previous item's bias
+        if (r == 0) *sFlags = 0u;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int kend = it.nblocks * TK;
+        uint32_t bits = 0u;
+        for (int key = r; key < kend; key += 128) {
+          float bv = 0.f;
+          if (key >= it.klen) bv = -INFINITY;
+          else if (it.use_mask && __ldg(mrow + key) == 0) bv = -10000.0f * LOG2E;
+          sBias[key] = bv;
+          if (bv != 0.f) bits |= 1u << (key / TK);
+        }
+        if (bits) atomicOr(sFlags, bits);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      const bool plain = ((*sFlags >> j) & 1u) == 0u;  // every key of the block is valid
+      const float* bias = sBias + j * TK;
+      mbar_wait(s_full + (c.blocks_done & 1), (c.blocks_done >> 1) & 1, abort_flag, err, SITE_ATT_S);
+      tc_fence_after();
+      // the 64 scores of the row: one TMEM round trip, kept in registers for both steps
+      uint32_t v[2][32];
+      tmem_ld32(t_s, v[0]);
+      tmem_ld32(t_s + 32, v[1]);
+      tmem_ld_wait();
+      // four independent chains for the maximum (and below for the sum): a single chain of 64
+      // dependent operations would leave the two warps an SM sub-partition holds mostly stalled
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (plain) {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = __uint_as_float(v[ch][i]) * scale;
+            v[ch][i] = __float_as_uint(x);
+            mx4[i & 3] = fmaxf(mx4[i & 3], x);
+          }
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 b4 = *reinterpret_cast<const float4*>(bias + ch * 32 + i);
+            const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float x = fmaf(__uint_as_float(v[ch][i + q]), scale, bb[q]);
+              v[ch][i + q] = __float_as_uint(x);
+              mx4[q] = fmaxf(mx4[q], x);
+            }
+          }
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // Reference point of the exponentials.  It only has to keep exp2 in range, so it follows the
+      // running maximum lazily: it moves (and O is rescaled in TMEM, a round trip) only when a block
+      // exceeds it by more than 8 in the log2 domain; until then probabilities may reach 2^8, which
+      // bf16 and the fp32 sums hold without loss.  The first block of an item sets it exactly.
+      float alpha = 1.0f;
+      if (j == 0) {
+        m_run = mx;  // finite: key 0 of block 0 is never masked with -inf
+      } else if (mx > m_run + 8.0f) {
+        alpha = fast_exp2(m_run - mx);
+        m_run = mx;
+      }
+      const float m_new = m_run;
+      l_run *= alpha;
+      if (j > 0) {
+        // the previous block's P.V must have landed before P is overwritten (and O rescaled)
+        mbar_wait(o_full, o_waits & 1, abort_flag, err, SITE_ATT_O);
+        ++o_waits;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+          uint32_t o[2][32];
+          tmem_ld32(t_lane + O_COL, o[0]);
+          tmem_ld32(t_lane + O_COL + 32, o[1]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[ch][i] = __float_as_uint(__uint_as_float(o[ch][i]) * alpha);
+            tmem_st32(t_lane + O_COL + ch * 32, o[ch]);
+          }
+          tmem_st_wait();
+        }
+      }
+      // P = exp2(x - max) -> bf16 -> swizzled A-operand tile
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        float p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          p[i] = fast_exp2(__uint_as_float(v[ch][i]) - m_new);
+          l4[i & 3] += p[i];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 t;
+          t.x = pack_bf16(p[8 * q], p[8 * q + 1]);
+          t.y = pack_bf16(p[8 * q + 2], p[8 * q + 3]);
+          t.z = pack_bf16(p[8 * q + 4], p[8 * q + 5]);
+          t.w = pack_bf16(p[8 * q + 6], p[8 * q + 7]);
+          *reinterpret_cast<uint4*>(my_p + (((ch * 4 + q) ^ (r & 7)) << 4)) = t;
+        }
+      }
+      l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      fence_proxy_async_smem();  // the tensor core reads P through the async proxy
+      tc_fence_before();
+      mbar_arrive(p_full);
+      if (j != it.nblocks - 1) continue;
+
+      // last block of the item: O / l -> bf16 -> this warp's staging rows -> coalesced stores
+      mbar_wait(o_full, o_waits & 1, abort_flag, err, SITE_ATT_O);
+      ++o_waits;
+      tc_fence_after();
+      const float inv = 1.0f / l_run;
+      uint8_t* my_row = stage + lane * 128;
+      uint32_t ov[2][32];
+      tmem_ld32(t_lane + O_COL, ov[0]);
+      tmem_ld32(t_lane + O_COL + 32, ov[1]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int ch = 0; ch < HD / 32; ++ch) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 t;
+          t.x = pack_bf16(__uint_as_float(ov[ch][8 * q]) * inv, __uint_as_float(ov[ch][8 * q + 1]) * inv);
+          t.y = pack_bf16(__uint_as_float(ov[ch][8 * q + 2]) * inv, __uint_as_float(ov[ch][8 * q + 3]) * inv);
+          t.z = pack_bf16(__uint_as_float(ov[ch][8 * q + 4]) * inv, __uint_as_float(ov[ch][8 * q + 5]) * inv);
+          t.w = pack_bf16(__uint_as_float(ov[ch][8 * q + 6]) * inv, __uint_as_float(ov[ch][8 * q + 7]) * inv);
+          *reinterpret_cast<uint4*>(my_row + (((ch * 4 + q) ^ (lane & 7)) << 4)) = t;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      __nv_bfloat16* out_base = ctx + static_cast<size_t>(it.first) * H + it.h * HD;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3), p2 = lane & 7;
+        const int qrow = it.q0 + warp * 32 + rr;
+        const uint4 t = *reinterpret_cast<const uint4*>(stage + rr * 128 + (p2 << 4));
+        if (qrow < it.nq)
+          *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(qrow) * H + ((p2 ^ (rr & 7)) << 3)) = t;
+      }
+      __syncwarp();  // the staging rows are this warp's P rows of the next block
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+// Which bf16 attention kernel a forward pass of padded length S uses.  This kernel works on
+// 128-query tiles of 64-key blocks whatever the number of live rows in them, so it wins where the
+// tiles are full (measured per layer, BERT-large: S = 512 full rows 95 us against 179 us for the
+// mma.sync kernel, S = 128 full rows 43 against 61) and loses where a batch's rows are much
+// shorter than the tile grid (S = 200 with lengths 16..200: 87 against 76; S = 64 with lengths
+// 8..64: 185 against 124).  The lengths live on the device, so the choice uses S alone: long
+// sequences, or S that fills its last query tile to 85 % or more.  CUDABERT_ATTENTION=tc / mma
+// forces one kernel.
+bool attention_use_tc(int S) {
+  static const int forced = [] {
+    const char* e = std::getenv("CUDABERT_ATTENTION");
+    if (!e || !*e) return -1;
+    return (e[0] == 't' || e[0] == '2') ? 1 : ((e[0] == 'm' || e[0] == '0' || e[0] == '1') ? 0 : -1);
+  }();
+  if (forced >= 0) return forced == 1;
+  const int tiles = (S + TQ - 1) / TQ;
+  return S >= 384 || S * 100 >= tiles * TQ * 85;
+}
+
+bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H) {
+  return make_tmap_bf16_kmajor(out, qkv, rows, static_cast<uint64_t>(3) * H, static_cast<uint64_t>(3) * H * 2, TK);
+}
+
+int attention_bf16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
+                      __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int* err_flag, cudaStream_t stream) {
+  if (B <= 0 || S <= 0 || S > 512 || heads <= 0) return -1;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM) != cudaSuccess)
+      return -2;
+    attr_set[dev] = true;
+  }
+  const long long items = static_cast<long long>(B) * heads * ((S + TQ - 1) / TQ);
+  const int grid = static_cast<int>(items < 2LL * num_sms ? items : 2LL * num_sms);
+  return launch_pdl(attention_tc_kernel, dim3(grid), dim3(ATC_THREADS), ATC_SMEM, stream, *tm_qkv, mask, kv_len,
+                    row_start, ctx, B, S, heads, err_flag) == cudaSuccess ? 1 : -3;
+}
+
+}  // namespace cb

@@ -13,17 +13,20 @@
 // memory per k-block instead of 48 KB; the operand feed is what bounds the single-CTA variant.
 // Loads are never shared between CTAs.  `gemm_tcgen05_kernel` is the single-CTA variant:
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0, one lane   TMA producer: per k-block one 128x64 tile of A and one BNx64 tile of W
 //                      (128-byte swizzle) into a ring of shared-memory stages guarded by
 //                      full/empty mbarriers.
 //   warp 1, one lane   issues tcgen05.mma (128 x BN x 16, bf16 in, fp32 accumulate in TMEM);
 //                      tcgen05.commit releases a stage back to the producer and, after the
 //                      last k-block, hands the accumulator to the epilogue.
-//   warps 2-5          epilogue: tcgen05.ld of the accumulator (each warp owns the TMEM lane
-//                      quarter warp_id % 4), bias / column scale / residual / GELU / tanh in
-//                      registers, 16-byte stores.  Two accumulators (2 x BN TMEM columns) let
-//                      the epilogue of tile i overlap the MMAs of tile i+1.
+//   warps 2-9          epilogue: tcgen05.ld of the accumulator (a warp can reach the TMEM lane
+//                      quarter warp_id % 4 only, so two warps share a quarter and each takes
+//                      half of the tile's columns: with one warp per SM sub-partition the
+//                      epilogue issues from a single warp there and is latency-bound), bias /
+//                      column scale / residual / GELU / tanh in registers, 16-byte stores.  Two
+//                      accumulators (2 x BN TMEM columns) let the epilogue of tile i overlap the
+//                      MMAs of tile i+1.
 #include "kernels.h"
 #include "ptx.cuh"
 
@@ -38,10 +41,12 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int GEMM_THREADS = 192;
-constexpr int EPI_WARP_BYTES = 32 * 128;           // one 32-row x 128-byte piece per epilogue warp
+constexpr int EPI_WARPS = 8;                         // two per lane quarter, each takes half of the columns
+constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int GEMM_THREADS = 64 + EPI_THREADS;
+constexpr int EPI_WARP_BYTES = 32 * 64;              // one 32-row x 64-byte piece per epilogue warp
 constexpr int EPI_VEC_BYTES = 2 * 256 * 4;           // bias and column scale of one tile
-constexpr int EPI_STAGE_BYTES = 4 * EPI_WARP_BYTES + EPI_VEC_BYTES;
+constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_WARP_BYTES + EPI_VEC_BYTES;
 
 template <int BN>
 struct Cfg {
@@ -70,20 +75,21 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return fmaf(hx, t, hx);
 }
 
-// Epilogue of one accumulator (128 TMEM lanes x BN columns at `t_acc`), run by the four epilogue
-// warps; each owns the lane quarter warp % 4.  `m0` is the first output row of THIS CTA's 128 rows.
+// Epilogue of one accumulator (128 TMEM lanes x BN columns at `t_acc`), run by the eight epilogue
+// warps; each owns the lane quarter warp % 4 and the column half `half`.  `m0` is the first output
+// row of THIS CTA's 128 rows.
 //
 // FLAGS >= 0 fixes the epilogue at compile time (the combinations the model uses); FLAGS < 0 takes
 // the run-time `flags`.  A thread reads one accumulator ROW from TMEM, but 32 threads storing to 32
 // different rows touch 32 cache lines per instruction, so each warp transposes 32-column chunks
-// through its own 4 KB of shared memory: phase 1, thread = row, writes 16-byte pieces at a swizzled
+// through its own 2 KB of shared memory: phase 1, thread = row, writes 16-byte pieces at a swizzled
 // position (conflict-free); phase 2, consecutive lanes cover consecutive bytes of a row, so global
 // stores are full-sector, row-contiguous accesses.  Bias and column scale of the tile are staged
 // in shared memory once per tile.  A residual (tests only: the model adds its residual in the
 // LayerNorm kernel) is read by the row's own thread in phase 1.
 template <int BN, int FLAGS>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restrict__ stage, const float* __restrict__ sbias,
-                                              const float* __restrict__ sscale, int warp, int lane, int m0, int n0,
+                                              const float* __restrict__ sscale, int warp, int half, int lane, int m0, int n0,
                                               int M, void* __restrict__ out, int ldo, int flags,
                                               const void* __restrict__ residual) {
   const int fl = (FLAGS >= 0) ? FLAGS : flags;
@@ -136,13 +142,15 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restric
     }
   };
 
+  // this warp's share of the tile: chunks of 32 columns in [half * BN / 2, (half + 1) * BN / 2)
+  const int c_begin = half * (BN / 64), c_end = c_begin + BN / 64;
+  const int r2 = lane >> 2, p2 = lane & 3;
+  uint8_t* my_row = stage + lane * 64;
   if (fl & EPI_OUT_F32) {
-    // 32 fp32 columns = 128 bytes per row; phase 2: 8 lanes per row, 4 rows per instruction
+    // two passes of 16 fp32 columns = 64 bytes per row; phase 2: 4 lanes per row, 8 rows per instruction
     float* outf = static_cast<float*>(out);
-    uint8_t* my_row = stage + lane * 128;
-    const int r2 = lane >> 3, p2 = lane & 7;
 #pragma unroll
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = c_begin; c < c_end; ++c) {
       const int col = c * 32;
       uint32_t v[32];
       tmem_ld32(t_row + col, v);
@@ -150,28 +158,30 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restric
       float f[32];
       finish32(v, f, col);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<float4*>(my_row + ((j ^ (lane & 7)) << 4)) =
-            make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]);
-      __syncwarp();
+      for (int h = 0; h < 2; ++h) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int r = i * 4 + r2;
-        const int row = row_base + r;
-        const float4 t = *reinterpret_cast<const float4*>(stage + r * 128 + (p2 << 4));
-        if (row < M)
-          *reinterpret_cast<float4*>(outf + static_cast<size_t>(row) * ldo + n0 + col + ((p2 ^ (r & 7)) << 2)) = t;
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<float4*>(my_row + ((j ^ ((lane >> 1) & 3)) << 4)) =
+              make_float4(f[16 * h + 4 * j], f[16 * h + 4 * j + 1], f[16 * h + 4 * j + 2], f[16 * h + 4 * j + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = i * 8 + r2;
+          const int row = row_base + r;
+          const float4 t = *reinterpret_cast<const float4*>(stage + r * 64 + (p2 << 4));
+          if (row < M)
+            *reinterpret_cast<float4*>(outf + static_cast<size_t>(row) * ldo + n0 + col + 16 * h +
+                                       ((p2 ^ ((r >> 1) & 3)) << 2)) = t;
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   } else {
     // 32 16-bit columns (bf16, or fp16 with EPI_OUT_F16) = 64 bytes per row; phase 2: 4 lanes per
     // row, 8 rows per instruction
     uint16_t* outh = static_cast<uint16_t*>(out);
-    uint8_t* my_row = stage + lane * 64;
-    const int r2 = lane >> 2, p2 = lane & 3;
 #pragma unroll
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = c_begin; c < c_end; ++c) {
       const int col = c * 32;
       uint32_t v[32];
       tmem_ld32(t_row + col, v);
@@ -210,7 +220,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restric
   __syncwarp();
 }
 
-// The four epilogue warps (128 threads, named barrier 1) stage bias / column scale of the tile's BN
+// The epilogue warps (EPI_THREADS threads, named barrier 1) stage bias / column scale of the tile's BN
 // columns in shared memory.  The first barrier keeps a fast warp from overwriting values a slow
 // warp still reads for the previous tile.
 template <int BN, int FLAGS>
@@ -219,13 +229,13 @@ __device__ __forceinline__ void stage_tile_vectors(float* __restrict__ sbias, fl
                                                    int n0) {
   const int fl = (FLAGS >= 0) ? FLAGS : flags;
   if (!(fl & (EPI_BIAS | EPI_COLSCALE))) return;
-  const int t = threadIdx.x - 64;  // 0..127
-  asm volatile("bar.sync 1, 128;" ::: "memory");
-  for (int i = t; i < BN; i += 128) {
+  const int t = threadIdx.x - 64;  // 0..EPI_THREADS-1
+  asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+  for (int i = t; i < BN; i += EPI_THREADS) {
     if (fl & EPI_BIAS) sbias[i] = __ldg(bias + n0 + i);
     if (fl & EPI_COLSCALE) sscale[i] = __ldg(colscale + n0 + i);
   }
-  asm volatile("bar.sync 1, 128;" ::: "memory");
+  asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
 }
 
 template <int BN, int FLAGS>
@@ -238,7 +248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;
-  float* sbias = reinterpret_cast<float*>(epi_stage + 4 * EPI_WARP_BYTES);
+  float* sbias = reinterpret_cast<float*>(epi_stage + EPI_WARPS * EPI_WARP_BYTES);
   float* sscale = sbias + 256;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + EPI_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + C::STAGES;
@@ -257,7 +267,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar + a, 1);
-      mbar_init(tempty_bar + a, 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar + a, EPI_WARPS);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -337,8 +347,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int m0 = (tile / tiles_n) * BM;
       stage_tile_vectors<BN, FLAGS>(sbias, sscale, flags, bias, colscale, n0);
       mbar_wait(tfull_bar + acc, acc_phase, abort_flag, err, SITE_TMEM_FULL);
-      epilogue_tile<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp & 3) * EPI_WARP_BYTES, sbias, sscale, warp, lane,
-                               m0, n0, M, out, ldo, flags, residual);
+      epilogue_tile<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp - 2) * EPI_WARP_BYTES, sbias, sscale, warp,
+                               (warp - 2) >> 2, lane, m0, n0, M, out, ldo, flags, residual);
       if (lane == 0) mbar_arrive(tempty_bar + acc);
     }
   }
@@ -366,8 +376,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 //               bytes of both CTAs are counted on the LEADER's full barrier.
 //   leader      warp 1 / one lane: tcgen05.mma.cta_group::2 for the pair; tcgen05.commit arrives
 //               on the empty barrier (and, per tile, the accumulator-full barrier) of BOTH CTAs.
-//   both CTAs   warps 2-5: epilogue of the CTA's own 128 accumulator rows; every epilogue warp
-//               of the pair arrives on the leader's accumulator-empty barrier (count 8).
+//   both CTAs   warps 2-9: epilogue of the CTA's own 128 accumulator rows; every epilogue warp
+//               of the pair arrives on the leader's accumulator-empty barrier (count 16).
 template <int BN>
 struct PairCfg {
   static constexpr int STAGES = 6;
@@ -389,7 +399,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;
-  float* sbias = reinterpret_cast<float*>(epi_stage + 4 * EPI_WARP_BYTES);
+  float* sbias = reinterpret_cast<float*>(epi_stage + EPI_WARPS * EPI_WARP_BYTES);
   float* sscale = sbias + 256;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + EPI_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + C::STAGES;
@@ -410,7 +420,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar + a, 1);
-      mbar_init(tempty_bar + a, 8);  // 4 epilogue warps of each CTA; only the leader's copy is used
+      mbar_init(tempty_bar + a, 2 * EPI_WARPS);  // the epilogue warps of both CTAs; only the leader's copy is used
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -490,8 +500,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const int m0 = (tile / tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
       stage_tile_vectors<BN, FLAGS>(sbias, sscale, flags, bias, colscale, n0);
       mbar_wait(tfull_bar + acc, acc_phase, abort_flag, err, SITE_TMEM_FULL);
-      epilogue_tile<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp & 3) * EPI_WARP_BYTES, sbias, sscale, warp, lane,
-                               m0, n0, M, out, ldo, flags, residual);
+      epilogue_tile<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp - 2) * EPI_WARP_BYTES, sbias, sscale, warp,
+                               (warp - 2) >> 2, lane, m0, n0, M, out, ldo, flags, residual);
       if (lane == 0) {
         if (leader) mbar_arrive(tempty_bar + acc);
         else mbar_arrive_cluster(mapa_u32(smem_u32(tempty_bar + acc), 0));

@@ -90,6 +90,13 @@ int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
                    __nv_bfloat16* ctx, int B, int S, int heads, cudaStream_t stream);
 int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,
                   int S, int heads, cudaStream_t stream);
+// tcgen05 variant of attention_bf16 (attention_tc.cu): Q, K, V tiles arrive by TMA through `tm_qkv`,
+// a map over the [rows, 3H] projection output made by make_tmap_qkv.  attention_use_tc says which
+// of the two kernels a forward pass of padded length S takes (CUDABERT_ATTENTION=tc|mma forces one).
+bool attention_use_tc(int S);
+bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H);
+int attention_bf16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
+                      __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int* err_flag, cudaStream_t stream);
 // kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none); mask null => S.
 // row_start (may be null): exclusive prefix sum of the sequence lengths (a length of 0 counts as S),
 // B + 1 entries, the last one being the number of packed rows.

@@ -319,7 +319,8 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
     bool ok = make_tmap_bf16_kmajor(&tm_x_, xa_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
               make_tmap_bf16_kmajor(&tm_x1_, x1a_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
               make_tmap_bf16_kmajor(&tm_ctx_, ctx_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
-              make_tmap_bf16_kmajor(&tm_z_, z_, rows, F_, static_cast<uint64_t>(F_) * 2, 128);
+              make_tmap_bf16_kmajor(&tm_z_, z_, rows, F_, static_cast<uint64_t>(F_) * 2, 128) &&
+              make_tmap_qkv(&tm_qkv_, qkv_, rows, H_);
     if (!ok) return fail(2, "cuTensorMapEncodeTiled failed for an activation buffer");
   }
   if (h_in_) cudaFreeHost(h_in_);
@@ -442,8 +443,13 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
     const LayerWeights& w = layer_[l];
     if (!dense(w.qkv, xa_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) return false;
     if (lowp) {
-      CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_, rs,
-                                             static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, stream_));
+      if (attention_use_tc(S)) {
+        CB_LAUNCH(KC_ATTENTION, attention_bf16_tc(&tm_qkv_, d_mask, kv_len_, rs, static_cast<__nv_bfloat16*>(ctx_), B, S,
+                                                  heads_, num_sms_, err_dev_, stream_));
+      } else {
+        CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_, rs,
+                                               static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, stream_));
+      }
       // y = ctx.Wo + bo in fp16; x1 = LN(y + x) with the add in fp32 inside the LayerNorm kernel
       if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, T, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_ATTN_OUT))
         return false;

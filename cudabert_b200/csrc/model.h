@@ -136,7 +136,7 @@ class Model {
   void* y_ = nullptr;  // dense outputs before the residual add: fp16 (bf16 / fp8 modes) or fp32 sums (fp32 mode)
   void *xa_ = nullptr, *x1a_ = nullptr, *ctx_ = nullptr, *qkv_ = nullptr, *z_ = nullptr;
   float *pooled_ = nullptr, *probs_ = nullptr;
-  CUtensorMap tm_x_, tm_x1_, tm_ctx_, tm_z_;
+  CUtensorMap tm_x_, tm_x1_, tm_ctx_, tm_z_, tm_qkv_;
 
   // pinned staging
   int* h_in_ = nullptr;

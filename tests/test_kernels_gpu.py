@@ -126,9 +126,9 @@ def _mask(B, S, mode, g):
     return m.contiguous()
 
 
-@pytest.mark.parametrize("bf16", [1, 0])
+@pytest.mark.parametrize("bf16", [2, 1, 0])
 @pytest.mark.parametrize("B,S,heads", [(2, 128, 12), (3, 200, 16), (1, 512, 16), (4, 17, 12), (2, 1, 12), (5, 64, 16),
-                                       (2, 65, 12)])
+                                       (2, 65, 12), (3, 129, 16), (2, 300, 12)])
 @pytest.mark.parametrize("mode", ["prefix", "none", "holes", "zero_row", "full"])
 def test_attention(pybert, bf16, B, S, heads, mode):
     g = torch.Generator(device="cuda").manual_seed(B * 1000 + S + heads)
