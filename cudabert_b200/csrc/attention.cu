@@ -44,6 +44,7 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   uint8_t* sQ = sV + static_cast<size_t>(R) * 128;
   const int nwarps = blockDim.x >> 5;
   float* sBias = reinterpret_cast<float*>(sQ + nwarps * 2048);
+  __shared__ unsigned int s_biased;  // bit t: 64-key tile t holds a masked key or lies partly beyond klen
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x, b = blockIdx.y;
@@ -69,14 +70,20 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   }
   cp_async_commit();
   const int* mrow = mask ? mask + static_cast<size_t>(b) * S : nullptr;
+  if (tid == 0) s_biased = 0u;
+  __syncthreads();
+  unsigned int bits = 0u;
   for (int key = tid; key < krows; key += blockDim.x) {
     float v = 0.f;
     if (key >= klen) v = -INFINITY;
     else if (use_mask && mrow[key] == 0) v = -10000.0f * LOG2E;
     sBias[key] = v;
+    if (v != 0.f) bits |= 1u << (key >> 6);
   }
+  if (bits) atomicOr(&s_biased, bits);
   cp_async_wait<0>();
   __syncthreads();
+  const unsigned int biased = s_biased;
 
   uint8_t* myQ = sQ + warp * 2048;
   const float scale = 0.125f * LOG2E;
@@ -120,17 +127,30 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
           mma_bf16_16816(s[2 * nb + 1], qf[kk], kf[2], kf[3]);
         }
       }
-      // scale + mask bias (log2 domain), running max
+      // running max of the scores in the log2 domain.  A tile whose keys are all valid keeps the
+      // raw dot products (the scale is folded into the exponential's multiply-add below); any
+      // other tile gets scale and mask bias applied here.
+      const bool plain = ((biased >> t) & 1u) == 0u;
       float tmax[2] = {-INFINITY, -INFINITY};
+      if (plain) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float2 bb = *reinterpret_cast<const float2*>(sBias + k0 + i * 8 + 2 * (lane & 3));
-        s[i][0] = fmaf(s[i][0], scale, bb.x);
-        s[i][1] = fmaf(s[i][1], scale, bb.y);
-        s[i][2] = fmaf(s[i][2], scale, bb.x);
-        s[i][3] = fmaf(s[i][3], scale, bb.y);
-        tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
-        tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
+        for (int i = 0; i < 8; ++i) {
+          tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
+          tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
+        }
+        tmax[0] *= scale;  // scale > 0: max(scale * s) = scale * max(s)
+        tmax[1] *= scale;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 bb = *reinterpret_cast<const float2*>(sBias + k0 + i * 8 + 2 * (lane & 3));
+          s[i][0] = fmaf(s[i][0], scale, bb.x);
+          s[i][1] = fmaf(s[i][1], scale, bb.y);
+          s[i][2] = fmaf(s[i][2], scale, bb.x);
+          s[i][3] = fmaf(s[i][3], scale, bb.y);
+          tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
+          tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
+        }
       }
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
@@ -142,17 +162,18 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
       for (int r = 0; r < 2; ++r) {
         m_new[r] = fmaxf(m_run[r], tmax[r]);
         // tile 0 always holds key 0 with a finite bias, so m_new is finite from the first tile on
-        alpha[r] = exp2f(m_run[r] - m_new[r]);
+        alpha[r] = ex2_approx(m_run[r] - m_new[r]);
         m_run[r] = m_new[r];
         l_run[r] *= alpha[r];
       }
       uint32_t pf[4][4];
+      const float e_scale = plain ? scale : 1.0f;  // p = 2^(s * e_scale - m)
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float p0 = exp2f(s[i][0] - m_new[0]);
-        const float p1 = exp2f(s[i][1] - m_new[0]);
-        const float p2 = exp2f(s[i][2] - m_new[1]);
-        const float p3 = exp2f(s[i][3] - m_new[1]);
+        const float p0 = ex2_approx(fmaf(s[i][0], e_scale, -m_new[0]));
+        const float p1 = ex2_approx(fmaf(s[i][1], e_scale, -m_new[0]));
+        const float p2 = ex2_approx(fmaf(s[i][2], e_scale, -m_new[1]));
+        const float p3 = ex2_approx(fmaf(s[i][3], e_scale, -m_new[1]));
         l_run[0] += p0 + p1;
         l_run[1] += p2 + p3;
         pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);

@@ -72,12 +72,6 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16_bmn(int m, int n) {
   return umma_idesc_bf16(m, n) | (1u << 16);
 }
 
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 struct ItemInfo {
   int b, h, q0, first, nq, klen, nblocks;
   bool use_mask, live;
@@ -289,11 +283,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float x = __uint_as_float(v[ch][i]) * scale;
-            v[ch][i] = __float_as_uint(x);
-            mx4[i & 3] = fmaxf(mx4[i & 3], x);
-          }
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[ch][i]));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) mx4[q] *= scale;  // the scale itself is folded into the exponential below
       } else {
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch)
@@ -318,7 +310,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       if (j == 0) {
         m_run = mx;  // finite: key 0 of block 0 is never masked with -inf
       } else if (mx > m_run + 8.0f) {
-        alpha = fast_exp2(m_run - mx);
+        alpha = ex2_approx(m_run - mx);
         m_run = mx;
       }
       const float m_new = m_run;
@@ -344,12 +336,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       }
       // P = exp2(x - max) -> bf16 -> swizzled A-operand tile
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float e_scale = plain ? scale : 1.0f;  // plain blocks still hold the raw dot products
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         float p[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          p[i] = fast_exp2(__uint_as_float(v[ch][i]) - m_new);
+          p[i] = ex2_approx(fmaf(__uint_as_float(v[ch][i]), e_scale, -m_new));
           l4[i & 3] += p[i];
         }
 #pragma unroll
