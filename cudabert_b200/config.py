@@ -39,6 +39,9 @@ class Engin_Config(object):
         current_path = os.path.abspath(__file__)
         self.cubert_pth = os.path.abspath(os.path.dirname(current_path)) + "/cuda_bert"
 
+        "Bucket and trim batches in the library's native batcher (False: the Python classes)."
+        self.native_batcher = True
+
         "fp32 | bf16 | fp8; None takes the environment variable CUDABERT_PRECISION (default bf16)."
         self.precision = None
 

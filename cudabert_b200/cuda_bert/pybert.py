@@ -111,6 +111,33 @@ classify = lib.Cuda_Classify
 classify.argtypes = [c_void_p, _f32, _i32, _i32, c_int, c_int, c_int, _OptionalI32]
 classify.restype = None
 
+# length-bucketing batcher of the engine's reader stage (host only)
+from ctypes import c_longlong as _c_ll
+batcher_create = lib.cudabert_batcher_create
+batcher_create.argtypes = [_i32, c_int, c_int, c_int]
+batcher_create.restype = c_void_p
+batcher_destroy = lib.cudabert_batcher_destroy
+batcher_destroy.argtypes = [c_void_p]
+batcher_destroy.restype = None
+batcher_put = lib.cudabert_batcher_put
+batcher_put.argtypes = [c_void_p, _c_ll, _i32, _i32, _i32, c_int]
+batcher_put.restype = c_int
+batcher_flush = lib.cudabert_batcher_flush
+batcher_flush.argtypes = [c_void_p]
+batcher_flush.restype = c_int
+batcher_ready = lib.cudabert_batcher_ready
+batcher_ready.argtypes = [c_void_p]
+batcher_ready.restype = c_int
+batcher_pending = lib.cudabert_batcher_pending
+batcher_pending.argtypes = [c_void_p]
+batcher_pending.restype = _c_ll
+batcher_next = lib.cudabert_batcher_next
+batcher_next.argtypes = [c_void_p, POINTER(c_int), POINTER(c_int), POINTER(_c_ll)]
+batcher_next.restype = c_int
+batcher_pop = lib.cudabert_batcher_pop
+batcher_pop.argtypes = [c_void_p, ndpointer(numpy.int64, flags="C_CONTIGUOUS"), _i32, _i32, _i32]
+batcher_pop.restype = c_int
+
 hidden_size = lib.cudabert_hidden_size
 hidden_size.argtypes = [c_void_p]
 hidden_size.restype = c_int

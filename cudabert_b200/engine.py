@@ -10,7 +10,8 @@
 Stages, one OS process each as in the reference (engine.py:385-397): a reader that tokenises,
 buckets lines by valid length (boundaries [0, start_split, start_split+split_size, ..., end_split,
 max_seq_length], engine.py:225-232) and right-trims every batch to its own longest line
-(utils.py:3-13); one worker per GPU id in ``config.gpu`` holding an independent replica (batch
+(utils.py:3-13); the bucketing itself runs in the library's native
+batcher unless ``config.native_batcher`` is False; one worker per GPU id in ``config.gpu`` holding an independent replica (batch
 sharding, no collective: workers pull whole batches from a shared queue); a writer that restores
 the input order in a sliding window and applies back-pressure through ``alert_size``
 (engine.py:303-375).
@@ -127,6 +128,67 @@ class queue_manager(object):
         return self.input_queue.get(timeout=timeout)
 
 
+class native_queue_manager(queue_manager):
+    """ queue_manager whose buckets live in the library's native batcher (csrc/batcher.cc): the
+    same put / enqueue / force_enqueue / get interface and the same batches, batch order and
+    right-trimming, without the per-line Python list handling and the per-batch numpy stacking. """
+    def __init__(self, seq_length_split, list_gpu, logger, batchsize, ctx=None, max_seq_length=512):
+        import numpy as np
+        from .cuda_bert import pybert
+        ctx = ctx or mp.get_context()
+        self._np = np
+        self._lib = pybert
+        self.boardlines = seq_length_split
+        self.num_containers = len(seq_length_split) - 1
+        self.output_queue = ctx.Queue()
+        self.force_queue = ctx.Queue(1)
+        self.input_queue = ctx.Queue(10)
+        self.logger = logger
+        self.batchsize = batchsize
+        self.max_seq_length = max_seq_length
+        bounds = np.ascontiguousarray(seq_length_split, dtype=np.int32)
+        self._batcher = pybert.batcher_create(bounds, len(bounds), batchsize, max_seq_length)
+        if not self._batcher:
+            raise ValueError("bad bucket boundaries %r / batch size %r" % (seq_length_split, batchsize))
+        self._lines = {}   # line number -> Tagged_line, until its batch leaves
+
+    def __del__(self):
+        if getattr(self, "_batcher", None):
+            self._lib.batcher_destroy(self._batcher)
+            self._batcher = None
+
+    def _row(self, values):
+        a = self._np.ascontiguousarray(values, dtype=self._np.int32)
+        return a[:self.max_seq_length] if a.shape[0] > self.max_seq_length else a
+
+    def put(self, line):
+        ids, seg, mask = self._row(line.input_ids), self._row(line.segment_ids), self._row(line.input_mask)
+        n = min(ids.shape[0], seg.shape[0], mask.shape[0])
+        if self._lib.batcher_put(self._batcher, line.num_line, ids, seg, mask, n) < 0:
+            raise ValueError("line %d: the batcher rejected a row of %d entries" % (line.num_line, n))
+        self._lines[line.num_line] = line
+        self.enqueue(False)
+
+    def force_enqueue(self):
+        self._lib.batcher_flush(self._batcher)
+        while self.enqueue(True) != -1:
+            pass
+
+    def enqueue(self, is_force):
+        from ctypes import byref, c_int, c_longlong
+        np = self._np
+        rows, seq, first = c_int(0), c_int(0), c_longlong(0)
+        if self._lib.batcher_next(self._batcher, byref(rows), byref(seq), byref(first)) != 1:
+            return -1
+        index = np.empty(rows.value, np.int64)
+        tensor = [np.empty((rows.value, seq.value), np.int32) for _ in range(3)]
+        got = self._lib.batcher_pop(self._batcher, index, tensor[0], tensor[1], tensor[2])
+        assert got == rows.value
+        lines = [self._lines.pop(int(i)) for i in index]
+        self.input_queue.put(Batch_Packed(lines, tensor))   # bounded queue: blocks while the GPUs are busy
+        return int(first.value)
+
+
 class Engine(object):
     def __init__(self, config):
         self.handle = None
@@ -148,8 +210,12 @@ class Engine(object):
         assert(self.output_line is not None)
         assert(self.config.gpu != [])
         self._ctx = mp.get_context(getattr(self.config, "mp_start_method", None))
-        self.handle = queue_manager(self.seq_length_split, self.config.gpu,
-                                    self.logger, self.config.batch_size, self._ctx)
+        if getattr(self.config, "native_batcher", True):
+            self.handle = native_queue_manager(self.seq_length_split, self.config.gpu, self.logger,
+                                               self.config.batch_size, self._ctx, self.config.max_seq_length)
+        else:
+            self.handle = queue_manager(self.seq_length_split, self.config.gpu,
+                                        self.logger, self.config.batch_size, self._ctx)
 
     def set_cuda_model(self, cuda_model):
         self.cuda_model = cuda_model

@@ -108,6 +108,29 @@ CUDABERT_API void cudabert_profile_enable(void* model, int on);
 CUDABERT_API void cudabert_profile_reset(void* model);
 CUDABERT_API int cudabert_profile_get(void* model, int kernel_class, double* total_ms, long* launches);
 
+/* ---- length-bucketing batcher of the file-to-file engine (host only, no CUDA call) ----
+ * Replaces the reference's Python reader-side batching: batch_container and queue_manager.put /
+ * enqueue / force_enqueue (engine.py:12-130), optimize_batch (utils.py:3-13) and the valid
+ * length of a line (utils.py:49-56).  boundaries[0..n): bucket q takes valid lengths in
+ * (boundaries[q], boundaries[q+1]], the last bucket also everything longer. */
+CUDABERT_API void* cudabert_batcher_create(const int* boundaries, int n_boundaries, int batch_size, int max_seq_length);
+CUDABERT_API void cudabert_batcher_destroy(void* batcher);
+/* Add one tokenised line (three int32 rows of n <= max_seq_length entries).  Returns its valid
+ * length (1 + index of the last mask entry equal to 1; n if there is none), -1 on a bad argument. */
+CUDABERT_API int cudabert_batcher_put(void* batcher, long long line_index, const int* ids, const int* seg, const int* mask,
+                                      int n);
+/* Turn every partly filled bucket into a ready batch; returns the number of ready batches. */
+CUDABERT_API int cudabert_batcher_flush(void* batcher);
+CUDABERT_API int cudabert_batcher_ready(void* batcher);
+/* Lines put but not yet popped. */
+CUDABERT_API long long cudabert_batcher_pending(void* batcher);
+/* Shape of the batch the next pop returns (the ready batch with the smallest first line number):
+ * 1 and rows / seq / first_line filled, 0 if no batch is ready. */
+CUDABERT_API int cudabert_batcher_next(void* batcher, int* rows, int* seq, long long* first_line);
+/* Pop that batch: line_index[rows], ids / seg / mask [rows, seq] right-trimmed to the batch's longest
+ * line.  Returns rows, 0 if no batch is ready. */
+CUDABERT_API int cudabert_batcher_pop(void* batcher, long long* line_index, int* ids, int* seg, int* mask);
+
 /* ---- single kernels on device buffers (stream 0, synchronous), for per-kernel parity tests ---- */
 
 /* out[M,N] = epilogue(A[M,K] bf16 (row stride lda elements) x W[N,K]^T bf16); flags: 1 bias, 2 GELU,

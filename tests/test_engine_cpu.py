@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from cudabert_b200.config import Engin_Config
-from cudabert_b200.engine import Engine, batch_container, queue_manager
+from cudabert_b200.engine import Engine, batch_container, native_queue_manager, queue_manager
 from cudabert_b200.utils import Tagged_line, optimize_batch
 
 MAX_SEQ = 64
@@ -78,12 +78,14 @@ def _config(gpus):
     return c
 
 
+@pytest.mark.parametrize("native", [True, False])
 @pytest.mark.parametrize("gpus,alert", [([0], 1000000), ([0, 1], 1000000), ([0, 1], 16)])
-def test_engine_orders_output_and_shards_batches(tmp_path, gpus, alert):
+def test_engine_orders_output_and_shards_batches(tmp_path, gpus, alert, native):
     src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
     lines = _write_input(src, 301)
     cfg = _config(gpus)
     cfg.alert_size = alert
+    cfg.native_batcher = native
     eng = Engine(cfg)
     eng.set_cuda_model(FakeReplica)
     eng.set_finetune_layer(Head)
@@ -127,3 +129,66 @@ def test_generate_splits_and_bucketing():
     bc.put(tl2)
     assert len(bc.prepare) == 1 and bc.min_index == 3
     assert bc.pop().tensor[0].shape == (2, 3) and bc.min_index > 10 ** 9
+
+
+class _ListQueue:
+    """Unbounded stand-in for the managers' input queue, so that one process can drive them."""
+    def __init__(self):
+        self.items = []
+
+    def put(self, x):
+        self.items.append(x)
+
+
+@pytest.mark.parametrize("seed,batch,flush_every", [(0, 8, 0), (1, 3, 37), (2, 1, 0), (3, 16, 5)])
+def test_native_batcher_matches_the_python_buckets(seed, batch, flush_every):
+    """Same stream into the Python buckets (the reference's algorithm, engine.py:12-130) and into
+    the native batcher: identical batches (line numbers, trimmed arrays) in identical order,
+    including forced flushes in mid-stream and lines whose mask has holes (a mask without any 1
+    makes the reference's own trimming fail; the native batcher keeps such a row whole)."""
+    rng = np.random.default_rng(seed)
+    bounds = [0, 8, 16, 24, 40, MAX_SEQ]
+    managers = [queue_manager(bounds, [0], None, batch), native_queue_manager(bounds, [0], None, batch, None, MAX_SEQ)]
+    for m in managers:
+        m.input_queue = _ListQueue()
+    for i in range(400):
+        n = int(rng.integers(1, MAX_SEQ + 1))
+        ids = rng.integers(1, 1000, MAX_SEQ).tolist()
+        seg = rng.integers(0, 2, MAX_SEQ).tolist()
+        mask = [1] * n + [0] * (MAX_SEQ - n)
+        if i % 41 == 7 and n > 1:
+            mask[n // 2] = 0                      # a hole: the length is still set by the last 1
+        for a in (ids, seg):
+            a[n:] = [0] * (MAX_SEQ - n)
+        for m in managers:
+            m.put(Tagged_line(i, "line %d" % i, list(ids), list(mask), list(seg)))
+            if flush_every and i % flush_every == flush_every - 1:
+                m.force_enqueue()
+    for m in managers:
+        m.force_enqueue()
+    py, nat = (m.input_queue.items for m in managers)
+    assert len(py) == len(nat) and sum(len(b.lines_list) for b in nat) == 400
+    for a, b in zip(py, nat):
+        assert [l.num_line for l in a.lines_list] == [l.num_line for l in b.lines_list]
+        assert [l.line_data for l in a.lines_list] == [l.line_data for l in b.lines_list]
+        for x, y in zip(a.tensor, b.tensor):
+            assert x.dtype == y.dtype == np.int32 and x.shape == y.shape
+            np.testing.assert_array_equal(x, y)
+
+
+def test_native_batcher_rejects_bad_arguments():
+    from cudabert_b200.cuda_bert import pybert
+    good = np.array([0, 8, 16], np.int32)
+    assert not pybert.batcher_create(np.array([0, 8, 4], np.int32), 3, 4, 16)     # not ascending
+    assert not pybert.batcher_create(good, 1, 4, 16) and not pybert.batcher_create(good, 3, 0, 16)
+    b = pybert.batcher_create(good, 3, 2, 16)
+    row = np.ones(16, np.int32)
+    assert pybert.batcher_put(b, 0, row, row, row, 17) == -1 and pybert.batcher_put(b, 0, row, row, row, 0) == -1
+    assert pybert.batcher_put(b, 0, row, row, np.zeros(16, np.int32), 16) == 16   # no 1 in the mask: whole row
+    assert pybert.batcher_ready(b) == 0 and pybert.batcher_pending(b) == 1
+    assert pybert.batcher_flush(b) == 1
+    idx = np.zeros(2, np.int64)
+    out = [np.zeros((2, 16), np.int32) for _ in range(3)]
+    assert pybert.batcher_pop(b, idx, *out) == 1 and pybert.batcher_pop(b, idx, *out) == 0
+    assert pybert.batcher_pending(b) == 0
+    pybert.batcher_destroy(b)
