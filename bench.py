@@ -215,7 +215,9 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     dims = synth.model_dims(True)
     B, S = WL["batch"], WL["seq"]
     wdir = weights_dir(local_rank, barrier)
+    t_load = time.perf_counter()
     model = pybert.load_model(True, wdir, dev, B, S, precision="bf16", num_layers=args.layers)
+    load_seconds = time.perf_counter() - t_load   # .npy directory -> device-resident bf16 K-major weights
     if args.layers:
         dims = dict(dims, layers=min(args.layers, dims["layers"]))
     C = pybert.num_classes(model)
@@ -348,6 +350,7 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
         "kernels": kernels,
         "attention_tflops": (attn_exec / (attn_ms / 1e3) / 1e12) if attn_ms else None,
         "layernorm_gbs": (ln_bytes * ln_n / (ln_ms / 1e3) / 1e9) if ln_ms else None,
+        "weight_load_seconds": round(load_seconds, 3),
         "cpu_baseline": cpu,
     }
     if args.layers:

@@ -279,14 +279,15 @@ int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, 
 int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads) {
   if (!qkv_dev || !ctx_dev || B <= 0 || S <= 0 || heads <= 0) return 1;
   int* kv = nullptr;
-  if (cudaMalloc(&kv, (static_cast<size_t>(B) + 1) * sizeof(int)) != cudaSuccess) return 2;
+  if (cudaMalloc(&kv, (3 * static_cast<size_t>(B) + 1) * sizeof(int)) != cudaSuccess) return 2;
   int* err = kv + B;
+  int* sched = bf16 == 3 ? kv + B + 1 : nullptr;  // 2 B entries
   cudaMemset(err, 0, sizeof(int));
   int rc = 0;
-  if (cb::row_layout(mask_dev, kv, nullptr, B, S, nullptr) < 0) rc = 3;
+  if (cb::row_layout(mask_dev, kv, nullptr, sched, B, S, nullptr) < 0) rc = 3;
   if (!rc) {
     int n;
-    if (bf16 == 2) {  // tcgen05 kernel
+    if (bf16 == 2 || bf16 == 3) {  // tcgen05 kernel, persistent mma.sync kernel: both read K and V by TMA
       CUtensorMap tm;
       int dev = 0, sms = 148;
       cudaGetDevice(&dev);
@@ -295,8 +296,12 @@ int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, voi
         cudaFree(kv);
         return 2;
       }
-      n = cb::attention_bf16_tc(&tm, mask_dev, kv, nullptr, static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, sms, err,
-                                nullptr);
+      if (bf16 == 2)
+        n = cb::attention_bf16_tc(&tm, mask_dev, kv, nullptr, static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, sms,
+                                  err, nullptr);
+      else
+        n = cb::attention_bf16_persist(&tm, static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr, sched,
+                                       static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, sms, err, nullptr);
     } else if (bf16) {
       n = cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
                              static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr);

@@ -29,6 +29,150 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
   return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
+// One 16-query block of one (sequence, head) against the sequence's keys and values resident in
+// shared memory (`sK`, `sV`: 128-byte rows, chunk c of row r at c ^ (r & 7)): QK^T -> scale + mask
+// bias -> online softmax -> P.V over 64-key tiles, then a coalesced store of the 16 x 64 block.
+// Run by one warp; `myQ` is the warp's own 2 KB staging buffer.  `base` points at the first Q
+// element of the sequence's first row (row stride `ld`), `out_base` at its first output element
+// (row stride `H`).  Bit t of `biased` says that key tile t needs the bias in `sBias`.
+__device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, const uint8_t* __restrict__ sV,
+                                              const float* __restrict__ sBias, unsigned int biased,
+                                              uint8_t* __restrict__ myQ, const __nv_bfloat16* __restrict__ base,
+                                              int ld, __nv_bfloat16* __restrict__ out_base, int H, int q0, int nq,
+                                              int ktiles, int lane) {
+  const float scale = 0.125f * LOG2E;
+  // stage the 16 x 64 Q block: lane l moves chunk l % 8 of rows l / 8 + 4 i
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = (lane >> 3) + 4 * i, c = lane & 7;
+    uint4 t = make_uint4(0u, 0u, 0u, 0u);
+    if (q0 + r < nq) t = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + r) * ld + c * 8));
+    *reinterpret_cast<uint4*>(myQ + swz(r, c)) = t;
+  }
+  __syncwarp();
+  uint32_t qf[4][4];
+#pragma unroll
+  for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(myQ + swz(lane & 15, kk * 2 + (lane >> 4))));
+
+  float o[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+
+  for (int t = 0; t < ktiles; ++t) {
+    const int k0 = t << 6;
+    // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    const int mid = lane >> 3;
+#pragma unroll
+    for (int nb = 0; nb < 4; ++nb) {
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        uint32_t kf[4];
+        ldmatrix_x4(kf, smem_u32(sK + swz(k0 + nb * 16 + (mid >> 1) * 8 + (lane & 7), kk * 2 + (mid & 1))));
+        mma_bf16_16816(s[2 * nb], qf[kk], kf[0], kf[1]);
+        mma_bf16_16816(s[2 * nb + 1], qf[kk], kf[2], kf[3]);
+      }
+    }
+    // running max of the scores in the log2 domain.  A tile whose keys are all valid keeps the
+    // raw dot products (the scale is folded into the exponential's multiply-add below); any
+    // other tile gets scale and mask bias applied here.
+    const bool plain = ((biased >> t) & 1u) == 0u;
+    float tmax[2] = {-INFINITY, -INFINITY};
+    if (plain) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
+        tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
+      }
+      tmax[0] *= scale;  // scale > 0: max(scale * s) = scale * max(s)
+      tmax[1] *= scale;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 bb = *reinterpret_cast<const float2*>(sBias + k0 + i * 8 + 2 * (lane & 3));
+        s[i][0] = fmaf(s[i][0], scale, bb.x);
+        s[i][1] = fmaf(s[i][1], scale, bb.y);
+        s[i][2] = fmaf(s[i][2], scale, bb.x);
+        s[i][3] = fmaf(s[i][3], scale, bb.y);
+        tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
+        tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+    }
+    float alpha[2], m_new[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      m_new[r] = fmaxf(m_run[r], tmax[r]);
+      // tile 0 always holds key 0 with a finite bias, so m_new is finite from the first tile on
+      alpha[r] = ex2_approx(m_run[r] - m_new[r]);
+      m_run[r] = m_new[r];
+      l_run[r] *= alpha[r];
+    }
+    uint32_t pf[4][4];
+    const float e_scale = plain ? scale : 1.0f;  // p = 2^(s * e_scale - m)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float p0 = ex2_approx(fmaf(s[i][0], e_scale, -m_new[0]));
+      const float p1 = ex2_approx(fmaf(s[i][1], e_scale, -m_new[0]));
+      const float p2 = ex2_approx(fmaf(s[i][2], e_scale, -m_new[1]));
+      const float p3 = ex2_approx(fmaf(s[i][3], e_scale, -m_new[1]));
+      l_run[0] += p0 + p1;
+      l_run[1] += p2 + p3;
+      pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+    // O += P V : 4 key steps of 16, 4 pairs of 8-wide d tiles
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int db = 0; db < 4; ++db) {
+        uint32_t vf[4];
+        ldmatrix_x4_trans(vf, smem_u32(sV + swz(k0 + j * 16 + (mid & 1) * 8 + (lane & 7), db * 2 + (mid >> 1))));
+        mma_bf16_16816(o[2 * db], pf[j], vf[0], vf[1]);
+        mma_bf16_16816(o[2 * db + 1], pf[j], vf[2], vf[3]);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
+  // stage the 16 x 64 output block in the Q buffer, then store it with 16-byte row-contiguous pieces
+  __syncwarp();
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    // columns i*8 + 2*t4, +1 of rows g and g + 8: chunk i, byte offset 4 * t4 inside the chunk
+    *reinterpret_cast<uint32_t*>(myQ + swz(g, i) + 4 * t4) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+    *reinterpret_cast<uint32_t*>(myQ + swz(g + 8, i) + 4 * t4) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = (lane >> 3) + 4 * i, c = lane & 7;
+    if (q0 + r < nq)
+      *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(q0 + r) * H + c * 8) =
+          *reinterpret_cast<const uint4*>(myQ + swz(r, c));
+  }
+}
+
 // One CTA per (batch row, head).  All keys and values the row can attend to (kv_len[b], rounded
 // up to 16) are loaded into shared memory once; then every warp takes 16-query blocks
 // (warp, warp + nwarps, ...) and runs QK^T -> scale + mask bias -> online softmax -> P.V over 64-key
@@ -86,141 +230,193 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   const unsigned int biased = s_biased;
 
   uint8_t* myQ = sQ + warp * 2048;
-  const float scale = 0.125f * LOG2E;
   const int qblocks = (nq + 15) >> 4;
-  for (int qb = warp; qb < qblocks; qb += nwarps) {
-    const int q0 = qb * 16;
-    // stage the 16 x 64 Q block: lane l moves chunk l % 8 of rows l / 8 + 4 i
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = (lane >> 3) + 4 * i, c = lane & 7;
-      uint4 t = make_uint4(0u, 0u, 0u, 0u);
-      if (q0 + r < nq) t = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + r) * ld + c * 8));
-      *reinterpret_cast<uint4*>(myQ + swz(r, c)) = t;
-    }
-    __syncwarp();
-    uint32_t qf[4][4];
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(myQ + swz(lane & 15, kk * 2 + (lane >> 4))));
+  __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
+  for (int qb = warp; qb < qblocks; qb += nwarps)
+    attend_qblock(sK, sV, sBias, biased, myQ, base, ld, out_base, H, qb * 16, nq, ktiles, lane);
+}
 
-    float o[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY};
-    float l_run[2] = {0.f, 0.f};
+// ---------------------------------------------------------------- persistent variant
+// The same arithmetic as attention_bf16_kernel (attend_qblock), scheduled differently.  With one
+// CTA per (sequence, head) a short sequence leaves most of the CTA's warps without a query block
+// while they still hold their registers, and every CTA first waits for its keys and values before
+// any warp computes.  Here one persistent CTA per SM keeps 15 consumer warps busy and a producer
+// warp several items ahead:
+//   items      (sequence, head) pairs in descending order of sequence length (`sched`, made by
+//              row_layout), dealt round-robin to the CTAs: every CTA gets the same mix of long and
+//              short items, the long ones first, and nothing about the order has to be fetched
+//              with an atomic, so the producer can look up a batch of 32 items' lengths and row
+//              offsets in one go, one item per lane;
+//   producer   per item: waits until the consumers have left the slot, writes the per-key bias
+//              (reading the mask only for a sequence that has masked keys below its last valid
+//              one), and loads the item's K and V rows with TMA box copies (64 rows x 128 bytes,
+//              128-byte swizzle = the layout swz() describes) that complete on the slot's `full`
+//              mbarrier;
+//   consumers  wait for `full`, then draw 16-query blocks of the item from a shared-memory
+//              counter until none is left, arrive on `empty` and move to the next slot, so a warp
+//              that finds no block in a short item is already working on the next one.
+// The number of slots is what fits: 3 for S = 200, up to 8 for short sequences.  Rows of a K / V
+// box beyond the sequence's last key hold whatever follows in the buffer (finite activations of
+// other rows, or zero fill beyond the tensor); their bias is -inf, so their probability is 0.
+constexpr int PA_CONSUMERS = 15;
+constexpr int PA_THREADS = (PA_CONSUMERS + 1) * 32;
+constexpr int PA_MAX_R = 384;  // two slots of R rows must fit in shared memory
+constexpr int PA_MAX_SLOTS = 8;
+constexpr int PA_TAIL_BYTES = 512;  // item records, mbarriers, abort flag
+constexpr size_t PA_SMEM_LIMIT = 232448;
+enum : int { SITE_PA_FULL = 21, SITE_PA_EMPTY = 22 };
 
-    for (int t = 0; t < ktiles; ++t) {
-      const int k0 = t << 6;
-      // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
-      float s[8][4];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-      const int mid = lane >> 3;
-#pragma unroll
-      for (int nb = 0; nb < 4; ++nb) {
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-          uint32_t kf[4];
-          ldmatrix_x4(kf, smem_u32(sK + swz(k0 + nb * 16 + (mid >> 1) * 8 + (lane & 7), kk * 2 + (mid & 1))));
-          mma_bf16_16816(s[2 * nb], qf[kk], kf[0], kf[1]);
-          mma_bf16_16816(s[2 * nb + 1], qf[kk], kf[2], kf[3]);
-        }
-      }
-      // running max of the scores in the log2 domain.  A tile whose keys are all valid keeps the
-      // raw dot products (the scale is folded into the exponential's multiply-add below); any
-      // other tile gets scale and mask bias applied here.
-      const bool plain = ((biased >> t) & 1u) == 0u;
-      float tmax[2] = {-INFINITY, -INFINITY};
-      if (plain) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
-          tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
-        }
-        tmax[0] *= scale;  // scale > 0: max(scale * s) = scale * max(s)
-        tmax[1] *= scale;
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float2 bb = *reinterpret_cast<const float2*>(sBias + k0 + i * 8 + 2 * (lane & 3));
-          s[i][0] = fmaf(s[i][0], scale, bb.x);
-          s[i][1] = fmaf(s[i][1], scale, bb.y);
-          s[i][2] = fmaf(s[i][2], scale, bb.x);
-          s[i][3] = fmaf(s[i][3], scale, bb.y);
-          tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
-          tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
-        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
-      }
-      float alpha[2], m_new[2];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        m_new[r] = fmaxf(m_run[r], tmax[r]);
-        // tile 0 always holds key 0 with a finite bias, so m_new is finite from the first tile on
-        alpha[r] = ex2_approx(m_run[r] - m_new[r]);
-        m_run[r] = m_new[r];
-        l_run[r] *= alpha[r];
-      }
-      uint32_t pf[4][4];
-      const float e_scale = plain ? scale : 1.0f;  // p = 2^(s * e_scale - m)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float p0 = ex2_approx(fmaf(s[i][0], e_scale, -m_new[0]));
-        const float p1 = ex2_approx(fmaf(s[i][1], e_scale, -m_new[0]));
-        const float p2 = ex2_approx(fmaf(s[i][2], e_scale, -m_new[1]));
-        const float p3 = ex2_approx(fmaf(s[i][3], e_scale, -m_new[1]));
-        l_run[0] += p0 + p1;
-        l_run[1] += p2 + p3;
-        pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
-        pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
-      }
-      // O += P V : 4 key steps of 16, 4 pairs of 8-wide d tiles
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-#pragma unroll
-        for (int db = 0; db < 4; ++db) {
-          uint32_t vf[4];
-          ldmatrix_x4_trans(vf, smem_u32(sV + swz(k0 + j * 16 + (mid & 1) * 8 + (lane & 7), db * 2 + (mid >> 1))));
-          mma_bf16_16816(o[2 * db], pf[j], vf[0], vf[1]);
-          mma_bf16_16816(o[2 * db + 1], pf[j], vf[2], vf[3]);
-        }
-      }
-    }
+struct PaItem {
+  int first, nq, ktiles, qblocks, h, done;
+  unsigned int biased;
+  int next_q;  // next query block to hand out
+};
 
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+constexpr size_t pa_smem_bytes(int R, int nslot) {
+  return static_cast<size_t>(nslot) * R * 260 + PA_CONSUMERS * 2048 + PA_TAIL_BYTES + 1024;
+}
+constexpr int pa_slots(int R) {
+  const size_t per_slot = static_cast<size_t>(R) * 260;
+  const size_t n = (PA_SMEM_LIMIT - PA_CONSUMERS * 2048 - PA_TAIL_BYTES - 1024) / per_slot;
+  return n > PA_MAX_SLOTS ? PA_MAX_SLOTS : static_cast<int>(n);
+}
+static_assert(pa_slots(PA_MAX_R) >= 2, "two slots must fit at the largest supported length");
+
+__global__ void __launch_bounds__(PA_THREADS, 1)
+attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const __nv_bfloat16* __restrict__ qkv,
+                              const int* __restrict__ mask, const int* __restrict__ kv_len,
+                              const int* __restrict__ row_start, const int* __restrict__ sched,
+                              __nv_bfloat16* __restrict__ ctx, int B, int S, int heads, int R, int nslot,
+                              int* __restrict__ err) {
+  extern __shared__ uint8_t pa_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pa_smem_raw) + 1023) & ~uintptr_t(1023));
+  const size_t slot_bytes = static_cast<size_t>(R) * 256;  // K then V of one item
+  uint8_t* sQ = smem + nslot * slot_bytes;
+  float* sBiasAll = reinterpret_cast<float*>(sQ + PA_CONSUMERS * 2048);
+  uint8_t* tail = reinterpret_cast<uint8_t*>(sBiasAll + static_cast<size_t>(nslot) * R);
+  PaItem* items = reinterpret_cast<PaItem*>(tail);              // [PA_MAX_SLOTS], 32 bytes each
+  uint64_t* full = reinterpret_cast<uint64_t*>(tail + 256);     // [PA_MAX_SLOTS]
+  uint64_t* empty = full + PA_MAX_SLOTS;                        // [PA_MAX_SLOTS]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + PA_MAX_SLOTS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < nslot; ++i) {
+      mbar_init(full + i, 1);
+      mbar_init(empty + i, PA_CONSUMERS);
     }
-    const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
-    // stage the 16 x 64 output block in the Q buffer, then store it with 16-byte row-contiguous pieces
-    __syncwarp();
-    const int g = lane >> 2, t4 = lane & 3;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      // columns i*8 + 2*t4, +1 of rows g and g + 8: chunk i, byte offset 4 * t4 inside the chunk
-      *reinterpret_cast<uint32_t*>(myQ + swz(g, i) + 4 * t4) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
-      *reinterpret_cast<uint32_t*>(myQ + swz(g + 8, i) + 4 * t4) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQKV);
+  }
+  __syncthreads();
+  griddep_wait();
+  griddep_launch();
+  const int H = heads * HD, ld = 3 * H;
+  const long long num_items = static_cast<long long>(B) * heads;
+
+  if (warp == PA_CONSUMERS) {
+    int slot = 0;
+    uint32_t phase = 0;
+    bool running = true;
+    for (long long it0 = 0; running; it0 += 32) {
+      // this CTA's next 32 items, one per lane
+      const long long idx = blockIdx.x + (it0 + lane) * static_cast<long long>(gridDim.x);
+      const bool valid = idx < num_items;
+      int my_h = 0, my_klen = 0, my_first = 0, my_nq = 0, my_b = 0, my_mask = 0;
+      if (valid) {
+        const int r = static_cast<int>(idx / heads);
+        my_h = static_cast<int>(idx - static_cast<long long>(r) * heads);
+        my_b = sched ? sched[r] : r;
+        int klen = kv_len[my_b];
+        // the mask row is read only if it exists, the row has a valid key, and (when known) it has holes
+        my_mask = (klen > 0 && mask != nullptr && (!sched || sched[B + my_b] != 0)) ? 1 : 0;
+        if (klen <= 0) klen = S;
+        my_klen = klen;
+        my_first = row_start ? row_start[my_b] : my_b * S;
+        my_nq = row_start ? klen : S;
+      }
+      for (int j = 0; j < 32; ++j) {
+        if (!mbar_wait(empty + slot, phase ^ 1, abort_flag, err, SITE_PA_EMPTY)) { running = false; break; }
+        PaItem* pi = items + slot;
+        if (!__shfl_sync(0xffffffffu, valid ? 1 : 0, j)) {
+          if (lane == 0) {
+            pi->done = 1;
+            mbar_arrive(full + slot);
+          }
+          running = false;
+          break;
+        }
+        const int h = __shfl_sync(0xffffffffu, my_h, j), b = __shfl_sync(0xffffffffu, my_b, j);
+        const int klen = __shfl_sync(0xffffffffu, my_klen, j), first = __shfl_sync(0xffffffffu, my_first, j);
+        const int nq = __shfl_sync(0xffffffffu, my_nq, j), read_mask = __shfl_sync(0xffffffffu, my_mask, j);
+        const int ktiles = (klen + 63) >> 6;
+        const int krows = ktiles << 6;
+        float* sBias = sBiasAll + static_cast<size_t>(slot) * R;
+        const int* mrow = mask + static_cast<size_t>(b) * S;
+        unsigned int bits = 0u;
+        for (int key = lane; key < krows; key += 32) {
+          float v = 0.f;
+          if (key >= klen) v = -INFINITY;
+          else if (read_mask && mrow[key] == 0) v = -10000.0f * LOG2E;
+          sBias[key] = v;
+          if (v != 0.f) bits |= 1u << (key >> 6);
+        }
+        bits = __reduce_or_sync(0xffffffffu, bits);
+        __syncwarp();  // the bias written by all lanes is ordered before lane 0's arrive below
+        if (lane == 0) {
+          pi->first = first;
+          pi->nq = nq;
+          pi->ktiles = ktiles;
+          pi->qblocks = (nq + 15) >> 4;
+          pi->h = h;
+          pi->done = 0;
+          pi->biased = bits;
+          pi->next_q = 0;
+          uint8_t* sK = smem + slot * slot_bytes;
+          uint8_t* sV = sK + static_cast<size_t>(R) * 128;
+          mbar_arrive_expect_tx(full + slot, static_cast<uint32_t>(ktiles) * 2u * 8192u);
+          for (int t = 0; t < ktiles; ++t) {
+            tma_load_2d(sK + t * 8192, &tmQKV, full + slot, H + h * HD, first + t * 64);
+            tma_load_2d(sV + t * 8192, &tmQKV, full + slot, 2 * H + h * HD, first + t * 64);
+          }
+        }
+        if (++slot == nslot) { slot = 0; phase ^= 1; }
+      }
     }
-    __syncwarp();
-    __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = (lane >> 3) + 4 * i, c = lane & 7;
-      if (q0 + r < nq)
-        *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(q0 + r) * H + c * 8) =
-            *reinterpret_cast<const uint4*>(myQ + swz(r, c));
+  } else {
+    uint8_t* myQ = sQ + warp * 2048;
+    int slot = 0;
+    uint32_t phase = 0;
+    for (;;) {
+      if (!mbar_wait(full + slot, phase, abort_flag, err, SITE_PA_FULL)) break;
+      PaItem* pi = items + slot;
+      if (pi->done) break;
+      const int first = pi->first, nq = pi->nq, ktiles = pi->ktiles, qblocks = pi->qblocks, h = pi->h;
+      const unsigned int biased = pi->biased;
+      const uint8_t* sK = smem + slot * slot_bytes;
+      const uint8_t* sV = sK + static_cast<size_t>(R) * 128;
+      const float* sBias = sBiasAll + static_cast<size_t>(slot) * R;
+      const __nv_bfloat16* base = qkv + static_cast<size_t>(first) * ld + h * HD;
+      __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
+      for (;;) {
+        int qb = 0;
+        if (lane == 0) qb = atomicAdd(&pi->next_q, 1);
+        qb = __shfl_sync(0xffffffffu, qb, 0);
+        if (qb >= qblocks) break;
+        attend_qblock(sK, sV, sBias, biased, myQ, base, ld, out_base, H, qb * 16, nq, ktiles, lane);
+      }
+      __syncwarp();  // every lane has finished reading the slot
+      if (lane == 0) mbar_arrive(empty + slot);
+      if (++slot == nslot) { slot = 0; phase ^= 1; }
     }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait gave up: give copies that may still be in flight time to land before shared memory is released
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
 }
 
@@ -316,16 +512,22 @@ attention_f32_kernel(const float* __restrict__ qkv, const int* __restrict__ mask
 // One block.  kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none; S if
 // mask is null).  With `row_start` (B + 1 entries) it also lays the sequences out back to back:
 // row_start[b] = sum of the lengths of the rows before b, a row of length 0 (no valid key: it
-// attends to everything) counting as S; row_start[B] is the number of packed rows.
+// attends to everything) counting as S; row_start[B] is the number of packed rows.  With `sched`
+// (2 B entries) it also prepares the persistent attention kernel's work order: sched[r] = the
+// sequence of rank r when sequences are sorted by descending length (counting sort; the order
+// among equal lengths is arbitrary and only affects scheduling), and sched[B + b] = 1 if row b
+// has a masked key below its last valid one (only then does attention have to read the mask).
 __global__ void __launch_bounds__(1024)
-row_layout_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int* __restrict__ row_start, int B, int S) {
+row_layout_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int* __restrict__ row_start,
+                  int* __restrict__ sched, int B, int S) {
   __shared__ int warp_tot[32];
   __shared__ int carry;
+  __shared__ int hist[544];  // bin 512 - length; 17 bins per lane of warp 0
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   griddep_wait();
   griddep_launch();
   for (int b = warp; b < B; b += 32) {
-    int last = 0;
+    int last = 0, holes = 0;
     if (mask == nullptr) {
       last = S;
     } else {
@@ -334,8 +536,46 @@ row_layout_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int* _
         if (row[i] != 0) last = i + 1;
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, off));
+      if (sched) {
+        for (int i = lane; i < last; i += 32)
+          if (row[i] == 0) holes = 1;
+        holes = __any_sync(0xffffffffu, holes);
+      }
     }
-    if (lane == 0) kv_len[b] = last;
+    if (lane == 0) {
+      kv_len[b] = last;
+      if (sched) sched[B + b] = holes;
+    }
+  }
+  if (sched) {
+    for (int i = tid; i < 544; i += 1024) hist[i] = 0;
+    __syncthreads();  // also orders the kv_len writes above before the reads below
+    for (int b = tid; b < B; b += 1024) {
+      int v = kv_len[b];
+      if (v <= 0 || v > 512) v = min(S, 512);
+      atomicAdd(&hist[512 - v], 1);
+    }
+    __syncthreads();
+    if (warp == 0) {  // exclusive prefix sum over the 544 bins
+      int local[17], sum = 0;
+#pragma unroll
+      for (int i = 0; i < 17; ++i) { local[i] = hist[lane * 17 + i]; sum += local[i]; }
+      int incl = sum;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += n;
+      }
+      int run = incl - sum;
+#pragma unroll
+      for (int i = 0; i < 17; ++i) { hist[lane * 17 + i] = run; run += local[i]; }
+    }
+    __syncthreads();
+    for (int b = tid; b < B; b += 1024) {
+      int v = kv_len[b];
+      if (v <= 0 || v > 512) v = min(S, 512);
+      sched[atomicAdd(&hist[512 - v], 1)] = b;
+    }
   }
   if (row_start == nullptr) return;
   if (tid == 0) carry = 0;
@@ -398,6 +638,29 @@ int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
                     heads, R) == cudaSuccess ? 1 : -3;
 }
 
+bool attention_persist_fits(int S) { return ((S + 63) / 64) * 64 <= PA_MAX_R; }
+
+int attention_bf16_persist(const CUtensorMap* tm_qkv, const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
+                           const int* row_start, const int* sched, __nv_bfloat16* ctx, int B, int S, int heads,
+                           int num_sms, int* err_flag, cudaStream_t stream) {
+  if (B <= 0 || S <= 0 || heads <= 0 || !attention_persist_fits(S)) return -1;
+  const int R = ((S + 63) / 64) * 64;
+  const int nslot = pa_slots(R);
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(attention_bf16_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(PA_SMEM_LIMIT)) != cudaSuccess)
+      return -2;
+    attr_set[dev] = true;
+  }
+  const long long items = static_cast<long long>(B) * heads;
+  const int grid = static_cast<int>(items < num_sms ? items : num_sms);
+  return launch_pdl(attention_bf16_persist_kernel, dim3(grid), dim3(PA_THREADS), pa_smem_bytes(R, nslot), stream, *tm_qkv,
+                    qkv, mask, kv_len, row_start, sched, ctx, B, S, heads, R, nslot, err_flag) == cudaSuccess ? 1 : -3;
+}
+
 int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,
                   int S, int heads, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || heads <= 0 || B > 65535) return -1;
@@ -406,9 +669,9 @@ int attention_f32(const float* qkv, const int* mask, const int* kv_len, const in
                  cudaSuccess ? 1 : -3;
 }
 
-int row_layout(const int* mask, int* kv_len, int* row_start, int B, int S, cudaStream_t stream) {
+int row_layout(const int* mask, int* kv_len, int* row_start, int* sched, int B, int S, cudaStream_t stream) {
   if (B <= 0 || S <= 0) return -1;
-  return launch_pdl(row_layout_kernel, dim3(1), dim3(1024), 0, stream, mask, kv_len, row_start, B, S) == cudaSuccess
+  return launch_pdl(row_layout_kernel, dim3(1), dim3(1024), 0, stream, mask, kv_len, row_start, sched, B, S) == cudaSuccess
              ? 1 : -3;
 }
 
@@ -456,7 +719,7 @@ extern "C" int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const
     kv = scratch_of_device[dev];
   }
   // every entry [0, B) is rewritten before it is read, so nothing left by an earlier call matters
-  if (cb::row_layout(mask_dev, kv, nullptr, B, S, nullptr) < 0) return 3;
+  if (cb::row_layout(mask_dev, kv, nullptr, nullptr, B, S, nullptr) < 0) return 3;
   const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
                                           static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr)
                      : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr,

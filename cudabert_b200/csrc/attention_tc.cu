@@ -414,23 +414,34 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
 
 }  // namespace
 
-// Which bf16 attention kernel a forward pass of padded length S uses.  This kernel works on
+// Which bf16 attention kernel a forward pass of padded length S uses.  The tcgen05 kernel works on
 // 128-query tiles of 64-key blocks whatever the number of live rows in them, so it wins where the
-// tiles are full (measured per layer, BERT-large: S = 512 full rows 95 us against 179 us for the
-// mma.sync kernel, S = 128 full rows 43 against 61) and loses where a batch's rows are much
-// shorter than the tile grid (S = 200 with lengths 16..200: 87 against 76; S = 64 with lengths
-// 8..64: 185 against 124).  The lengths live on the device, so the choice uses S alone: long
-// sequences, or S that fills its last query tile to 85 % or more.  CUDABERT_ATTENTION=tc / mma
-// forces one kernel.
-bool attention_use_tc(int S) {
-  static const int forced = [] {
+// tiles are full and loses where a batch's rows are much shorter than the tile grid.  Measured per
+// layer, BERT-large unless noted, in microseconds for tcgen05 / persistent mma.sync / mma.sync with
+// one CTA per item:  S = 512 full rows 95 / - / 165;  S = 512 lengths 64..512: 137 / - / 176;
+// S = 128 full rows 42 / 62 / 59;  BERT-base S = 128 lengths ~N(60, 25): 50 / 51 / 57;
+// S = 200 lengths 16..200: 88 / 70 / 74;  S = 64 lengths 8..64: 185 / 140 / 125.
+// The lengths live on the device, so the choice uses S alone: tcgen05 for long sequences or an S
+// that fills its last query tile to 85 % or more, the per-item kernel below 96, the persistent
+// kernel otherwise.  CUDABERT_ATTENTION=tc / persist / mma forces one kernel (persist falls back to
+// mma beyond the sequence length it can hold).
+int attention_kernel_for(int S) {
+  static const int forced = []() -> int {
     const char* e = std::getenv("CUDABERT_ATTENTION");
     if (!e || !*e) return -1;
-    return (e[0] == 't' || e[0] == '2') ? 1 : ((e[0] == 'm' || e[0] == '0' || e[0] == '1') ? 0 : -1);
+    if (e[0] == 't' || e[0] == '2') return ATT_KERNEL_TC;
+    if (e[0] == 'p' || e[0] == '3') return ATT_KERNEL_PERSIST;
+    if (e[0] == 'm' || e[0] == '0' || e[0] == '1') return ATT_KERNEL_MMA;
+    return -1;
   }();
-  if (forced >= 0) return forced == 1;
-  const int tiles = (S + TQ - 1) / TQ;
-  return S >= 384 || S * 100 >= tiles * TQ * 85;
+  int k = forced;
+  if (k < 0) {
+    const int tiles = (S + TQ - 1) / TQ;
+    if (S >= 384 || (S >= 96 && S * 100 >= tiles * TQ * 85)) k = ATT_KERNEL_TC;
+    else k = S >= 96 ? ATT_KERNEL_PERSIST : ATT_KERNEL_MMA;
+  }
+  if (k == ATT_KERNEL_PERSIST && !attention_persist_fits(S)) k = ATT_KERNEL_MMA;
+  return k;
 }
 
 bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H) {

@@ -91,16 +91,24 @@ int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
 int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,
                   int S, int heads, cudaStream_t stream);
 // tcgen05 variant of attention_bf16 (attention_tc.cu): Q, K, V tiles arrive by TMA through `tm_qkv`,
-// a map over the [rows, 3H] projection output made by make_tmap_qkv.  attention_use_tc says which
-// of the two kernels a forward pass of padded length S takes (CUDABERT_ATTENTION=tc|mma forces one).
-bool attention_use_tc(int S);
+// a map over the [rows, 3H] projection output made by make_tmap_qkv.  attention_kernel_for says which
+// bf16 kernel a forward pass of padded length S takes (CUDABERT_ATTENTION=tc|persist|mma forces one).
+// Persistent variant of attention_bf16 (one CTA per SM, TMA-fed K/V slots, query blocks drawn
+// dynamically).  `sched` (2 B entries from row_layout, may be null) orders the items by descending
+// length and says which rows need their mask read; S <= 384.
+bool attention_persist_fits(int S);
+int attention_bf16_persist(const CUtensorMap* tm_qkv, const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
+                           const int* row_start, const int* sched, __nv_bfloat16* ctx, int B, int S, int heads,
+                           int num_sms, int* err_flag, cudaStream_t stream);
+enum AttentionKernel : int { ATT_KERNEL_MMA = 1, ATT_KERNEL_TC = 2, ATT_KERNEL_PERSIST = 3 };
+int attention_kernel_for(int S);
 bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H);
 int attention_bf16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
                       __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int* err_flag, cudaStream_t stream);
 // kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none); mask null => S.
 // row_start (may be null): exclusive prefix sum of the sequence lengths (a length of 0 counts as S),
 // B + 1 entries, the last one being the number of packed rows.
-int row_layout(const int* mask, int* kv_len, int* row_start, int B, int S, cudaStream_t stream);
+int row_layout(const int* mask, int* kv_len, int* row_start, int* sched, int B, int S, cudaStream_t stream);
 
 // ---- row-wise kernels.  The residual stream is kept in fp32; TOut (float or __nv_bfloat16) is
 // the copy that feeds the next GEMM.  out_f32 (may be null) receives the same values in fp32.

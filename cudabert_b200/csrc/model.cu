@@ -291,6 +291,7 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   const size_t o_ints = slot(3 * ct * sizeof(int));
   const size_t o_kv = slot(static_cast<size_t>(cbatch) * sizeof(int));
   const size_t o_rs = slot((static_cast<size_t>(cbatch) + 1) * sizeof(int));
+  const size_t o_sched = slot(2 * static_cast<size_t>(cbatch) * sizeof(int));
   const size_t o_xf = slot(ct * H_ * sizeof(float));
   const size_t o_x1f = slot(ct * H_ * sizeof(float));
   const size_t o_y = slot(ct * H_ * (lowp ? 2 : 4));
@@ -306,6 +307,7 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   ids_ = reinterpret_cast<int*>(base + o_ints);
   kv_len_ = reinterpret_cast<int*>(base + o_kv);
   row_start_ = reinterpret_cast<int*>(base + o_rs);
+  att_sched_ = reinterpret_cast<int*>(base + o_sched);
   xf_ = reinterpret_cast<float*>(base + o_xf);
   x1f_ = reinterpret_cast<float*>(base + o_x1f);
   y_ = base + o_y;
@@ -428,8 +430,10 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
   m_dev_cur_ = packed_ ? row_start_ + B : nullptr;
   const int* rs = packed_ ? row_start_ : nullptr;          // first row of every sequence
   const int* live = packed_ ? row_start_ + B : nullptr;     // live row count (device)
-  CB_LAUNCH(KC_OTHER, row_layout(d_mask, kv_len_, packed_ ? row_start_ : nullptr, B, S, stream_));
   const bool lowp = prec_ != PREC_FP32;
+  const int att_kernel = lowp ? attention_kernel_for(S) : ATT_KERNEL_MMA;
+  int* sched = att_kernel == ATT_KERNEL_PERSIST ? att_sched_ : nullptr;
+  CB_LAUNCH(KC_OTHER, row_layout(d_mask, kv_len_, packed_ ? row_start_ : nullptr, sched, B, S, stream_));
   __nv_bfloat16* xa = static_cast<__nv_bfloat16*>(xa_);
   __nv_bfloat16* x1a = static_cast<__nv_bfloat16*>(x1a_);
   if (lowp) {
@@ -443,9 +447,13 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
     const LayerWeights& w = layer_[l];
     if (!dense(w.qkv, xa_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) return false;
     if (lowp) {
-      if (attention_use_tc(S)) {
+      if (att_kernel == ATT_KERNEL_TC) {
         CB_LAUNCH(KC_ATTENTION, attention_bf16_tc(&tm_qkv_, d_mask, kv_len_, rs, static_cast<__nv_bfloat16*>(ctx_), B, S,
                                                   heads_, num_sms_, err_dev_, stream_));
+      } else if (att_kernel == ATT_KERNEL_PERSIST) {
+        CB_LAUNCH(KC_ATTENTION, attention_bf16_persist(&tm_qkv_, static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_,
+                                                       rs, sched, static_cast<__nv_bfloat16*>(ctx_), B, S, heads_,
+                                                       num_sms_, err_dev_, stream_));
       } else {
         CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_, rs,
                                                static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, stream_));

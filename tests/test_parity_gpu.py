@@ -169,3 +169,49 @@ def test_errors_do_not_kill_the_process(models, weight_dirs):
     assert np.isfinite(good).all()
     with pytest.raises(RuntimeError):
         pybert.load_model(False, "/nonexistent/dir")
+
+
+@pytest.mark.parametrize("style", ["pytorch_converter", "tf_checkpoint"])
+def test_weight_directories_of_both_converters_resolve(models, tmp_path, style):
+    """The two converters of the reference name files differently and leave files the encoder does
+    not use beside the ones it does; the loader has to pick the same tensors from each.
+    convert_pytorch_model_to_npys.py:27-43 turns every 2-D `weight` into `kernel` -- embedding
+    tables included, whose files then end in `_embeddings_kernel.npy` -- and writes the
+    pre-training heads (`cls_*`); convert_tf_ckpt_to_npys.py:47-61 writes every checkpoint variable
+    with `/` -> `_`, optimizer slots and `global_step` included.  Values of the extra files are
+    garbage here, so picking one of them changes the output."""
+    from cudabert_b200.cuda_bert import pybert
+    base = cases.get_weights("base_affine")
+    rng = np.random.default_rng(5)
+    w = {}
+    for name, arr in base.items():
+        if style == "pytorch_converter" and name.endswith("_embeddings") and arr.ndim == 2:
+            w[name + "_kernel"] = arr
+        else:
+            w[name] = arr
+        if style == "tf_checkpoint":
+            w[name + "_adam_m"] = rng.standard_normal(arr.shape).astype(np.float32)
+            w[name + "_adam_v"] = rng.standard_normal(arr.shape).astype(np.float32)
+    H = base["bert_pooler_dense_kernel"].shape[0]
+    junk = lambda *shape: rng.standard_normal(shape).astype(np.float32)
+    w["cls_predictions_transform_dense_kernel"] = junk(H, H)
+    w["cls_predictions_transform_dense_bias"] = junk(H)
+    w["cls_predictions_transform_LayerNorm_gamma"] = junk(H)
+    w["cls_predictions_transform_LayerNorm_beta"] = junk(H)
+    w["cls_seq_relationship_kernel" if style == "pytorch_converter" else "cls_seq_relationship_output_weights"] = junk(H, 2)
+    w["cls_predictions_bias" if style == "pytorch_converter" else "cls_predictions_output_bias"] = junk(64)
+    if style == "tf_checkpoint":
+        w["global_step"] = np.zeros((1,), np.float32)
+    d = str(tmp_path / style)
+    synth.write_weight_dir(d, w)
+    ids, seg, mask = cases.case_inputs("c0_affine")
+    want = models("base_affine", "bf16").encode([ids, seg, mask])
+    layers = sum(1 for k in base if k.endswith("attention_output_dense_kernel"))
+    model = pybert.load_model(False, d, 0, 0, 0, precision="bf16", num_layers=layers)
+    try:
+        got = np.zeros_like(want)
+        pybert.bert(model, got, ids, seg, ids.shape[0], ids.shape[1], mask)
+        pybert.check(model)
+    finally:
+        pybert.unload_model(model)
+    np.testing.assert_array_equal(got, want)
