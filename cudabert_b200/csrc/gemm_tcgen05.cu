@@ -61,18 +61,38 @@ struct Cfg {
 
 // erf-GELU x * 0.5 * (1 + erf(x / sqrt 2)) evaluated as 0.5 x (1 + tanh(x (c0 + c1 x^2 + c2 x^4))) with
 // coefficients fitted to the erf form (max abs deviation 2.5e-5 over the reals, below one bf16
-// rounding of the result everywhere) and the hardware tanh (relative error 2^-11): 9 instructions
-// per element instead of ~45 for erff, which otherwise makes the FFN1 epilogue slower than its
-// main loop.  |x| is clamped to 8 inside the polynomial (tanh is +-1 to fp32 precision beyond 6).
-__device__ __forceinline__ float gelu_erf(float x) {
-  const float xc = fminf(fmaxf(x, -8.0f), 8.0f);
-  const float x2 = xc * xc;
-  float p = fmaf(x2, -0.000351516789798119f, 0.03700564602858787f);
-  p = fmaf(x2, p, 0.7975078842834395f);
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(xc * p));
-  const float hx = 0.5f * x;
-  return fmaf(hx, t, hx);
+// rounding of the result everywhere) and the hardware tanh (relative error 2^-11), instead of ~45
+// instructions per element for erff, which otherwise makes the FFN1 epilogue slower than its main loop.
+// Two values at a time with the packed fp32 instructions of sm_100 (mul / fma .f32x2: one issue
+// slot for two lanes of arithmetic; the epilogue of the GELU GEMM is bound by issue slots).  The
+// clamp is applied to x^2 (<= 64), which keeps the polynomial positive, so that beyond |x| = 8 the
+// tanh argument has the sign of x and a magnitude above 13: tanh is +-1 there.
+__device__ __forceinline__ void gelu_erf2(float& a, float& b) {
+  uint64_t x, x2, p, u, hx;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(a), "f"(b));
+  asm("mul.rn.f32x2 %0, %1, %1;" : "=l"(x2) : "l"(x));
+  float qa, qb;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(qa), "=f"(qb) : "l"(x2));
+  qa = fminf(qa, 64.0f);
+  qb = fminf(qb, 64.0f);
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x2) : "f"(qa), "f"(qb));
+  uint64_t c0, c1, c2, half;
+  asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(-0.000351516789798119f));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(c1) : "f"(0.03700564602858787f));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(c0) : "f"(0.7975078842834395f));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(half) : "f"(0.5f));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(p) : "l"(x2), "l"(c2), "l"(c1));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(p) : "l"(x2), "l"(p), "l"(c0));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(u) : "l"(x), "l"(p));
+  float ua, ub, ta, tb;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(ua), "=f"(ub) : "l"(u));
+  asm("tanh.approx.f32 %0, %1;" : "=f"(ta) : "f"(ua));
+  asm("tanh.approx.f32 %0, %1;" : "=f"(tb) : "f"(ub));
+  uint64_t t;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(t) : "f"(ta), "f"(tb));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(hx) : "l"(x), "l"(half));
+  asm("fma.rn.f32x2 %0, %1, %2, %1;" : "=l"(x) : "l"(hx), "l"(t));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(x));
 }
 
 // Epilogue of one accumulator (128 TMEM lanes x BN columns at `t_acc`), run by the eight epilogue
@@ -135,10 +155,13 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restric
         }
       }
     }
+    if (fl & EPI_GELU) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (fl & EPI_GELU) f[j] = gelu_erf(f[j]);
-      if (fl & EPI_TANH) f[j] = tanhf(f[j]);
+      for (int j = 0; j < 32; j += 2) gelu_erf2(f[j], f[j + 1]);
+    }
+    if (fl & EPI_TANH) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = tanhf(f[j]);
     }
   };
 
