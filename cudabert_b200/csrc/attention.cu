@@ -32,28 +32,38 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 // One 16-query block of one (sequence, head) against the sequence's keys and values resident in
 // shared memory (`sK`, `sV`: 128-byte rows, chunk c of row r at c ^ (r & 7)): QK^T -> scale + mask
 // bias -> online softmax -> P.V over 64-key tiles, then a coalesced store of the 16 x 64 block.
-// Run by one warp; `myQ` is the warp's own 2 KB staging buffer.  `base` points at the first Q
-// element of the sequence's first row (row stride `ld`), `out_base` at its first output element
-// (row stride `H`).  Bit t of `biased` says that key tile t needs the bias in `sBias`.
+// Run by one warp; `myQ` is the warp's own 2 KB staging buffer.  The queries come either from
+// global memory (`sQ` null: `base` points at the first Q element of the sequence's first row, row
+// stride `ld`) or from shared memory (`sQ`: the sequence's Q rows in the layout of sK).  `out_base`
+// points at the sequence's first output element (row stride `H`).  Bit t of `biased` says that key
+// tile t needs the bias in `sBias`.
+template <bool Q_IN_SMEM>
 __device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, const uint8_t* __restrict__ sV,
                                               const float* __restrict__ sBias, unsigned int biased,
-                                              uint8_t* __restrict__ myQ, const __nv_bfloat16* __restrict__ base,
-                                              int ld, __nv_bfloat16* __restrict__ out_base, int H, int q0, int nq,
+                                              uint8_t* __restrict__ myQ, const uint8_t* __restrict__ sQ,
+                                              const __nv_bfloat16* __restrict__ base, int ld,
+                                              __nv_bfloat16* __restrict__ out_base, int H, int q0, int nq,
                                               int ktiles, int lane) {
   const float scale = 0.125f * LOG2E;
-  // stage the 16 x 64 Q block: lane l moves chunk l % 8 of rows l / 8 + 4 i
-  __syncwarp();
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = (lane >> 3) + 4 * i, c = lane & 7;
-    uint4 t = make_uint4(0u, 0u, 0u, 0u);
-    if (q0 + r < nq) t = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + r) * ld + c * 8));
-    *reinterpret_cast<uint4*>(myQ + swz(r, c)) = t;
-  }
-  __syncwarp();
   uint32_t qf[4][4];
+  if (Q_IN_SMEM) {
+    // rows at or beyond nq hold other rows' (finite) values; their results are never stored
 #pragma unroll
-  for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(myQ + swz(lane & 15, kk * 2 + (lane >> 4))));
+    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(sQ + swz(q0 + (lane & 15), kk * 2 + (lane >> 4))));
+  } else {
+    // stage the 16 x 64 Q block: lane l moves chunk l % 8 of rows l / 8 + 4 i
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = (lane >> 3) + 4 * i, c = lane & 7;
+      uint4 t = make_uint4(0u, 0u, 0u, 0u);
+      if (q0 + r < nq) t = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + r) * ld + c * 8));
+      *reinterpret_cast<uint4*>(myQ + swz(r, c)) = t;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(myQ + swz(lane & 15, kk * 2 + (lane >> 4))));
+  }
 
   float o[8][4];
 #pragma unroll
@@ -233,7 +243,7 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   const int qblocks = (nq + 15) >> 4;
   __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
   for (int qb = warp; qb < qblocks; qb += nwarps)
-    attend_qblock(sK, sV, sBias, biased, myQ, base, ld, out_base, H, qb * 16, nq, ktiles, lane);
+    attend_qblock<false>(sK, sV, sBias, biased, myQ, nullptr, base, ld, out_base, H, qb * 16, nq, ktiles, lane);
 }
 
 // ---------------------------------------------------------------- persistent variant
@@ -250,17 +260,17 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
 //   producer   per item: waits until the consumers have left the slot, writes the per-key bias
 //              (reading the mask only for a sequence that has masked keys below its last valid
 //              one), and loads the item's K and V rows with TMA box copies (64 rows x 128 bytes,
-//              128-byte swizzle = the layout swz() describes) that complete on the slot's `full`
-//              mbarrier;
+//              128-byte swizzle = the layout swz() describes), and its Q rows the same way, all
+//              completing on the slot's `full` mbarrier, so no consumer ever waits on a global load;
 //   consumers  wait for `full`, then draw 16-query blocks of the item from a shared-memory
 //              counter until none is left, arrive on `empty` and move to the next slot, so a warp
 //              that finds no block in a short item is already working on the next one.
-// The number of slots is what fits: 3 for S = 200, up to 8 for short sequences.  Rows of a K / V
+// The number of slots is what fits: 2 for S = 200, up to 8 for short sequences.  Rows of a K / V
 // box beyond the sequence's last key hold whatever follows in the buffer (finite activations of
 // other rows, or zero fill beyond the tensor); their bias is -inf, so their probability is 0.
 constexpr int PA_CONSUMERS = 15;
 constexpr int PA_THREADS = (PA_CONSUMERS + 1) * 32;
-constexpr int PA_MAX_R = 384;  // two slots of R rows must fit in shared memory
+constexpr int PA_MAX_R = 256;  // two slots of R rows (K, V and Q) must fit in shared memory
 constexpr int PA_MAX_SLOTS = 8;
 constexpr int PA_TAIL_BYTES = 512;  // item records, mbarriers, abort flag
 constexpr size_t PA_SMEM_LIMIT = 232448;
@@ -273,10 +283,10 @@ struct PaItem {
 };
 
 constexpr size_t pa_smem_bytes(int R, int nslot) {
-  return static_cast<size_t>(nslot) * R * 260 + PA_CONSUMERS * 2048 + PA_TAIL_BYTES + 1024;
+  return static_cast<size_t>(nslot) * R * 388 + PA_CONSUMERS * 2048 + PA_TAIL_BYTES + 1024;
 }
 constexpr int pa_slots(int R) {
-  const size_t per_slot = static_cast<size_t>(R) * 260;
+  const size_t per_slot = static_cast<size_t>(R) * 388;  // K, V, Q rows of 128 bytes + 4 bytes of bias per key
   const size_t n = (PA_SMEM_LIMIT - PA_CONSUMERS * 2048 - PA_TAIL_BYTES - 1024) / per_slot;
   return n > PA_MAX_SLOTS ? PA_MAX_SLOTS : static_cast<int>(n);
 }
@@ -290,7 +300,7 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const _
                               int* __restrict__ err) {
   extern __shared__ uint8_t pa_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pa_smem_raw) + 1023) & ~uintptr_t(1023));
-  const size_t slot_bytes = static_cast<size_t>(R) * 256;  // K then V of one item
+  const size_t slot_bytes = static_cast<size_t>(R) * 384;  // K, V, Q of one item
   uint8_t* sQ = smem + nslot * slot_bytes;
   float* sBiasAll = reinterpret_cast<float*>(sQ + PA_CONSUMERS * 2048);
   uint8_t* tail = reinterpret_cast<uint8_t*>(sBiasAll + static_cast<size_t>(nslot) * R);
@@ -375,11 +385,14 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const _
           pi->next_q = 0;
           uint8_t* sK = smem + slot * slot_bytes;
           uint8_t* sV = sK + static_cast<size_t>(R) * 128;
-          mbar_arrive_expect_tx(full + slot, static_cast<uint32_t>(ktiles) * 2u * 8192u);
+          uint8_t* sQi = sV + static_cast<size_t>(R) * 128;
+          const int qtiles = (nq + 63) >> 6;
+          mbar_arrive_expect_tx(full + slot, static_cast<uint32_t>(2 * ktiles + qtiles) * 8192u);
           for (int t = 0; t < ktiles; ++t) {
             tma_load_2d(sK + t * 8192, &tmQKV, full + slot, H + h * HD, first + t * 64);
             tma_load_2d(sV + t * 8192, &tmQKV, full + slot, 2 * H + h * HD, first + t * 64);
           }
+          for (int t = 0; t < qtiles; ++t) tma_load_2d(sQi + t * 8192, &tmQKV, full + slot, h * HD, first + t * 64);
         }
         if (++slot == nslot) { slot = 0; phase ^= 1; }
       }
@@ -396,15 +409,15 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const _
       const unsigned int biased = pi->biased;
       const uint8_t* sK = smem + slot * slot_bytes;
       const uint8_t* sV = sK + static_cast<size_t>(R) * 128;
+      const uint8_t* sQi = sV + static_cast<size_t>(R) * 128;
       const float* sBias = sBiasAll + static_cast<size_t>(slot) * R;
-      const __nv_bfloat16* base = qkv + static_cast<size_t>(first) * ld + h * HD;
       __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
       for (;;) {
         int qb = 0;
         if (lane == 0) qb = atomicAdd(&pi->next_q, 1);
         qb = __shfl_sync(0xffffffffu, qb, 0);
         if (qb >= qblocks) break;
-        attend_qblock(sK, sV, sBias, biased, myQ, base, ld, out_base, H, qb * 16, nq, ktiles, lane);
+        attend_qblock<true>(sK, sV, sBias, biased, myQ, sQi, nullptr, ld, out_base, H, qb * 16, nq, ktiles, lane);
       }
       __syncwarp();  // every lane has finished reading the slot
       if (lane == 0) mbar_arrive(empty + slot);

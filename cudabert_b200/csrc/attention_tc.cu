@@ -419,12 +419,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
 // tiles are full and loses where a batch's rows are much shorter than the tile grid.  Measured per
 // layer, BERT-large unless noted, in microseconds for tcgen05 / persistent mma.sync / mma.sync with
 // one CTA per item:  S = 512 full rows 95 / - / 165;  S = 512 lengths 64..512: 137 / - / 176;
-// S = 128 full rows 42 / 62 / 59;  BERT-base S = 128 lengths ~N(60, 25): 50 / 51 / 57;
-// S = 200 lengths 16..200: 88 / 70 / 74;  S = 64 lengths 8..64: 185 / 140 / 125.
+// S = 128 full rows 42 / 52 / 59;  BERT-base S = 128 lengths ~N(60, 25): 50 / 45 / 57;
+// S = 200 lengths 16..200: 88 / 68 / 74;  S = 64 lengths 8..64: 185 / 124 / 125.
 // The lengths live on the device, so the choice uses S alone: tcgen05 for long sequences or an S
-// that fills its last query tile to 85 % or more, the per-item kernel below 96, the persistent
-// kernel otherwise.  CUDABERT_ATTENTION=tc / persist / mma forces one kernel (persist falls back to
-// mma beyond the sequence length it can hold).
+// of at least 96 that fills its last query tile to 85 % or more, the persistent kernel otherwise
+// (the per-item kernel beyond the length the persistent one can hold).
+// CUDABERT_ATTENTION=tc / persist / mma forces one kernel.
 int attention_kernel_for(int S) {
   static const int forced = []() -> int {
     const char* e = std::getenv("CUDABERT_ATTENTION");
@@ -437,8 +437,7 @@ int attention_kernel_for(int S) {
   int k = forced;
   if (k < 0) {
     const int tiles = (S + TQ - 1) / TQ;
-    if (S >= 384 || (S >= 96 && S * 100 >= tiles * TQ * 85)) k = ATT_KERNEL_TC;
-    else k = S >= 96 ? ATT_KERNEL_PERSIST : ATT_KERNEL_MMA;
+    k = (S >= 384 || (S >= 96 && S * 100 >= tiles * TQ * 85)) ? ATT_KERNEL_TC : ATT_KERNEL_PERSIST;
   }
   if (k == ATT_KERNEL_PERSIST && !attention_persist_fits(S)) k = ATT_KERNEL_MMA;
   return k;

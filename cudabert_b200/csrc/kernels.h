@@ -95,7 +95,7 @@ int attention_f32(const float* qkv, const int* mask, const int* kv_len, const in
 // bf16 kernel a forward pass of padded length S takes (CUDABERT_ATTENTION=tc|persist|mma forces one).
 // Persistent variant of attention_bf16 (one CTA per SM, TMA-fed K/V slots, query blocks drawn
 // dynamically).  `sched` (2 B entries from row_layout, may be null) orders the items by descending
-// length and says which rows need their mask read; S <= 384.
+// length and says which rows need their mask read; S <= 256.
 bool attention_persist_fits(int S);
 int attention_bf16_persist(const CUtensorMap* tm_qkv, const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
                            const int* row_start, const int* sched, __nv_bfloat16* ctx, int B, int S, int heads,
