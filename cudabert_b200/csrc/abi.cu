@@ -300,8 +300,8 @@ int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, voi
         n = cb::attention_bf16_tc(&tm, mask_dev, kv, nullptr, static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, sms,
                                   err, nullptr);
       else
-        n = cb::attention_bf16_persist(&tm, static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr, sched,
-                                       static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, sms, err, nullptr);
+        n = cb::attention_bf16_persist(&tm, mask_dev, kv, nullptr, sched, static_cast<__nv_bfloat16*>(ctx_dev), B, S,
+                                       heads, sms, err, nullptr);
     } else if (bf16) {
       n = cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
                              static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr);

@@ -29,18 +29,33 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
   return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
+// Where the 64-row tiles (8 KB: 128-byte rows, chunk c of row r at c ^ (r & 7)) of an item's K and V
+// live in shared memory: back to back (per-item kernel), or anywhere in a ring of tiles
+// (persistent kernel).
+struct ContigTiles {
+  const uint8_t *sK, *sV;
+  __device__ __forceinline__ const uint8_t* k(int t) const { return sK + t * 8192; }
+  __device__ __forceinline__ const uint8_t* v(int t) const { return sV + t * 8192; }
+};
+struct RingTiles {
+  const uint8_t* ring;
+  int nt, k0, v0;  // ring size in tiles; ring index (< nt) of the item's first K tile and first V tile
+  __device__ __forceinline__ const uint8_t* at(int i) const { return ring + (i >= nt ? i - nt : i) * 8192; }
+  __device__ __forceinline__ const uint8_t* k(int t) const { return at(k0 + t); }
+  __device__ __forceinline__ const uint8_t* v(int t) const { return at(v0 + t); }
+};
+
 // One 16-query block of one (sequence, head) against the sequence's keys and values resident in
-// shared memory (`sK`, `sV`: 128-byte rows, chunk c of row r at c ^ (r & 7)): QK^T -> scale + mask
-// bias -> online softmax -> P.V over 64-key tiles, then a coalesced store of the 16 x 64 block.
-// Run by one warp; `myQ` is the warp's own 2 KB staging buffer.  The queries come either from
-// global memory (`sQ` null: `base` points at the first Q element of the sequence's first row, row
-// stride `ld`) or from shared memory (`sQ`: the sequence's Q rows in the layout of sK).  `out_base`
-// points at the sequence's first output element (row stride `H`).  Bit t of `biased` says that key
-// tile t needs the bias in `sBias`.
-template <bool Q_IN_SMEM>
-__device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, const uint8_t* __restrict__ sV,
-                                              const float* __restrict__ sBias, unsigned int biased,
-                                              uint8_t* __restrict__ myQ, const uint8_t* __restrict__ sQ,
+// shared memory: QK^T -> scale + mask bias -> online softmax -> P.V over 64-key tiles, then a
+// coalesced store of the 16 x 64 block.  Run by one warp; `stage` is 2 KB of shared memory that
+// only this warp touches while it works on the block.  The queries come either from global memory
+// (`sQ` null: `base` points at the first Q element of the sequence's first row, row stride `ld`;
+// they pass through `stage`) or from shared memory (`sQ`: the block's own 16 rows of a Q tile,
+// which may be `stage` itself).  `out_base` points at the sequence's first output element (row
+// stride `H`).  Bit t of `biased` says that key tile t needs the bias in `sBias`.
+template <bool Q_IN_SMEM, typename Tiles>
+__device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __restrict__ sBias, unsigned int biased,
+                                              uint8_t* __restrict__ stage, const uint8_t* __restrict__ sQ,
                                               const __nv_bfloat16* __restrict__ base, int ld,
                                               __nv_bfloat16* __restrict__ out_base, int H, int q0, int nq,
                                               int ktiles, int lane) {
@@ -49,7 +64,7 @@ __device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, co
   if (Q_IN_SMEM) {
     // rows at or beyond nq hold other rows' (finite) values; their results are never stored
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(sQ + swz(q0 + (lane & 15), kk * 2 + (lane >> 4))));
+    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(sQ + swz(lane & 15, kk * 2 + (lane >> 4))));
   } else {
     // stage the 16 x 64 Q block: lane l moves chunk l % 8 of rows l / 8 + 4 i
     __syncwarp();
@@ -58,11 +73,11 @@ __device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, co
       const int r = (lane >> 3) + 4 * i, c = lane & 7;
       uint4 t = make_uint4(0u, 0u, 0u, 0u);
       if (q0 + r < nq) t = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + r) * ld + c * 8));
-      *reinterpret_cast<uint4*>(myQ + swz(r, c)) = t;
+      *reinterpret_cast<uint4*>(stage + swz(r, c)) = t;
     }
     __syncwarp();
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(myQ + swz(lane & 15, kk * 2 + (lane >> 4))));
+    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(stage + swz(lane & 15, kk * 2 + (lane >> 4))));
   }
 
   float o[8][4];
@@ -73,6 +88,8 @@ __device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, co
 
   for (int t = 0; t < ktiles; ++t) {
     const int k0 = t << 6;
+    const uint8_t* kt = tiles.k(t);
+    const uint8_t* vt = tiles.v(t);
     // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
     float s[8][4];
 #pragma unroll
@@ -83,7 +100,7 @@ __device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, co
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
         uint32_t kf[4];
-        ldmatrix_x4(kf, smem_u32(sK + swz(k0 + nb * 16 + (mid >> 1) * 8 + (lane & 7), kk * 2 + (mid & 1))));
+        ldmatrix_x4(kf, smem_u32(kt + swz(nb * 16 + (mid >> 1) * 8 + (lane & 7), kk * 2 + (mid & 1))));
         mma_bf16_16816(s[2 * nb], qf[kk], kf[0], kf[1]);
         mma_bf16_16816(s[2 * nb + 1], qf[kk], kf[2], kf[3]);
       }
@@ -151,7 +168,7 @@ __device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, co
 #pragma unroll
       for (int db = 0; db < 4; ++db) {
         uint32_t vf[4];
-        ldmatrix_x4_trans(vf, smem_u32(sV + swz(k0 + j * 16 + (mid & 1) * 8 + (lane & 7), db * 2 + (mid >> 1))));
+        ldmatrix_x4_trans(vf, smem_u32(vt + swz(j * 16 + (mid & 1) * 8 + (lane & 7), db * 2 + (mid >> 1))));
         mma_bf16_16816(o[2 * db], pf[j], vf[0], vf[1]);
         mma_bf16_16816(o[2 * db + 1], pf[j], vf[2], vf[3]);
       }
@@ -170,8 +187,8 @@ __device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, co
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     // columns i*8 + 2*t4, +1 of rows g and g + 8: chunk i, byte offset 4 * t4 inside the chunk
-    *reinterpret_cast<uint32_t*>(myQ + swz(g, i) + 4 * t4) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
-    *reinterpret_cast<uint32_t*>(myQ + swz(g + 8, i) + 4 * t4) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+    *reinterpret_cast<uint32_t*>(stage + swz(g, i) + 4 * t4) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+    *reinterpret_cast<uint32_t*>(stage + swz(g + 8, i) + 4 * t4) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
   }
   __syncwarp();
 #pragma unroll
@@ -179,7 +196,7 @@ __device__ __forceinline__ void attend_qblock(const uint8_t* __restrict__ sK, co
     const int r = (lane >> 3) + 4 * i, c = lane & 7;
     if (q0 + r < nq)
       *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(q0 + r) * H + c * 8) =
-          *reinterpret_cast<const uint4*>(myQ + swz(r, c));
+          *reinterpret_cast<const uint4*>(stage + swz(r, c));
   }
 }
 
@@ -243,7 +260,8 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   const int qblocks = (nq + 15) >> 4;
   __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
   for (int qb = warp; qb < qblocks; qb += nwarps)
-    attend_qblock<false>(sK, sV, sBias, biased, myQ, nullptr, base, ld, out_base, H, qb * 16, nq, ktiles, lane);
+    attend_qblock<false>(ContigTiles{sK, sV}, sBias, biased, myQ, nullptr, base, ld, out_base, H, qb * 16, nq, ktiles,
+                         lane);
 }
 
 // ---------------------------------------------------------------- persistent variant
@@ -257,22 +275,26 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
 //              short items, the long ones first, and nothing about the order has to be fetched
 //              with an atomic, so the producer can look up a batch of 32 items' lengths and row
 //              offsets in one go, one item per lane;
-//   producer   per item: waits until the consumers have left the slot, writes the per-key bias
-//              (reading the mask only for a sequence that has masked keys below its last valid
-//              one), and loads the item's K and V rows with TMA box copies (64 rows x 128 bytes,
-//              128-byte swizzle = the layout swz() describes), and its Q rows the same way, all
-//              completing on the slot's `full` mbarrier, so no consumer ever waits on a global load;
+//   memory     a ring of 8 KB tiles (64 rows x 128 bytes, 128-byte swizzle = the layout swz()
+//              describes) holds the K, V and Q rows of up to 8 items in flight; an item takes
+//              exactly the tiles its length needs (3 for up to 64 rows, 12 for 193..256), so many
+//              short items or two of the longest are resident at once;
+//   producer   per item: waits (oldest item first) until enough tiles and an item record are
+//              free, writes the per-key bias (reading the mask only for a sequence that has
+//              masked keys below its last valid one), and issues the TMA box copies, which all
+//              complete on the record's `full` mbarrier, so no consumer waits on a global load;
 //   consumers  wait for `full`, then draw 16-query blocks of the item from a shared-memory
-//              counter until none is left, arrive on `empty` and move to the next slot, so a warp
-//              that finds no block in a short item is already working on the next one.
-// The number of slots is what fits: 2 for S = 200, up to 8 for short sequences.  Rows of a K / V
-// box beyond the sequence's last key hold whatever follows in the buffer (finite activations of
-// other rows, or zero fill beyond the tensor); their bias is -inf, so their probability is 0.
+//              counter until none is left, arrive on `empty` and move to the next record, so a
+//              warp that finds no block in a short item is already working on the next one.  A
+//              block's output is staged in the block's own Q rows, which nobody else reads.
+// Rows of a K / V tile beyond the sequence's last key hold whatever follows in the buffer (finite
+// activations of other rows, or zero fill beyond the tensor); their bias is -inf, so their
+// probability is 0.
 constexpr int PA_CONSUMERS = 15;
 constexpr int PA_THREADS = (PA_CONSUMERS + 1) * 32;
-constexpr int PA_MAX_R = 256;  // two slots of R rows (K, V and Q) must fit in shared memory
-constexpr int PA_MAX_SLOTS = 8;
-constexpr int PA_TAIL_BYTES = 512;  // item records, mbarriers, abort flag
+constexpr int PA_MAX_R = 256;   // longest sequence: two of them (12 tiles each) fit in the ring
+constexpr int PA_RECORDS = 8;   // items in flight
+constexpr int PA_TAIL_BYTES = 640;  // item records, mbarriers, abort flag
 constexpr size_t PA_SMEM_LIMIT = 232448;
 enum : int { SITE_PA_FULL = 21, SITE_PA_EMPTY = 22 };
 
@@ -280,38 +302,36 @@ struct PaItem {
   int first, nq, ktiles, qblocks, h, done;
   unsigned int biased;
   int next_q;  // next query block to hand out
+  int tile0;   // ring index of the item's first tile: K tiles, then V tiles, then Q tiles
+  int pad[3];
 };
+static_assert(sizeof(PaItem) == 48, "record layout");
 
-constexpr size_t pa_smem_bytes(int R, int nslot) {
-  return static_cast<size_t>(nslot) * R * 388 + PA_CONSUMERS * 2048 + PA_TAIL_BYTES + 1024;
+constexpr int pa_ring_tiles(int R) {
+  return static_cast<int>((PA_SMEM_LIMIT - 1024 - PA_TAIL_BYTES - static_cast<size_t>(PA_RECORDS) * R * 4) / 8192);
 }
-constexpr int pa_slots(int R) {
-  const size_t per_slot = static_cast<size_t>(R) * 388;  // K, V, Q rows of 128 bytes + 4 bytes of bias per key
-  const size_t n = (PA_SMEM_LIMIT - PA_CONSUMERS * 2048 - PA_TAIL_BYTES - 1024) / per_slot;
-  return n > PA_MAX_SLOTS ? PA_MAX_SLOTS : static_cast<int>(n);
+constexpr size_t pa_smem_bytes(int R) {
+  return static_cast<size_t>(pa_ring_tiles(R)) * 8192 + static_cast<size_t>(PA_RECORDS) * R * 4 + PA_TAIL_BYTES + 1024;
 }
-static_assert(pa_slots(PA_MAX_R) >= 2, "two slots must fit at the largest supported length");
+static_assert(pa_ring_tiles(PA_MAX_R) >= 24, "two items of the largest supported length must fit");
 
 __global__ void __launch_bounds__(PA_THREADS, 1)
-attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const __nv_bfloat16* __restrict__ qkv,
-                              const int* __restrict__ mask, const int* __restrict__ kv_len,
-                              const int* __restrict__ row_start, const int* __restrict__ sched,
-                              __nv_bfloat16* __restrict__ ctx, int B, int S, int heads, int R, int nslot,
-                              int* __restrict__ err) {
+attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __restrict__ mask,
+                              const int* __restrict__ kv_len, const int* __restrict__ row_start,
+                              const int* __restrict__ sched, __nv_bfloat16* __restrict__ ctx, int B, int S, int heads,
+                              int R, int NT, int* __restrict__ err) {
   extern __shared__ uint8_t pa_smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pa_smem_raw) + 1023) & ~uintptr_t(1023));
-  const size_t slot_bytes = static_cast<size_t>(R) * 384;  // K, V, Q of one item
-  uint8_t* sQ = smem + nslot * slot_bytes;
-  float* sBiasAll = reinterpret_cast<float*>(sQ + PA_CONSUMERS * 2048);
-  uint8_t* tail = reinterpret_cast<uint8_t*>(sBiasAll + static_cast<size_t>(nslot) * R);
-  PaItem* items = reinterpret_cast<PaItem*>(tail);              // [PA_MAX_SLOTS], 32 bytes each
-  uint64_t* full = reinterpret_cast<uint64_t*>(tail + 256);     // [PA_MAX_SLOTS]
-  uint64_t* empty = full + PA_MAX_SLOTS;                        // [PA_MAX_SLOTS]
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + PA_MAX_SLOTS);
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pa_smem_raw) + 1023) & ~uintptr_t(1023));
+  float* sBiasAll = reinterpret_cast<float*>(ring + static_cast<size_t>(NT) * 8192);
+  uint8_t* tail = reinterpret_cast<uint8_t*>(sBiasAll + static_cast<size_t>(PA_RECORDS) * R);
+  PaItem* items = reinterpret_cast<PaItem*>(tail);              // [PA_RECORDS], 48 bytes each
+  uint64_t* full = reinterpret_cast<uint64_t*>(tail + 384);     // [PA_RECORDS]
+  uint64_t* empty = full + PA_RECORDS;                          // [PA_RECORDS]
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + PA_RECORDS);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < nslot; ++i) {
+    for (int i = 0; i < PA_RECORDS; ++i) {
       mbar_init(full + i, 1);
       mbar_init(empty + i, PA_CONSUMERS);
     }
@@ -322,12 +342,30 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const _
   __syncthreads();
   griddep_wait();
   griddep_launch();
-  const int H = heads * HD, ld = 3 * H;
+  const int H = heads * HD;
   const long long num_items = static_cast<long long>(B) * heads;
 
   if (warp == PA_CONSUMERS) {
-    int slot = 0;
-    uint32_t phase = 0;
+    // All lanes keep the same bookkeeping (it is warp-uniform).  Records are used round-robin;
+    // `oldest` is the record of the oldest item whose tiles have not been taken back yet.
+    int rec = 0, oldest = 0, outstanding = 0;
+    int head = 0, free_tiles = NT;
+    unsigned int wait_parity = 0u;  // bit r: parity that completes the current use of empty[r]
+    unsigned int rec_tiles_lo = 0u, rec_tiles_hi = 0u;  // 4 bits per record: tiles it holds (<= 12)
+    auto get_tiles = [&](int r) { return static_cast<int>(((r < 4 ? rec_tiles_lo >> (8 * r) : rec_tiles_hi >> (8 * (r - 4)))) & 0xffu); };
+    auto set_tiles = [&](int r, int n) {
+      if (r < 4) rec_tiles_lo = (rec_tiles_lo & ~(0xffu << (8 * r))) | (static_cast<unsigned int>(n) << (8 * r));
+      else rec_tiles_hi = (rec_tiles_hi & ~(0xffu << (8 * (r - 4)))) | (static_cast<unsigned int>(n) << (8 * (r - 4)));
+    };
+    // take back the oldest item's tiles once every consumer warp has left it
+    auto reclaim_oldest = [&]() -> bool {
+      if (!mbar_wait(empty + oldest, (wait_parity >> oldest) & 1u, abort_flag, err, SITE_PA_EMPTY)) return false;
+      wait_parity ^= 1u << oldest;
+      free_tiles += get_tiles(oldest);
+      --outstanding;
+      if (++oldest == PA_RECORDS) oldest = 0;
+      return true;
+    };
     bool running = true;
     for (long long it0 = 0; running; it0 += 32) {
       // this CTA's next 32 items, one per lane
@@ -346,23 +384,26 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const _
         my_first = row_start ? row_start[my_b] : my_b * S;
         my_nq = row_start ? klen : S;
       }
-      for (int j = 0; j < 32; ++j) {
-        if (!mbar_wait(empty + slot, phase ^ 1, abort_flag, err, SITE_PA_EMPTY)) { running = false; break; }
-        PaItem* pi = items + slot;
-        if (!__shfl_sync(0xffffffffu, valid ? 1 : 0, j)) {
+      for (int j = 0; j < 32 && running; ++j) {
+        const bool more = __shfl_sync(0xffffffffu, valid ? 1 : 0, j) != 0;
+        const int h = __shfl_sync(0xffffffffu, my_h, j), b = __shfl_sync(0xffffffffu, my_b, j);
+        const int klen = __shfl_sync(0xffffffffu, my_klen, j), first = __shfl_sync(0xffffffffu, my_first, j);
+        const int nq = __shfl_sync(0xffffffffu, my_nq, j), read_mask = __shfl_sync(0xffffffffu, my_mask, j);
+        const int ktiles = (klen + 63) >> 6, qtiles = (nq + 63) >> 6;
+        const int need = more ? 2 * ktiles + qtiles : 0;
+        while (running && outstanding > 0 && (outstanding == PA_RECORDS || free_tiles < need)) running = reclaim_oldest();
+        if (!running) break;
+        PaItem* pi = items + rec;
+        if (!more) {  // no item left for this CTA: tell the consumers and stop
           if (lane == 0) {
             pi->done = 1;
-            mbar_arrive(full + slot);
+            mbar_arrive(full + rec);
           }
           running = false;
           break;
         }
-        const int h = __shfl_sync(0xffffffffu, my_h, j), b = __shfl_sync(0xffffffffu, my_b, j);
-        const int klen = __shfl_sync(0xffffffffu, my_klen, j), first = __shfl_sync(0xffffffffu, my_first, j);
-        const int nq = __shfl_sync(0xffffffffu, my_nq, j), read_mask = __shfl_sync(0xffffffffu, my_mask, j);
-        const int ktiles = (klen + 63) >> 6;
         const int krows = ktiles << 6;
-        float* sBias = sBiasAll + static_cast<size_t>(slot) * R;
+        float* sBias = sBiasAll + static_cast<size_t>(rec) * R;
         const int* mrow = mask + static_cast<size_t>(b) * S;
         unsigned int bits = 0u;
         for (int key = lane; key < krows; key += 32) {
@@ -383,45 +424,52 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const _
           pi->done = 0;
           pi->biased = bits;
           pi->next_q = 0;
-          uint8_t* sK = smem + slot * slot_bytes;
-          uint8_t* sV = sK + static_cast<size_t>(R) * 128;
-          uint8_t* sQi = sV + static_cast<size_t>(R) * 128;
-          const int qtiles = (nq + 63) >> 6;
-          mbar_arrive_expect_tx(full + slot, static_cast<uint32_t>(2 * ktiles + qtiles) * 8192u);
-          for (int t = 0; t < ktiles; ++t) {
-            tma_load_2d(sK + t * 8192, &tmQKV, full + slot, H + h * HD, first + t * 64);
-            tma_load_2d(sV + t * 8192, &tmQKV, full + slot, 2 * H + h * HD, first + t * 64);
-          }
-          for (int t = 0; t < qtiles; ++t) tma_load_2d(sQi + t * 8192, &tmQKV, full + slot, h * HD, first + t * 64);
+          pi->tile0 = head;
+          mbar_arrive_expect_tx(full + rec, static_cast<uint32_t>(need) * 8192u);
+          int t_idx = head;
+          auto next_tile = [&]() { uint8_t* p = ring + static_cast<size_t>(t_idx) * 8192; if (++t_idx == NT) t_idx = 0; return p; };
+          for (int t = 0; t < ktiles; ++t) tma_load_2d(next_tile(), &tmQKV, full + rec, H + h * HD, first + t * 64);
+          for (int t = 0; t < ktiles; ++t) tma_load_2d(next_tile(), &tmQKV, full + rec, 2 * H + h * HD, first + t * 64);
+          for (int t = 0; t < qtiles; ++t) tma_load_2d(next_tile(), &tmQKV, full + rec, h * HD, first + t * 64);
         }
-        if (++slot == nslot) { slot = 0; phase ^= 1; }
+        head += need;
+        if (head >= NT) head -= NT;
+        free_tiles -= need;
+        set_tiles(rec, need);
+        ++outstanding;
+        if (++rec == PA_RECORDS) rec = 0;
       }
     }
   } else {
-    uint8_t* myQ = sQ + warp * 2048;
-    int slot = 0;
+    int rec = 0;
     uint32_t phase = 0;
     for (;;) {
-      if (!mbar_wait(full + slot, phase, abort_flag, err, SITE_PA_FULL)) break;
-      PaItem* pi = items + slot;
+      if (!mbar_wait(full + rec, phase, abort_flag, err, SITE_PA_FULL)) break;
+      PaItem* pi = items + rec;
       if (pi->done) break;
       const int first = pi->first, nq = pi->nq, ktiles = pi->ktiles, qblocks = pi->qblocks, h = pi->h;
       const unsigned int biased = pi->biased;
-      const uint8_t* sK = smem + slot * slot_bytes;
-      const uint8_t* sV = sK + static_cast<size_t>(R) * 128;
-      const uint8_t* sQi = sV + static_cast<size_t>(R) * 128;
-      const float* sBias = sBiasAll + static_cast<size_t>(slot) * R;
+      const int tile0 = pi->tile0;
+      RingTiles tiles;
+      tiles.ring = ring;
+      tiles.nt = NT;
+      tiles.k0 = tile0;
+      tiles.v0 = tile0 + ktiles >= NT ? tile0 + ktiles - NT : tile0 + ktiles;
+      const int q_first = tiles.v0 + ktiles >= NT ? tiles.v0 + ktiles - NT : tiles.v0 + ktiles;
+      const float* sBias = sBiasAll + static_cast<size_t>(rec) * R;
       __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
       for (;;) {
         int qb = 0;
         if (lane == 0) qb = atomicAdd(&pi->next_q, 1);
         qb = __shfl_sync(0xffffffffu, qb, 0);
         if (qb >= qblocks) break;
-        attend_qblock<true>(sK, sV, sBias, biased, myQ, sQi, nullptr, ld, out_base, H, qb * 16, nq, ktiles, lane);
+        // the block's 16 query rows: tile qb / 4 of the item's Q tiles, rows (qb % 4) * 16 ...
+        uint8_t* qrows = const_cast<uint8_t*>(tiles.at(q_first + (qb >> 2))) + (qb & 3) * 2048;
+        attend_qblock<true>(tiles, sBias, biased, qrows, qrows, nullptr, 0, out_base, H, qb * 16, nq, ktiles, lane);
       }
-      __syncwarp();  // every lane has finished reading the slot
-      if (lane == 0) mbar_arrive(empty + slot);
-      if (++slot == nslot) { slot = 0; phase ^= 1; }
+      __syncwarp();  // every lane has finished with the item's tiles
+      if (lane == 0) mbar_arrive(empty + rec);
+      if (++rec == PA_RECORDS) { rec = 0; phase ^= 1; }
     }
   }
 
@@ -653,12 +701,12 @@ int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
 
 bool attention_persist_fits(int S) { return ((S + 63) / 64) * 64 <= PA_MAX_R; }
 
-int attention_bf16_persist(const CUtensorMap* tm_qkv, const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
-                           const int* row_start, const int* sched, __nv_bfloat16* ctx, int B, int S, int heads,
-                           int num_sms, int* err_flag, cudaStream_t stream) {
+int attention_bf16_persist(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
+                           const int* sched, __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int* err_flag,
+                           cudaStream_t stream) {
   if (B <= 0 || S <= 0 || heads <= 0 || !attention_persist_fits(S)) return -1;
   const int R = ((S + 63) / 64) * 64;
-  const int nslot = pa_slots(R);
+  const int NT = pa_ring_tiles(R);
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -670,8 +718,8 @@ int attention_bf16_persist(const CUtensorMap* tm_qkv, const __nv_bfloat16* qkv, 
   }
   const long long items = static_cast<long long>(B) * heads;
   const int grid = static_cast<int>(items < num_sms ? items : num_sms);
-  return launch_pdl(attention_bf16_persist_kernel, dim3(grid), dim3(PA_THREADS), pa_smem_bytes(R, nslot), stream, *tm_qkv,
-                    qkv, mask, kv_len, row_start, sched, ctx, B, S, heads, R, nslot, err_flag) == cudaSuccess ? 1 : -3;
+  return launch_pdl(attention_bf16_persist_kernel, dim3(grid), dim3(PA_THREADS), pa_smem_bytes(R), stream, *tm_qkv, mask,
+                    kv_len, row_start, sched, ctx, B, S, heads, R, NT, err_flag) == cudaSuccess ? 1 : -3;
 }
 
 int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,

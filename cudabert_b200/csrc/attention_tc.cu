@@ -419,8 +419,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
 // tiles are full and loses where a batch's rows are much shorter than the tile grid.  Measured per
 // layer, BERT-large unless noted, in microseconds for tcgen05 / persistent mma.sync / mma.sync with
 // one CTA per item:  S = 512 full rows 95 / - / 165;  S = 512 lengths 64..512: 137 / - / 176;
-// S = 128 full rows 42 / 52 / 59;  BERT-base S = 128 lengths ~N(60, 25): 50 / 45 / 57;
-// S = 200 lengths 16..200: 88 / 68 / 74;  S = 64 lengths 8..64: 185 / 124 / 125.
+// S = 128 full rows 42 / 51 / 59;  BERT-base S = 128 lengths ~N(60, 25): 50 / 42 / 57;
+// S = 200 lengths 16..200: 88 / 57 / 74;  S = 64 lengths 8..64: 185 / 132 / 125.
 // The lengths live on the device, so the choice uses S alone: tcgen05 for long sequences or an S
 // of at least 96 that fills its last query tile to 85 % or more, the persistent kernel otherwise
 // (the per-item kernel beyond the length the persistent one can hold).

@@ -97,9 +97,9 @@ int attention_f32(const float* qkv, const int* mask, const int* kv_len, const in
 // dynamically).  `sched` (2 B entries from row_layout, may be null) orders the items by descending
 // length and says which rows need their mask read; S <= 256.
 bool attention_persist_fits(int S);
-int attention_bf16_persist(const CUtensorMap* tm_qkv, const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
-                           const int* row_start, const int* sched, __nv_bfloat16* ctx, int B, int S, int heads,
-                           int num_sms, int* err_flag, cudaStream_t stream);
+int attention_bf16_persist(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
+                           const int* sched, __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int* err_flag,
+                           cudaStream_t stream);
 enum AttentionKernel : int { ATT_KERNEL_MMA = 1, ATT_KERNEL_TC = 2, ATT_KERNEL_PERSIST = 3 };
 int attention_kernel_for(int S);
 bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H);

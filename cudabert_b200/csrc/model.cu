@@ -451,9 +451,9 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
         CB_LAUNCH(KC_ATTENTION, attention_bf16_tc(&tm_qkv_, d_mask, kv_len_, rs, static_cast<__nv_bfloat16*>(ctx_), B, S,
                                                   heads_, num_sms_, err_dev_, stream_));
       } else if (att_kernel == ATT_KERNEL_PERSIST) {
-        CB_LAUNCH(KC_ATTENTION, attention_bf16_persist(&tm_qkv_, static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_,
-                                                       rs, sched, static_cast<__nv_bfloat16*>(ctx_), B, S, heads_,
-                                                       num_sms_, err_dev_, stream_));
+        CB_LAUNCH(KC_ATTENTION, attention_bf16_persist(&tm_qkv_, d_mask, kv_len_, rs, sched,
+                                                       static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, num_sms_,
+                                                       err_dev_, stream_));
       } else {
         CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_, rs,
                                                static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, stream_));
