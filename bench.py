@@ -15,7 +15,10 @@ One step = one batch of 128 synthetic lines (valid lengths uniform in [16, 200],
   roofline   achieved TFLOP/s of the tcgen05 GEMM kernel (the kernel that holds ~97 % of the
              FLOPs), from CUDA events recorded around every launch on the launching stream
   cpu_baseline  the CPU oracle (a restatement of the reference's bundled PyTorch model) on a
-             bounded sample of the same workload, on this box's host cores
+             bounded sample of the same workload, on this box's host cores; when a build of the
+             reference's own CUDA library is present (oracle/_ref), also that library's
+             sequences/s on one batch of the workload on this GPU and the relative error of this
+             library's pooler output against it (`reference_cuda_library_on_this_gpu`)
 
 N > 1: one process per GPU (torchrun), independent replicas, weak scaling, no data-path
 collective; ranks only meet in a host (gloo) barrier and a max-reduction of the timings.
@@ -145,12 +148,37 @@ def make_batches(n_batches, rank):
 def weights_dir(rank_local, barrier):
     """Seeded synthetic BERT-large weights in the reference's .npy layout, written once per box."""
     d = os.path.join(tempfile.gettempdir(), "cudabert_bench_large_seed%d" % synth.weight_seed(CFG))
-    done = os.path.join(d, ".complete")
+    done = d + ".complete"   # beside the directory: the reference's loader parses every file inside it
     if rank_local == 0 and not os.path.exists(done):
         synth.write_weight_dir(d, synth.make_weights(True, synth.weight_seed(CFG)))
         open(done, "w").close()
     barrier()
     return d
+
+
+def reference_cuda_library(wdir, batch):
+    """The reference's own CUDA library (fp32, cuBLAS), when oracle/_ref holds a build of it, on one
+    batch of the workload on this GPU, in a process of its own: its sequences/s (host arrays in, pooler
+    output out, like `e2e`) and its pooler output.  Reported beside the CPU baseline; never on the
+    product path."""
+    lib = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "libcudaBERT_ref.so")
+    if not os.path.exists(lib):
+        return None
+    tmp = tempfile.mkdtemp(prefix="cudabert_ref_")
+    inp, out = os.path.join(tmp, "in.npz"), os.path.join(tmp, "out.npy")
+    np.savez(inp, ids=batch[0], seg=batch[1], mask=batch[2])
+    try:
+        r = subprocess.run([sys.executable, os.path.join(os.path.dirname(lib), "..", "run_ref_cuda.py"), wdir, "1", inp,
+                            out, "5"], capture_output=True, text=True, timeout=300)
+        if r.returncode != 0:
+            why = (r.stderr.strip().splitlines() or r.stdout.strip().splitlines() or [""])[-1][:200]
+            return {"unavailable": "reference CUDA library exited with %d: %s" % (r.returncode, why)}
+        info = json.loads(r.stdout.strip().splitlines()[-1])
+        return {"value": info["sequences_per_s"], "unit": UNIT, "ms_per_batch": info["ms_per_batch"],
+                "sample": "%d calls of Cuda_Bert on one batch of the workload (padded, fp32, cuBLAS), wall clock"
+                          % info["calls"], "pooled": np.load(out)}
+    except Exception as e:   # timeout, unreadable output
+        return {"unavailable": "reference CUDA library: %s" % type(e).__name__}
 
 
 # ------------------------------------------------------------------ CPU baseline / reference arm
@@ -215,6 +243,11 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     dims = synth.model_dims(True)
     B, S = WL["batch"], WL["seq"]
     wdir = weights_dir(local_rank, barrier)
+    n_pool = 4
+    host = make_batches(n_pool, rank)
+    ref_cuda = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.layers:
+        ref_cuda = reference_cuda_library(wdir, host[0])   # before this process takes device memory
     t_load = time.perf_counter()
     model = pybert.load_model(True, wdir, dev, B, S, precision="bf16", num_layers=args.layers)
     load_seconds = time.perf_counter() - t_load   # .npy directory -> device-resident bf16 K-major weights
@@ -223,8 +256,6 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     C = pybert.num_classes(model)
     stream = torch.cuda.ExternalStream(pybert.stream(model), device=dev)
 
-    n_pool = 4
-    host = make_batches(n_pool, rank)
     devb = [tuple(torch.from_numpy(a).to("cuda:%d" % dev) for a in hb) for hb in host]
     probs = np.zeros((B, C), np.float32)
 
@@ -316,6 +347,20 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     # LayerNorm: read fp16 dense output + fp32 residual, write the bf16 GEMM copy + the fp32 residual copy
     ln_bytes = ln_rows * dims["hidden"] * 12
 
+    if ref_cuda and ref_cuda.get("pooled") is not None:
+        # the reference's own fp32 pooler output for batch 0 against this library's bf16 mode, full size
+        from oracle import bert_oracle
+        ours = np.zeros((B, dims["hidden"]), np.float32)
+        pybert.bert(model, ours, host[0][0], host[0][1], B, S, host[0][2])
+        pybert.check(model)
+        ref = ref_cuda.pop("pooled")
+        # max |a - b| / max |b| (the measure the parity tests bound by 2e-2 on their cases) and the
+        # relative Frobenius norm, over all 128 x 1024 pooler outputs of the batch
+        ref_cuda["rel_err_of_this_library_bf16"] = float(bert_oracle.rel_err(ours, ref))
+        ref_cuda["rel_fro_err_of_this_library_bf16"] = float(np.linalg.norm(ours - ref) / np.linalg.norm(ref))
+    elif ref_cuda:
+        ref_cuda.pop("pooled", None)
+
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
@@ -324,6 +369,8 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
         cpu = {"value": rate, "unit": UNIT, "cores": threads, "kind": "port",
                "sample": "%d sequences of the workload (seq 200, lengths U[16,200]) in one batch, fp32, "
                          "torch CPU ops, %.1f s" % (n_seq, dt)}
+        if ref_cuda:
+            cpu["reference_cuda_library_on_this_gpu"] = ref_cuda
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
