@@ -131,14 +131,12 @@ class queue_manager(object):
 class native_queue_manager(queue_manager):
     """ queue_manager whose buckets live in the library's native batcher (csrc/batcher.cc): the
     same put / enqueue / force_enqueue / get interface and the same batches, batch order and
-    right-trimming, without the per-line Python list handling and the per-batch numpy stacking. """
+    right-trimming, without the per-line Python list handling and the per-batch numpy stacking.
+    The batcher itself is created in the process that first puts a line (the reader stage), so
+    the manager can be handed to spawned processes. """
     def __init__(self, seq_length_split, list_gpu, logger, batchsize, ctx=None, max_seq_length=512):
-        import numpy as np
-        from .cuda_bert import pybert
         ctx = ctx or mp.get_context()
-        self._np = np
-        self._lib = pybert
-        self.boardlines = seq_length_split
+        self.boardlines = list(seq_length_split)
         self.num_containers = len(seq_length_split) - 1
         self.output_queue = ctx.Queue()
         self.force_queue = ctx.Queue(1)
@@ -146,43 +144,63 @@ class native_queue_manager(queue_manager):
         self.logger = logger
         self.batchsize = batchsize
         self.max_seq_length = max_seq_length
-        bounds = np.ascontiguousarray(seq_length_split, dtype=np.int32)
-        self._batcher = pybert.batcher_create(bounds, len(bounds), batchsize, max_seq_length)
-        if not self._batcher:
+        if (self.num_containers < 1 or batchsize < 1 or max_seq_length < 1 or
+                any(b > a for b, a in zip(self.boardlines, self.boardlines[1:]))):
             raise ValueError("bad bucket boundaries %r / batch size %r" % (seq_length_split, batchsize))
+        self._batcher = None
         self._lines = {}   # line number -> Tagged_line, until its batch leaves
+
+    def __getstate__(self):
+        state = dict(self.__dict__)
+        state["_batcher"] = None    # a pointer of the creating process; each process makes its own
+        state["_lines"] = {}
+        return state
+
+    def _native(self):
+        from .cuda_bert import pybert
+        if self._batcher is None:
+            import numpy as np
+            bounds = np.ascontiguousarray(self.boardlines, dtype=np.int32)
+            self._batcher = pybert.batcher_create(bounds, len(bounds), self.batchsize, self.max_seq_length)
+            if not self._batcher:
+                raise ValueError("the native batcher rejected boundaries %r" % (self.boardlines,))
+        return pybert
 
     def __del__(self):
         if getattr(self, "_batcher", None):
-            self._lib.batcher_destroy(self._batcher)
+            from .cuda_bert import pybert
+            pybert.batcher_destroy(self._batcher)
             self._batcher = None
 
     def _row(self, values):
-        a = self._np.ascontiguousarray(values, dtype=self._np.int32)
+        import numpy as np
+        a = np.ascontiguousarray(values, dtype=np.int32)
         return a[:self.max_seq_length] if a.shape[0] > self.max_seq_length else a
 
     def put(self, line):
+        lib = self._native()
         ids, seg, mask = self._row(line.input_ids), self._row(line.segment_ids), self._row(line.input_mask)
         n = min(ids.shape[0], seg.shape[0], mask.shape[0])
-        if self._lib.batcher_put(self._batcher, line.num_line, ids, seg, mask, n) < 0:
+        if lib.batcher_put(self._batcher, line.num_line, ids, seg, mask, n) < 0:
             raise ValueError("line %d: the batcher rejected a row of %d entries" % (line.num_line, n))
         self._lines[line.num_line] = line
         self.enqueue(False)
 
     def force_enqueue(self):
-        self._lib.batcher_flush(self._batcher)
+        self._native().batcher_flush(self._batcher)
         while self.enqueue(True) != -1:
             pass
 
     def enqueue(self, is_force):
         from ctypes import byref, c_int, c_longlong
-        np = self._np
+        import numpy as np
+        lib = self._native()
         rows, seq, first = c_int(0), c_int(0), c_longlong(0)
-        if self._lib.batcher_next(self._batcher, byref(rows), byref(seq), byref(first)) != 1:
+        if lib.batcher_next(self._batcher, byref(rows), byref(seq), byref(first)) != 1:
             return -1
         index = np.empty(rows.value, np.int64)
         tensor = [np.empty((rows.value, seq.value), np.int32) for _ in range(3)]
-        got = self._lib.batcher_pop(self._batcher, index, tensor[0], tensor[1], tensor[2])
+        got = lib.batcher_pop(self._batcher, index, tensor[0], tensor[1], tensor[2])
         assert got == rows.value
         lines = [self._lines.pop(int(i)) for i in index]
         self.input_queue.put(Batch_Packed(lines, tensor))   # bounded queue: blocks while the GPUs are busy

@@ -99,6 +99,26 @@ def test_engine_orders_output_and_shards_batches(tmp_path, gpus, alert, native):
         assert got == "%s\t%d\t%d" % (raw, sum(toks), len(toks))
 
 
+def test_engine_with_spawned_stages(tmp_path):
+    """Start method "spawn" (what a parent that already holds a CUDA context needs): everything the
+    stages receive has to survive pickling, the native batcher included."""
+    src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
+    lines = _write_input(src, 120)
+    cfg = _config([0, 1])
+    cfg.mp_start_method = "spawn"
+    eng = Engine(cfg)
+    eng.set_cuda_model(FakeReplica)
+    eng.set_finetune_layer(Head)
+    eng.set_tokenlizer_function(tokenize)
+    eng.set_output_function(output_line)
+    eng.run(src, dst)
+    out = open(dst).read().splitlines()
+    assert len(out) == len(lines)
+    for raw, got in zip(lines, out):
+        toks = [int(t) for t in raw.split()]
+        assert got == "%s\t%d\t%d" % (raw, sum(toks), len(toks))
+
+
 def test_engine_reports_a_dead_replica(tmp_path):
     src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
     _write_input(src, 200)
