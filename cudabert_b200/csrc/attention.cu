@@ -45,31 +45,37 @@ struct RingTiles {
   __device__ __forceinline__ const uint8_t* v(int t) const { return at(v0 + t); }
 };
 
-// One 16-query block of one (sequence, head) against the sequence's keys and values resident in
-// shared memory: QK^T -> scale + mask bias -> online softmax -> P.V over 64-key tiles, then a
-// coalesced store of the 16 x 64 block.  Run by one warp; `stage` is 2 KB of shared memory that
-// only this warp touches while it works on the block.  The queries come either from global memory
-// (`sQ` null: `base` points at the first Q element of the sequence's first row, row stride `ld`;
-// they pass through `stage`) or from shared memory (`sQ`: the block's own 16 rows of a Q tile,
-// which may be `stage` itself).  `out_base` points at the sequence's first output element (row
-// stride `H`).  Bit t of `biased` says that key tile t needs the bias in `sBias`.
-template <bool Q_IN_SMEM, typename Tiles>
+// One block of MB x 16 queries of one (sequence, head) against the sequence's keys and values
+// resident in shared memory: QK^T -> scale + mask bias -> online softmax -> P.V over 64-key tiles,
+// then a coalesced store of the (MB x 16) x 64 block.  Run by one warp.  With MB = 2 every K / V
+// fragment a warp loads with ldmatrix feeds four MMAs instead of two and the warp has twice as
+// many independent accumulator chains, at twice the registers (so half as many warps fit).
+// `stage` is MB x 2 KB of shared memory that only this warp touches while it works on the block.
+// The queries come either from global memory (`sQ` null: `base` points at the first Q element of
+// the sequence's first row, row stride `ld`; they pass through `stage`) or from shared memory
+// (`sQ`: the block's own rows of a Q tile, which may be `stage` itself).  `out_base` points at the
+// sequence's first output element (row stride `H`).  Bit t of `biased` says that key tile t needs
+// the bias in `sBias`.
+template <int MB, bool Q_IN_SMEM, typename Tiles>
 __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __restrict__ sBias, unsigned int biased,
                                               uint8_t* __restrict__ stage, const uint8_t* __restrict__ sQ,
                                               const __nv_bfloat16* __restrict__ base, int ld,
                                               __nv_bfloat16* __restrict__ out_base, int H, int q0, int nq,
                                               int ktiles, int lane) {
   const float scale = 0.125f * LOG2E;
-  uint32_t qf[4][4];
+  uint32_t qf[MB][4][4];
   if (Q_IN_SMEM) {
     // rows at or beyond nq hold other rows' (finite) values; their results are never stored
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(sQ + swz(lane & 15, kk * 2 + (lane >> 4))));
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        ldmatrix_x4(qf[mb][kk], smem_u32(sQ + swz(mb * 16 + (lane & 15), kk * 2 + (lane >> 4))));
   } else {
-    // stage the 16 x 64 Q block: lane l moves chunk l % 8 of rows l / 8 + 4 i
+    // stage the Q block: lane l moves chunk l % 8 of rows l / 8 + 4 i
     __syncwarp();
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 4 * MB; ++i) {
       const int r = (lane >> 3) + 4 * i, c = lane & 7;
       uint4 t = make_uint4(0u, 0u, 0u, 0u);
       if (q0 + r < nq) t = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + r) * ld + c * 8));
@@ -77,23 +83,32 @@ __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __
     }
     __syncwarp();
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) ldmatrix_x4(qf[kk], smem_u32(stage + swz(lane & 15, kk * 2 + (lane >> 4))));
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        ldmatrix_x4(qf[mb][kk], smem_u32(stage + swz(mb * 16 + (lane & 15), kk * 2 + (lane >> 4))));
   }
 
-  float o[8][4];
+  float o[MB][8][4];
+  float m_run[MB][2], l_run[MB][2];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY};
-  float l_run[2] = {0.f, 0.f};
+  for (int mb = 0; mb < MB; ++mb) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[mb][i][0] = o[mb][i][1] = o[mb][i][2] = o[mb][i][3] = 0.f;
+    m_run[mb][0] = m_run[mb][1] = -INFINITY;
+    l_run[mb][0] = l_run[mb][1] = 0.f;
+  }
 
   for (int t = 0; t < ktiles; ++t) {
     const int k0 = t << 6;
     const uint8_t* kt = tiles.k(t);
     const uint8_t* vt = tiles.v(t);
     // S = Q K^T for 64 keys: 8 n-tiles of 8 keys
-    float s[8][4];
+    float s[MB][8][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s[mb][i][0] = s[mb][i][1] = s[mb][i][2] = s[mb][i][3] = 0.f;
     const int mid = lane >> 3;
 #pragma unroll
     for (int nb = 0; nb < 4; ++nb) {
@@ -101,66 +116,72 @@ __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __
       for (int kk = 0; kk < 4; ++kk) {
         uint32_t kf[4];
         ldmatrix_x4(kf, smem_u32(kt + swz(nb * 16 + (mid >> 1) * 8 + (lane & 7), kk * 2 + (mid & 1))));
-        mma_bf16_16816(s[2 * nb], qf[kk], kf[0], kf[1]);
-        mma_bf16_16816(s[2 * nb + 1], qf[kk], kf[2], kf[3]);
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          mma_bf16_16816(s[mb][2 * nb], qf[mb][kk], kf[0], kf[1]);
+          mma_bf16_16816(s[mb][2 * nb + 1], qf[mb][kk], kf[2], kf[3]);
+        }
       }
     }
     // running max of the scores in the log2 domain.  A tile whose keys are all valid keeps the
     // raw dot products (the scale is folded into the exponential's multiply-add below); any
     // other tile gets scale and mask bias applied here.
     const bool plain = ((biased >> t) & 1u) == 0u;
-    float tmax[2] = {-INFINITY, -INFINITY};
-    if (plain) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
-        tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
-      }
-      tmax[0] *= scale;  // scale > 0: max(scale * s) = scale * max(s)
-      tmax[1] *= scale;
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float2 bb = *reinterpret_cast<const float2*>(sBias + k0 + i * 8 + 2 * (lane & 3));
-        s[i][0] = fmaf(s[i][0], scale, bb.x);
-        s[i][1] = fmaf(s[i][1], scale, bb.y);
-        s[i][2] = fmaf(s[i][2], scale, bb.x);
-        s[i][3] = fmaf(s[i][3], scale, bb.y);
-        tmax[0] = fmaxf(tmax[0], fmaxf(s[i][0], s[i][1]));
-        tmax[1] = fmaxf(tmax[1], fmaxf(s[i][2], s[i][3]));
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
-      tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
-    }
-    float alpha[2], m_new[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      m_new[r] = fmaxf(m_run[r], tmax[r]);
-      // tile 0 always holds key 0 with a finite bias, so m_new is finite from the first tile on
-      alpha[r] = ex2_approx(m_run[r] - m_new[r]);
-      m_run[r] = m_new[r];
-      l_run[r] *= alpha[r];
-    }
-    uint32_t pf[4][4];
     const float e_scale = plain ? scale : 1.0f;  // p = 2^(s * e_scale - m)
+    uint32_t pf[MB][4][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float p0 = ex2_approx(fmaf(s[i][0], e_scale, -m_new[0]));
-      const float p1 = ex2_approx(fmaf(s[i][1], e_scale, -m_new[0]));
-      const float p2 = ex2_approx(fmaf(s[i][2], e_scale, -m_new[1]));
-      const float p3 = ex2_approx(fmaf(s[i][3], e_scale, -m_new[1]));
-      l_run[0] += p0 + p1;
-      l_run[1] += p2 + p3;
-      pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
-      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
-    }
+    for (int mb = 0; mb < MB; ++mb) {
+      float tmax[2] = {-INFINITY, -INFINITY};
+      if (plain) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        for (int i = 0; i < 8; ++i) {
+          tmax[0] = fmaxf(tmax[0], fmaxf(s[mb][i][0], s[mb][i][1]));
+          tmax[1] = fmaxf(tmax[1], fmaxf(s[mb][i][2], s[mb][i][3]));
+        }
+        tmax[0] *= scale;  // scale > 0: max(scale * s) = scale * max(s)
+        tmax[1] *= scale;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 bb = *reinterpret_cast<const float2*>(sBias + k0 + i * 8 + 2 * (lane & 3));
+          s[mb][i][0] = fmaf(s[mb][i][0], scale, bb.x);
+          s[mb][i][1] = fmaf(s[mb][i][1], scale, bb.y);
+          s[mb][i][2] = fmaf(s[mb][i][2], scale, bb.x);
+          s[mb][i][3] = fmaf(s[mb][i][3], scale, bb.y);
+          tmax[0] = fmaxf(tmax[0], fmaxf(s[mb][i][0], s[mb][i][1]));
+          tmax[1] = fmaxf(tmax[1], fmaxf(s[mb][i][2], s[mb][i][3]));
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+        tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+      }
+      float alpha[2], m_new[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        m_new[r] = fmaxf(m_run[mb][r], tmax[r]);
+        // tile 0 always holds key 0 with a finite bias, so m_new is finite from the first tile on
+        alpha[r] = ex2_approx(m_run[mb][r] - m_new[r]);
+        m_run[mb][r] = m_new[r];
+        l_run[mb][r] *= alpha[r];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p0 = ex2_approx(fmaf(s[mb][i][0], e_scale, -m_new[0]));
+        const float p1 = ex2_approx(fmaf(s[mb][i][1], e_scale, -m_new[0]));
+        const float p2 = ex2_approx(fmaf(s[mb][i][2], e_scale, -m_new[1]));
+        const float p3 = ex2_approx(fmaf(s[mb][i][3], e_scale, -m_new[1]));
+        l_run[mb][0] += p0 + p1;
+        l_run[mb][1] += p2 + p3;
+        pf[mb][i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+        pf[mb][i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        o[mb][i][0] *= alpha[0]; o[mb][i][1] *= alpha[0];
+        o[mb][i][2] *= alpha[1]; o[mb][i][3] *= alpha[1];
+      }
     }
     // O += P V : 4 key steps of 16, 4 pairs of 8-wide d tiles
 #pragma unroll
@@ -169,30 +190,38 @@ __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __
       for (int db = 0; db < 4; ++db) {
         uint32_t vf[4];
         ldmatrix_x4_trans(vf, smem_u32(vt + swz(j * 16 + (mid & 1) * 8 + (lane & 7), db * 2 + (mid >> 1))));
-        mma_bf16_16816(o[2 * db], pf[j], vf[0], vf[1]);
-        mma_bf16_16816(o[2 * db + 1], pf[j], vf[2], vf[3]);
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          mma_bf16_16816(o[mb][2 * db], pf[mb][j], vf[0], vf[1]);
+          mma_bf16_16816(o[mb][2 * db + 1], pf[mb][j], vf[2], vf[3]);
+        }
       }
     }
   }
 
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-  }
-  const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
-  // stage the 16 x 64 output block in the Q buffer, then store it with 16-byte row-contiguous pieces
+  // stage the output block in the Q buffer, then store it with 16-byte row-contiguous pieces
   __syncwarp();
   const int g = lane >> 2, t4 = lane & 3;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    // columns i*8 + 2*t4, +1 of rows g and g + 8: chunk i, byte offset 4 * t4 inside the chunk
-    *reinterpret_cast<uint32_t*>(stage + swz(g, i) + 4 * t4) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
-    *reinterpret_cast<uint32_t*>(stage + swz(g + 8, i) + 4 * t4) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+  for (int mb = 0; mb < MB; ++mb) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[mb][r] += __shfl_xor_sync(0xffffffffu, l_run[mb][r], 1);
+      l_run[mb][r] += __shfl_xor_sync(0xffffffffu, l_run[mb][r], 2);
+    }
+    const float inv0 = 1.0f / l_run[mb][0], inv1 = 1.0f / l_run[mb][1];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      // columns i*8 + 2*t4, +1 of rows g and g + 8: chunk i, byte offset 4 * t4 inside the chunk
+      *reinterpret_cast<uint32_t*>(stage + swz(mb * 16 + g, i) + 4 * t4) =
+          pack_bf16(o[mb][i][0] * inv0, o[mb][i][1] * inv0);
+      *reinterpret_cast<uint32_t*>(stage + swz(mb * 16 + g + 8, i) + 4 * t4) =
+          pack_bf16(o[mb][i][2] * inv1, o[mb][i][3] * inv1);
+    }
   }
   __syncwarp();
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 4 * MB; ++i) {
     const int r = (lane >> 3) + 4 * i, c = lane & 7;
     if (q0 + r < nq)
       *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(q0 + r) * H + c * 8) =
@@ -260,8 +289,8 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   const int qblocks = (nq + 15) >> 4;
   __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
   for (int qb = warp; qb < qblocks; qb += nwarps)
-    attend_qblock<false>(ContigTiles{sK, sV}, sBias, biased, myQ, nullptr, base, ld, out_base, H, qb * 16, nq, ktiles,
-                         lane);
+    attend_qblock<1, false>(ContigTiles{sK, sV}, sBias, biased, myQ, nullptr, base, ld, out_base, H, qb * 16, nq,
+                            ktiles, lane);
 }
 
 // ---------------------------------------------------------------- persistent variant
@@ -283,14 +312,20 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
 //              free, writes the per-key bias (reading the mask only for a sequence that has
 //              masked keys below its last valid one), and issues the TMA box copies, which all
 //              complete on the record's `full` mbarrier, so no consumer waits on a global load;
-//   consumers  wait for `full`, then draw 16-query blocks of the item from a shared-memory
+//   consumers  wait for `full`, then draw query blocks of the item from a shared-memory
 //              counter until none is left, arrive on `empty` and move to the next record, so a
 //              warp that finds no block in a short item is already working on the next one.  A
 //              block's output is staged in the block's own Q rows, which nobody else reads.
 // Rows of a K / V tile beyond the sequence's last key hold whatever follows in the buffer (finite
 // activations of other rows, or zero fill beyond the tensor); their bias is -inf, so their
 // probability is 0.
-constexpr int PA_CONSUMERS = 15;
+// Work unit of a consumer warp: PA_MB 16-query blocks.  Measured per layer on the benchmark workload
+// (S = 200, lengths 16..200): 15 warps x 1 block 57 us, 7 warps x 2 blocks (254 registers) 59 us; the
+// two tie within a few percent on every shape tried, so the kernel keeps the smaller unit, which
+// wastes less on ragged lengths.
+constexpr int PA_MB = 1;
+constexpr int PA_QROWS = PA_MB * 16;
+constexpr int PA_CONSUMERS = PA_MB == 1 ? 15 : 7;  // what the register file holds at 128 / 254 registers
 constexpr int PA_THREADS = (PA_CONSUMERS + 1) * 32;
 constexpr int PA_MAX_R = 256;   // longest sequence: two of them (12 tiles each) fit in the ring
 constexpr int PA_RECORDS = 8;   // items in flight
@@ -419,7 +454,7 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const i
           pi->first = first;
           pi->nq = nq;
           pi->ktiles = ktiles;
-          pi->qblocks = (nq + 15) >> 4;
+          pi->qblocks = (nq + PA_QROWS - 1) / PA_QROWS;
           pi->h = h;
           pi->done = 0;
           pi->biased = bits;
@@ -463,9 +498,11 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const i
         if (lane == 0) qb = atomicAdd(&pi->next_q, 1);
         qb = __shfl_sync(0xffffffffu, qb, 0);
         if (qb >= qblocks) break;
-        // the block's 16 query rows: tile qb / 4 of the item's Q tiles, rows (qb % 4) * 16 ...
-        uint8_t* qrows = const_cast<uint8_t*>(tiles.at(q_first + (qb >> 2))) + (qb & 3) * 2048;
-        attend_qblock<true>(tiles, sBias, biased, qrows, qrows, nullptr, 0, out_base, H, qb * 16, nq, ktiles, lane);
+        // the block's query rows inside the item's Q tiles (a tile holds 64 / PA_QROWS blocks)
+        constexpr int PER_TILE = 64 / PA_QROWS;
+        uint8_t* qrows = const_cast<uint8_t*>(tiles.at(q_first + qb / PER_TILE)) + (qb % PER_TILE) * (PA_QROWS * 128);
+        attend_qblock<PA_MB, true>(tiles, sBias, biased, qrows, qrows, nullptr, 0, out_base, H, qb * PA_QROWS, nq,
+                                   ktiles, lane);
       }
       __syncwarp();  // every lane has finished with the item's tiles
       if (lane == 0) mbar_arrive(empty + rec);
