@@ -168,8 +168,11 @@ class native_queue_manager(queue_manager):
 
     def __del__(self):
         if getattr(self, "_batcher", None):
-            from .cuda_bert import pybert
-            pybert.batcher_destroy(self._batcher)
+            try:
+                from .cuda_bert import pybert
+                pybert.batcher_destroy(self._batcher)
+            except ImportError:   # interpreter shutdown: the process's memory goes with it
+                pass
             self._batcher = None
 
     def _row(self, values):
@@ -181,8 +184,10 @@ class native_queue_manager(queue_manager):
         lib = self._native()
         ids, seg, mask = self._row(line.input_ids), self._row(line.segment_ids), self._row(line.input_mask)
         n = min(ids.shape[0], seg.shape[0], mask.shape[0])
-        if lib.batcher_put(self._batcher, line.num_line, ids, seg, mask, n) < 0:
+        length = lib.batcher_put(self._batcher, line.num_line, ids, seg, mask, n)
+        if length < 0:
             raise ValueError("line %d: the batcher rejected a row of %d entries" % (line.num_line, n))
+        line.length = length
         self._lines[line.num_line] = line
         self.enqueue(False)
 
@@ -203,6 +208,8 @@ class native_queue_manager(queue_manager):
         got = lib.batcher_pop(self._batcher, index, tensor[0], tensor[1], tensor[2])
         assert got == rows.value
         lines = [self._lines.pop(int(i)) for i in index]
+        for tl in lines:
+            tl.drop_features()    # they are in `tensor` now; pickling them again per line is the reader's main cost
         self.input_queue.put(Batch_Packed(lines, tensor))   # bounded queue: blocks while the GPUs are busy
         return int(first.value)
 
@@ -286,7 +293,8 @@ class Engine(object):
                 line_data=user_output[1],
                 input_ids=user_output[2],
                 input_mask=user_output[3],
-                segment_ids=user_output[4])
+                segment_ids=user_output[4],
+                measure=not isinstance(self.handle, native_queue_manager))
 
     def _engine_preprocess(self, input_file):
         config = self.config

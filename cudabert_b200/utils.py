@@ -38,15 +38,21 @@ class Batch_Packed(object):
 class Tagged_line(object):
     """A single set of features of data."""
 
-    def __init__(self, num_line, line_data, input_ids, input_mask, segment_ids):
+    def __init__(self, num_line, line_data, input_ids, input_mask, segment_ids, measure=True):
         self.num_line = num_line
         self.line_data = line_data
         self.input_ids = input_ids
         self.input_mask = input_mask
         self.segment_ids = segment_ids
         self.length = 512
-        self._get_length()
+        if measure:          # the native batcher measures the line itself
+            self._get_length()
         self.output = None
+
+    def drop_features(self):
+        """Forget the token arrays once they are inside a batch tensor: what travels on to the
+        replica and the writer is the line number, the raw line and, later, the output."""
+        self.input_ids = self.input_mask = self.segment_ids = None
 
     def _get_length(self):
         """ Useful length of the ids: 1 + index of the last mask entry equal to 1
