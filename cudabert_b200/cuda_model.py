@@ -82,3 +82,43 @@ class Cuda_BERT(object):
             self.close()
         except Exception:
             pass
+
+
+class Cuda_BERT_Pool(object):
+    """Several replicas inside ONE process, one host thread per replica (ctypes releases the GIL
+    during a call): ``encode`` / ``classify`` cut the batch into contiguous row shards, run them
+    concurrently and gather the rows on the host in the original order.  It is the in-process form
+    of the engine's multi-GPU mode (reference: one OS process per GPU id, engine.py:385-397): batch
+    sharding over independent replicas, no collective, nothing shared between GPUs.  ``gpus`` may
+    name a GPU more than once (two replicas on one device share it through their own streams)."""
+
+    def __init__(self, gpus, config):
+        from concurrent.futures import ThreadPoolExecutor
+        if not gpus:
+            raise ValueError("Cuda_BERT_Pool needs at least one GPU id")
+        self.replicas = [Cuda_BERT(g, config) for g in gpus]
+        self.hidden_size = self.replicas[0].hidden_size
+        self._threads = ThreadPoolExecutor(max_workers=len(self.replicas))
+
+    def _shards(self, input_tensor):
+        rows = np.asarray(input_tensor[0]).shape[0]
+        n = min(len(self.replicas), rows)
+        bounds = [rows * i // n for i in range(n + 1)]
+        return [[None if t is None else np.asarray(t)[bounds[i]:bounds[i + 1]] for t in input_tensor]
+                for i in range(n)]
+
+    def _run(self, method, input_tensor):
+        shards = self._shards(input_tensor)
+        futures = [self._threads.submit(getattr(r, method), s) for r, s in zip(self.replicas, shards)]
+        return np.concatenate([f.result() for f in futures], axis=0)
+
+    def encode(self, input_tensor):
+        return self._run("encode", input_tensor)
+
+    def classify(self, input_tensor):
+        return self._run("classify", input_tensor)
+
+    def close(self):
+        for r in self.replicas:
+            r.close()
+        self._threads.shutdown(wait=True)

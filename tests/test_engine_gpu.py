@@ -91,3 +91,27 @@ def test_engine_run_matches_direct_calls(tmp_path, weight_dirs, n_gpus):
             np.testing.assert_allclose(got, want, rtol=2e-6, atol=1e-7)
     finally:
         direct.close()
+
+
+@pytest.mark.parametrize("gpus", [[0, 0], [0, 1], [0, 0, 0]])
+def test_replica_pool_in_one_process(weight_dirs, gpus):
+    """Thread-per-replica pool: rows sharded over the replicas and gathered in order give exactly
+    what one replica returns for the whole batch, for batches smaller than the pool too."""
+    import torch
+    from cudabert_b200.cuda_model import Cuda_BERT_Pool
+    if torch.cuda.device_count() <= max(gpus):
+        pytest.skip("needs %d GPUs" % (max(gpus) + 1))
+    cfg = _config([0], weight_dirs("base_affine"))
+    ids, seg, mask = cases.case_inputs("c0_affine")
+    single = Cuda_BERT(0, cfg)
+    pool = Cuda_BERT_Pool(gpus, cfg)
+    try:
+        want = single.encode([ids, seg, mask])
+        for _ in range(3):      # repeated calls reuse the threads and the handles
+            np.testing.assert_array_equal(pool.encode([ids, seg, mask]), want)
+        np.testing.assert_array_equal(pool.encode([ids[:2], seg[:2], mask[:2]]), want[:2])
+        np.testing.assert_array_equal(pool.encode([ids[:1], seg[:1], None]), single.encode([ids[:1], seg[:1], None]))
+        np.testing.assert_array_equal(pool.classify([ids, seg, mask]), single.classify([ids, seg, mask]))
+    finally:
+        pool.close()
+        single.close()
