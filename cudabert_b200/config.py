@@ -39,6 +39,9 @@ class Engin_Config(object):
         current_path = os.path.abspath(__file__)
         self.cubert_pth = os.path.abspath(os.path.dirname(current_path)) + "/cuda_bert"
 
+        "If a replica's process dies: resume from the last written line on the remaining GPUs."
+        self.resume_without_dead_gpu = True
+
         "Bucket and trim batches in the library's native batcher (False: the Python classes)."
         self.native_batcher = True
 

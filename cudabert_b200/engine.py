@@ -18,10 +18,12 @@ the input order in a sliding window and applies back-pressure through ``alert_si
 
 Differences from the reference, on purpose: workers block on the queue instead of busy-polling
 ``empty()`` (engine.py:253-264); every stage is joined and a stage that dies is detected by the
-parent, which stops the others and raises instead of waiting forever on a sentinel count
-(engine.py:312, 401); the standard ``logging`` module replaces the reference's colour logger.
+parent instead of being waited for forever on a sentinel count (engine.py:312, 401): a dead replica
+is dropped and the run resumes after the last line written, anything else stops the run with an
+error; the standard ``logging`` module replaces the reference's colour logger.
 """
 import copy
+import os
 import logging
 import multiprocessing as mp
 import queue as pyqueue
@@ -296,13 +298,15 @@ class Engine(object):
                 segment_ids=user_output[4],
                 measure=not isinstance(self.handle, native_queue_manager))
 
-    def _engine_preprocess(self, input_file):
+    def _engine_preprocess(self, input_file, start_line=0):
         config = self.config
         handle = self.handle
         with open(input_file, 'r', encoding='utf-8') as f:
             if self.config.skip_first_line:
                 f.readline()
-            index = 0
+            for _ in range(start_line):      # a resumed run: these lines are in the output file already
+                f.readline()
+            index = start_line
             for line in f:
                 handle.put(self._generate_tagged_line(self.tokenlizer_line(config.max_seq_length, line, index)))
                 index += 1
@@ -316,12 +320,14 @@ class Engine(object):
             handle.input_queue.put(_DONE)
         self.logger.info("engine_preprocess done: %d lines", index)
 
-    def _engine_postprocess(self, output_file):
+    def _engine_postprocess(self, output_file, start_line=0, progress=None):
+        """ progress: shared [lines written, bytes written], updated after every flush, so that the
+        parent can cut the file back to a consistent state and resume if a replica dies. """
         handle = self.handle
         done = 0
         window = {}            # line number -> formatted text, for lines that arrived early
-        next_line = 0
-        with open(output_file, 'w', encoding='utf-8') as f:
+        next_line = start_line
+        with open(output_file, 'a' if start_line else 'w', encoding='utf-8') as f:
             while done < len(self.config.gpu):
                 packed_batch = handle.output_queue.get()
                 if packed_batch == _DONE:
@@ -335,6 +341,10 @@ class Engine(object):
                 while next_line in window:
                     f.write(window.pop(next_line) + '\n')
                     next_line += 1
+                if progress is not None:
+                    f.flush()
+                    with progress.get_lock():
+                        progress[0], progress[1] = next_line, os.fstat(f.fileno()).st_size
                 if len(window) > self.config.alert_size:
                     # too many lines wait for a slow bucket: make the reader flush its partial buckets
                     try:
@@ -347,16 +357,42 @@ class Engine(object):
 
     # ------------------------------------------------------------------ driver
     def run(self, input_file, output_file):
+        """ Runs the pipeline.  If a replica's process dies, the stages are stopped, the output file
+        is cut back to the last line the writer had flushed, and the pipeline starts again from the
+        next input line on the remaining GPUs (``config.resume_without_dead_gpu``, default True;
+        the reference waits forever for the dead replica's end marker, engine.py:312).  A reader or
+        writer that dies, or the last replica dying, ends the run with RuntimeError. """
         assert(type(output_file) == str)
         assert(type(input_file) == str)
-        self._init()
         self.config.input_file = input_file
         self.config.output_file = output_file
+        start_line = 0
+        while True:
+            failed, progress = self._run_once(input_file, output_file, start_line)
+            if failed is None:
+                break
+            name, code = failed
+            gpus = list(self.config.gpu)
+            dead = [g for g in gpus if name == "gpu%s" % g]
+            if not (dead and len(gpus) > 1 and getattr(self.config, "resume_without_dead_gpu", True)):
+                raise RuntimeError("engine stage %s died with exit code %s; the run was stopped" % failed)
+            start_line, offset = int(progress[0]), int(progress[1])
+            with open(output_file, 'a', encoding='utf-8') as f:
+                f.truncate(offset if start_line else 0)
+            self.config.gpu = [g for g in gpus if g not in dead]
+            self.logger.warning("replica on gpu %s died with exit code %s: resuming at line %d on gpus %s",
+                                dead[0], code, start_line, self.config.gpu)
+        self.logger.info("ALL JOBS DONE")
+
+    def _run_once(self, input_file, output_file, start_line):
+        self._init()
         ctx = self._ctx
-        procs = [("reader", ctx.Process(target=self._engine_preprocess, args=(input_file,), daemon=True))]
+        progress = ctx.Array('q', [start_line, 0])
+        procs = [("reader", ctx.Process(target=self._engine_preprocess, args=(input_file, start_line), daemon=True))]
         for num_gpu in self.config.gpu:
             procs.append(("gpu%s" % num_gpu, ctx.Process(target=self._engine_model, args=(num_gpu,), daemon=True)))
-        procs.append(("writer", ctx.Process(target=self._engine_postprocess, args=(output_file,), daemon=True)))
+        procs.append(("writer", ctx.Process(target=self._engine_postprocess, args=(output_file, start_line, progress),
+                                            daemon=True)))
         for _, p in procs:
             p.start()
         failed = None
@@ -375,7 +411,7 @@ class Engine(object):
                     p.terminate()
             for _, p in procs:
                 p.join(5)
-            raise RuntimeError("engine stage %s died with exit code %s; the run was stopped" % failed)
+            return failed, progress
         for _, p in procs:
             p.join()
-        self.logger.info("ALL JOBS DONE")
+        return None, progress

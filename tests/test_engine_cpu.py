@@ -119,10 +119,44 @@ def test_engine_with_spawned_stages(tmp_path):
         assert got == "%s\t%d\t%d" % (raw, sum(toks), len(toks))
 
 
+def test_engine_resumes_without_a_dead_replica(tmp_path):
+    """The replica on gpu 1 disappears at its first batch: the run is cut back to the last written
+    line and finished on gpu 0 alone; every line is in the output exactly once and in order."""
+    src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
+    lines = _write_input(src, 300)
+    cfg = _config([0, 1])
+    eng = Engine(cfg)
+    eng.set_cuda_model(DyingReplica)
+    eng.set_finetune_layer(Head)
+    eng.set_tokenlizer_function(tokenize)
+    eng.set_output_function(output_line)
+    eng.run(src, dst)
+    assert cfg.gpu == [0]
+    out = open(dst).read().splitlines()
+    assert len(out) == len(lines)
+    for raw, got in zip(lines, out):
+        toks = [int(t) for t in raw.split()]
+        assert got == "%s\t%d\t%d" % (raw, sum(toks), len(toks))
+
+
 def test_engine_reports_a_dead_replica(tmp_path):
     src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
     _write_input(src, 200)
-    eng = Engine(_config([0, 1]))
+    cfg = _config([0, 1])
+    cfg.resume_without_dead_gpu = False
+    eng = Engine(cfg)
+    eng.set_cuda_model(DyingReplica)
+    eng.set_finetune_layer(Head)
+    eng.set_tokenlizer_function(tokenize)
+    eng.set_output_function(output_line)
+    with pytest.raises(RuntimeError, match="gpu1 died with exit code 7"):
+        eng.run(src, dst)
+
+
+def test_engine_stops_when_its_only_replica_dies(tmp_path):
+    src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
+    _write_input(src, 50)
+    eng = Engine(_config([1]))
     eng.set_cuda_model(DyingReplica)
     eng.set_finetune_layer(Head)
     eng.set_tokenlizer_function(tokenize)
