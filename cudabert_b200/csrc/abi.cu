@@ -224,6 +224,8 @@ int cudabert_sync(void* model) {
 float* cudabert_pooled_dev(void* model) { return model ? as_model(model)->pooled_dev() : nullptr; }
 void* cudabert_stream(void* model) { return model ? static_cast<void*>(as_model(model)->stream()) : nullptr; }
 long cudabert_launch_count(void* model) { return model ? as_model(model)->launches_last_forward() : 0; }
+long cudabert_graph_captures(void* model) { return model ? as_model(model)->graph_captures() : 0; }
+long cudabert_graph_replays(void* model) { return model ? as_model(model)->graph_replays() : 0; }
 void cudabert_profile_enable(void* model, int on) {
   if (model) as_model(model)->set_profiling(on != 0);
 }

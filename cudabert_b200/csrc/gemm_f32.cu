@@ -115,47 +115,64 @@ gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
   }
 }
 
-// Pooler: out[b, :] = tanh(x[b * ldx + 0..H) . W[H, H] + bias), fp32, for the few rows of a batch
+// Pooler: out[b, :] = tanh(x[first row of sequence b, 0..H) . W[H, H] + bias), fp32
 // (reference: copy_pooler + op_Linear + op_Tanh, ops/elementwise.cu:6-32, 57-70, utils/bert.cu:239-247).
-// 16 rows x 64 columns per CTA so that a batch of 128 fills 128 CTAs; thread = 1 row x 4 columns.
-constexpr int PM = 16, PN = 64, PK = 32;
+// It is a skinny product (B rows against an H x H matrix that has to be streamed once), so the work
+// is cut for parallel weight streaming, not for arithmetic: a CTA owns PN = 64 output columns and
+// PB = 8 sequences; its 256 threads are 4 slices of the reduction dimension x 64 columns, so that
+// consecutive threads read consecutive weights of one row (coalesced), every weight is loaded
+// once per CTA and used for 8 sequences, the 8 inputs of a k are a shared-memory broadcast, and the
+// four partial sums meet in shared memory at the end.
+constexpr int PN = 64, PB = 8, PSLICES = 4;
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(PN * PSLICES)
 pooler_f32_kernel(const float* __restrict__ x, int rows_per_seq, const int* __restrict__ row_start,
                   const float* __restrict__ W, const float* __restrict__ bias, float* __restrict__ out, int B, int H) {
-  __shared__ float xs[PM][PK + 1];
-  __shared__ __align__(16) float ws[PK][PN];
+  extern __shared__ float pool_smem[];
+  float* xs = pool_smem;                 // [H][PB]: the CTA's 8 input rows, k-major
+  float* part = pool_smem + H * PB;      // [PSLICES][PB][PN] partial sums
   const int tid = threadIdx.x;
-  const int n0 = blockIdx.x * PN, b0 = blockIdx.y * PM;
-  const int row = tid >> 4, c4 = (tid & 15) * 4;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int c = tid % PN, slice = tid / PN;
+  const int n0 = blockIdx.x * PN, b0 = blockIdx.y * PB;
   griddep_wait();
   griddep_launch();
-  for (int k0 = 0; k0 < H; k0 += PK) {
-    for (int i = tid; i < PM * PK; i += 256) {
-      const int r = i / PK, k = i % PK;
-      const int bb = b0 + r;
-      const size_t xrow = bb < B ? (row_start ? static_cast<size_t>(row_start[bb]) : static_cast<size_t>(bb) * rows_per_seq) : 0;
-      xs[r][k] = (bb < B) ? x[xrow * H + k0 + k] : 0.f;
+  for (int i = tid; i < H * PB; i += PN * PSLICES) {
+    const int r = i / H, k = i - r * H;  // consecutive threads read consecutive elements of a row
+    const int bb = b0 + r;
+    float v = 0.f;
+    if (bb < B) {
+      const size_t xrow = row_start ? static_cast<size_t>(row_start[bb]) : static_cast<size_t>(bb) * rows_per_seq;
+      v = x[xrow * H + k];
     }
-    for (int i = tid; i < PK * PN / 4; i += 256) {
-      const int k = i / (PN / 4), c = (i % (PN / 4)) * 4;
-      *reinterpret_cast<float4*>(&ws[k][c]) = __ldg(reinterpret_cast<const float4*>(W + static_cast<size_t>(k0 + k) * H + n0 + c));
-    }
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < PK; ++k) {
-      const float a = xs[row][k];
-      const float4 w = *reinterpret_cast<const float4*>(&ws[k][c4]);
-      acc[0] = fmaf(a, w.x, acc[0]); acc[1] = fmaf(a, w.y, acc[1]);
-      acc[2] = fmaf(a, w.z, acc[2]); acc[3] = fmaf(a, w.w, acc[3]);
-    }
-    __syncthreads();
+    xs[k * PB + r] = v;
   }
-  if (b0 + row < B) {
-    const float4 bv = __ldg(reinterpret_cast<const float4*>(bias + n0 + c4));
-    *reinterpret_cast<float4*>(out + static_cast<size_t>(b0 + row) * H + n0 + c4) =
-        make_float4(tanhf(acc[0] + bv.x), tanhf(acc[1] + bv.y), tanhf(acc[2] + bv.z), tanhf(acc[3] + bv.w));
+  __syncthreads();
+  const int kper = H / PSLICES;
+  const float* wp = W + static_cast<size_t>(slice) * kper * H + n0 + c;
+  const float* xp = xs + slice * kper * PB;
+  float acc[PB];
+#pragma unroll
+  for (int r = 0; r < PB; ++r) acc[r] = 0.f;
+#pragma unroll 8
+  for (int k = 0; k < kper; ++k) {
+    const float w = __ldg(wp + static_cast<size_t>(k) * H);
+    const float4 x0 = *reinterpret_cast<const float4*>(xp + k * PB);
+    const float4 x1 = *reinterpret_cast<const float4*>(xp + k * PB + 4);
+    acc[0] = fmaf(x0.x, w, acc[0]); acc[1] = fmaf(x0.y, w, acc[1]);
+    acc[2] = fmaf(x0.z, w, acc[2]); acc[3] = fmaf(x0.w, w, acc[3]);
+    acc[4] = fmaf(x1.x, w, acc[4]); acc[5] = fmaf(x1.y, w, acc[5]);
+    acc[6] = fmaf(x1.z, w, acc[6]); acc[7] = fmaf(x1.w, w, acc[7]);
+  }
+#pragma unroll
+  for (int r = 0; r < PB; ++r) part[(slice * PB + r) * PN + c] = acc[r];
+  __syncthreads();
+  for (int i = tid; i < PB * PN; i += PN * PSLICES) {
+    const int r = i / PN, cc = i - r * PN;
+    if (b0 + r >= B) continue;
+    float v = bias[n0 + cc];
+#pragma unroll
+    for (int sl = 0; sl < PSLICES; ++sl) v += part[(sl * PB + r) * PN + cc];  // fixed order: deterministic
+    out[static_cast<size_t>(b0 + r) * H + n0 + cc] = tanhf(v);
   }
 }
 
@@ -163,11 +180,12 @@ pooler_f32_kernel(const float* __restrict__ x, int rows_per_seq, const int* __re
 
 int pooler_f32(const float* x, int rows_per_seq, const int* row_start, const float* W, const float* bias, float* out,
                int B, int H, cudaStream_t stream) {
-  if (B <= 0 || H <= 0 || (H % PN) != 0 || (H % PK) != 0) return -1;
-  dim3 grid(H / PN, (B + PM - 1) / PM);
+  if (B <= 0 || H <= 0 || (H % PN) != 0 || (H % (4 * PSLICES)) != 0 || H > 1024) return -1;
+  dim3 grid(H / PN, (B + PB - 1) / PB);
   if (grid.y > 65535) return -1;
-  return launch_pdl(pooler_f32_kernel, grid, dim3(256), 0, stream, x, rows_per_seq, row_start, W, bias, out, B, H) ==
-                 cudaSuccess ? 1 : -3;
+  const size_t smem = (static_cast<size_t>(H) * PB + PSLICES * PB * PN) * sizeof(float);  // 40 KB at H = 1024
+  return launch_pdl(pooler_f32_kernel, grid, dim3(PN * PSLICES), smem, stream, x, rows_per_seq, row_start, W, bias, out,
+                    B, H) == cudaSuccess ? 1 : -3;
 }
 
 int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float* out, int ldo,

@@ -42,7 +42,14 @@ Model::~Model() {
   if (h_out_) cudaFreeHost(h_out_);
   if (h_err_) cudaFreeHost(h_err_);
   for (cudaEvent_t e : ev_) cudaEventDestroy(e);
+  drop_graphs();
   if (stream_) cudaStreamDestroy(stream_);
+}
+
+void Model::drop_graphs() {
+  for (auto& kv : graphs_)
+    if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+  graphs_.clear();
 }
 
 bool Model::init(bool large, int gpu, int max_batch, int max_seq, const std::string& dir, int precision,
@@ -67,6 +74,9 @@ bool Model::init(bool large, int gpu, int max_batch, int max_seq, const std::str
     // CUDABERT_PACK=0 keeps the padded layout (hidden states are then computed for padding tokens too)
     const char* e = std::getenv("CUDABERT_PACK");
     packed_ = !(e && e[0] == '0');
+    // CUDABERT_GRAPH=0: enqueue every forward pass kernel by kernel, never replay a captured graph
+    const char* gr = std::getenv("CUDABERT_GRAPH");
+    graphs_enabled_ = !(gr && gr[0] == '0');
   }
   esize_ = (precision == PREC_FP32) ? 4 : 2;
   if (!check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
@@ -270,6 +280,7 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   const size_t T = static_cast<size_t>(B) * S;
   if (want_hidden_f32 && packed_ && hidden_unpacked_tokens_ < T) {
     if (!check(cudaStreamSynchronize(stream_), "sync")) return false;
+    drop_graphs();
     if (hidden_unpacked_) cudaFree(hidden_unpacked_);
     hidden_unpacked_ = nullptr;
     hidden_unpacked_tokens_ = 0;
@@ -279,6 +290,7 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   }
   if (T <= cap_tokens_ && B <= cap_batch_) return true;
   if (!check(cudaStreamSynchronize(stream_), "sync before arena growth")) return false;
+  drop_graphs();  // they hold addresses inside the arena that is about to be replaced
   const size_t ct = std::max(T, cap_tokens_);
   const int cbatch = std::max(B, cap_batch_);
   if (arena_) cudaFree(arena_);
@@ -414,6 +426,51 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
   if (want_probs && classes_ == 0) return fail(1, "the model directory has no classifier_kernel/bias");
   if (!check(cudaSetDevice(dev_), "cudaSetDevice")) return false;
   if (!ensure_capacity(B, S, want_hidden_f32)) return false;
+  if (!graphs_enabled_ || profiling_) return enqueue_forward(d_ids, d_seg, d_mask, B, S, want_hidden_f32, want_probs);
+
+  // The first pass with a given argument set runs kernel by kernel (it also does every one-time
+  // set-up a launcher may need); the second is captured into a CUDA graph; from then on the pass is
+  // one graph launch, which takes the per-kernel launch cost off the host for small batches.
+  const GraphKey key{d_ids, d_seg, d_mask, B, S, (want_hidden_f32 ? 1 : 0) | (want_probs ? 2 : 0)};
+  auto it = graphs_.find(key);
+  if (it == graphs_.end()) {
+    if (graphs_.size() >= 32) drop_graphs();
+    graphs_[key] = GraphEntry();
+    return enqueue_forward(d_ids, d_seg, d_mask, B, S, want_hidden_f32, want_probs);
+  }
+  GraphEntry& entry = it->second;
+  if (!entry.exec) {
+    if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+      cudaGetLastError();
+      graphs_enabled_ = false;
+      return enqueue_forward(d_ids, d_seg, d_mask, B, S, want_hidden_f32, want_probs);
+    }
+    const bool ok = enqueue_forward(d_ids, d_seg, d_mask, B, S, want_hidden_f32, want_probs);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e_end = cudaStreamEndCapture(stream_, &graph);
+    if (!ok) {  // the same rejection a direct enqueue would have met; status_ says why
+      if (graph) cudaGraphDestroy(graph);
+      return false;
+    }
+    cudaGraphExec_t exec = nullptr;
+    if (e_end != cudaSuccess || !graph || cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) {
+      cudaGetLastError();
+      if (graph) cudaGraphDestroy(graph);
+      graphs_enabled_ = false;  // this driver does not take the capture: stay with direct launches
+      return enqueue_forward(d_ids, d_seg, d_mask, B, S, want_hidden_f32, want_probs);
+    }
+    cudaGraphDestroy(graph);
+    entry.exec = exec;
+    entry.launches = launches_;
+    ++graph_captures_;
+  }
+  launches_ = entry.launches;
+  ++graph_replays_;
+  return check(cudaGraphLaunch(entry.exec, stream_), "cudaGraphLaunch");
+}
+
+bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mask, int B, int S, bool want_hidden_f32,
+                            bool want_probs) {
   const int T = B * S;
   launches_ = 0;
   int n;

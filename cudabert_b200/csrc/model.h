@@ -12,7 +12,9 @@
 //     (the reference exits, utils/common.h:58-65).
 #pragma once
 #include <cstdint>
+#include <map>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "kernels.h"
@@ -59,6 +61,10 @@ class Model {
   bool forward_device(const int* d_ids, const int* d_seg, const int* d_mask, int B, int S, bool want_hidden_f32,
                       bool want_probs);
   bool sync();
+  // CUDA graphs replayed / captured so far (a forward pass is captured the second time its exact
+  // arguments are seen; CUDABERT_GRAPH=0 turns this off)
+  long graph_replays() const { return graph_replays_; }
+  long graph_captures() const { return graph_captures_; }
 
   float* pooled_dev() const { return pooled_; }
   // fp32 final hidden states [B, S, H] of the last call that asked for them (Cuda_Inference)
@@ -98,6 +104,28 @@ class Model {
   bool collect_profile();
   bool dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, int lda, int M, void* out, int flags,
              const void* residual, int kclass);
+
+  // Enqueues the kernels of one forward pass on stream_ (directly, or into a stream capture).
+  bool enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mask, int B, int S, bool want_hidden_f32,
+                       bool want_probs);
+  void drop_graphs();
+
+  // One captured forward pass per exact argument set.  The kernel arguments hold device addresses
+  // of the activation arena, so every graph is dropped when the arena is reallocated.
+  struct GraphKey {
+    const int *ids, *seg, *mask;
+    int B, S, flags;
+    bool operator<(const GraphKey& o) const {
+      return std::tie(ids, seg, mask, B, S, flags) < std::tie(o.ids, o.seg, o.mask, o.B, o.S, o.flags);
+    }
+  };
+  struct GraphEntry {
+    cudaGraphExec_t exec = nullptr;
+    long launches = 0;
+  };
+  std::map<GraphKey, GraphEntry> graphs_;
+  bool graphs_enabled_ = true;
+  long graph_replays_ = 0, graph_captures_ = 0;
 
   int dev_ = 0, num_sms_ = 148;
   bool large_ = false;

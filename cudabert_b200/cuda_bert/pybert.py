@@ -177,6 +177,12 @@ stream.restype = c_void_p
 launch_count = lib.cudabert_launch_count
 launch_count.argtypes = [c_void_p]
 launch_count.restype = c_long
+graph_captures = lib.cudabert_graph_captures
+graph_captures.argtypes = [c_void_p]
+graph_captures.restype = c_long
+graph_replays = lib.cudabert_graph_replays
+graph_replays.argtypes = [c_void_p]
+graph_replays.restype = c_long
 
 profile_enable = lib.cudabert_profile_enable
 profile_enable.argtypes = [c_void_p, c_int]

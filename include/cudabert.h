@@ -101,6 +101,12 @@ CUDABERT_API void* cudabert_stream(void* model);
 
 /* Kernels launched by the last forward pass of this handle. */
 CUDABERT_API long cudabert_launch_count(void* model);
+/* A forward pass is enqueued kernel by kernel the first time its exact arguments (input addresses,
+ * batch, sequence length) are seen, captured into a CUDA graph the second time and replayed as one
+ * graph launch from then on (environment CUDABERT_GRAPH=0: never).  These count the captures and the
+ * replays of this handle so far. */
+CUDABERT_API long cudabert_graph_captures(void* model);
+CUDABERT_API long cudabert_graph_replays(void* model);
 /* Per-kernel-class device timing with CUDA events on the handle's stream.  Classes: 0 embedding+LN,
  * 1 QKV GEMM, 2 attention, 3 attention-output GEMM, 4 LayerNorm, 5 FFN1 GEMM, 6 FFN2 GEMM,
  * 7 pooler GEMM, 8 other.  Enable, run forwards + sync, then read accumulated ms and launches. */

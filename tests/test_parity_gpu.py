@@ -215,3 +215,42 @@ def test_weight_directories_of_both_converters_resolve(models, tmp_path, style):
     finally:
         pybert.unload_model(model)
     np.testing.assert_array_equal(got, want)
+
+
+def test_graph_replay_gives_the_same_results(weight_dirs):
+    """The third and later forward passes with the same arguments replay a captured CUDA graph:
+    identical bits to the kernel-by-kernel pass, also when shapes alternate, when the arena grows
+    in between (which drops every graph) and while profiling (which bypasses them)."""
+    from cudabert_b200.cuda_bert import pybert
+    ids, seg, mask = cases.case_inputs("c0_affine")
+    model = pybert.load_model(False, weight_dirs("base_affine"), 0, 0, 0, precision="bf16")
+    H = pybert.hidden_size(model)
+
+    def run(n_rows, n_cols, with_mask=True):
+        i, s, m = (np.ascontiguousarray(a[:n_rows, :n_cols]) for a in (ids, seg, mask))
+        out = np.zeros((n_rows, H), np.float32)
+        pybert.bert(model, out, i, s, n_rows, n_cols, m if with_mask else None)
+        pybert.check(model)
+        return out
+    try:
+        first = {k: run(*k) for k in [(4, 64, True), (4, 64, False), (2, 33, True)]}
+        assert pybert.graph_captures(model) == 0
+        for _ in range(3):
+            for k, want in first.items():
+                np.testing.assert_array_equal(run(*k), want)
+        assert pybert.graph_captures(model) == 3 and pybert.graph_replays(model) == 9
+        big = run(8, 128)                       # grows the arena: the graphs are gone
+        for k, want in first.items():
+            np.testing.assert_array_equal(run(*k), want)
+        np.testing.assert_array_equal(run(8, 128), big)
+        np.testing.assert_array_equal(run(8, 128), big)
+        assert pybert.graph_captures(model) == 4
+        pybert.profile_enable(model, 1)
+        replays = pybert.graph_replays(model)
+        np.testing.assert_array_equal(run(8, 128), big)
+        assert pybert.graph_replays(model) == replays
+        pybert.profile_enable(model, 0)
+        np.testing.assert_array_equal(run(8, 128), big)
+        assert pybert.graph_replays(model) == replays + 1
+    finally:
+        pybert.unload_model(model)
