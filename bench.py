@@ -406,6 +406,27 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     pybert.unload_model(model)
 
 
+def rank_plumbing(world, rank):
+    """(barrier, allmax) for `world` ranks launched by torchrun: the ranks are independent replicas
+    and meet only here, on the host (gloo): a barrier around the timed regions and a max-reduction
+    of the per-rank device times.  One rank: no process group at all."""
+    if world <= 1:
+        return (lambda: None), (lambda x: float(x))
+    import torch
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def barrier():
+        dist.barrier()
+
+    def allmax(x):
+        t = torch.tensor([float(x)], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return barrier, allmax
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -432,25 +453,7 @@ def main():
         run_reference(args, rank, world)
         return
 
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("gloo", rank=rank, world_size=world)
-
-        def barrier():
-            dist.barrier()
-
-        def allmax(x):
-            t = torch.tensor([float(x)], dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item())
-    else:
-        def barrier():
-            pass
-
-        def allmax(x):
-            return float(x)
+    barrier, allmax = rank_plumbing(world, rank)
 
     run_ours(args, rank, local_rank, world, barrier, allmax)
     if world > 1:
