@@ -1,71 +1,72 @@
-"""Line and batch containers of the engine: same names and fields as the reference's utils.py
-(utils.py:3-67)."""
+"""Containers that travel between the engine's stages.  Class, method and attribute names are the
+ones code written against the reference uses (utils.py:3-67): ``Tagged_line`` (one tokenised input
+line), ``Batch_Packed`` (a bucket's lines plus their stacked arrays) and ``optimize_batch``."""
 import numpy as np
 
-
-def optimize_batch(tg_line_list):
-    """Right-trim a bucket to its own longest valid length and stack it into three int32 arrays
-    [ids, segment ids, mask] of shape [n, max_length] (reference: utils.py:3-13)."""
-    max_length = max(tg_line.length for tg_line in tg_line_list)
-    batch = []
-    for i in range(3):
-        new = np.ones([len(tg_line_list), max_length], dtype=np.int32)
-        for j, tg_line in enumerate(tg_line_list):
-            new[j] = np.asarray(tg_line.get_tensor(i)[0:max_length], dtype=np.int32)
-        batch.append(new)
-    return batch
-
-
-class Batch_Packed(object):
-    '''
-        lines_list : list of Tagged_lines
-        Tensor : [input_id, seg_id, mask], each [batchsize, seq]
-        output : [batchsize, output_custom]
-    '''
-    def __init__(self, lines_list, tensor):
-        self.lines_list = lines_list
-        self.tensor = tensor
-        self.output = None
-
-    def set_output(self, output):
-        self.output = output
-
-    def write_line(self):
-        for i in range(len(self.lines_list)):
-            self.lines_list[i].output = self.output[i]
+_FEATURES = ("input_ids", "segment_ids", "input_mask")   # order of Batch_Packed.tensor
 
 
 class Tagged_line(object):
-    """A single set of features of data."""
+    """One line: its number in the input file, the raw text, the three token arrays, its valid
+    length and, once a replica has seen it, its output row."""
+
+    __slots__ = ("num_line", "line_data", "input_ids", "input_mask", "segment_ids", "length", "output")
 
     def __init__(self, num_line, line_data, input_ids, input_mask, segment_ids, measure=True):
-        self.num_line = num_line
-        self.line_data = line_data
-        self.input_ids = input_ids
-        self.input_mask = input_mask
-        self.segment_ids = segment_ids
-        self.length = 512
-        if measure:          # the native batcher measures the line itself
-            self._get_length()
+        self.num_line, self.line_data = num_line, line_data
+        self.input_ids, self.input_mask, self.segment_ids = input_ids, input_mask, segment_ids
         self.output = None
+        self.length = 512        # what the reference leaves when the mask holds no 1 (utils.py:43-56)
+        if measure:              # the native batcher measures the line itself
+            self._get_length()
+
+    def _get_length(self):
+        """Valid length = 1 + position of the last mask entry equal to 1."""
+        ones = np.flatnonzero(np.asarray(self.input_mask) == 1)
+        if ones.size:
+            self.length = int(ones[-1]) + 1
+
+    def get_tensor(self, index):
+        """0: ids, 1: segment ids, 2: mask."""
+        return getattr(self, _FEATURES[index])
 
     def drop_features(self):
         """Forget the token arrays once they are inside a batch tensor: what travels on to the
         replica and the writer is the line number, the raw line and, later, the output."""
         self.input_ids = self.input_mask = self.segment_ids = None
 
-    def _get_length(self):
-        """ Useful length of the ids: 1 + index of the last mask entry equal to 1
-        (stays 512 when the mask has none, as in the reference, utils.py:49-56)."""
-        mask = np.asarray(self.input_mask)
-        ones = np.nonzero(mask == 1)[0]
-        if ones.size:
-            self.length = int(ones[-1]) + 1
+    def __getstate__(self):
+        return tuple(getattr(self, name) for name in self.__slots__)
 
-    def get_tensor(self, index):
-        if index == 0:
-            return self.input_ids
-        if index == 1:
-            return self.segment_ids
-        if index == 2:
-            return self.input_mask
+    def __setstate__(self, state):
+        for name, value in zip(self.__slots__, state):
+            setattr(self, name, value)
+
+
+def optimize_batch(tg_line_list):
+    """[ids, segment ids, mask], each int32 [lines, L] with L the longest valid length among the
+    lines: the bucket is right-trimmed to its own need (reference: utils.py:3-13)."""
+    width = max(line.length for line in tg_line_list)
+    stacked = []
+    for which in range(len(_FEATURES)):
+        rows = np.ones((len(tg_line_list), width), dtype=np.int32)
+        for r, line in enumerate(tg_line_list):
+            rows[r] = np.asarray(line.get_tensor(which)[:width], dtype=np.int32)
+        stacked.append(rows)
+    return stacked
+
+
+class Batch_Packed(object):
+    """A batch on its way through the pipeline: ``lines_list`` (Tagged_lines), ``tensor``
+    ([ids, segment ids, mask], each [lines, L]) and, after the replica, ``output`` ([lines, ...])."""
+
+    def __init__(self, lines_list, tensor):
+        self.lines_list, self.tensor, self.output = lines_list, tensor, None
+
+    def set_output(self, output):
+        self.output = output
+
+    def write_line(self):
+        """Hand every line its own output row."""
+        for line, row in zip(self.lines_list, self.output):
+            line.output = row
