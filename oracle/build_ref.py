@@ -1,6 +1,6 @@
 """Build the reference's own CUDA library (fp32, cuBLAS) for sm_100a into oracle/_ref/.
 
-    python oracle/build_ref.py [--reference /root/reference]
+    python oracle/build_ref.py [--reference <checkout of the reference>]
 
 TEST INFRASTRUCTURE: the result, oracle/_ref/libcudaBERT_ref.so, is a second checker for the
 GPU parity tests and the "reference CUDA on the same box" line of the benchmark notes.  The

@@ -1,6 +1,6 @@
 """Generate the golden fixtures by running the REAL reference implementation.
 
-Run in a container that has the reference tree (default ``/root/reference``)::
+Run where a checkout of the reference is present (``--reference``)::
 
     python tests/golden/make_golden.py [--reference /path/to/cudaBERT]
 
