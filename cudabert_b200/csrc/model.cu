@@ -474,6 +474,11 @@ bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mas
   const int T = B * S;
   launches_ = 0;
   int n;
+  // programmatic dependent launch pays for short passes only (kernels.h: pdl_enabled)
+  struct PdlScope {
+    explicit PdlScope(bool on) { tl_pdl_allowed = on; }
+    ~PdlScope() { tl_pdl_allowed = true; }
+  } pdl_scope(T <= PDL_MAX_TOKENS);
 
 #define CB_LAUNCH(kclass, call)                                         \
   do {                                                                  \

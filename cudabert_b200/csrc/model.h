@@ -125,6 +125,7 @@ class Model {
   };
   std::map<GraphKey, GraphEntry> graphs_;
   bool graphs_enabled_ = true;
+  static constexpr int PDL_MAX_TOKENS = 4096;  // forward passes up to this many token slots use dependent launch
   long graph_replays_ = 0, graph_captures_ = 0;
 
   int dev_ = 0, num_sms_ = 148;
