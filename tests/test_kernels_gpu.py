@@ -150,7 +150,7 @@ def test_attention(pybert, bf16, B, S, heads, mode):
 
 
 @pytest.mark.parametrize("B,S,heads,mode", [(64, 200, 16, "prefix"), (300, 64, 12, "prefix"), (40, 256, 16, "holes"),
-                                            (33, 130, 16, "zero_row")])
+                                            (33, 130, 16, "zero_row"), (2500, 16, 12, "prefix"), (1025, 33, 16, "holes")])
 def test_attention_persistent_matches_per_item_kernel(pybert, B, S, heads, mode):
     """Many more items than SMs, ragged lengths: the persistent kernel hands items and query blocks
     out dynamically, and every block must come out exactly as the one-CTA-per-item kernel computes
