@@ -700,6 +700,11 @@ int gemm_bf16_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int
   if ((epi.flags & EPI_BIAS) && !epi.bias) return -1;
   if ((epi.flags & EPI_RESIDUAL) && !epi.residual) return -1;
   if ((epi.flags & EPI_COLSCALE) && !epi.colscale) return -1;
+  // Up to 128 rows a CTA pair's 256-row tile would be at least half padding, and with so few tiles the
+  // k loop of one tile is the whole run time: single CTAs with 128 x 128 tiles halve that loop and use
+  // twice as many SMs.  (The pair's W map has 128-row boxes, which is what this kernel loads too.)
+  if (M <= BM && gemm_w_box_rows(N) == 128)
+    return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
   if (gemm_uses_pairs(N)) return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   if (gemm_block_n(N) == 256) return launch<256>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
   return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
