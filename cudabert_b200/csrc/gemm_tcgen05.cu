@@ -673,6 +673,14 @@ bool pair_enabled() {
 
 int gemm_block_n(int N) { return (N % 256 == 0) ? 256 : 128; }
 
+static bool small_tiles_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("CUDABERT_GEMM_SMALL_TILES");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
+
 bool gemm_uses_pairs(int N) { return pair_enabled() && (N % 256 == 0); }
 
 // Rows of the W tensor map's box: a CTA of a pair loads half of the 256-row tile.
@@ -700,11 +708,24 @@ int gemm_bf16_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int
   if ((epi.flags & EPI_BIAS) && !epi.bias) return -1;
   if ((epi.flags & EPI_RESIDUAL) && !epi.residual) return -1;
   if ((epi.flags & EPI_COLSCALE) && !epi.colscale) return -1;
-  // Up to 128 rows a CTA pair's 256-row tile would be at least half padding, and with so few tiles the
-  // k loop of one tile is the whole run time: single CTAs with 128 x 128 tiles halve that loop and use
-  // twice as many SMs.  (The pair's W map has 128-row boxes, which is what this kernel loads too.)
-  if (M <= BM && gemm_w_box_rows(N) == 128)
-    return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
+  // Few rows: a CTA pair's 256 x 256 tiles are too few to occupy the SMs, and the k loop of one
+  // tile is then the whole run time.  Single CTAs with 128 x 128 tiles have a k loop half as long
+  // and four times as many tiles (BERT-base, 8 x 128 tokens: 0.80 against 0.88 ms per pass; one
+  // sequence of 32 tokens: 0.71 against 0.78 ms).  It is opt-in (CUDABERT_GEMM_SMALL_TILES=1):
+  // the two tile shapes do not round identically, so with it a sequence's result depends, in the
+  // last bits, on how many other rows share its batch, and by default it never does.  The choice
+  // compares (waves of tiles) x (tensor-pipe time of one tile's k loop) for the two shapes and takes
+  // the small tiles only for a clear win.  The pair's W map has 128-row boxes, which is what the
+  // 128 x 128 kernel loads too.
+  if (small_tiles_enabled() && gemm_uses_pairs(N) && gemm_w_box_rows(N) == 128) {
+    const long pairs = num_sms / 2 > 0 ? num_sms / 2 : 1;
+    const long tiles_p = static_cast<long>((M + 2 * BM - 1) / (2 * BM)) * (N / 256);
+    const long tiles_s = static_cast<long>((M + BM - 1) / BM) * (N / 128);
+    const long cost_p = ((tiles_p + pairs - 1) / pairs) * 2;  // a 256 x 256 x 16 MMA takes twice a 128 x 128 x 16 one
+    const long cost_s = (tiles_s + num_sms - 1) / num_sms;
+    if (cost_s * 10 <= cost_p * 8)
+      return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
+  }
   if (gemm_uses_pairs(N)) return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   if (gemm_block_n(N) == 256) return launch<256>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
   return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
