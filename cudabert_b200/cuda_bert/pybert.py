@@ -138,6 +138,23 @@ batcher_pop = lib.cudabert_batcher_pop
 batcher_pop.argtypes = [c_void_p, ndpointer(numpy.int64, flags="C_CONTIGUOUS"), _i32, _i32, _i32]
 batcher_pop.restype = c_int
 
+# BERT tokenizer of the engine's reader stage (host only)
+tokenizer_create = lib.cudabert_tokenizer_create
+tokenizer_create.argtypes = [c_char_p, c_int]
+tokenizer_create.restype = c_void_p
+tokenizer_destroy = lib.cudabert_tokenizer_destroy
+tokenizer_destroy.argtypes = [c_void_p]
+tokenizer_destroy.restype = None
+tokenizer_vocab_size = lib.cudabert_tokenizer_vocab_size
+tokenizer_vocab_size.argtypes = [c_void_p]
+tokenizer_vocab_size.restype = c_int
+tokenizer_tokenize = lib.cudabert_tokenizer_tokenize
+tokenizer_tokenize.argtypes = [c_void_p, c_char_p, _i32, c_int]
+tokenizer_tokenize.restype = c_int
+tokenizer_encode_pair = lib.cudabert_tokenizer_encode_pair
+tokenizer_encode_pair.argtypes = [c_void_p, c_char_p, c_char_p, c_int, _i32, _i32, _i32]
+tokenizer_encode_pair.restype = c_int
+
 hidden_size = lib.cudabert_hidden_size
 hidden_size.argtypes = [c_void_p]
 hidden_size.restype = c_int

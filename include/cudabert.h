@@ -137,6 +137,24 @@ CUDABERT_API int cudabert_batcher_next(void* batcher, int* rows, int* seq, long 
  * line.  Returns rows, 0 if no batch is ready. */
 CUDABERT_API int cudabert_batcher_pop(void* batcher, long long* line_index, int* ids, int* seg, int* mask);
 
+/* ---- BERT tokenizer of the file-to-file engine's reader stage (host only, no CUDA call) ----
+ * Replaces, for speed, the Python tokenisation of the reference's sample application: BertTokenizer =
+ * BasicTokenizer + WordpieceTokenizer (apps/pytorch_pretrained_bert/tokenization.py:75-331) and the
+ * packing of one or two texts into fixed-length features (apps/tokenlizer.py:45-134).  vocab_path: one
+ * token per line (the line number is the id); it must hold [UNK], [CLS] and [SEP].  Returns NULL if the
+ * file cannot be read or lacks them. */
+CUDABERT_API void* cudabert_tokenizer_create(const char* vocab_path, int do_lower_case);
+CUDABERT_API void cudabert_tokenizer_destroy(void* tokenizer);
+CUDABERT_API int cudabert_tokenizer_vocab_size(void* tokenizer);
+/* Word-piece ids of a UTF-8 text.  Returns their number (which may exceed capacity; at most capacity are
+ * written), -1 on a bad argument. */
+CUDABERT_API int cudabert_tokenizer_tokenize(void* tokenizer, const char* text_utf8, int* ids_out, int capacity);
+/* [CLS] a [SEP] (b [SEP]) truncated and zero-padded to max_seq_length entries each of ids, mask (1 for
+ * real tokens) and segment ids (1 for b and its [SEP]); text_b may be NULL or empty.  Returns the number
+ * of real tokens, -1 on a bad argument. */
+CUDABERT_API int cudabert_tokenizer_encode_pair(void* tokenizer, const char* text_a, const char* text_b, int max_seq_length,
+                                                int* ids, int* mask, int* seg);
+
 /* ---- single kernels on device buffers (stream 0, synchronous), for per-kernel parity tests ---- */
 
 /* out[M,N] = epilogue(A[M,K] bf16 (row stride lda elements) x W[N,K]^T bf16); flags: 1 bias, 2 GELU,

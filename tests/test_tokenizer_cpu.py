@@ -1,0 +1,96 @@
+"""The native tokenizer against golden vectors made by the reference's own Python tokenizer
+(tests/golden/make_tokenizer_golden.py): word-piece ids of hand-made sentences in several scripts and
+of random strings over many Unicode blocks, and the fixed-length features of tab-separated lines,
+lower-cased and cased."""
+import json
+import os
+import pickle
+
+import numpy as np
+import pytest
+
+from cudabert_b200.tokenizer import Tokenlizer, WordPieceTokenizer
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tokenizer_golden.json")
+
+
+@pytest.fixture(scope="module")
+def golden(tmp_path_factory):
+    with open(GOLDEN, encoding="utf-8") as f:
+        g = json.load(f)
+    vf = tmp_path_factory.mktemp("vocab") / "vocab.txt"
+    vf.write_text("\n".join(g["vocab"]) + "\n", encoding="utf-8")
+    g["vocab_file"] = str(vf)
+    return g
+
+
+@pytest.mark.parametrize("mode", ["lower", "cased"])
+def test_word_piece_ids_match_the_reference(golden, mode):
+    tok = WordPieceTokenizer(golden["vocab_file"], do_lower_case=(mode == "lower"))
+    assert tok.vocab_size == len(set(golden["vocab"]))
+    bad = []
+    for text, want in golden["cases"][mode]["tokenize"]:
+        got = tok.tokenize(text).tolist()
+        if got != want:
+            bad.append((text, got, want))
+    assert not bad, "%d of %d texts differ, first: %r" % (len(bad), len(golden["cases"][mode]["tokenize"]), bad[0])
+
+
+@pytest.mark.parametrize("mode", ["lower", "cased"])
+def test_line_features_match_the_reference(golden, mode):
+    fn = Tokenlizer(golden["vocab_file"], do_lower_case=(mode == "lower"))
+    fn = pickle.loads(pickle.dumps(fn))        # what a spawned reader process receives
+    for k, (max_seq, line, ids_valid, n0) in enumerate(golden["cases"][mode]["features"]):
+        index, raw, ids, mask, seg = fn(max_seq, line, k)
+        n = len(ids_valid)
+        assert index == k and raw == "\t".join(line.replace("\0", "").rstrip().split("\t"))
+        assert ids.dtype == mask.dtype == seg.dtype == np.int32 and ids.shape == (max_seq,)
+        assert ids.tolist() == ids_valid + [0] * (max_seq - n), (line, max_seq)
+        assert mask.tolist() == [1] * n + [0] * (max_seq - n)
+        assert seg.tolist() == [0] * n0 + [1] * (n - n0) + [0] * (max_seq - n)
+
+
+def test_tokenizer_rejects_bad_arguments(tmp_path, golden):
+    from cudabert_b200.cuda_bert import pybert
+    assert not pybert.tokenizer_create(str(tmp_path / "missing.txt").encode(), 1)
+    no_specials = tmp_path / "v.txt"
+    no_specials.write_text("hello\nworld\n")
+    assert not pybert.tokenizer_create(str(no_specials).encode(), 1)
+    with pytest.raises(ValueError):
+        WordPieceTokenizer(str(no_specials)).tokenize("hello")
+    tok = WordPieceTokenizer(golden["vocab_file"])
+    with pytest.raises(ValueError):
+        tok.encode_pair("a", None, 2)
+    # invalid UTF-8 is dropped, not fatal
+    h = pybert.tokenizer_create(golden["vocab_file"].encode(), 1)
+    out = np.zeros(8, np.int32)
+    assert pybert.tokenizer_tokenize(h, b"\xff\xfe\xc3", out, 8) == 0
+    assert pybert.tokenizer_tokenize(h, b"a b c d e f g h i j k l", out, 8) == 12   # reports the full count
+    pybert.tokenizer_destroy(h)
+
+
+def test_tokenizer_feeds_the_engine(tmp_path, golden):
+    """Tokenlizer as Engine's tokenizer function with spawned stages (the fake replica of the engine
+    tests returns the id sum and valid length of every line)."""
+    from cudabert_b200.engine import Engine
+    from test_engine_cpu import FakeReplica, Head, output_line, _config
+    lines = [l for _, l, _, _ in golden["cases"]["lower"]["features"][:60] if "\n" not in l and "\r" not in l
+             and "\x0b" not in l and "\x0c" not in l and "\x1c" not in l and "\x1d" not in l and "\x1e" not in l
+             and "\x85" not in l and " " not in l and " " not in l]
+    src, dst = tmp_path / "in.tsv", tmp_path / "out.tsv"
+    src.write_text("\n".join(lines) + "\n", encoding="utf-8")
+    cfg = _config([0, 1])
+    cfg.mp_start_method = "spawn"
+    eng = Engine(cfg)
+    eng.set_cuda_model(FakeReplica)
+    eng.set_finetune_layer(Head)
+    fn = Tokenlizer(golden["vocab_file"])
+    eng.set_tokenlizer_function(fn)
+    eng.set_output_function(output_line)
+    eng.run(str(src), str(dst))
+    out = dst.read_text(encoding="utf-8").splitlines()
+    read_back = src.read_text(encoding="utf-8").splitlines()
+    assert len(out) == len(read_back)
+    for k, line in enumerate(read_back):
+        _, raw, ids, mask, _ = fn(cfg.max_seq_length, line + "\n", k)
+        assert out[k] == "%s\t%d\t%d" % (raw, int((ids * mask).sum()), int(mask.sum()))
