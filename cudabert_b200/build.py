@@ -21,7 +21,7 @@ LIB = os.path.join(HERE, "cuda_bert", "libcudaBERT.so")
 UNIT_TEST = os.path.join(HERE, "cuda_bert", "unit_test")
 
 CUDA_SOURCES = ["gemm_tcgen05.cu", "gemm_f32.cu", "attention.cu", "attention_tc.cu", "rowwise.cu", "model.cu", "abi.cu"]
-CXX_SOURCES = ["npy.cc", "batcher.cc", "tokenizer.cc"]
+CXX_SOURCES = ["npy.cc", "batcher.cc", "tokenizer.cc", "reader.cc"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

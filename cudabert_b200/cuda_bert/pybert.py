@@ -155,6 +155,30 @@ tokenizer_encode_pair = lib.cudabert_tokenizer_encode_pair
 tokenizer_encode_pair.argtypes = [c_void_p, c_char_p, c_char_p, c_int, _i32, _i32, _i32]
 tokenizer_encode_pair.restype = c_int
 
+# native reader stage: file -> tokenizer threads -> batcher
+_i64 = ndpointer(numpy.int64, flags="C_CONTIGUOUS")
+reader_create = lib.cudabert_reader_create
+reader_create.argtypes = [c_char_p, c_void_p, c_int, _i32, c_int, c_int, c_int, _c_ll, _c_ll]
+reader_create.restype = c_void_p
+reader_destroy = lib.cudabert_reader_destroy
+reader_destroy.argtypes = [c_void_p]
+reader_destroy.restype = None
+reader_next = lib.cudabert_reader_next
+reader_next.argtypes = [c_void_p, POINTER(c_int), POINTER(c_int), POINTER(_c_ll)]
+reader_next.restype = c_int
+reader_pop = lib.cudabert_reader_pop
+reader_pop.argtypes = [c_void_p, _i64, _i32, _i32, _i32, _i64]
+reader_pop.restype = c_int
+reader_raw = lib.cudabert_reader_raw
+reader_raw.argtypes = [c_void_p, c_char_p, _c_ll]
+reader_raw.restype = _c_ll
+reader_flush = lib.cudabert_reader_flush
+reader_flush.argtypes = [c_void_p]
+reader_flush.restype = c_int
+reader_lines = lib.cudabert_reader_lines
+reader_lines.argtypes = [c_void_p]
+reader_lines.restype = _c_ll
+
 hidden_size = lib.cudabert_hidden_size
 hidden_size.argtypes = [c_void_p]
 hidden_size.restype = c_int

@@ -298,9 +298,65 @@ class Engine(object):
                 segment_ids=user_output[4],
                 measure=not isinstance(self.handle, native_queue_manager))
 
+    def _engine_preprocess_native(self, input_file, start_line):
+        """ The reader stage on the library's native reader (csrc/reader.cc): tokenizer threads fill
+        the buckets, this loop only forwards finished batches. """
+        import threading
+        from ctypes import byref, c_int, c_longlong, create_string_buffer
+        import numpy as np
+        from .cuda_bert import pybert
+        config, handle, tok = self.config, self.handle, self.tokenlizer_line
+        tok._native()
+        bounds = np.ascontiguousarray(self.seq_length_split, dtype=np.int32)
+        threads = int(getattr(config, "reader_threads", 0)) or max(1, min(8, (os.cpu_count() or 2) - 1))
+        reader = pybert.reader_create(input_file.encode("utf-8"), tok._handle, config.max_seq_length, bounds,
+                                      len(bounds), config.batch_size, threads,
+                                      start_line + (1 if config.skip_first_line else 0), start_line)
+        if not reader:
+            raise RuntimeError("native reader: cannot open %r" % (input_file,))
+        stop = threading.Event()
+
+        def forward_flush_requests():      # the writer asks for the partly filled buckets
+            while not stop.is_set():
+                try:
+                    handle.force_queue.get(timeout=0.2)
+                    pybert.reader_flush(reader)
+                except pyqueue.Empty:
+                    pass
+        flusher = threading.Thread(target=forward_flush_requests, daemon=True)
+        flusher.start()
+        try:
+            rows, seq, first = c_int(0), c_int(0), c_longlong(0)
+            while pybert.reader_next(reader, byref(rows), byref(seq), byref(first)) == 1:
+                index = np.empty(rows.value, np.int64)
+                offsets = np.empty(rows.value + 1, np.int64)
+                tensor = [np.empty((rows.value, seq.value), np.int32) for _ in range(3)]
+                got = pybert.reader_pop(reader, index, tensor[0], tensor[1], tensor[2], offsets)
+                assert got == rows.value
+                raw = create_string_buffer(int(offsets[-1]) + 1)
+                pybert.reader_raw(reader, raw, int(offsets[-1]))
+                text = raw.raw[:int(offsets[-1])]
+                lines = []
+                for i in range(got):
+                    tl = Tagged_line(int(index[i]), text[offsets[i]:offsets[i + 1]].decode("utf-8", "replace"),
+                                     None, None, None, measure=False)
+                    lines.append(tl)
+                handle.input_queue.put(Batch_Packed(lines, tensor))
+            total = pybert.reader_lines(reader)
+        finally:
+            stop.set()
+            flusher.join()
+            pybert.reader_destroy(reader)
+        for _ in self.config.gpu:
+            handle.input_queue.put(_DONE)
+        self.logger.info("engine_preprocess (native reader, %d threads) done: %d lines", threads, total)
+
     def _engine_preprocess(self, input_file, start_line=0):
         config = self.config
         handle = self.handle
+        from .tokenizer import Tokenlizer
+        if getattr(config, "native_reader", True) and isinstance(self.tokenlizer_line, Tokenlizer):
+            return self._engine_preprocess_native(input_file, start_line)
         with open(input_file, 'r', encoding='utf-8') as f:
             if self.config.skip_first_line:
                 f.readline()

@@ -155,6 +155,36 @@ CUDABERT_API int cudabert_tokenizer_tokenize(void* tokenizer, const char* text_u
 CUDABERT_API int cudabert_tokenizer_encode_pair(void* tokenizer, const char* text_a, const char* text_b, int max_seq_length,
                                                 int* ids, int* mask, int* seg);
 
+/* ---- reader stage of the file-to-file engine: file -> tokenizer threads -> batcher (host only) ----
+ * Replaces the reference's reader process (engine.py:266-280 with apps/tokenlizer.py:136-147 as its
+ * per-line function): `threads` threads read lines of `input_path` after its first skip_lines lines (a
+ * header, lines a resumed run has written already), number them from first_index on, split them at
+ * tabs into text_a and text_b, tokenise them with `tokenizer` (a cudabert_tokenizer, not owned) and put
+ * them into length buckets (boundaries / batch_size as for cudabert_batcher_create).  NULL if the file
+ * cannot be opened or an argument is bad. */
+CUDABERT_API void* cudabert_reader_create(const char* input_path, void* tokenizer, int max_seq_length,
+                                          const int* boundaries, int n_boundaries, int batch_size, int threads,
+                                          long long skip_lines, long long first_index);
+/* Stops the threads and frees the reader (the tokenizer stays). */
+CUDABERT_API void cudabert_reader_destroy(void* reader);
+/* Blocks until a batch is ready and takes it out of the buckets (1: its shape in rows / seq /
+ * first_line; the batch waits inside the reader for cudabert_reader_pop), or until the file is
+ * finished and every batch has been taken (0). */
+CUDABERT_API int cudabert_reader_next(void* reader, int* rows, int* seq, long long* first_line);
+/* Copies that batch out: line_index[rows], ids / seg / mask [rows, seq], raw_offsets[rows + 1] = where each
+ * line's raw text (the line without NULs and trailing white space) starts in the text that
+ * cudabert_reader_raw then copies out.  Returns rows. */
+CUDABERT_API int cudabert_reader_pop(void* reader, long long* line_index, int* ids, int* seg, int* mask,
+                                     long long* raw_offsets);
+/* Raw text of the batch popped last, lines back to back (UTF-8, no terminator).  Returns its size in
+ * bytes; copies at most capacity bytes. */
+CUDABERT_API long long cudabert_reader_raw(void* reader, char* buf, long long capacity);
+/* Turns the partly filled buckets into batches now (the writer asks for this when too many lines wait
+ * for their predecessors).  Returns the number of ready batches. */
+CUDABERT_API int cudabert_reader_flush(void* reader);
+/* Lines tokenised so far. */
+CUDABERT_API long long cudabert_reader_lines(void* reader);
+
 /* ---- single kernels on device buffers (stream 0, synchronous), for per-kernel parity tests ---- */
 
 /* out[M,N] = epilogue(A[M,K] bf16 (row stride lda elements) x W[N,K]^T bf16); flags: 1 bias, 2 GELU,

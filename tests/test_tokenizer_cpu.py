@@ -94,3 +94,40 @@ def test_tokenizer_feeds_the_engine(tmp_path, golden):
     for k, line in enumerate(read_back):
         _, raw, ids, mask, _ = fn(cfg.max_seq_length, line + "\n", k)
         assert out[k] == "%s\t%d\t%d" % (raw, int((ids * mask).sum()), int(mask.sum()))
+
+
+@pytest.mark.parametrize("threads,native", [(1, True), (4, True), (0, False)])
+def test_engine_with_native_reader(tmp_path, golden, threads, native):
+    """Engine.run with the tokenizer threads + batcher inside the library (and, for comparison, with
+    the same tokenizer called line by line from the Python reader loop): every line comes out once,
+    in order, with the features the tokenizer gives for it.  Lines hold a header, tabs, trailing
+    blanks, NUL bytes and several scripts."""
+    from cudabert_b200.engine import Engine
+    from test_engine_cpu import FakeReplica, Head, output_line, _config
+    texts = [t for t, _ in golden["cases"]["lower"]["tokenize"]]
+    body = []
+    for i in range(0, len(texts) - 1, 2):
+        clean = lambda s: "".join(ch for ch in s if ch not in "\t\n\r\x0b\x0c\x1c\x1d\x1e\x85  ")
+        a, b = clean(texts[i]), clean(texts[i + 1])
+        body.append(a + "\t" + b + ("  " if i % 3 == 0 else ""))
+        body.append(a + ("\0" if i % 5 == 0 else "") + ("\t" if i % 2 else ""))
+    src, dst = tmp_path / "in.tsv", tmp_path / "out.tsv"
+    src.write_bytes(("a header line\n" + "\n".join(body) + "\n").encode("utf-8"))
+    cfg = _config([0, 1])
+    cfg.mp_start_method = "spawn"
+    cfg.skip_first_line = True
+    cfg.native_reader = native
+    cfg.reader_threads = threads
+    cfg.alert_size = 40           # the writer will ask for flushes
+    eng = Engine(cfg)
+    eng.set_cuda_model(FakeReplica)
+    eng.set_finetune_layer(Head)
+    fn = Tokenlizer(golden["vocab_file"])
+    eng.set_tokenlizer_function(fn)
+    eng.set_output_function(output_line)
+    eng.run(str(src), str(dst))
+    out = dst.read_bytes().decode("utf-8").split("\n")[:-1]
+    assert len(out) == len(body)
+    for k, line in enumerate(body):
+        _, raw, ids, mask, _ = fn(cfg.max_seq_length, line, k)
+        assert out[k] == "%s\t%d\t%d" % (raw, int((ids * mask).sum()), int(mask.sum())), k
