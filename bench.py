@@ -61,11 +61,16 @@ def flops_per_step(batch, seq, dims):
     return dense, attn, batch * 2 * H * H
 
 
-def gemm_flops(tokens, dims):
+def gemm_flops(tokens, dims, sequences=None):
     """FLOPs the tensor-core GEMMs execute for `tokens` rows (QKV, attention-output, FFN1, FFN2 of
-    every layer).  With the packed layout only the valid tokens of a batch are rows."""
+    every layer).  With the packed layout only the valid tokens of a batch are rows.  `sequences`:
+    the pass returns the pooler output only, so the last layer computes its attention-output and FFN
+    GEMMs for the first token of every sequence only (its QKV GEMM still takes every token)."""
     H, L, F = dims["hidden"], dims["layers"], dims["ffn"]
-    return L * 2 * tokens * (3 * H * H + H * H + 2 * H * F)
+    full = 2 * tokens * (3 * H * H + H * H + 2 * H * F)
+    if sequences is None or os.environ.get("CUDABERT_LAST_LAYER", "")[:1] == "f":
+        return L * full
+    return (L - 1) * full + 2 * tokens * 3 * H * H + 2 * sequences * (H * H + 2 * H * F)
 
 
 def live_tokens(mask):
@@ -337,7 +342,7 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     packed = os.environ.get("CUDABERT_PACK", "1") != "0"
     lens = [live_tokens(hb[2]) if packed else np.full(B, S) for hb in host]
     prof_lens = [lens[i % n_pool] for i in range(prof_steps)]
-    gflops = sum(gemm_flops(int(l.sum()), dims) for l in prof_lens)
+    gflops = sum(gemm_flops(int(l.sum()), dims, sequences=B) for l in prof_lens)
     attn_exec = sum(dims["layers"] * 4 * dims["hidden"] * float((l.astype(np.float64) ** 2).sum()) for l in prof_lens)
     ln_rows = sum(int(l.sum()) for l in prof_lens) / prof_steps
     achieved = gflops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
@@ -385,6 +390,9 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
                    "tflops_per_step_padded": (dense + attn + pool) / 1e12,
                    "layout": ("packed: padding tokens are not computed (%.0f live of %d token slots per step)"
                               % (ln_rows, B * S)) if packed else "padded",
+                   "last_layer": ("every token" if os.environ.get("CUDABERT_LAST_LAYER", "")[:1] == "f" else
+                                  "attention-output, FFN and LayerNorm for the first token of each sequence "
+                                  "only (all the pooler reads; same bits out as the full layer)"),
                    "tflops_per_step_executed_gemm": gflops / prof_steps / 1e12},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,

@@ -280,6 +280,9 @@ int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, 
 
 int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads) {
   if (!qkv_dev || !ctx_dev || B <= 0 || S <= 0 || heads <= 0) return 1;
+  const int cls_only = (bf16 & 16) ? 1 : 0;  // + 16: first query of every sequence only, ctx is [B, H]
+  bf16 &= 15;
+  if (cls_only && bf16 == 0) return 1;
   int* kv = nullptr;
   if (cudaMalloc(&kv, (3 * static_cast<size_t>(B) + 1) * sizeof(int)) != cudaSuccess) return 2;
   int* err = kv + B;
@@ -300,13 +303,13 @@ int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, voi
       }
       if (bf16 == 2)
         n = cb::attention_bf16_tc(&tm, mask_dev, kv, nullptr, static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, sms,
-                                  err, nullptr);
+                                  cls_only, err, nullptr);
       else
         n = cb::attention_bf16_persist(&tm, mask_dev, kv, nullptr, sched, static_cast<__nv_bfloat16*>(ctx_dev), B, S,
-                                       heads, sms, err, nullptr);
+                                       heads, sms, cls_only, err, nullptr);
     } else if (bf16) {
       n = cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
-                             static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr);
+                             static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, cls_only, nullptr);
     } else {
       n = cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr, static_cast<float*>(ctx_dev), B,
                             S, heads, nullptr);

@@ -237,7 +237,7 @@ __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __
 __global__ void __launch_bounds__(ATT_MAX_WARPS * 32, 2)
 attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ mask,
                       const int* __restrict__ kv_len, const int* __restrict__ row_start,
-                      __nv_bfloat16* __restrict__ ctx, int S, int heads, int R) {
+                      __nv_bfloat16* __restrict__ ctx, int S, int heads, int R, int cls_only) {
   extern __shared__ __align__(1024) uint8_t att_smem[];
   uint8_t* sK = att_smem;
   uint8_t* sV = sK + static_cast<size_t>(R) * 128;
@@ -256,7 +256,8 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   if (klen <= 0) klen = S;
   // rows of this sequence: [first, first + nq).  Packed: only the klen rows that exist; else all S.
   const int first = row_start ? row_start[b] : b * S;
-  const int nq = row_start ? klen : S;
+  // cls_only: only the sequence's first query is wanted, and its result goes to output row b
+  const int nq = cls_only ? 1 : (row_start ? klen : S);
   const int ktiles = (klen + 63) >> 6;
   const int krows = ktiles << 6;  // rows of K / V the tiles touch; rows >= klen are zero-filled
   const __nv_bfloat16* base = qkv + static_cast<size_t>(first) * ld + h * HD;
@@ -287,7 +288,7 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
 
   uint8_t* myQ = sQ + warp * 2048;
   const int qblocks = (nq + 15) >> 4;
-  __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
+  __nv_bfloat16* out_base = ctx + static_cast<size_t>(cls_only ? b : first) * H + h * HD;
   for (int qb = warp; qb < qblocks; qb += nwarps)
     attend_qblock<1, false>(ContigTiles{sK, sV}, sBias, biased, myQ, nullptr, base, ld, out_base, H, qb * 16, nq,
                             ktiles, lane);
@@ -334,11 +335,12 @@ constexpr size_t PA_SMEM_LIMIT = 232448;
 enum : int { SITE_PA_FULL = 21, SITE_PA_EMPTY = 22 };
 
 struct PaItem {
-  int first, nq, ktiles, qblocks, h, done;
+  int first, nq, ktiles, qblocks, h, done;  // first: the sequence's first row in qkv
   unsigned int biased;
   int next_q;  // next query block to hand out
   int tile0;   // ring index of the item's first tile: K tiles, then V tiles, then Q tiles
-  int pad[3];
+  int out_row; // first output row of the item
+  int pad[2];
 };
 static_assert(sizeof(PaItem) == 48, "record layout");
 
@@ -354,7 +356,7 @@ __global__ void __launch_bounds__(PA_THREADS, 1)
 attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __restrict__ mask,
                               const int* __restrict__ kv_len, const int* __restrict__ row_start,
                               const int* __restrict__ sched, __nv_bfloat16* __restrict__ ctx, int B, int S, int heads,
-                              int R, int NT, int* __restrict__ err) {
+                              int R, int NT, int cls_only, int* __restrict__ err) {
   extern __shared__ uint8_t pa_smem_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pa_smem_raw) + 1023) & ~uintptr_t(1023));
   float* sBiasAll = reinterpret_cast<float*>(ring + static_cast<size_t>(NT) * 8192);
@@ -417,7 +419,7 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const i
         if (klen <= 0) klen = S;
         my_klen = klen;
         my_first = row_start ? row_start[my_b] : my_b * S;
-        my_nq = row_start ? klen : S;
+        my_nq = cls_only ? 1 : (row_start ? klen : S);  // cls_only: the first query alone, result to row b
       }
       for (int j = 0; j < 32 && running; ++j) {
         const bool more = __shfl_sync(0xffffffffu, valid ? 1 : 0, j) != 0;
@@ -460,6 +462,7 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const i
           pi->biased = bits;
           pi->next_q = 0;
           pi->tile0 = head;
+          pi->out_row = cls_only ? b : first;
           mbar_arrive_expect_tx(full + rec, static_cast<uint32_t>(need) * 8192u);
           int t_idx = head;
           auto next_tile = [&]() { uint8_t* p = ring + static_cast<size_t>(t_idx) * 8192; if (++t_idx == NT) t_idx = 0; return p; };
@@ -484,7 +487,7 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const i
       if (pi->done) break;
       const int first = pi->first, nq = pi->nq, ktiles = pi->ktiles, qblocks = pi->qblocks, h = pi->h;
       const unsigned int biased = pi->biased;
-      const int tile0 = pi->tile0;
+      const int tile0 = pi->tile0, out_row = pi->out_row;
       RingTiles tiles;
       tiles.ring = ring;
       tiles.nt = NT;
@@ -492,7 +495,7 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const i
       tiles.v0 = tile0 + ktiles >= NT ? tile0 + ktiles - NT : tile0 + ktiles;
       const int q_first = tiles.v0 + ktiles >= NT ? tiles.v0 + ktiles - NT : tiles.v0 + ktiles;
       const float* sBias = sBiasAll + static_cast<size_t>(rec) * R;
-      __nv_bfloat16* out_base = ctx + static_cast<size_t>(first) * H + h * HD;
+      __nv_bfloat16* out_base = ctx + static_cast<size_t>(out_row) * H + h * HD;
       for (;;) {
         int qb = 0;
         if (lane == 0) qb = atomicAdd(&pi->next_q, 1);
@@ -715,7 +718,7 @@ row_layout_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int* _
 }  // namespace
 
 int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, const int* row_start,
-                   __nv_bfloat16* ctx, int B, int S, int heads, cudaStream_t stream) {
+                   __nv_bfloat16* ctx, int B, int S, int heads, int cls_only, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || S > 512 || heads <= 0 || B > 65535) return -1;
   const int R = ((S + 63) / 64) * 64;
   const int qblocks = (S + 15) / 16;
@@ -733,14 +736,14 @@ int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len,
   }
   dim3 grid(heads, B);
   return launch_pdl(attention_bf16_kernel, grid, dim3(nwarps * 32), smem, stream, qkv, mask, kv_len, row_start, ctx, S,
-                    heads, R) == cudaSuccess ? 1 : -3;
+                    heads, R, cls_only) == cudaSuccess ? 1 : -3;
 }
 
 bool attention_persist_fits(int S) { return ((S + 63) / 64) * 64 <= PA_MAX_R; }
 
 int attention_bf16_persist(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                           const int* sched, __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int* err_flag,
-                           cudaStream_t stream) {
+                           const int* sched, __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int cls_only,
+                           int* err_flag, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || heads <= 0 || !attention_persist_fits(S)) return -1;
   const int R = ((S + 63) / 64) * 64;
   const int NT = pa_ring_tiles(R);
@@ -756,7 +759,7 @@ int attention_bf16_persist(const CUtensorMap* tm_qkv, const int* mask, const int
   const long long items = static_cast<long long>(B) * heads;
   const int grid = static_cast<int>(items < num_sms ? items : num_sms);
   return launch_pdl(attention_bf16_persist_kernel, dim3(grid), dim3(PA_THREADS), pa_smem_bytes(R), stream, *tm_qkv, mask,
-                    kv_len, row_start, sched, ctx, B, S, heads, R, NT, err_flag) == cudaSuccess ? 1 : -3;
+                    kv_len, row_start, sched, ctx, B, S, heads, R, NT, cls_only, err_flag) == cudaSuccess ? 1 : -3;
 }
 
 int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,
@@ -819,7 +822,7 @@ extern "C" int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const
   // every entry [0, B) is rewritten before it is read, so nothing left by an earlier call matters
   if (cb::row_layout(mask_dev, kv, nullptr, nullptr, B, S, nullptr) < 0) return 3;
   const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
-                                          static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, nullptr)
+                                          static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, 0, nullptr)
                      : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr,
                                          static_cast<float*>(ctx_dev), B, S, heads, nullptr);
   if (n < 0) return 3;

@@ -77,8 +77,11 @@ struct ItemInfo {
   bool use_mask, live;
 };
 
+// cls_only: only the first query of every sequence is wanted (the last encoder layer of a call that
+// returns the pooler output alone); its result goes to output row b instead of the sequence's first row.
 __device__ __forceinline__ ItemInfo decode_item(int item, int QT, int heads, int S, const int* __restrict__ kv_len,
-                                                const int* __restrict__ row_start, const int* __restrict__ mask) {
+                                                const int* __restrict__ row_start, const int* __restrict__ mask,
+                                                int cls_only) {
   ItemInfo it;
   const int qt = item % QT;
   it.h = (item / QT) % heads;
@@ -88,7 +91,7 @@ __device__ __forceinline__ ItemInfo decode_item(int item, int QT, int heads, int
   if (klen <= 0) klen = S;
   it.klen = klen;
   it.first = row_start ? row_start[it.b] : it.b * S;
-  it.nq = row_start ? klen : S;
+  it.nq = cls_only ? 1 : (row_start ? klen : S);
   it.q0 = qt * TQ;
   it.live = it.q0 < it.nq;
   it.nblocks = (klen + TK - 1) / TK;
@@ -98,7 +101,7 @@ __device__ __forceinline__ ItemInfo decode_item(int item, int QT, int heads, int
 __global__ void __launch_bounds__(ATC_THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __restrict__ mask,
                     const int* __restrict__ kv_len, const int* __restrict__ row_start,
-                    __nv_bfloat16* __restrict__ ctx, int B, int S, int heads, int* err) {
+                    __nv_bfloat16* __restrict__ ctx, int B, int S, int heads, int cls_only, int* err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* sBias = reinterpret_cast<float*>(smem + SMEM_BIAS);
@@ -143,7 +146,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
   auto cursor_seek = [&](Cursor& c) {  // position on the first live item at or after c.item
     c.valid = false;
     while (c.item < num_items) {
-      c.it = decode_item(c.item, QT, heads, S, kv_len, row_start, mask);
+      c.it = decode_item(c.item, QT, heads, S, kv_len, row_start, mask, cls_only);
       if (c.it.live) { c.valid = true; break; }
       c.item += gridDim.x;
     }
@@ -385,7 +388,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       }
       tc_fence_before();
       __syncwarp();
-      __nv_bfloat16* out_base = ctx + static_cast<size_t>(it.first) * H + it.h * HD;
+      __nv_bfloat16* out_base = ctx + static_cast<size_t>(cls_only ? it.b : it.first) * H + it.h * HD;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int rr = i * 4 + (lane >> 3), p2 = lane & 7;
@@ -448,7 +451,8 @@ bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H) {
 }
 
 int attention_bf16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                      __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int* err_flag, cudaStream_t stream) {
+                      __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
+                      cudaStream_t stream) {
   if (B <= 0 || S <= 0 || S > 512 || heads <= 0) return -1;
   static bool attr_set[64] = {};
   int dev = 0;
@@ -461,7 +465,7 @@ int attention_bf16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_
   const long long items = static_cast<long long>(B) * heads * ((S + TQ - 1) / TQ);
   const int grid = static_cast<int>(items < 2LL * num_sms ? items : 2LL * num_sms);
   return launch_pdl(attention_tc_kernel, dim3(grid), dim3(ATC_THREADS), ATC_SMEM, stream, *tm_qkv, mask, kv_len,
-                    row_start, ctx, B, S, heads, err_flag) == cudaSuccess ? 1 : -3;
+                    row_start, ctx, B, S, heads, cls_only, err_flag) == cudaSuccess ? 1 : -3;
 }
 
 }  // namespace cb

@@ -110,8 +110,11 @@ int pooler_f32(const float* x, int rows_per_seq, const int* row_start, const flo
 // row_start == null: sequence b occupies rows [b*S, (b+1)*S) (padded layout).  row_start != null
 // (B + 1 entries from row_layout): sequences are packed back to back, sequence b occupies rows
 // [row_start[b], row_start[b+1]) and has no rows for its padding.
+// cls_only != 0 (the three bf16 kernels): only the first query of every sequence is computed and its
+// result is written to row b of ctx ([B, H]) -- what the last encoder layer needs when only the
+// pooler output is wanted; the arithmetic of that row is the same as in a full pass.
 int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, const int* row_start,
-                   __nv_bfloat16* ctx, int B, int S, int heads, cudaStream_t stream);
+                   __nv_bfloat16* ctx, int B, int S, int heads, int cls_only, cudaStream_t stream);
 int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,
                   int S, int heads, cudaStream_t stream);
 // tcgen05 variant of attention_bf16 (attention_tc.cu): Q, K, V tiles arrive by TMA through `tm_qkv`,
@@ -122,13 +125,14 @@ int attention_f32(const float* qkv, const int* mask, const int* kv_len, const in
 // length and says which rows need their mask read; S <= 256.
 bool attention_persist_fits(int S);
 int attention_bf16_persist(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                           const int* sched, __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int* err_flag,
-                           cudaStream_t stream);
+                           const int* sched, __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int cls_only,
+                           int* err_flag, cudaStream_t stream);
 enum AttentionKernel : int { ATT_KERNEL_MMA = 1, ATT_KERNEL_TC = 2, ATT_KERNEL_PERSIST = 3 };
 int attention_kernel_for(int S);
 bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H);
 int attention_bf16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                      __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int* err_flag, cudaStream_t stream);
+                      __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
+                      cudaStream_t stream);
 // kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none); mask null => S.
 // row_start (may be null): exclusive prefix sum of the sequence lengths (a length of 0 counts as S),
 // B + 1 entries, the last one being the number of packed rows.
@@ -148,7 +152,8 @@ int embed_layernorm(const int* ids, const int* seg, const float* word, const flo
 // (rows_dev: device int, may be null) are processed.
 template <typename TIn, typename TOut>
 int layernorm(const TIn* x, const float* residual, const float* gamma, const float* beta, TOut* out, float* out_f32,
-              int tokens, int H, const int* rows_dev, cudaStream_t stream);
+              int tokens, int H, const int* rows_dev, cudaStream_t stream, const int* res_rows = nullptr,
+              int res_stride = 1);
 // dst[B*S, H] (fp32) = packed src rows scattered back to the padded layout, zeros for padding.
 int unpack_rows(const float* src, const int* row_start, float* dst, int tokens, int S, int H, cudaStream_t stream);
 // probs[b, :] = softmax(pooled[b, :] . W[H, C] + bias[C]),  C <= 32

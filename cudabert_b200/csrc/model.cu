@@ -77,6 +77,10 @@ bool Model::init(bool large, int gpu, int max_batch, int max_seq, const std::str
     // CUDABERT_GRAPH=0: enqueue every forward pass kernel by kernel, never replay a captured graph
     const char* gr = std::getenv("CUDABERT_GRAPH");
     graphs_enabled_ = !(gr && gr[0] == '0');
+    // CUDABERT_LAST_LAYER=full: compute the last layer for every token even when only the pooler
+    // output is asked for
+    const char* ll = std::getenv("CUDABERT_LAST_LAYER");
+    cls_last_ = !(ll && ll[0] == 'f');
   }
   esize_ = (precision == PREC_FP32) ? 4 : 2;
   if (!check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
@@ -505,30 +509,43 @@ bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mas
     CB_LAUNCH(KC_EMBED, embed_layernorm<float>(d_ids, d_seg, word_, pos_, type_, emb_g_, emb_b_, xf_, nullptr, T, S, H_,
                                                vocab_rows_, err_dev_, rs, stream_));
   }
+  bool compact_out = false;  // the final hidden states hold one row per sequence (rows [0, B))
   for (int l = 0; l < L_; ++l) {
     const LayerWeights& w = layer_[l];
     if (!dense(w.qkv, xa_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) return false;
     if (lowp) {
+      // The pooler reads the first token of every sequence only.  When nothing else of the final
+      // hidden states is wanted, the LAST layer therefore computes, after its K and V, only that
+      // token: attention for the first query, then the rest of the layer on B rows written compactly
+      // into rows [0, B) of the same buffers.  Every step is row-wise (or, in attention, per query),
+      // so the pooler output has the same bits as after a full last layer.
+      const int cls = (cls_last_ && !want_hidden_f32 && l == L_ - 1) ? 1 : 0;
       if (att_kernel == ATT_KERNEL_TC) {
         CB_LAUNCH(KC_ATTENTION, attention_bf16_tc(&tm_qkv_, d_mask, kv_len_, rs, static_cast<__nv_bfloat16*>(ctx_), B, S,
-                                                  heads_, num_sms_, err_dev_, stream_));
+                                                  heads_, num_sms_, cls, err_dev_, stream_));
       } else if (att_kernel == ATT_KERNEL_PERSIST) {
         CB_LAUNCH(KC_ATTENTION, attention_bf16_persist(&tm_qkv_, d_mask, kv_len_, rs, sched,
-                                                       static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, num_sms_,
+                                                       static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, num_sms_, cls,
                                                        err_dev_, stream_));
       } else {
         CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_, rs,
-                                               static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, stream_));
+                                               static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, cls, stream_));
       }
+      const int rows = cls ? B : T;               // rows the rest of the layer works on
+      const int* rows_live = cls ? nullptr : live;  // ... all of them live in the compact case
+      if (cls) m_dev_cur_ = nullptr;
       // y = ctx.Wo + bo in fp16; x1 = LN(y + x) with the add in fp32 inside the LayerNorm kernel
-      if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, T, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_ATTN_OUT))
+      if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, rows, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_ATTN_OUT))
         return false;
+      // compact case: the residual of output row b is the first row of sequence b
       CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __nv_bfloat16>(static_cast<const __half*>(y_), xf_, w.ln1_g, w.ln1_b,
-                                                                x1a, x1f_, T, H_, live, stream_)));
-      if (!dense(w.ffn1, x1a_, &tm_x1_, H_, T, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
-      if (!dense(w.ffn2, z_, &tm_z_, F_, T, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_FFN2)) return false;
+                                                                x1a, x1f_, rows, H_, rows_live, stream_,
+                                                                cls ? rs : nullptr, (cls && !rs) ? S : 1)));
+      if (!dense(w.ffn1, x1a_, &tm_x1_, H_, rows, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
+      if (!dense(w.ffn2, z_, &tm_z_, F_, rows, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_FFN2)) return false;
       CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __nv_bfloat16>(static_cast<const __half*>(y_), x1f_, w.ln2_g, w.ln2_b,
-                                                                xa, xf_, T, H_, live, stream_)));
+                                                                xa, xf_, rows, H_, rows_live, stream_)));
+      compact_out = cls != 0;
     } else {
       CB_LAUNCH(KC_ATTENTION, attention_f32(static_cast<const float*>(qkv_), d_mask, kv_len_, rs,
                                             static_cast<float*>(ctx_), B, S, heads_, stream_));
@@ -544,8 +561,8 @@ bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mas
   }
   // pooler: rows b*S of the fp32 final hidden states, tanh(dense) -> fp32 [B, H]
   // (utils/bert.cu:239-247); always the fp32 kernel, it is 2 H^2 FLOPs per sequence
-  CB_LAUNCH(KC_POOLER, pooler_f32(xf_, S, rs, static_cast<const float*>(pooler_.w), pooler_.bias, pooled_, B, H_,
-                                  stream_));
+  CB_LAUNCH(KC_POOLER, pooler_f32(xf_, compact_out ? 1 : S, compact_out ? nullptr : rs,
+                                  static_cast<const float*>(pooler_.w), pooler_.bias, pooled_, B, H_, stream_));
   if (want_hidden_f32 && packed_)
     CB_LAUNCH(KC_OTHER, unpack_rows(xf_, row_start_, hidden_unpacked_, T, S, H_, stream_));
   if (want_probs)

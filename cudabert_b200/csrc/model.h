@@ -125,6 +125,7 @@ class Model {
   };
   std::map<GraphKey, GraphEntry> graphs_;
   bool graphs_enabled_ = true;
+  bool cls_last_ = true;  // pooler-only passes compute the last layer for the first token of every sequence only
   static constexpr int PDL_MAX_TOKENS = 4096;  // forward passes up to this many token slots use dependent launch
   long graph_replays_ = 0, graph_captures_ = 0;
 

@@ -148,14 +148,17 @@ template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(ROWS_PER_BLOCK * 32)
 layernorm_kernel(const TIn* __restrict__ in, const float* __restrict__ residual, const float* __restrict__ gamma,
                  const float* __restrict__ beta, TOut* __restrict__ out, float* __restrict__ out_f32, int tokens,
-                 int H, const int* __restrict__ rows_dev) {
+                 int H, const int* __restrict__ rows_dev, const int* __restrict__ res_rows, int res_stride) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * ROWS_PER_BLOCK + (threadIdx.x >> 5);
   griddep_wait();
   griddep_launch();
   if (t >= tokens || (rows_dev && t >= __ldg(rows_dev))) return;
   const TIn* row = in + static_cast<size_t>(t) * H;
-  const float* res = residual ? residual + static_cast<size_t>(t) * H : nullptr;
+  // the residual of output row t is row res_rows[t], or t * res_stride without a table (stride 1:
+  // the same row; the compact last layer reads the first row of every sequence)
+  const size_t res_row = res_rows ? static_cast<size_t>(__ldg(res_rows + t)) : static_cast<size_t>(t) * res_stride;
+  const float* res = residual ? residual + res_row * H : nullptr;
   const int nvec = H / 128;
   float x[MAXV][4];
 #pragma unroll
@@ -290,11 +293,11 @@ int embed_layernorm(const int* ids, const int* seg, const float* word, const flo
 
 template <typename TIn, typename TOut>
 int layernorm(const TIn* x, const float* residual, const float* gamma, const float* beta, TOut* out, float* out_f32,
-              int tokens, int H, const int* rows_dev, cudaStream_t stream) {
+              int tokens, int H, const int* rows_dev, cudaStream_t stream, const int* res_rows, int res_stride) {
   if (tokens <= 0 || !ln_shape_ok(H)) return -1;
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
   return launch_pdl(layernorm_kernel<TIn, TOut>, dim3(blocks), dim3(ROWS_PER_BLOCK * 32), 0, stream, x, residual, gamma,
-                    beta, out, out_f32, tokens, H, rows_dev) == cudaSuccess ? 1 : -3;
+                    beta, out, out_f32, tokens, H, rows_dev, res_rows, res_stride) == cudaSuccess ? 1 : -3;
 }
 
 template int embed_layernorm<float>(const int*, const int*, const float*, const float*, const float*, const float*,
@@ -303,13 +306,13 @@ template int embed_layernorm<__nv_bfloat16>(const int*, const int*, const float*
                                             const float*, const float*, __nv_bfloat16*, float*, int, int, int, int,
                                             int*, const int*, cudaStream_t);
 template int layernorm<float, float>(const float*, const float*, const float*, const float*, float*, float*, int, int,
-                                     const int*, cudaStream_t);
+                                     const int*, cudaStream_t, const int*, int);
 template int layernorm<float, __nv_bfloat16>(const float*, const float*, const float*, const float*, __nv_bfloat16*,
-                                             float*, int, int, const int*, cudaStream_t);
+                                             float*, int, int, const int*, cudaStream_t, const int*, int);
 template int layernorm<__half, float>(const __half*, const float*, const float*, const float*, float*, float*, int, int,
-                                      const int*, cudaStream_t);
+                                      const int*, cudaStream_t, const int*, int);
 template int layernorm<__half, __nv_bfloat16>(const __half*, const float*, const float*, const float*, __nv_bfloat16*,
-                                              float*, int, int, const int*, cudaStream_t);
+                                              float*, int, int, const int*, cudaStream_t, const int*, int);
 
 int unpack_rows(const float* src, const int* row_start, float* dst, int tokens, int S, int H, cudaStream_t stream) {
   if (tokens <= 0 || S <= 0 || H % 4 != 0) return -1;

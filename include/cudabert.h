@@ -198,7 +198,8 @@ CUDABERT_API int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W
                         int flags, const float* bias_dev, const float* residual_dev);
 /* ctx[T,H] = attention(qkv[T,3H]); mask_dev int32 [B,S] or NULL; bf16: 0 = fp32 kernel, 1 = bf16
  * mma.sync kernel (one CTA per sequence and head), 2 = bf16 tcgen05 kernel, 3 = bf16 mma.sync kernel,
- * persistent (S <= 256). */
+ * persistent (S <= 256).  Adding 16 to a bf16 kernel's number computes only the first query of every
+ * sequence and writes it to row b of ctx_dev, then [B, H] (the last encoder layer of a pooler-only pass). */
 CUDABERT_API int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads);
 /* No counterpart in the reference.  cudabert_k_attention for callers that must not allocate device
  * memory: code that runs where cudaMalloc is not allowed (inside another framework's memory pool

@@ -168,6 +168,27 @@ def test_attention_persistent_matches_per_item_kernel(pybert, B, S, heads, mode)
     assert torch.equal(out[0], out[1]) and torch.equal(out[1], out[2])
 
 
+@pytest.mark.parametrize("kernel", [1, 2, 3])
+@pytest.mark.parametrize("B,S,heads,mode", [(37, 200, 16, "prefix"), (300, 64, 12, "holes"), (9, 256, 16, "zero_row"),
+                                            (5, 512, 16, "full"), (64, 17, 12, "none")])
+def test_attention_first_query_only(pybert, kernel, B, S, heads, mode):
+    """The last layer of a pooler-only pass asks every bf16 attention kernel for the first query of
+    each sequence alone, written to row b: the same bits as row b * S of a full run of that kernel."""
+    if kernel == 3 and S > 256:
+        pytest.skip("the persistent kernel holds sequences of up to 256 tokens")
+    g = torch.Generator(device="cuda").manual_seed(B * 31 + S)
+    H = heads * 64
+    x = torch.randn(B * S, 3 * H, device="cuda", generator=g).bfloat16()
+    mask = _mask(B, S, mode, g)
+    mptr = None if mask is None else mask.data_ptr()
+    full = torch.full((B * S, H), float("nan"), device="cuda", dtype=torch.bfloat16)
+    first = torch.full((B, H), float("nan"), device="cuda", dtype=torch.bfloat16)
+    assert pybert.k_attention(kernel, x.data_ptr(), mptr, full.data_ptr(), B, S, heads) == 0
+    assert pybert.k_attention(kernel + 16, x.data_ptr(), mptr, first.data_ptr(), B, S, heads) == 0
+    assert torch.isfinite(first.float()).all()
+    assert torch.equal(first, full.view(B, S, H)[:, 0])
+
+
 @pytest.mark.parametrize("bf16", [1, 0])
 @pytest.mark.parametrize("H", [768, 1024])
 def test_embed_layernorm_and_layernorm(pybert, bf16, H):

@@ -113,6 +113,26 @@ def test_cuda_inference_returns_device_hidden_states(models):
     assert np.abs(hidden[:, 0, :] - gold["cls_hidden"]).max() <= 2e-3
 
 
+@pytest.mark.parametrize("name,precision", [("c1_small", "bf16"), ("c3_small", "bf16"), ("c4_small", "bf16"),
+                                            ("c2_small", "bf16"), ("edge_s17", "bf16"), ("edge_holes", "bf16"),
+                                            ("c4_small", "fp8"), ("edge_zero_row", "bf16")])
+def test_pooler_only_pass_equals_full_pass(models, name, precision):
+    """Cuda_Bert computes the last layer for the first token of every sequence only; Cuda_Inference,
+    which also returns every hidden state, computes it in full.  The pooler outputs of the two must be
+    the same bits (all three attention kernels and both layouts of the last layer are met by the cases)."""
+    from cudabert_b200.cuda_bert import pybert
+    m = models(cases.CASES[name]["weights"], precision)
+    ids, seg, mask = cases.case_inputs(name)
+    B, S = ids.shape
+    short = m.encode([ids, seg, mask])
+    ret = pybert.inference(m.model, ids, seg, B, S, mask)
+    pybert.check(m.model)
+    full = np.empty_like(short)
+    assert pybert.copy_to_host(full.ctypes.data, ret.Pooled_Output, full.nbytes) == 0
+    np.testing.assert_array_equal(short, full)
+    np.testing.assert_array_equal(m.encode([ids, seg, mask]), short)      # and again, through the graph
+
+
 # ---------------------------------------------------------------- full-size workloads
 def _full_inputs(cfg):
     c = synth.CONFIGS[cfg]
