@@ -1,0 +1,73 @@
+"""The library's environment switches (read once per process): each setting runs the same cases in a
+child process.  Switches that only change how the work is scheduled must give the same bits as the
+default; switches that pick another kernel or tile shape must stay within a small distance of it."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BASE_CASES = ["c0_affine", "c2_small", "edge_s17", "edge_b1s1", "edge_nomask", "edge_zero_row", "edge_holes"]
+LARGE_CASES = ["c1_small", "c3_small", "c4_small"]
+SWITCHES = ("CUDABERT_PACK", "CUDABERT_GRAPH", "CUDABERT_PDL", "CUDABERT_LAST_LAYER", "CUDABERT_ATTENTION",
+            "CUDABERT_GEMM_PAIR", "CUDABERT_GEMM_SMALL_TILES", "CUDABERT_PRECISION")
+
+
+@pytest.fixture(scope="module")
+def run_with(weight_dirs, tmp_path_factory):
+    specs = ["%s:0:%s" % (weight_dirs("base_affine"), ",".join(BASE_CASES)),
+             "%s:1:%s" % (weight_dirs("large_affine"), ",".join(LARGE_CASES))]
+    folder = tmp_path_factory.mktemp("switches")
+    cache = {}
+
+    def run(**switches):
+        key = tuple(sorted(switches.items()))
+        if key not in cache:
+            env = {k: v for k, v in os.environ.items() if k not in SWITCHES}
+            env.update(switches)
+            out = str(folder / ("out_%d.npz" % len(cache)))
+            r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "switch_child.py"), out] + specs,
+                               env=env, capture_output=True, text=True, timeout=600)
+            assert r.returncode == 0, "%s: rc=%d\n%s\n%s" % (switches, r.returncode, r.stdout[-1500:], r.stderr[-1500:])
+            cache[key] = dict(np.load(out))
+        return cache[key]
+
+    return run
+
+
+@pytest.mark.parametrize("switch", ["CUDABERT_PACK=0", "CUDABERT_GRAPH=0", "CUDABERT_PDL=0", "CUDABERT_PDL=1",
+                                    "CUDABERT_LAST_LAYER=full"])
+def test_scheduling_switches_keep_every_bit(run_with, switch):
+    """Padded instead of packed rows, no graphs, dependent launch off or forced on, the last layer
+    computed for every token: none of these may change a single bit of the pooler output."""
+    default = run_with()
+    name, value = switch.split("=")
+    other = run_with(**{name: value})
+    for case in BASE_CASES + LARGE_CASES:
+        np.testing.assert_array_equal(other[case], default[case], err_msg="%s, case %s" % (switch, case))
+
+
+@pytest.mark.parametrize("switch", ["CUDABERT_ATTENTION=tc", "CUDABERT_ATTENTION=persist", "CUDABERT_ATTENTION=mma",
+                                    "CUDABERT_GEMM_PAIR=0", "CUDABERT_GEMM_SMALL_TILES=1"])
+def test_kernel_choice_switches_stay_close(run_with, switch):
+    """Another attention kernel or GEMM tile shape rounds at other places, and twelve or twenty-four
+    layers of bf16 activations amplify that: the output stays within the bf16 mode's budget against the
+    golden fp32 output (2e-2 of its scale), and within 1.5e-2 of the default's output."""
+    default = run_with()
+    name, value = switch.split("=")
+    other = run_with(**{name: value})
+    worst = {}
+    for case in BASE_CASES + LARGE_CASES:
+        gold = cases.load_golden(case)["pooled"]
+        worst[case] = (float(np.abs(other[case] - gold).max() / np.abs(gold).max()),
+                       float(np.abs(other[case] - default[case]).max() / np.abs(default[case]).max()))
+    print(switch, {k: (round(a, 4), round(b, 4)) for k, (a, b) in worst.items()})
+    for case, (to_gold, to_default) in worst.items():
+        assert to_gold <= 2e-2, "%s, case %s vs golden: %g" % (switch, case, to_gold)
+        assert to_default <= 1.5e-2, "%s, case %s vs default: %g" % (switch, case, to_default)
