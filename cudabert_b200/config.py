@@ -23,7 +23,7 @@ _DEFAULTS = {
     "precision": (None, '"fp32", "bf16" or "fp8"; None = environment CUDABERT_PRECISION, else bf16'),
     "native_batcher": (True, "bucket and trim in the library's batcher; False = the Python classes"),
     "native_reader": (True, "with a tokenizer.Tokenlizer as tokenizer function: read, tokenise and bucket in native threads"),
-    "reader_threads": (0, "tokenizer threads of the native reader; 0 = up to 8, one core left free"),
+    "reader_threads": (0, "tokenizer threads of the native reader; 0 = up to 16, one core left free"),
     "resume_without_dead_gpu": (True, "if a replica's process dies, resume after the last written line on the rest"),
     "mp_start_method": (None, 'multiprocessing start method; use "spawn" when the parent already holds a CUDA context'),
 }

@@ -30,7 +30,7 @@ import queue as pyqueue
 import sys
 import time
 
-from .utils import optimize_batch, Batch_Packed, Tagged_line
+from .utils import optimize_batch, Batch_Blob, Batch_Packed, Tagged_line
 
 _DONE = "__stage_done__"
 
@@ -284,8 +284,9 @@ class Engine(object):
                 break
             output = model.encode(packed_batch.tensor)
             packed_batch.output = user_layer.run(output)
-            handle.output_queue.put(packed_batch)
             total_length += packed_batch.tensor[0].shape[0]
+            packed_batch.drop_tensor()       # the writer wants line numbers, raw lines and outputs only
+            handle.output_queue.put(packed_batch)
         handle.output_queue.put(_DONE)
         self.logger.info("engine_model on gpu %s done: %d lines in %.2f s", id_gpu, total_length, time.time() - start)
 
@@ -308,7 +309,7 @@ class Engine(object):
         config, handle, tok = self.config, self.handle, self.tokenlizer_line
         tok._native()
         bounds = np.ascontiguousarray(self.seq_length_split, dtype=np.int32)
-        threads = int(getattr(config, "reader_threads", 0)) or max(1, min(8, (os.cpu_count() or 2) - 1))
+        threads = int(getattr(config, "reader_threads", 0)) or max(1, min(16, (os.cpu_count() or 2) - 1))
         reader = pybert.reader_create(input_file.encode("utf-8"), tok._handle, config.max_seq_length, bounds,
                                       len(bounds), config.batch_size, threads,
                                       start_line + (1 if config.skip_first_line else 0), start_line)
@@ -335,13 +336,7 @@ class Engine(object):
                 assert got == rows.value
                 raw = create_string_buffer(int(offsets[-1]) + 1)
                 pybert.reader_raw(reader, raw, int(offsets[-1]))
-                text = raw.raw[:int(offsets[-1])]
-                lines = []
-                for i in range(got):
-                    tl = Tagged_line(int(index[i]), text[offsets[i]:offsets[i + 1]].decode("utf-8", "replace"),
-                                     None, None, None, measure=False)
-                    lines.append(tl)
-                handle.input_queue.put(Batch_Packed(lines, tensor))
+                handle.input_queue.put(Batch_Blob(index, raw.raw[:int(offsets[-1])], offsets, tensor))
             total = pybert.reader_lines(reader)
         finally:
             stop.set()
@@ -389,11 +384,10 @@ class Engine(object):
                 if packed_batch == _DONE:
                     done += 1
                     continue
-                packed_batch.write_line()
-                for tl in packed_batch.lines_list:
-                    if tl.num_line in window or tl.num_line < next_line:
-                        raise RuntimeError("Line Index {} is written twice!".format(tl.num_line))
-                    window[tl.num_line] = self.output_line(tl.line_data, tl.output)
+                for num_line, line_data, output in packed_batch.results():
+                    if num_line in window or num_line < next_line:
+                        raise RuntimeError("Line Index {} is written twice!".format(num_line))
+                    window[num_line] = self.output_line(line_data, output)
                 while next_line in window:
                     f.write(window.pop(next_line) + '\n')
                     next_line += 1

@@ -1,6 +1,7 @@
 """Containers that travel between the engine's stages.  Class, method and attribute names are the
 ones code written against the reference uses (utils.py:3-67): ``Tagged_line`` (one tokenised input
-line), ``Batch_Packed`` (a bucket's lines plus their stacked arrays) and ``optimize_batch``."""
+line), ``Batch_Packed`` (a bucket's lines plus their stacked arrays) and ``optimize_batch``;
+``Batch_Blob`` is the compact form of a batch that the native reader produces."""
 import numpy as np
 
 _FEATURES = ("input_ids", "segment_ids", "input_mask")   # order of Batch_Packed.tensor
@@ -70,3 +71,50 @@ class Batch_Packed(object):
         """Hand every line its own output row."""
         for line, row in zip(self.lines_list, self.output):
             line.output = row
+
+    def results(self):
+        """(line number, raw line, output row) of every line, for the writer."""
+        for line, row in zip(self.lines_list, self.output):
+            yield line.num_line, line.line_data, row
+
+    def drop_tensor(self):
+        """The replica is done with the token arrays; the writer does not need them."""
+        self.tensor = None
+
+
+class Batch_Blob(Batch_Packed):
+    """A batch as the native reader delivers it: line numbers as one array and the raw text of all
+    lines as one byte string with offsets, instead of one Python object per line.  Pickling it costs a
+    few buffer copies, where a list of Tagged_lines costs several microseconds per line in each of the
+    three hops between the stages.  ``lines_list`` is built on demand for code that wants the objects."""
+
+    def __init__(self, index, text, offsets, tensor):
+        self.index, self.text, self.offsets = index, text, offsets
+        self.tensor, self.output = tensor, None
+        self._lines = None
+
+    def _raw(self, i):
+        return self.text[self.offsets[i]:self.offsets[i + 1]].decode("utf-8", "replace")
+
+    @property
+    def lines_list(self):
+        if self._lines is None:
+            self._lines = [Tagged_line(int(n), self._raw(i), None, None, None, measure=False)
+                           for i, n in enumerate(self.index)]
+        return self._lines
+
+    def write_line(self):
+        for line, row in zip(self.lines_list, self.output):
+            line.output = row
+
+    def results(self):
+        text, offsets = self.text, self.offsets.tolist()
+        for i, (n, row) in enumerate(zip(self.index.tolist(), self.output)):
+            yield n, text[offsets[i]:offsets[i + 1]].decode("utf-8", "replace"), row
+
+    def __getstate__(self):
+        return self.index, self.text, self.offsets, self.tensor, self.output
+
+    def __setstate__(self, state):
+        self.index, self.text, self.offsets, self.tensor, self.output = state
+        self._lines = None
