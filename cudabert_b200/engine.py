@@ -278,8 +278,20 @@ class Engine(object):
         model = self.cuda_model(id_gpu, config)
         start = time.time()
         total_length = 0
+        # A thread keeps the next batches ready (reading the pipe and unpickling take about a
+        # millisecond per batch, during which the GPU would idle; the replica's call releases the GIL).
+        import threading
+        ahead = pyqueue.Queue(maxsize=2)
+
+        def prefetch():
+            while True:
+                item = handle.get()
+                ahead.put(item)
+                if item == _DONE:
+                    return
+        threading.Thread(target=prefetch, daemon=True).start()
         while True:
-            packed_batch = handle.get()
+            packed_batch = ahead.get()
             if packed_batch == _DONE:
                 break
             output = model.encode(packed_batch.tensor)

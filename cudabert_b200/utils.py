@@ -112,9 +112,22 @@ class Batch_Blob(Batch_Packed):
         for i, (n, row) in enumerate(zip(self.index.tolist(), self.output)):
             yield n, text[offsets[i]:offsets[i + 1]].decode("utf-8", "replace"), row
 
+    @staticmethod
+    def _narrow(a):
+        """Token arrays cross the process boundary in the smallest unsigned type that holds them
+        (ids of a 30 522-word vocabulary in 16 bits, segment ids and mask in 8): a third of the bytes
+        through the pipe.  __setstate__ widens them to int32 again."""
+        lo, hi = (int(a.min()), int(a.max())) if a.size else (0, 0)
+        if lo < 0 or hi > 0xFFFF:
+            return a
+        return a.astype(np.uint8 if hi <= 0xFF else np.uint16)
+
     def __getstate__(self):
-        return self.index, self.text, self.offsets, self.tensor, self.output
+        tensor = None if self.tensor is None else [None if t is None else self._narrow(t) for t in self.tensor]
+        return self.index, self.text, self.offsets, tensor, self.output
 
     def __setstate__(self, state):
-        self.index, self.text, self.offsets, self.tensor, self.output = state
+        self.index, self.text, self.offsets, tensor, self.output = state
+        self.tensor = None if tensor is None else [None if t is None else t.astype(np.int32, copy=False)
+                                                   for t in tensor]
         self._lines = None
