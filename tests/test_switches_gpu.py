@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BASE_CASES = ["c0_affine", "c2_small", "edge_s17", "edge_b1s1", "edge_nomask", "edge_zero_row", "edge_holes"]
 LARGE_CASES = ["c1_small", "c3_small", "c4_small"]
 SWITCHES = ("CUDABERT_PACK", "CUDABERT_GRAPH", "CUDABERT_PDL", "CUDABERT_LAST_LAYER", "CUDABERT_ATTENTION",
-            "CUDABERT_GEMM_PAIR", "CUDABERT_GEMM_SMALL_TILES", "CUDABERT_PRECISION")
+            "CUDABERT_GEMM_PAIR", "CUDABERT_GEMM_SMALL_TILES", "CUDABERT_PRECISION", "CUDABERT_LN")
 
 
 @pytest.fixture(scope="module")
@@ -42,10 +42,11 @@ def run_with(weight_dirs, tmp_path_factory):
 
 
 @pytest.mark.parametrize("switch", ["CUDABERT_PACK=0", "CUDABERT_GRAPH=0", "CUDABERT_PDL=0", "CUDABERT_PDL=1",
-                                    "CUDABERT_LAST_LAYER=full"])
+                                    "CUDABERT_LAST_LAYER=full", "CUDABERT_LN=block"])
 def test_scheduling_switches_keep_every_bit(run_with, switch):
     """Padded instead of packed rows, no graphs, dependent launch off or forced on, the last layer
-    computed for every token: none of these may change a single bit of the pooler output."""
+    computed for every token, the other LayerNorm kernel: none of these may change a single bit of the
+    pooler output."""
     default = run_with()
     name, value = switch.split("=")
     other = run_with(**{name: value})
