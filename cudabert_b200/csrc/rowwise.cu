@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(LNP_THREADS, LNP_BLOCKS_PER_SM)
 layernorm_persist_kernel(const TIn* __restrict__ in, const float* __restrict__ residual, const float* __restrict__ gamma,
                          const float* __restrict__ beta, TOut* __restrict__ out, float* __restrict__ out_f32,
                          int tokens, int H, const int* __restrict__ rows_dev, const int* __restrict__ res_rows,
-                         int res_stride, int l2_ahead) {
+                         int res_stride) {
   typedef typename RawVec<TIn>::type Raw;
   const int lane = threadIdx.x & 31;
   const int nwarps = gridDim.x * (LNP_THREADS / 32);
@@ -351,19 +351,6 @@ layernorm_persist_kernel(const TIn* __restrict__ in, const float* __restrict__ r
       }
     const int next = t + nwarps;
     if (next < rows) issue(next);
-    if (l2_ahead > 0) {
-      const int far = t + (1 + l2_ahead) * nwarps;
-      if (far < rows) {
-        const size_t far_res = res_rows ? static_cast<size_t>(__ldg(res_rows + far)) : static_cast<size_t>(far) * res_stride;
-        const char* pi = reinterpret_cast<const char*>(in + static_cast<size_t>(far) * H);
-        const int in_bytes = H * static_cast<int>(sizeof(TIn));
-        if (lane * 128 < in_bytes) asm volatile("prefetch.global.L2 [%0];" ::"l"(pi + lane * 128));
-        if (residual) {
-          const char* pr = reinterpret_cast<const char*>(residual + far_res * H);
-          if (lane * 128 < H * 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(pr + lane * 128));
-        }
-      }
-    }
     normalise_and_store<TOut>(x, nvec, lane, H, gamma, beta, out + static_cast<size_t>(t) * H,
                               out_f32 ? out_f32 + static_cast<size_t>(t) * H : nullptr);
     t = next;
@@ -377,14 +364,6 @@ static bool layernorm_persistent() {
     return !(e && e[0] == 'b');
   }();
   return on;
-}
-
-static int l2_ahead() {
-  static const int v = [] {
-    const char* e = std::getenv("CUDABERT_LN_L2");
-    return e && *e ? std::atoi(e) : 0;
-  }();
-  return v;
 }
 
 static int sm_count() {
@@ -407,8 +386,8 @@ int layernorm(const TIn* x, const float* residual, const float* gamma, const flo
     const int want = (tokens + warps_per_block - 1) / warps_per_block;
     const int cap = sm_count() * LNP_BLOCKS_PER_SM;
     return launch_pdl(layernorm_persist_kernel<TIn, TOut>, dim3(want < cap ? want : cap), dim3(LNP_THREADS), 0, stream, x,
-                      residual, gamma, beta, out, out_f32, tokens, H, rows_dev, res_rows, res_stride, l2_ahead()) ==
-                   cudaSuccess ? 1 : -3;
+                      residual, gamma, beta, out, out_f32, tokens, H, rows_dev, res_rows, res_stride) == cudaSuccess
+               ? 1 : -3;
   }
   const int blocks = (tokens + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK;
   return launch_pdl(layernorm_kernel<TIn, TOut>, dim3(blocks), dim3(ROWS_PER_BLOCK * 32), 0, stream, x, residual, gamma,

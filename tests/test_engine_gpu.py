@@ -107,11 +107,13 @@ def test_replica_pool_in_one_process(weight_dirs, gpus):
     pool = Cuda_BERT_Pool(gpus, cfg)
     try:
         want = single.encode([ids, seg, mask])
-        for _ in range(3):      # repeated calls reuse the threads and the handles
-            np.testing.assert_array_equal(pool.encode([ids, seg, mask]), want)
-        np.testing.assert_array_equal(pool.encode([ids[:2], seg[:2], mask[:2]]), want[:2])
-        np.testing.assert_array_equal(pool.encode([ids[:1], seg[:1], None]), single.encode([ids[:1], seg[:1], None]))
-        np.testing.assert_array_equal(pool.classify([ids, seg, mask]), single.classify([ids, seg, mask]))
+        for call in range(3):      # repeated calls reuse the threads and the handles
+            np.testing.assert_array_equal(pool.encode([ids, seg, mask]), want, err_msg="whole batch, call %d" % call)
+        np.testing.assert_array_equal(pool.encode([ids[:2], seg[:2], mask[:2]]), want[:2], err_msg="two rows")
+        np.testing.assert_array_equal(pool.encode([ids[:1], seg[:1], None]), single.encode([ids[:1], seg[:1], None]),
+                                      err_msg="one row, no mask")
+        np.testing.assert_array_equal(pool.classify([ids, seg, mask]), single.classify([ids, seg, mask]),
+                                      err_msg="classify")
     finally:
         pool.close()
         single.close()
