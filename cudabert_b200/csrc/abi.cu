@@ -239,12 +239,12 @@ int cudabert_profile_get(void* model, int kernel_class, double* total_ms, long* 
 }
 
 // ------------------------------------------------------------------ single kernels
-int cudabert_k_gemm_bf16(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev, int flags,
+int cudabert_k_gemm_tcgen05(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev, int flags,
                          const float* bias_dev, const void* residual_dev, const float* colscale_dev, int* err_dev) {
   if (!A_dev || !W_dev || !out_dev || M <= 0 || N <= 0 || K <= 0 || lda < K) return 1;
   CUtensorMap tmA, tmW;
-  if (!cb::make_tmap_bf16_kmajor(&tmA, A_dev, M, K, static_cast<uint64_t>(lda) * 2, 128)) return 2;
-  if (!cb::make_tmap_bf16_kmajor(&tmW, W_dev, N, K, static_cast<uint64_t>(K) * 2, cb::gemm_w_box_rows(N))) return 2;
+  if (!cb::make_tmap_16bit_kmajor(&tmA, A_dev, M, K, static_cast<uint64_t>(lda) * 2, 128)) return 2;
+  if (!cb::make_tmap_16bit_kmajor(&tmW, W_dev, N, K, static_cast<uint64_t>(K) * 2, cb::gemm_w_box_rows(N))) return 2;
   static thread_local DevErr scratch;
   int* err = err_dev;
   if (!err) {
@@ -259,7 +259,7 @@ int cudabert_k_gemm_bf16(const void* A_dev, long lda, const void* W_dev, int M, 
   epi.bias = bias_dev;
   epi.residual = residual_dev;
   epi.colscale = colscale_dev;
-  const int n = cb::gemm_bf16_tcgen05(&tmA, &tmW, M, N, K, out_dev, N, epi, err, sms, nullptr, nullptr);
+  const int n = cb::gemm_tcgen05(&tmA, &tmW, M, N, K, out_dev, N, epi, err, sms, nullptr, nullptr);
   if (n < 0) return 3;
   if (cudaDeviceSynchronize() != cudaSuccess) return 4;
   int herr = 0;
@@ -278,21 +278,21 @@ int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, 
   return cudaDeviceSynchronize() == cudaSuccess ? 0 : 4;
 }
 
-int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads) {
+int cudabert_k_attention(int kernel, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads) {
   if (!qkv_dev || !ctx_dev || B <= 0 || S <= 0 || heads <= 0) return 1;
-  const int cls_only = (bf16 & 16) ? 1 : 0;  // + 16: first query of every sequence only, ctx is [B, H]
-  bf16 &= 15;
-  if (cls_only && bf16 == 0) return 1;
+  const int cls_only = (kernel & 16) ? 1 : 0;  // + 16: first query of every sequence only, ctx is [B, H]
+  kernel &= 15;
+  if (cls_only && kernel == 0) return 1;
   int* kv = nullptr;
   if (cudaMalloc(&kv, (3 * static_cast<size_t>(B) + 1) * sizeof(int)) != cudaSuccess) return 2;
   int* err = kv + B;
-  int* sched = bf16 == 3 ? kv + B + 1 : nullptr;  // 2 B entries
+  int* sched = kernel == 3 ? kv + B + 1 : nullptr;  // 2 B entries
   cudaMemset(err, 0, sizeof(int));
   int rc = 0;
   if (cb::row_layout(mask_dev, kv, nullptr, sched, B, S, nullptr) < 0) rc = 3;
   if (!rc) {
     int n;
-    if (bf16 == 2 || bf16 == 3) {  // tcgen05 kernel, persistent mma.sync kernel: both read K and V by TMA
+    if (kernel == 2 || kernel == 3) {  // tcgen05 kernel, persistent mma.sync kernel: both read K and V by TMA
       CUtensorMap tm;
       int dev = 0, sms = 148;
       cudaGetDevice(&dev);
@@ -301,15 +301,15 @@ int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, voi
         cudaFree(kv);
         return 2;
       }
-      if (bf16 == 2)
-        n = cb::attention_bf16_tc(&tm, mask_dev, kv, nullptr, static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, sms,
+      if (kernel == 2)
+        n = cb::attention_f16_tc(&tm, mask_dev, kv, nullptr, static_cast<__half*>(ctx_dev), B, S, heads, sms,
                                   cls_only, err, nullptr);
       else
-        n = cb::attention_bf16_persist(&tm, mask_dev, kv, nullptr, sched, static_cast<__nv_bfloat16*>(ctx_dev), B, S,
+        n = cb::attention_f16_persist(&tm, mask_dev, kv, nullptr, sched, static_cast<__half*>(ctx_dev), B, S,
                                        heads, sms, cls_only, err, nullptr);
-    } else if (bf16) {
-      n = cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
-                             static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, cls_only, nullptr);
+    } else if (kernel) {
+      n = cb::attention_f16(static_cast<const __half*>(qkv_dev), mask_dev, kv, nullptr,
+                             static_cast<__half*>(ctx_dev), B, S, heads, cls_only, nullptr);
     } else {
       n = cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr, static_cast<float*>(ctx_dev), B,
                             S, heads, nullptr);
@@ -323,16 +323,16 @@ int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, voi
   return rc;
 }
 
-int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev, const float* word_dev,
+int cudabert_k_embed_layernorm(int half, const int* ids_dev, const int* seg_dev, const float* word_dev,
                                const float* pos_dev, const float* type_dev, const float* gamma_dev,
                                const float* beta_dev, void* out_dev, float* out_f32_dev, int tokens, int S, int H,
                                int vocab) {
   static thread_local DevErr scratch;
   if (!scratch.ok()) return 2;
   int n;
-  if (bf16)
-    n = cb::embed_layernorm<__nv_bfloat16>(ids_dev, seg_dev, word_dev, pos_dev, type_dev, gamma_dev, beta_dev,
-                                           static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, S, H, vocab,
+  if (half)
+    n = cb::embed_layernorm<__half>(ids_dev, seg_dev, word_dev, pos_dev, type_dev, gamma_dev, beta_dev,
+                                           static_cast<__half*>(out_dev), out_f32_dev, tokens, S, H, vocab,
                                            scratch.p, nullptr, nullptr);
   else
     n = cb::embed_layernorm<float>(ids_dev, seg_dev, word_dev, pos_dev, type_dev, gamma_dev, beta_dev,
@@ -345,18 +345,18 @@ int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev,
   return herr ? 5 : 0;
 }
 
-int cudabert_k_layernorm(int out_bf16, int in_f16, const void* x_dev, const float* residual_dev,
+int cudabert_k_layernorm(int out_f16, int in_f16, const void* x_dev, const float* residual_dev,
                          const float* gamma_dev, const float* beta_dev, void* out_dev, float* out_f32_dev, int tokens,
                          int H) {
   int n;
   const __half* xh = static_cast<const __half*>(x_dev);
   const float* xf = static_cast<const float*>(x_dev);
-  if (out_bf16 && in_f16)
-    n = cb::layernorm<__half, __nv_bfloat16>(xh, residual_dev, gamma_dev, beta_dev,
-                                             static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, H, nullptr, nullptr);
-  else if (out_bf16)
-    n = cb::layernorm<float, __nv_bfloat16>(xf, residual_dev, gamma_dev, beta_dev,
-                                            static_cast<__nv_bfloat16*>(out_dev), out_f32_dev, tokens, H, nullptr, nullptr);
+  if (out_f16 && in_f16)
+    n = cb::layernorm<__half, __half>(xh, residual_dev, gamma_dev, beta_dev,
+                                             static_cast<__half*>(out_dev), out_f32_dev, tokens, H, nullptr, nullptr);
+  else if (out_f16)
+    n = cb::layernorm<float, __half>(xf, residual_dev, gamma_dev, beta_dev,
+                                            static_cast<__half*>(out_dev), out_f32_dev, tokens, H, nullptr, nullptr);
   else if (in_f16)
     n = cb::layernorm<__half, float>(xh, residual_dev, gamma_dev, beta_dev, static_cast<float*>(out_dev), out_f32_dev,
                                      tokens, H, nullptr, nullptr);

@@ -4,6 +4,11 @@
 // (ops/softmax.cu:86-143) and Prob_Value::forward (ops/batch_matmul.cu:85-140) of the
 // reference, and reads Q, K, V straight from the packed projection output [T, 3H].
 //
+// The 16-bit kernels take Q, K and V in fp16 and round the probabilities to fp16 (both operands of
+// QK^T and of P.V are activations, and fp16 keeps three more significand
+// bits than bf16); accumulation and the softmax are fp32, the output is fp16, the
+// A-operand format of the attention-output GEMM.
+//
 // Mask semantics (ops/softmax.cu:97-101, modeling.py:237-240): score/8 + (1-mask[key])*-10000.
 // A masked key's probability is exactly 0 in fp32 whenever the row has at least one valid key,
 // so key tiles at or beyond kv_len[b] (all padding) are skipped.  A row with no valid key
@@ -12,6 +17,7 @@
 #include "ptx.cuh"
 #include "../../include/cudabert.h"
 
+#include <atomic>
 #include <cmath>
 #include <mutex>
 
@@ -51,7 +57,7 @@ struct RingTiles {
 // fragment a warp loads with ldmatrix feeds four MMAs instead of two and the warp has twice as
 // many independent accumulator chains, at twice the registers (so half as many warps fit).
 // `stage` is MB x 2 KB of shared memory that only this warp touches while it works on the block.
-// The queries come either from global memory (`sQ` null: `base` points at the first Q element of
+// The queries come either from global memory (`sQ` null: `base` points at the first Q element (fp16) of
 // the sequence's first row, row stride `ld`; they pass through `stage`) or from shared memory
 // (`sQ`: the block's own rows of a Q tile, which may be `stage` itself).  `out_base` points at the
 // sequence's first output element (row stride `H`).  Bit t of `biased` says that key tile t needs
@@ -59,8 +65,8 @@ struct RingTiles {
 template <int MB, bool Q_IN_SMEM, typename Tiles>
 __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __restrict__ sBias, unsigned int biased,
                                               uint8_t* __restrict__ stage, const uint8_t* __restrict__ sQ,
-                                              const __nv_bfloat16* __restrict__ base, int ld,
-                                              __nv_bfloat16* __restrict__ out_base, int H, int q0, int nq,
+                                              const __half* __restrict__ base, int ld,
+                                              __half* __restrict__ out_base, int H, int q0, int nq,
                                               int ktiles, int lane) {
   const float scale = 0.125f * LOG2E;
   uint32_t qf[MB][4][4];
@@ -118,8 +124,8 @@ __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __
         ldmatrix_x4(kf, smem_u32(kt + swz(nb * 16 + (mid >> 1) * 8 + (lane & 7), kk * 2 + (mid & 1))));
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
-          mma_bf16_16816(s[mb][2 * nb], qf[mb][kk], kf[0], kf[1]);
-          mma_bf16_16816(s[mb][2 * nb + 1], qf[mb][kk], kf[2], kf[3]);
+          mma_f16_16816(s[mb][2 * nb], qf[mb][kk], kf[0], kf[1]);
+          mma_f16_16816(s[mb][2 * nb + 1], qf[mb][kk], kf[2], kf[3]);
         }
       }
     }
@@ -174,8 +180,8 @@ __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __
         const float p3 = ex2_approx(fmaf(s[mb][i][3], e_scale, -m_new[1]));
         l_run[mb][0] += p0 + p1;
         l_run[mb][1] += p2 + p3;
-        pf[mb][i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
-        pf[mb][i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+        pf[mb][i >> 1][(i & 1) * 2] = pack_f16(p0, p1);
+        pf[mb][i >> 1][(i & 1) * 2 + 1] = pack_f16(p2, p3);
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -192,8 +198,8 @@ __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __
         ldmatrix_x4_trans(vf, smem_u32(vt + swz(j * 16 + (mid & 1) * 8 + (lane & 7), db * 2 + (mid >> 1))));
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
-          mma_bf16_16816(o[mb][2 * db], pf[mb][j], vf[0], vf[1]);
-          mma_bf16_16816(o[mb][2 * db + 1], pf[mb][j], vf[2], vf[3]);
+          mma_f16_16816(o[mb][2 * db], pf[mb][j], vf[0], vf[1]);
+          mma_f16_16816(o[mb][2 * db + 1], pf[mb][j], vf[2], vf[3]);
         }
       }
     }
@@ -214,9 +220,9 @@ __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __
     for (int i = 0; i < 8; ++i) {
       // columns i*8 + 2*t4, +1 of rows g and g + 8: chunk i, byte offset 4 * t4 inside the chunk
       *reinterpret_cast<uint32_t*>(stage + swz(mb * 16 + g, i) + 4 * t4) =
-          pack_bf16(o[mb][i][0] * inv0, o[mb][i][1] * inv0);
+          pack_f16(o[mb][i][0] * inv0, o[mb][i][1] * inv0);
       *reinterpret_cast<uint32_t*>(stage + swz(mb * 16 + g + 8, i) + 4 * t4) =
-          pack_bf16(o[mb][i][2] * inv1, o[mb][i][3] * inv1);
+          pack_f16(o[mb][i][2] * inv1, o[mb][i][3] * inv1);
     }
   }
   __syncwarp();
@@ -235,9 +241,9 @@ __device__ __forceinline__ void attend_qblock(const Tiles tiles, const float* __
 // tiles entirely out of shared memory, with no further block-wide synchronisation.
 //   smem: K [R][64] | V [R][64] | per-warp Q / O staging [16][64] | bias [R]   (R = keys rounded to 64)
 __global__ void __launch_bounds__(ATT_MAX_WARPS * 32, 2)
-attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ mask,
+attention_f16_kernel(const __half* __restrict__ qkv, const int* __restrict__ mask,
                       const int* __restrict__ kv_len, const int* __restrict__ row_start,
-                      __nv_bfloat16* __restrict__ ctx, int S, int heads, int R, int cls_only) {
+                      __half* __restrict__ ctx, int S, int heads, int R, int cls_only) {
   extern __shared__ __align__(1024) uint8_t att_smem[];
   uint8_t* sK = att_smem;
   uint8_t* sV = sK + static_cast<size_t>(R) * 128;
@@ -260,12 +266,12 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
   const int nq = cls_only ? 1 : (row_start ? klen : S);
   const int ktiles = (klen + 63) >> 6;
   const int krows = ktiles << 6;  // rows of K / V the tiles touch; rows >= klen are zero-filled
-  const __nv_bfloat16* base = qkv + static_cast<size_t>(first) * ld + h * HD;
+  const __half* base = qkv + static_cast<size_t>(first) * ld + h * HD;
 
   for (int i = tid; i < krows * 8; i += blockDim.x) {
     const int r = i >> 3, c = i & 7;
     const bool ok = r < klen;
-    const __nv_bfloat16* src = base + static_cast<size_t>(ok ? r : 0) * ld + c * 8;
+    const __half* src = base + static_cast<size_t>(ok ? r : 0) * ld + c * 8;
     cp_async16(smem_u32(sK + swz(r, c)), src + H, ok);
     cp_async16(smem_u32(sV + swz(r, c)), src + 2 * H, ok);
   }
@@ -288,14 +294,14 @@ attention_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restri
 
   uint8_t* myQ = sQ + warp * 2048;
   const int qblocks = (nq + 15) >> 4;
-  __nv_bfloat16* out_base = ctx + static_cast<size_t>(cls_only ? b : first) * H + h * HD;
+  __half* out_base = ctx + static_cast<size_t>(cls_only ? b : first) * H + h * HD;
   for (int qb = warp; qb < qblocks; qb += nwarps)
     attend_qblock<1, false>(ContigTiles{sK, sV}, sBias, biased, myQ, nullptr, base, ld, out_base, H, qb * 16, nq,
                             ktiles, lane);
 }
 
 // ---------------------------------------------------------------- persistent variant
-// The same arithmetic as attention_bf16_kernel (attend_qblock), scheduled differently.  With one
+// The same arithmetic as attention_f16_kernel (attend_qblock), scheduled differently.  With one
 // CTA per (sequence, head) a short sequence leaves most of the CTA's warps without a query block
 // while they still hold their registers, and every CTA first waits for its keys and values before
 // any warp computes.  Here one persistent CTA per SM keeps 15 consumer warps busy and a producer
@@ -353,9 +359,9 @@ constexpr size_t pa_smem_bytes(int R) {
 static_assert(pa_ring_tiles(PA_MAX_R) >= 24, "two items of the largest supported length must fit");
 
 __global__ void __launch_bounds__(PA_THREADS, 1)
-attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __restrict__ mask,
+attention_f16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __restrict__ mask,
                               const int* __restrict__ kv_len, const int* __restrict__ row_start,
-                              const int* __restrict__ sched, __nv_bfloat16* __restrict__ ctx, int B, int S, int heads,
+                              const int* __restrict__ sched, __half* __restrict__ ctx, int B, int S, int heads,
                               int R, int NT, int cls_only, int* __restrict__ err) {
   extern __shared__ uint8_t pa_smem_raw[];
   uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(pa_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -495,7 +501,7 @@ attention_bf16_persist_kernel(const __grid_constant__ CUtensorMap tmQKV, const i
       tiles.v0 = tile0 + ktiles >= NT ? tile0 + ktiles - NT : tile0 + ktiles;
       const int q_first = tiles.v0 + ktiles >= NT ? tiles.v0 + ktiles - NT : tiles.v0 + ktiles;
       const float* sBias = sBiasAll + static_cast<size_t>(rec) * R;
-      __nv_bfloat16* out_base = ctx + static_cast<size_t>(out_row) * H + h * HD;
+      __half* out_base = ctx + static_cast<size_t>(out_row) * H + h * HD;
       for (;;) {
         int qb = 0;
         if (lane == 0) qb = atomicAdd(&pi->next_q, 1);
@@ -717,48 +723,48 @@ row_layout_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int* _
 
 }  // namespace
 
-int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, const int* row_start,
-                   __nv_bfloat16* ctx, int B, int S, int heads, int cls_only, cudaStream_t stream) {
+int attention_f16(const __half* qkv, const int* mask, const int* kv_len, const int* row_start,
+                   __half* ctx, int B, int S, int heads, int cls_only, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || S > 512 || heads <= 0 || B > 65535) return -1;
   const int R = ((S + 63) / 64) * 64;
   const int qblocks = (S + 15) / 16;
   const int nwarps = qblocks < ATT_MAX_WARPS ? qblocks : ATT_MAX_WARPS;
   const size_t smem = static_cast<size_t>(R) * 256 + nwarps * 2048 + static_cast<size_t>(R) * 4;
-  static size_t attr_max[64] = {};
+  static std::atomic<bool> attr_set[64] = {};  // per device; a repeated set by a racing thread is harmless
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && smem > attr_max[dev]) {
-    const size_t want = 512 * 256 + ATT_MAX_WARPS * 2048 + 512 * 4;
-    if (cudaFuncSetAttribute(attention_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
+    const size_t want = 512 * 256 + ATT_MAX_WARPS * 2048 + 512 * 4;  // the largest S
+    if (cudaFuncSetAttribute(attention_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(want)) != cudaSuccess)
       return -2;
-    attr_max[dev] = want;
+    if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
   }
   dim3 grid(heads, B);
-  return launch_pdl(attention_bf16_kernel, grid, dim3(nwarps * 32), smem, stream, qkv, mask, kv_len, row_start, ctx, S,
+  return launch_pdl(attention_f16_kernel, grid, dim3(nwarps * 32), smem, stream, qkv, mask, kv_len, row_start, ctx, S,
                     heads, R, cls_only) == cudaSuccess ? 1 : -3;
 }
 
 bool attention_persist_fits(int S) { return ((S + 63) / 64) * 64 <= PA_MAX_R; }
 
-int attention_bf16_persist(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                           const int* sched, __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int cls_only,
+int attention_f16_persist(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
+                           const int* sched, __half* ctx, int B, int S, int heads, int num_sms, int cls_only,
                            int* err_flag, cudaStream_t stream) {
   if (B <= 0 || S <= 0 || heads <= 0 || !attention_persist_fits(S)) return -1;
   const int R = ((S + 63) / 64) * 64;
   const int NT = pa_ring_tiles(R);
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(attention_bf16_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
+    if (cudaFuncSetAttribute(attention_f16_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(PA_SMEM_LIMIT)) != cudaSuccess)
       return -2;
-    attr_set[dev] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
   }
   const long long items = static_cast<long long>(B) * heads;
   const int grid = static_cast<int>(items < num_sms ? items : num_sms);
-  return launch_pdl(attention_bf16_persist_kernel, dim3(grid), dim3(PA_THREADS), pa_smem_bytes(R), stream, *tm_qkv, mask,
+  return launch_pdl(attention_f16_persist_kernel, dim3(grid), dim3(PA_THREADS), pa_smem_bytes(R), stream, *tm_qkv, mask,
                     kv_len, row_start, sched, ctx, B, S, heads, R, NT, cls_only, err_flag) == cudaSuccess ? 1 : -3;
 }
 
@@ -786,8 +792,25 @@ static __device__ __align__(256) int g_noalloc_kv_len[CUDABERT_NOALLOC_MAX_BATCH
 
 extern "C" int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B,
                                             int S, int heads) {
+  // Everything is validated before the first launch: a kernel number this entry point cannot serve
+  // must not fall through to another kernel that would write a differently shaped output.
   if (!qkv_dev || !ctx_dev || B <= 0 || S <= 0 || heads <= 0) {
     cb::set_thread_error("cudabert_k_attention_noalloc: null buffer or non-positive size");
+    return 1;
+  }
+  const int cls_only = (bf16 & 16) ? 1 : 0;  // + 16: first query of every sequence only, ctx is [B, H]
+  const int kernel = bf16 & ~16;
+  if (kernel != 0 && kernel != 1) {
+    cb::set_thread_error("cudabert_k_attention_noalloc: only kernels 0 (fp32) and 1 (16-bit mma.sync, optionally + 16) "
+                         "are served; kernels 2 and 3 need scheduling and error scratch beyond the built-in array");
+    return 1;
+  }
+  if (cls_only && kernel == 0) {
+    cb::set_thread_error("cudabert_k_attention_noalloc: + 16 (first query only) needs a 16-bit kernel");
+    return 1;
+  }
+  if (kernel == 1 && S > 512) {
+    cb::set_thread_error("cudabert_k_attention_noalloc: the 16-bit kernel holds sequences of up to 512 keys");
     return 1;
   }
   if (B > CUDABERT_NOALLOC_MAX_BATCH) {
@@ -820,12 +843,16 @@ extern "C" int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const
     kv = scratch_of_device[dev];
   }
   // every entry [0, B) is rewritten before it is read, so nothing left by an earlier call matters
-  if (cb::row_layout(mask_dev, kv, nullptr, nullptr, B, S, nullptr) < 0) return 3;
-  const int n = bf16 ? cb::attention_bf16(static_cast<const __nv_bfloat16*>(qkv_dev), mask_dev, kv, nullptr,
-                                          static_cast<__nv_bfloat16*>(ctx_dev), B, S, heads, 0, nullptr)
-                     : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr,
-                                         static_cast<float*>(ctx_dev), B, S, heads, nullptr);
-  if (n < 0) return 3;
+  int n = cb::row_layout(mask_dev, kv, nullptr, nullptr, B, S, nullptr);
+  if (n >= 0)
+    n = kernel ? cb::attention_f16(static_cast<const __half*>(qkv_dev), mask_dev, kv, nullptr,
+                                    static_cast<__half*>(ctx_dev), B, S, heads, cls_only, nullptr)
+               : cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr,
+                                   static_cast<float*>(ctx_dev), B, S, heads, nullptr);
+  if (n < 0) {
+    cb::set_thread_error("cudabert_k_attention_noalloc: kernel launch rejected (code " + std::to_string(n) + ")");
+    return 3;
+  }
   const cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     cb::set_thread_error(std::string("cudabert_k_attention_noalloc: ") + cudaGetErrorString(e));

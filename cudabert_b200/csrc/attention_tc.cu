@@ -1,5 +1,5 @@
 // Fused masked attention on the tcgen05 tensor cores (bf16 / fp8 modes).  Same contract as
-// attention_bf16 in attention.cu (which stays as the `mma.sync` variant): QK^T, 1/8 scale, additive
+// attention_f16 in attention.cu (which stays as the `mma.sync` variant): QK^T, 1/8 scale, additive
 // key mask, softmax, P.V in one kernel, keys at or beyond kv_len[b] never touched.  Replaces
 // Query_Key::forward (ops/batch_matmul.cu:24-82), cuApplySoftmax (ops/softmax.cu:86-143) and
 // Prob_Value::forward (ops/batch_matmul.cu:85-140) of the reference.
@@ -23,6 +23,7 @@
 #include "kernels.h"
 #include "ptx.cuh"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace cb {
@@ -67,9 +68,9 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr) {
   return static_cast<uint64_t>((smem_addr >> 4) & 0x3fff) | (64ull << 16) | (64ull << 32) | (1ull << 46) |
          (2ull << 61);
 }
-// Instruction descriptor: D fp32, A bf16 K-major, B bf16 MN-major, shape M x N (x 16).
-__host__ __device__ constexpr uint32_t umma_idesc_bf16_bmn(int m, int n) {
-  return umma_idesc_bf16(m, n) | (1u << 16);
+// Instruction descriptor: D fp32, A fp16 K-major, B fp16 MN-major, shape M x N (x 16).
+__host__ __device__ constexpr uint32_t umma_idesc_f16_bmn(int m, int n) {
+  return umma_idesc_f16(m, n) | (1u << 16);
 }
 
 struct ItemInfo {
@@ -101,7 +102,7 @@ __device__ __forceinline__ ItemInfo decode_item(int item, int QT, int heads, int
 __global__ void __launch_bounds__(ATC_THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __restrict__ mask,
                     const int* __restrict__ kv_len, const int* __restrict__ row_start,
-                    __nv_bfloat16* __restrict__ ctx, int B, int S, int heads, int cls_only, int* err) {
+                    __half* __restrict__ ctx, int B, int S, int heads, int cls_only, int* err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* sBias = reinterpret_cast<float*>(smem + SMEM_BIAS);
@@ -185,8 +186,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(TQ, TK);
-      constexpr uint32_t idesc_o = umma_idesc_bf16_bmn(TQ, HD);
+      constexpr uint32_t idesc_s = umma_idesc_f16(TQ, TK);
+      constexpr uint32_t idesc_o = umma_idesc_f16_bmn(TQ, HD);
       const uint32_t sq = smem_u32(smem + SMEM_Q), sk = smem_u32(smem + SMEM_K), sv = smem_u32(smem + SMEM_V),
                      sp = smem_u32(smem + SMEM_P);
       // S = Q K^T of the block under `c` into S buffer blocks_done & 1.  That buffer was last read by
@@ -198,7 +199,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
         tc_fence_after();
         const uint64_t da = umma_desc_sw128(sq + qb * Q_BYTES), db = umma_desc_sw128(sk + kb * KV_BYTES);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) umma_bf16(tmem_base + S_COL + kb * TK, da + 2 * k, db + 2 * k, idesc_s, k != 0);
+        for (int k = 0; k < HD / 16; ++k) umma_f16(tmem_base + S_COL + kb * TK, da + 2 * k, db + 2 * k, idesc_s, k != 0);
         umma_commit(s_full + kb);
         umma_commit(k_empty + kb);
         if (c.j == c.it.nblocks - 1) umma_commit(q_empty + qb);
@@ -213,7 +214,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
         for (int k = 0; k < TK / 16; ++k) {
           const uint64_t da = umma_desc_sw128(sp) + 2 * k;
           const uint64_t db = umma_desc_sw128_mn(sv + vb * KV_BYTES) + static_cast<uint64_t>(k) * (2048 >> 4);
-          umma_bf16(tmem_base + O_COL, da, db, idesc_o, (c.j | k) != 0);
+          umma_f16(tmem_base + O_COL, da, db, idesc_o, (c.j | k) != 0);
         }
         umma_commit(o_full);
         umma_commit(v_empty + vb);
@@ -351,10 +352,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 t;
-          t.x = pack_bf16(p[8 * q], p[8 * q + 1]);
-          t.y = pack_bf16(p[8 * q + 2], p[8 * q + 3]);
-          t.z = pack_bf16(p[8 * q + 4], p[8 * q + 5]);
-          t.w = pack_bf16(p[8 * q + 6], p[8 * q + 7]);
+          t.x = pack_f16(p[8 * q], p[8 * q + 1]);
+          t.y = pack_f16(p[8 * q + 2], p[8 * q + 3]);
+          t.z = pack_f16(p[8 * q + 4], p[8 * q + 5]);
+          t.w = pack_f16(p[8 * q + 6], p[8 * q + 7]);
           *reinterpret_cast<uint4*>(my_p + (((ch * 4 + q) ^ (r & 7)) << 4)) = t;
         }
       }
@@ -379,16 +380,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint4 t;
-          t.x = pack_bf16(__uint_as_float(ov[ch][8 * q]) * inv, __uint_as_float(ov[ch][8 * q + 1]) * inv);
-          t.y = pack_bf16(__uint_as_float(ov[ch][8 * q + 2]) * inv, __uint_as_float(ov[ch][8 * q + 3]) * inv);
-          t.z = pack_bf16(__uint_as_float(ov[ch][8 * q + 4]) * inv, __uint_as_float(ov[ch][8 * q + 5]) * inv);
-          t.w = pack_bf16(__uint_as_float(ov[ch][8 * q + 6]) * inv, __uint_as_float(ov[ch][8 * q + 7]) * inv);
+          t.x = pack_f16(__uint_as_float(ov[ch][8 * q]) * inv, __uint_as_float(ov[ch][8 * q + 1]) * inv);
+          t.y = pack_f16(__uint_as_float(ov[ch][8 * q + 2]) * inv, __uint_as_float(ov[ch][8 * q + 3]) * inv);
+          t.z = pack_f16(__uint_as_float(ov[ch][8 * q + 4]) * inv, __uint_as_float(ov[ch][8 * q + 5]) * inv);
+          t.w = pack_f16(__uint_as_float(ov[ch][8 * q + 6]) * inv, __uint_as_float(ov[ch][8 * q + 7]) * inv);
           *reinterpret_cast<uint4*>(my_row + (((ch * 4 + q) ^ (lane & 7)) << 4)) = t;
         }
       }
       tc_fence_before();
       __syncwarp();
-      __nv_bfloat16* out_base = ctx + static_cast<size_t>(cls_only ? it.b : it.first) * H + it.h * HD;
+      __half* out_base = ctx + static_cast<size_t>(cls_only ? it.b : it.first) * H + it.h * HD;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int rr = i * 4 + (lane >> 3), p2 = lane & 7;
@@ -447,20 +448,20 @@ int attention_kernel_for(int S) {
 }
 
 bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H) {
-  return make_tmap_bf16_kmajor(out, qkv, rows, static_cast<uint64_t>(3) * H, static_cast<uint64_t>(3) * H * 2, TK);
+  return make_tmap_16bit_kmajor(out, qkv, rows, static_cast<uint64_t>(3) * H, static_cast<uint64_t>(3) * H * 2, TK);
 }
 
-int attention_bf16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                      __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
+int attention_f16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
+                      __half* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
                       cudaStream_t stream) {
   if (B <= 0 || S <= 0 || S > 512 || heads <= 0) return -1;
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64] = {};  // per device; a repeated set by a racing thread is harmless
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && !attr_set[dev]) {
+  if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM) != cudaSuccess)
       return -2;
-    attr_set[dev] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
   }
   const long long items = static_cast<long long>(B) * heads * ((S + TQ - 1) / TQ);
   const int grid = static_cast<int>(items < 2LL * num_sms ? items : 2LL * num_sms);

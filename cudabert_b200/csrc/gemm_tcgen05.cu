@@ -32,6 +32,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 namespace cb {
@@ -126,6 +127,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restric
     for (int j = 0; j < 32; ++j) {
       f[j] = __uint_as_float(v[j]);
       if (fl & EPI_COLSCALE) f[j] *= sscale[col + j];
+      if (fl & EPI_WSCALE) f[j] *= (1.0f / W_CONTAINER_SCALE);  // fuses with the bias add into one FMA
       if (fl & EPI_BIAS) f[j] += sbias[col + j];
     }
     if (fl & EPI_RESIDUAL) {
@@ -334,7 +336,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      const uint32_t idesc = (((FLAGS >= 0) ? FLAGS : flags) & EPI_IN_F16) ? umma_idesc_f16(BM, BN) : umma_idesc_bf16(BM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -353,7 +355,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advance 16 elements (32 bytes) along K inside the 128-byte swizzle row
-            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            umma_f16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
           }
           umma_commit(empty_bar + stage);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -490,7 +492,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     }
   } else if (warp == 1) {
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN);
+      const uint32_t idesc =
+          (((FLAGS >= 0) ? FLAGS : flags) & EPI_IN_F16) ? umma_idesc_f16(2 * BM, BN) : umma_idesc_bf16(2 * BM, BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -507,7 +510,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const uint64_t da = umma_desc_sw128(sa);
           const uint64_t db = umma_desc_sw128(sa + C::A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          for (int k = 0; k < BK / UMMA_K; ++k) umma_f16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
           umma_commit_pair(empty_bar + stage, 3);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
@@ -565,22 +568,23 @@ EncodeTiledFn get_encode_fn() {
 
 // Epilogue combinations compiled with the flags fixed (the ones the encoder uses; for CTA pairs
 // also with the FP8 column scale); everything else runs the FLAGS = -1 instantiation.
-constexpr int F_QKV = EPI_BIAS;
-constexpr int F_FFN1 = EPI_BIAS | EPI_GELU;
-constexpr int F_H16 = EPI_BIAS | EPI_OUT_F16;
+constexpr int F_LIN = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_WSCALE;                  // QKV, attention-output, FFN2
+constexpr int F_FFN1 = F_LIN | EPI_GELU;
+constexpr int F_LIN8 = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_COLSCALE;               // the same in FP8-weight mode
+constexpr int F_FFN18 = F_LIN8 | EPI_GELU;
 
 template <int BN, int FLAGS>
 int launch_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
                const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream) {
   using C = Cfg<BN>;
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64] = {};  // per device; a repeated set by a racing thread is harmless
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && !attr_set[dev]) {
+  if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, FLAGS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::SMEM_BYTES) != cudaSuccess)
       return -2;
-    attr_set[dev] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
   }
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
@@ -593,9 +597,8 @@ template <int BN>
 int launch(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
            const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream) {
   switch (epi.flags) {
-    case F_QKV: return launch_one<BN, F_QKV>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
+    case F_LIN: return launch_one<BN, F_LIN>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
     case F_FFN1: return launch_one<BN, F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
-    case F_H16: return launch_one<BN, F_H16>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
     default: return launch_one<BN, -1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
   }
 }
@@ -604,8 +607,8 @@ int launch(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, 
 // GPC); a persistent grid larger than that would run its last pairs after all the others.
 template <int FLAGS>
 int max_resident_pairs(int dev) {
-  static int cached[64] = {};
-  if (dev < 64 && cached[dev] > 0) return cached[dev];
+  static std::atomic<int> cached[64] = {};  // per device; racing threads compute the same value
+  if (dev >= 0 && dev < 64 && cached[dev].load(std::memory_order_acquire) > 0) return cached[dev].load();
   using C = PairCfg<256>;
   if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<256, FLAGS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            C::SMEM_BYTES) != cudaSuccess)
@@ -626,7 +629,7 @@ int max_resident_pairs(int dev) {
     cudaGetLastError();
     return -1;
   }
-  if (dev < 64) cached[dev] = n;
+  if (dev >= 0 && dev < 64) cached[dev].store(n, std::memory_order_release);
   return n;
 }
 
@@ -648,15 +651,10 @@ int launch_pair_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N
 int launch_pair(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
                 const GemmEpilogue& epi, int* err_flag, const int* m_dev, cudaStream_t stream) {
   switch (epi.flags) {
-    case F_QKV: return launch_pair_one<F_QKV>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_LIN: return launch_pair_one<F_LIN>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_FFN1: return launch_pair_one<F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    case F_H16: return launch_pair_one<F_H16>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    case F_QKV | EPI_COLSCALE:
-      return launch_pair_one<F_QKV | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    case F_FFN1 | EPI_COLSCALE:
-      return launch_pair_one<F_FFN1 | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    case F_H16 | EPI_COLSCALE:
-      return launch_pair_one<F_H16 | EPI_COLSCALE>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_LIN8: return launch_pair_one<F_LIN8>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_FFN18: return launch_pair_one<F_FFN18>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     default: return launch_pair_one<-1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   }
 }
@@ -686,7 +684,7 @@ bool gemm_uses_pairs(int N) { return pair_enabled() && (N % 256 == 0); }
 // Rows of the W tensor map's box: a CTA of a pair loads half of the 256-row tile.
 int gemm_w_box_rows(int N) { return gemm_uses_pairs(N) ? 128 : gemm_block_n(N); }
 
-bool make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+bool make_tmap_16bit_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                            uint64_t row_stride_bytes, uint32_t box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
@@ -696,13 +694,14 @@ bool make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, ui
   const cuuint64_t strides[1] = {row_stride_bytes};
   const cuuint32_t box[2] = {BK, box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  // the copy moves 16-bit elements untouched (fp16 or bf16 alike); out-of-range elements read as zero bits
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
-int gemm_bf16_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
+int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
                       const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (N % 128) != 0 || (K % BK) != 0 || (ldo % 8) != 0) return -1;
   if ((epi.flags & EPI_BIAS) && !epi.bias) return -1;

@@ -64,9 +64,17 @@ enum EpiFlags : int {
   EPI_TANH = 8,      // tanh (pooler, reference: ops/elementwise.cu:57-61)
   EPI_OUT_F32 = 16,  // write fp32 instead of bf16 (tcgen05 GEMM only; the fp32 GEMM always does)
   EPI_COLSCALE = 32, // multiply the accumulator by colscale[n] (FP8 weight de-quantisation)
-  EPI_OUT_F16 = 64   // write fp16 instead of bf16 (tcgen05 GEMM only): the dense outputs that the
-                     // LayerNorm kernel adds to the fp32 residual stream
+  EPI_OUT_F16 = 64,  // write fp16 instead of bf16 (tcgen05 GEMM only)
+  EPI_WSCALE = 128,  // multiply the accumulator by 1 / W_CONTAINER_SCALE (weights held as scaled fp16, below)
+  EPI_IN_F16 = 256   // A and W are fp16 (tcgen05 GEMM only; bf16 otherwise)
 };
+
+// The encoder's dense weights are ROUNDED to bf16 (8 significand bits: the weight format of the bf16
+// mode) and HELD as fp16 numbers, multiplied by this power of two so that even the smallest of them
+// stay above fp16's subnormal range: every bf16 value of magnitude 2^-37 .. 15.9 is represented
+// exactly.  Both MMA operands are then fp16, so the activations keep 11 significand bits instead
+// of bf16's 8; the epilogue takes the factor out again (EPI_WSCALE).
+constexpr float W_CONTAINER_SCALE = 4096.0f;
 
 struct GemmEpilogue {
   int flags = 0;
@@ -75,21 +83,22 @@ struct GemmEpilogue {
   const float* colscale = nullptr;
 };
 
-// ---- tcgen05 GEMM: out[M, N] = A[M, K] (bf16, K contiguous) x W[N, K]^T (bf16, K contiguous)
+// ---- tcgen05 GEMM: out[M, N] = A[M, K] (K contiguous) x W[N, K]^T (K contiguous), both bf16, or both
+// fp16 with EPI_IN_F16
 // N must be a multiple of 128 and K of 64; M is arbitrary (tail rows are zero-filled by TMA
-// and never stored).  `tmA` / `tmW` are tiled tensor maps made by make_tmap_bf16_kmajor with
+// and never stored).  `tmA` / `tmW` are tiled tensor maps made by make_tmap_16bit_kmajor with
 // box rows 128 (A) and gemm_w_box_rows(N) (W).
 // m_dev (device int, may be null): the live row count; the kernel then computes rows
 // [0, min(M, *m_dev)) while the launch is sized for M.
-int gemm_bf16_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
+int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
                       const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream);
 int gemm_block_n(int N);
-// Box rows the W tensor map must be encoded with for the kernel variant that gemm_bf16_tcgen05
+// Box rows the W tensor map must be encoded with for the kernel variant that gemm_tcgen05
 // will pick for this N (128 when CTA pairs each load half of a 256-row tile, else gemm_block_n).
 int gemm_w_box_rows(int N);
-// Encode a 2-D tiled map over a row-major bf16 matrix [rows, cols] with `row_stride_bytes`
-// between rows, box = 64 columns (128 bytes, 128-byte swizzle) x `box_rows` rows.
-bool make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+// Encode a 2-D tiled map over a row-major matrix of 16-bit elements [rows, cols] with
+// `row_stride_bytes` between rows, box = 64 columns (128 bytes, 128-byte swizzle) x `box_rows` rows.
+bool make_tmap_16bit_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                            uint64_t row_stride_bytes, uint32_t box_rows);
 
 // ---- fp32 CUDA-core GEMM: out[M, N] = A[M, K] (fp32, row stride lda) x W[K, N] (fp32, the
@@ -102,8 +111,8 @@ int gemm_f32(const float* A, int lda, const float* W, int M, int N, int K, float
 int pooler_f32(const float* x, int rows_per_seq, const int* row_start, const float* W, const float* bias, float* out,
                int B, int H, cudaStream_t stream);
 
-// ---- masked attention.  qkv is [rows, 3H] (Q | K | V column blocks, head h at columns h*64),
-// ctx is [rows, H].  kv_len[b] > 0: keys >= kv_len[b] are all masked and are skipped; the
+// ---- masked attention.  qkv is [rows, 3H] (Q | K | V column blocks, head h at columns h*64; fp16 for
+// the 16-bit kernels, fp32 for attention_f32), ctx is [rows, H] (fp16 / fp32).  kv_len[b] > 0: keys >= kv_len[b] are all masked and are skipped; the
 // int32 key mask [B, S] (may be null) is applied to the keys below kv_len.  kv_len[b] == 0: the row
 // has no valid key, every key gets the same -10000 so the mask is ignored (softmax is shift
 // invariant) and the row counts as S long.  Head size is 64.
@@ -113,32 +122,32 @@ int pooler_f32(const float* x, int rows_per_seq, const int* row_start, const flo
 // cls_only != 0 (the three bf16 kernels): only the first query of every sequence is computed and its
 // result is written to row b of ctx ([B, H]) -- what the last encoder layer needs when only the
 // pooler output is wanted; the arithmetic of that row is the same as in a full pass.
-int attention_bf16(const __nv_bfloat16* qkv, const int* mask, const int* kv_len, const int* row_start,
-                   __nv_bfloat16* ctx, int B, int S, int heads, int cls_only, cudaStream_t stream);
+int attention_f16(const __half* qkv, const int* mask, const int* kv_len, const int* row_start,
+                   __half* ctx, int B, int S, int heads, int cls_only, cudaStream_t stream);
 int attention_f32(const float* qkv, const int* mask, const int* kv_len, const int* row_start, float* ctx, int B,
                   int S, int heads, cudaStream_t stream);
-// tcgen05 variant of attention_bf16 (attention_tc.cu): Q, K, V tiles arrive by TMA through `tm_qkv`,
+// tcgen05 variant of attention_f16 (attention_tc.cu): Q, K, V tiles arrive by TMA through `tm_qkv`,
 // a map over the [rows, 3H] projection output made by make_tmap_qkv.  attention_kernel_for says which
 // bf16 kernel a forward pass of padded length S takes (CUDABERT_ATTENTION=tc|persist|mma forces one).
-// Persistent variant of attention_bf16 (one CTA per SM, TMA-fed K/V slots, query blocks drawn
+// Persistent variant of attention_f16 (one CTA per SM, TMA-fed K/V slots, query blocks drawn
 // dynamically).  `sched` (2 B entries from row_layout, may be null) orders the items by descending
 // length and says which rows need their mask read; S <= 256.
 bool attention_persist_fits(int S);
-int attention_bf16_persist(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                           const int* sched, __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int cls_only,
+int attention_f16_persist(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
+                           const int* sched, __half* ctx, int B, int S, int heads, int num_sms, int cls_only,
                            int* err_flag, cudaStream_t stream);
 enum AttentionKernel : int { ATT_KERNEL_MMA = 1, ATT_KERNEL_TC = 2, ATT_KERNEL_PERSIST = 3 };
 int attention_kernel_for(int S);
 bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H);
-int attention_bf16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                      __nv_bfloat16* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
+int attention_f16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
+                      __half* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
                       cudaStream_t stream);
 // kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none); mask null => S.
 // row_start (may be null): exclusive prefix sum of the sequence lengths (a length of 0 counts as S),
 // B + 1 entries, the last one being the number of packed rows.
 int row_layout(const int* mask, int* kv_len, int* row_start, int* sched, int B, int S, cudaStream_t stream);
 
-// ---- row-wise kernels.  The residual stream is kept in fp32; TOut (float or __nv_bfloat16) is
+// ---- row-wise kernels.  The residual stream is kept in fp32; TOut (float or __half) is
 // the copy that feeds the next GEMM.  out_f32 (may be null) receives the same values in fp32.
 // out[row(t)] = LayerNorm(word[ids[t]] + pos[t % S] + type[seg[t]]) for t < tokens = B*S; err bit 1
 // set on a bad id.  row_start == null: row(t) = t.  Packed (row_start from row_layout): token
@@ -161,15 +170,14 @@ int classify_softmax(const float* pooled, const float* W, const float* bias, flo
                      cudaStream_t stream);
 
 // ---- weight preparation (load time)
-// dst[n, k] = bf16(src[k, n])  (on-disk [in, out] -> K-contiguous [out, in]); dst row offset lets
-// Q, K, V be packed into one [3H, H] operand.
-int transpose_to_bf16(const float* src, __nv_bfloat16* dst, int K, int N, cudaStream_t stream);
+// dst[n, k] = bf16-rounded src[k, n] held as fp16 x W_CONTAINER_SCALE (on-disk [in, out] -> K-contiguous
+// [out, in]); dst row offset lets Q, K, V be packed into one [3H, H] operand.
+int transpose_round_bf16(const float* src, __half* dst, int K, int N, cudaStream_t stream);
 // FP8 weights: q[n, k] = e4m3(src[k, n] / scale) stored as bytes, and the same values widened
-// exactly to bf16 for the tensor-core operand; scale = maxabs / 448 is computed on the device
+// exactly to fp16 for the tensor-core operand; scale = maxabs / 448 is computed on the device
 // and written to *scale_out.
-int quantize_fp8_weight(const float* src, uint8_t* dst_q, __nv_bfloat16* dst_op, float* scale_out, int K, int N,
+int quantize_fp8_weight(const float* src, uint8_t* dst_q, __half* dst_op, float* scale_out, int K, int N,
                         cudaStream_t stream);
-int convert_f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream);
 int fill_f32(float* dst, float value, size_t n, cudaStream_t stream);
 
 // Message that cudabert_last_error(NULL) returns on the calling thread.

@@ -189,13 +189,13 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
                                  static_cast<size_t>(N) * 4, K, cudaMemcpyDeviceToDevice, stream_), "pack"))
       return false;
   } else if (prec == PREC_BF16) {
-    if (transpose_to_bf16(stage_f32_, static_cast<__nv_bfloat16*>(d->w) + static_cast<size_t>(n_off) * K, K, N,
+    if (transpose_round_bf16(stage_f32_, static_cast<__half*>(d->w) + static_cast<size_t>(n_off) * K, K, N,
                           stream_) < 0)
       return fail(2, "transpose launch failed");
   } else {
     float* scale_dev = d->colscale + n_off;  // first element of the segment doubles as the scalar slot
     if (quantize_fp8_weight(stage_f32_, d->w_fp8 + static_cast<size_t>(n_off) * K,
-                            static_cast<__nv_bfloat16*>(d->w) + static_cast<size_t>(n_off) * K, scale_dev, K, N,
+                            static_cast<__half*>(d->w) + static_cast<size_t>(n_off) * K, scale_dev, K, N,
                             stream_) < 0)
       return fail(2, "quantise launch failed");
     float scale = 0.f;
@@ -214,7 +214,7 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
 
 bool Model::finish_dense(DenseWeight* d, int prec) {
   if (prec == PREC_FP32) return true;
-  if (!make_tmap_bf16_kmajor(&d->tmap, d->w, d->N, d->K, static_cast<uint64_t>(d->K) * 2, gemm_w_box_rows(d->N)))
+  if (!make_tmap_16bit_kmajor(&d->tmap, d->w, d->N, d->K, static_cast<uint64_t>(d->K) * 2, gemm_w_box_rows(d->N)))
     return fail(2, "cuTensorMapEncodeTiled failed for a weight matrix");
   return true;
 }
@@ -334,10 +334,10 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   if (!check(cudaMemsetAsync(arena_, 0, off, stream_), "cudaMemset(arena)")) return false;
   if (lowp) {
     const uint64_t rows = ct;
-    bool ok = make_tmap_bf16_kmajor(&tm_x_, xa_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
-              make_tmap_bf16_kmajor(&tm_x1_, x1a_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
-              make_tmap_bf16_kmajor(&tm_ctx_, ctx_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
-              make_tmap_bf16_kmajor(&tm_z_, z_, rows, F_, static_cast<uint64_t>(F_) * 2, 128) &&
+    bool ok = make_tmap_16bit_kmajor(&tm_x_, xa_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
+              make_tmap_16bit_kmajor(&tm_x1_, x1a_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
+              make_tmap_16bit_kmajor(&tm_ctx_, ctx_, rows, H_, static_cast<uint64_t>(H_) * 2, 128) &&
+              make_tmap_16bit_kmajor(&tm_z_, z_, rows, F_, static_cast<uint64_t>(F_) * 2, 128) &&
               make_tmap_qkv(&tm_qkv_, qkv_, rows, H_);
     if (!ok) return fail(2, "cuTensorMapEncodeTiled failed for an activation buffer");
   }
@@ -409,11 +409,16 @@ bool Model::dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, i
     n = gemm_f32(static_cast<const float*>(A), lda, static_cast<const float*>(w.w), M, w.N, w.K,
                  static_cast<float*>(out), w.N, epi, m_dev_cur_, stream_);
   } else {
+    // 16-bit modes: fp16 operands and output; the weights' container scale (bf16 mode) or their
+    // FP8 de-quantisation scale comes out in the epilogue
+    epi.flags |= EPI_IN_F16 | EPI_OUT_F16;
     if (prec_ == PREC_FP8) {
       epi.flags |= EPI_COLSCALE;
       epi.colscale = w.colscale;
+    } else {
+      epi.flags |= EPI_WSCALE;
     }
-    n = gemm_bf16_tcgen05(tmA, &w.tmap, M, w.N, w.K, out, w.N, epi, err_dev_, num_sms_, m_dev_cur_, stream_);
+    n = gemm_tcgen05(tmA, &w.tmap, M, w.N, w.K, out, w.N, epi, err_dev_, num_sms_, m_dev_cur_, stream_);
   }
   prof_end(kclass);
   if (n < 0) return fail(2, "GEMM launch rejected (code " + std::to_string(n) + ")");
@@ -500,10 +505,10 @@ bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mas
   const int att_kernel = lowp ? attention_kernel_for(S) : ATT_KERNEL_MMA;
   int* sched = att_kernel == ATT_KERNEL_PERSIST ? att_sched_ : nullptr;
   CB_LAUNCH(KC_OTHER, row_layout(d_mask, kv_len_, packed_ ? row_start_ : nullptr, sched, B, S, stream_));
-  __nv_bfloat16* xa = static_cast<__nv_bfloat16*>(xa_);
-  __nv_bfloat16* x1a = static_cast<__nv_bfloat16*>(x1a_);
+  __half* xa = static_cast<__half*>(xa_);
+  __half* x1a = static_cast<__half*>(x1a_);
   if (lowp) {
-    CB_LAUNCH(KC_EMBED, embed_layernorm<__nv_bfloat16>(d_ids, d_seg, word_, pos_, type_, emb_g_, emb_b_, xa, xf_, T, S,
+    CB_LAUNCH(KC_EMBED, embed_layernorm<__half>(d_ids, d_seg, word_, pos_, type_, emb_g_, emb_b_, xa, xf_, T, S,
                                                        H_, vocab_rows_, err_dev_, rs, stream_));
   } else {
     CB_LAUNCH(KC_EMBED, embed_layernorm<float>(d_ids, d_seg, word_, pos_, type_, emb_g_, emb_b_, xf_, nullptr, T, S, H_,
@@ -521,29 +526,29 @@ bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mas
       // so the pooler output has the same bits as after a full last layer.
       const int cls = (cls_last_ && !want_hidden_f32 && l == L_ - 1) ? 1 : 0;
       if (att_kernel == ATT_KERNEL_TC) {
-        CB_LAUNCH(KC_ATTENTION, attention_bf16_tc(&tm_qkv_, d_mask, kv_len_, rs, static_cast<__nv_bfloat16*>(ctx_), B, S,
+        CB_LAUNCH(KC_ATTENTION, attention_f16_tc(&tm_qkv_, d_mask, kv_len_, rs, static_cast<__half*>(ctx_), B, S,
                                                   heads_, num_sms_, cls, err_dev_, stream_));
       } else if (att_kernel == ATT_KERNEL_PERSIST) {
-        CB_LAUNCH(KC_ATTENTION, attention_bf16_persist(&tm_qkv_, d_mask, kv_len_, rs, sched,
-                                                       static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, num_sms_, cls,
+        CB_LAUNCH(KC_ATTENTION, attention_f16_persist(&tm_qkv_, d_mask, kv_len_, rs, sched,
+                                                       static_cast<__half*>(ctx_), B, S, heads_, num_sms_, cls,
                                                        err_dev_, stream_));
       } else {
-        CB_LAUNCH(KC_ATTENTION, attention_bf16(static_cast<const __nv_bfloat16*>(qkv_), d_mask, kv_len_, rs,
-                                               static_cast<__nv_bfloat16*>(ctx_), B, S, heads_, cls, stream_));
+        CB_LAUNCH(KC_ATTENTION, attention_f16(static_cast<const __half*>(qkv_), d_mask, kv_len_, rs,
+                                               static_cast<__half*>(ctx_), B, S, heads_, cls, stream_));
       }
       const int rows = cls ? B : T;               // rows the rest of the layer works on
       const int* rows_live = cls ? nullptr : live;  // ... all of them live in the compact case
       if (cls) m_dev_cur_ = nullptr;
       // y = ctx.Wo + bo in fp16; x1 = LN(y + x) with the add in fp32 inside the LayerNorm kernel
-      if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, rows, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_ATTN_OUT))
+      if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, rows, y_, EPI_BIAS, nullptr, KC_GEMM_ATTN_OUT))
         return false;
       // compact case: the residual of output row b is the first row of sequence b
-      CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __nv_bfloat16>(static_cast<const __half*>(y_), xf_, w.ln1_g, w.ln1_b,
+      CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __half>(static_cast<const __half*>(y_), xf_, w.ln1_g, w.ln1_b,
                                                                 x1a, x1f_, rows, H_, rows_live, stream_,
                                                                 cls ? rs : nullptr, (cls && !rs) ? S : 1)));
       if (!dense(w.ffn1, x1a_, &tm_x1_, H_, rows, z_, EPI_BIAS | EPI_GELU, nullptr, KC_GEMM_FFN1)) return false;
-      if (!dense(w.ffn2, z_, &tm_z_, F_, rows, y_, EPI_BIAS | EPI_OUT_F16, nullptr, KC_GEMM_FFN2)) return false;
-      CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __nv_bfloat16>(static_cast<const __half*>(y_), x1f_, w.ln2_g, w.ln2_b,
+      if (!dense(w.ffn2, z_, &tm_z_, F_, rows, y_, EPI_BIAS, nullptr, KC_GEMM_FFN2)) return false;
+      CB_LAUNCH(KC_LAYERNORM, (layernorm<__half, __half>(static_cast<const __half*>(y_), x1f_, w.ln2_g, w.ln2_b,
                                                                 xa, xf_, rows, H_, rows_live, stream_)));
       compact_out = cls != 0;
     } else {

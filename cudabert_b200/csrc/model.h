@@ -29,7 +29,7 @@ enum KernelClass : int {
 };
 
 struct DenseWeight {      // one projection
-  void* w = nullptr;      // fp32 [K, N] (fp32 mode) or bf16 [N, K] (bf16 / fp8 modes)
+  void* w = nullptr;      // fp32 [K, N] (fp32 mode); else fp16 [N, K] holding the bf16-rounded (x 4096) or e4m3 weights
   uint8_t* w_fp8 = nullptr;  // fp8 mode: e4m3 bytes [N, K] (the stored quantised weights)
   float* bias = nullptr;     // [N]
   float* colscale = nullptr; // fp8 mode: [N] de-quantisation scale per output column
@@ -161,7 +161,7 @@ class Model {
   float* hidden_unpacked_ = nullptr;
   size_t hidden_unpacked_tokens_ = 0;
   // residual stream in fp32: xf_ (layer input / output), x1f_ (after the attention block),
-  // y_ (dense outputs, added to the stream by the LayerNorm kernel).  xa_ / x1a_ are the copies that feed the GEMMs (bf16 in the bf16 and
+  // y_ (dense outputs, added to the stream by the LayerNorm kernel).  xa_ / x1a_ are the copies that feed the GEMMs (fp16 in the bf16 and
   // fp8 modes; in fp32 mode they alias xf_ / x1f_).  ctx_, qkv_, z_ are in the GEMM element type.
   float *xf_ = nullptr, *x1f_ = nullptr;
   void* y_ = nullptr;  // dense outputs before the residual add: fp16 (bf16 / fp8 modes) or fp32 sums (fp32 mode)

@@ -7,12 +7,14 @@
 //
 //   embed_layernorm  replaces DeviceApplyEmbeddings (ops/embedding.cu:3-20) + the LayerNorm
 //                    that follows it (ops/embedding.cu:39-58): one pass instead of three.
-//   layernorm        replaces cuApplyLayerNorm (ops/layernorm.cu:136-182); the residual add
-//                    it did in place now happens in the producing GEMM's epilogue.
+//   layernorm        replaces cuApplyLayerNorm (ops/layernorm.cu:136-182), its in-place residual
+//                    add included (`residual`, added in fp32; the fp32 mode passes none because
+//                    its GEMM epilogue has added it already).
 //   classify_softmax the sample app's fine-tune head (apps/finetune.py:16-24) on the device.
 #include "kernels.h"
 #include "ptx.cuh"
 
+#include <atomic>
 #include <cstdlib>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -40,10 +42,10 @@ __device__ __forceinline__ void store4<float>(float* p, const float (&y)[4]) {
   *reinterpret_cast<float4*>(p) = make_float4(y[0], y[1], y[2], y[3]);
 }
 template <>
-__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&y)[4]) {
+__device__ __forceinline__ void store4<__half>(__half* p, const float (&y)[4]) {
   uint2 t;
-  t.x = pack_bf16(y[0], y[1]);
-  t.y = pack_bf16(y[2], y[3]);
+  t.x = pack_f16(y[0], y[1]);
+  t.y = pack_f16(y[2], y[3]);
   *reinterpret_cast<uint2*>(p) = t;
 }
 
@@ -215,8 +217,9 @@ __global__ void classify_softmax_kernel(const float* __restrict__ pooled, const 
   if (lane < C) probs[static_cast<size_t>(b) * C + lane] = e / den;
 }
 
-// dst[n, k] = bf16(src[k, n]) through a 32x33 shared tile
-__global__ void transpose_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int K, int N) {
+// dst[n, k] = the bf16 rounding of src[k, n], held as the fp16 number W_CONTAINER_SCALE times that
+// value (exact, see kernels.h), through a 32x33 shared tile
+__global__ void transpose_round_bf16_kernel(const float* __restrict__ src, __half* __restrict__ dst, int K, int N) {
   __shared__ float tile[32][33];
   const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
@@ -226,7 +229,9 @@ __global__ void transpose_to_bf16_kernel(const float* __restrict__ src, __nv_bfl
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     const int n = n0 + r, k = k0 + threadIdx.x;
-    if (n < N && k < K) dst[static_cast<size_t>(n) * K + k] = __float2bfloat16_rn(tile[threadIdx.x][r]);
+    if (n < N && k < K)
+      dst[static_cast<size_t>(n) * K + k] =
+          __float2half_rn(__bfloat162float(__float2bfloat16_rn(tile[threadIdx.x][r])) * W_CONTAINER_SCALE);
   }
 }
 
@@ -246,7 +251,7 @@ __global__ void finish_scale_kernel(float* scale_io) {
 }
 
 __global__ void quantize_fp8_kernel(const float* __restrict__ src, uint8_t* __restrict__ dst_q,
-                                    __nv_bfloat16* __restrict__ dst_op, const float* __restrict__ scale, int K, int N) {
+                                    __half* __restrict__ dst_op, const float* __restrict__ scale, int K, int N) {
   __shared__ float tile[32][33];
   const float inv = 1.0f / *scale;
   const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
@@ -261,15 +266,9 @@ __global__ void quantize_fp8_kernel(const float* __restrict__ src, uint8_t* __re
       const __nv_fp8_e4m3 q(tile[threadIdx.x][r] * inv);
       const size_t o = static_cast<size_t>(n) * K + k;
       dst_q[o] = q.__x;
-      dst_op[o] = __float2bfloat16_rn(static_cast<float>(q));  // e4m3 is exactly representable in bf16
+      dst_op[o] = __float2half_rn(static_cast<float>(q));  // e4m3 is exactly representable in fp16
     }
   }
-}
-
-__global__ void convert_f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x)
-    dst[i] = __float2bfloat16_rn(src[i]);
 }
 
 __global__ void fill_f32_kernel(float* dst, float v, size_t n) {
@@ -367,13 +366,13 @@ static bool layernorm_persistent() {
 }
 
 static int sm_count() {
-  static int cached[64] = {};
+  static std::atomic<int> cached[64] = {};  // per device; racing threads store the same value
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && cached[dev] > 0) return cached[dev];
+  if (dev >= 0 && dev < 64 && cached[dev].load(std::memory_order_relaxed) > 0) return cached[dev].load(std::memory_order_relaxed);
   int n = 148;
   cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  if (dev < 64) cached[dev] = n;
+  if (dev >= 0 && dev < 64) cached[dev].store(n, std::memory_order_relaxed);
   return n;
 }
 
@@ -396,16 +395,16 @@ int layernorm(const TIn* x, const float* residual, const float* gamma, const flo
 
 template int embed_layernorm<float>(const int*, const int*, const float*, const float*, const float*, const float*,
                                     const float*, float*, float*, int, int, int, int, int*, const int*, cudaStream_t);
-template int embed_layernorm<__nv_bfloat16>(const int*, const int*, const float*, const float*, const float*,
-                                            const float*, const float*, __nv_bfloat16*, float*, int, int, int, int,
+template int embed_layernorm<__half>(const int*, const int*, const float*, const float*, const float*,
+                                            const float*, const float*, __half*, float*, int, int, int, int,
                                             int*, const int*, cudaStream_t);
 template int layernorm<float, float>(const float*, const float*, const float*, const float*, float*, float*, int, int,
                                      const int*, cudaStream_t, const int*, int);
-template int layernorm<float, __nv_bfloat16>(const float*, const float*, const float*, const float*, __nv_bfloat16*,
+template int layernorm<float, __half>(const float*, const float*, const float*, const float*, __half*,
                                              float*, int, int, const int*, cudaStream_t, const int*, int);
 template int layernorm<__half, float>(const __half*, const float*, const float*, const float*, float*, float*, int, int,
                                       const int*, cudaStream_t, const int*, int);
-template int layernorm<__half, __nv_bfloat16>(const __half*, const float*, const float*, const float*, __nv_bfloat16*,
+template int layernorm<__half, __half>(const __half*, const float*, const float*, const float*, __half*,
                                               float*, int, int, const int*, cudaStream_t, const int*, int);
 
 int unpack_rows(const float* src, const int* row_start, float* dst, int tokens, int S, int H, cudaStream_t stream) {
@@ -422,13 +421,13 @@ int classify_softmax(const float* pooled, const float* W, const float* bias, flo
                  cudaSuccess ? 1 : -3;
 }
 
-int transpose_to_bf16(const float* src, __nv_bfloat16* dst, int K, int N, cudaStream_t stream) {
+int transpose_round_bf16(const float* src, __half* dst, int K, int N, cudaStream_t stream) {
   dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
-  transpose_to_bf16_kernel<<<grid, block, 0, stream>>>(src, dst, K, N);
+  transpose_round_bf16_kernel<<<grid, block, 0, stream>>>(src, dst, K, N);
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
-int quantize_fp8_weight(const float* src, uint8_t* dst_q, __nv_bfloat16* dst_op, float* scale_out, int K, int N,
+int quantize_fp8_weight(const float* src, uint8_t* dst_q, __half* dst_op, float* scale_out, int K, int N,
                         cudaStream_t stream) {
   if (cudaMemsetAsync(scale_out, 0, sizeof(float), stream) != cudaSuccess) return -3;
   maxabs_kernel<<<296, 256, 0, stream>>>(src, static_cast<size_t>(K) * N, reinterpret_cast<unsigned int*>(scale_out));
@@ -436,12 +435,6 @@ int quantize_fp8_weight(const float* src, uint8_t* dst_q, __nv_bfloat16* dst_op,
   dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
   quantize_fp8_kernel<<<grid, block, 0, stream>>>(src, dst_q, dst_op, scale_out, K, N);
   return cudaGetLastError() == cudaSuccess ? 3 : -3;
-}
-
-int convert_f32_to_bf16(const float* src, __nv_bfloat16* dst, size_t n, cudaStream_t stream) {
-  if (n == 0) return 0;
-  convert_f32_to_bf16_kernel<<<592, 256, 0, stream>>>(src, dst, n);
-  return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
 int fill_f32(float* dst, float value, size_t n, cudaStream_t stream) {

@@ -250,10 +250,10 @@ def profile_get(model):
 
 
 # single kernels on device pointers (integers), used by the per-kernel parity tests
-k_gemm_bf16 = lib.cudabert_k_gemm_bf16
-k_gemm_bf16.argtypes = [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+k_gemm_tcgen05 = lib.cudabert_k_gemm_tcgen05
+k_gemm_tcgen05.argtypes = [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_void_p]
-k_gemm_bf16.restype = c_int
+k_gemm_tcgen05.restype = c_int
 k_gemm_f32 = lib.cudabert_k_gemm_f32
 k_gemm_f32.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
 k_gemm_f32.restype = c_int

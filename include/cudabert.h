@@ -38,7 +38,9 @@ typedef struct Retval {
  * utils/manager.cu:8-15); `dir` is a directory of float32 .npy files (name.txt layout), "" means
  * "model_npy/base_uncased" or "model_npy/large_uncased"; max_batchsize == max_seq_length == 0
  * sizes the activation arena lazily at the first call.  The precision mode comes from the
- * environment variable CUDABERT_PRECISION = fp32 | bf16 (default) | fp8.                    */
+ * environment variable CUDABERT_PRECISION = fp32 | bf16 (default) | fp8.  bf16: dense weights
+ * rounded to bf16, activations between kernels in fp16, fp32 accumulation, fp32 residual stream.
+ * fp8: the same with the dense weights quantised to E4M3 with one scale per tensor.           */
 CUDABERT_API void* init_model(bool large, int num_gpu, int max_batchsize, int max_seq_length, char* dir);
 
 /* Reference: release_model (cuda_bert/cuda_bert.cu:34-37). */
@@ -187,20 +189,23 @@ CUDABERT_API long long cudabert_reader_lines(void* reader);
 
 /* ---- single kernels on device buffers (stream 0, synchronous), for per-kernel parity tests ---- */
 
-/* out[M,N] = epilogue(A[M,K] bf16 (row stride lda elements) x W[N,K]^T bf16); flags: 1 bias, 2 GELU,
- * 4 residual, 8 tanh, 16 fp32 output, 32 per-column scale, 64 fp16 output.  err_dev: device int, set non-zero if a
- * pipeline wait timed out.  N % 128 == 0, K % 64 == 0.                                        */
-CUDABERT_API int cudabert_k_gemm_bf16(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev,
+/* out[M,N] = epilogue(A[M,K] (row stride lda elements) x W[N,K]^T), A and W both bf16, or both fp16 with
+ * flag 256; flags: 1 bias, 2 GELU, 4 residual, 8 tanh, 16 fp32 output, 32 per-column scale, 64 fp16 output
+ * (bf16 otherwise), 128 accumulator x 1/4096 (the encoder holds its bf16-rounded weights as fp16 numbers
+ * times 4096), 256 fp16 operands.  err_dev: device int, set non-zero if a pipeline wait timed out.
+ * N % 128 == 0, K % 64 == 0.                                                                  */
+CUDABERT_API int cudabert_k_gemm_tcgen05(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev,
                          int flags, const float* bias_dev, const void* residual_dev, const float* colscale_dev,
                          int* err_dev);
 /* out[M,N] = epilogue(A[M,K] fp32 (row stride lda) x W[K,N] fp32). */
 CUDABERT_API int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, int N, int K, float* out_dev,
                         int flags, const float* bias_dev, const float* residual_dev);
-/* ctx[T,H] = attention(qkv[T,3H]); mask_dev int32 [B,S] or NULL; bf16: 0 = fp32 kernel, 1 = bf16
- * mma.sync kernel (one CTA per sequence and head), 2 = bf16 tcgen05 kernel, 3 = bf16 mma.sync kernel,
- * persistent (S <= 256).  Adding 16 to a bf16 kernel's number computes only the first query of every
- * sequence and writes it to row b of ctx_dev, then [B, H] (the last encoder layer of a pooler-only pass). */
-CUDABERT_API int cudabert_k_attention(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads);
+/* ctx[T,H] = attention(qkv[T,3H]); mask_dev int32 [B,S] or NULL; kernel: 0 = fp32 kernel (fp32 in and
+ * out), 1 = 16-bit mma.sync kernel (one CTA per sequence and head), 2 = 16-bit tcgen05 kernel, 3 = 16-bit
+ * mma.sync kernel, persistent (S <= 256); the 16-bit kernels take fp16 Q, K, V and write fp16.  Adding 16
+ * to a 16-bit kernel's number computes only the first query of every sequence and writes it to row b of
+ * ctx_dev, then [B, H] (the last encoder layer of a pooler-only pass). */
+CUDABERT_API int cudabert_k_attention(int kernel, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads);
 /* No counterpart in the reference.  cudabert_k_attention for callers that must not allocate device
  * memory: code that runs where cudaMalloc is not allowed (inside another framework's memory pool
  * or allocator callback, in a process whose device memory is fully pre-partitioned, or in a
@@ -210,24 +215,28 @@ CUDABERT_API int cudabert_k_attention(int bf16, const void* qkv_dev, const int* 
  * (return code 6 and a message in cudabert_last_error(NULL) beyond that) and every GPU that loads
  * the library holds those 16 KiB until the process exits.  Inputs and outputs are the caller's, as
  * for cudabert_k_attention; no cudaMalloc / cudaFree or allocating library routine is called.
+ * Only kernels 0 (fp32) and 1 (16-bit mma.sync), and 1 + 16 (first query only, output [B, H]), are
+ * served: kernels 2 and 3 need scheduling and error scratch that the fixed array does not hold,
+ * and any other number returns 1 before anything is launched.  Every non-zero return leaves its
+ * reason in cudabert_last_error(NULL).
  * The first call on each device looks up the array's device address; make that first call before
  * starting any stream capture.  All calls share the one array: it is fully rewritten by each call
  * before use, and two calls of one process that overlap on the same GPU (for example from two
  * host threads) race on it -- serialise them.  Separate processes have separate copies.        */
 #define CUDABERT_NOALLOC_MAX_BATCH 4096
-CUDABERT_API int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev,
+CUDABERT_API int cudabert_k_attention_noalloc(int kernel, const void* qkv_dev, const int* mask_dev, void* ctx_dev,
                                               int B, int S, int heads);
-/* out[T,H] = LayerNorm(word[ids] + pos[t % S] + type[seg]); tables fp32; out is bf16 (bf16 != 0) or
+/* out[T,H] = LayerNorm(word[ids] + pos[t % S] + type[seg]); tables fp32; out is fp16 (half != 0) or
  * fp32; out_f32_dev (may be NULL) receives the same values in fp32.  Returns 5 after clamping an
  * id outside [0, vocab) or a segment id outside {0, 1}.                                        */
-CUDABERT_API int cudabert_k_embed_layernorm(int bf16, const int* ids_dev, const int* seg_dev, const float* word_dev,
+CUDABERT_API int cudabert_k_embed_layernorm(int half, const int* ids_dev, const int* seg_dev, const float* word_dev,
                                             const float* pos_dev, const float* type_dev, const float* gamma_dev,
                                             const float* beta_dev, void* out_dev, float* out_f32_dev, int tokens,
                                             int S, int H, int vocab);
 /* out[T,H] = LayerNorm(x[T,H] + residual[T,H]) * gamma + beta.  x is fp32, or fp16 when in_f16 != 0;
- * residual is fp32 or NULL; out is bf16 when out_bf16 != 0, else fp32; out_f32_dev (may be NULL)
+ * residual is fp32 or NULL; out is fp16 when out_f16 != 0, else fp32; out_f32_dev (may be NULL)
  * receives the same values in fp32.                                                          */
-CUDABERT_API int cudabert_k_layernorm(int out_bf16, int in_f16, const void* x_dev, const float* residual_dev,
+CUDABERT_API int cudabert_k_layernorm(int out_f16, int in_f16, const void* x_dev, const float* residual_dev,
                                       const float* gamma_dev, const float* beta_dev, void* out_dev,
                                       float* out_f32_dev, int tokens, int H);
 

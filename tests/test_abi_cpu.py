@@ -74,3 +74,27 @@ def test_fp8_roundtrip_properties():
     out = bert_oracle.quantize_encoder_weights_fp8(t)
     assert np.array_equal(out["bert_pooler_dense_kernel"], w) and not np.array_equal(
         out["bert_encoder_layer_0_output_dense_kernel"], w)
+
+
+def test_reference_application_import_lines():
+    """The import block of the reference's sample application (apps/example.py:6-10) works unchanged
+    and names the same module objects as the package's own import root."""
+    import subprocess
+    import sys
+    code = (
+        "from cuda_bert.engine import Engine\n"
+        "from cuda_bert.config import Engin_Config\n"
+        "from cuda_bert.cuda_model import Cuda_BERT\n"
+        "import cudabert_b200.engine, cudabert_b200.config, cudabert_b200.cuda_model\n"
+        "assert Engine is cudabert_b200.engine.Engine\n"
+        "assert Engin_Config is cudabert_b200.config.Engin_Config\n"
+        "assert Cuda_BERT is cudabert_b200.cuda_model.Cuda_BERT\n"
+        "from cuda_bert.cuda_bert import pybert\n"
+        "import cudabert_b200.cuda_bert.pybert as packaged\n"
+        "assert pybert is packaged\n"
+        "e = Engine(Engin_Config())\n"
+        "for n in ('set_cuda_model', 'set_finetune_layer', 'set_tokenlizer_function', 'set_output_function', 'run'):\n"
+        "    assert callable(getattr(e, n))\n"
+        "print('ok')\n")
+    r = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr

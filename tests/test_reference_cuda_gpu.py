@@ -23,7 +23,7 @@ def _run_reference(weight_dir, large, ids, seg, mask, tmp_path):
         arrays["mask"] = mask
     np.savez(inp, **arrays)
     r = subprocess.run([sys.executable, os.path.join(ROOT, "oracle", "run_ref_cuda.py"), weight_dir, str(int(large)),
-                        inp, out], capture_output=True, text=True, timeout=300)
+                        inp, out], capture_output=True, text=True, timeout=600)
     if r.returncode != 0:
         pytest.fail("reference CUDA library failed: rc=%d\n%s\n%s" % (r.returncode, r.stdout[-1500:], r.stderr[-1500:]))
     return np.load(out)
@@ -42,3 +42,62 @@ def test_fp32_mode_matches_reference_cuda_library(models, weight_dirs, tmp_path,
     # agree with each other, and the fp32 mode agrees with both, within the fp32 tolerance
     assert np.abs(ref - gold).max() <= 1e-3
     assert np.abs(ours - ref).max() <= 1e-3
+
+
+def _oracle_full_batch(weights, ids, seg, mask, dims):
+    """CPU oracle over a whole batch, sixteen sequences at a time in order of length, each group
+    trimmed to its longest sequence (padding is masked, so trimming changes nothing but the time)."""
+    from oracle import bert_oracle
+    w = bert_oracle.Weights(weights)
+    lens = mask.sum(1)
+    order = np.argsort(-lens, kind="stable")
+    out = np.zeros((ids.shape[0], dims["hidden"]), np.float32)
+    for c in range(0, len(order), 16):
+        idx = order[c:c + 16]
+        n = int(lens[idx].max())
+        out[idx] = bert_oracle.bert_forward(w, ids[idx, :n], seg[idx, :n], mask[idx, :n], dims["heads"], dims["layers"])[1]
+    return out
+
+
+@pytest.mark.skipif(not os.path.exists(REF_LIB), reason="oracle/_ref is not built")
+def test_full_c1_bf16_against_reference_cuda(tmp_path, record_property):
+    """The headline workload at FULL size (BERT-large, 128 x 200, lengths U[16, 200], the benchmark's
+    own weights and first batch): this library's bf16 mode against the reference's CUDA library
+    (fp32, cuBLAS) on the same GPU, all 128 x 1024 pooler outputs in the maximum.
+
+    Bar: max|a-b| / max|b| <= 2e-2, asserted with a 10 % margin.  Rounding the dense weights to
+    bf16 -- the mode's weight format -- moves the pooler by 1.66e-2 on this batch when everything
+    else is computed in fp32; that part is measured here on the CPU oracle and recorded, and the
+    rest (this library against the oracle on the SAME rounded weights: what the kernels add) must
+    stay below a quarter of the bar."""
+    import torch
+    from cudabert_b200 import synth
+    from cudabert_b200.cuda_bert import pybert
+    from oracle import bert_oracle
+    cfg = 1
+    wl = synth.CONFIGS[cfg]
+    dims = synth.model_dims(True)
+    weights = synth.make_weights(True, synth.weight_seed(cfg))
+    ids, seg, mask = synth.make_inputs(synth.input_seed(cfg), wl["batch"], wl["seq"], wl["dist"])
+    wdir = str(tmp_path / "w")
+    synth.write_weight_dir(wdir, weights)
+    ref = _run_reference(wdir, True, ids, seg, mask, tmp_path)
+    model = pybert.load_model(True, wdir, 0, wl["batch"], wl["seq"], precision="bf16")
+    ours = np.zeros((wl["batch"], dims["hidden"]), np.float32)
+    pybert.bert(model, ours, ids, seg, wl["batch"], wl["seq"], mask)
+    pybert.check(model)
+    pybert.unload_model(model)
+    assert np.isfinite(ours).all()
+    torch.set_num_threads(os.cpu_count() or 1)
+    oracle_bf16w = _oracle_full_batch(bert_oracle.round_encoder_weights_bf16(weights), ids, seg, mask, dims)
+    vs_ref = bert_oracle.rel_err(ours, ref)
+    weight_format = bert_oracle.rel_err(oracle_bf16w, ref)
+    kernels_only = bert_oracle.rel_err(ours, oracle_bf16w)
+    fro = float(np.linalg.norm(ours - ref) / np.linalg.norm(ref))
+    for k, v in (("vs_reference_cuda", vs_ref), ("bf16_weights_alone", weight_format), ("kernels_only", kernels_only),
+                 ("vs_reference_cuda_frobenius", fro)):
+        record_property("full_c1_" + k, v)
+    print("full C1 bf16: vs reference CUDA library %.4f (Frobenius %.4f); bf16 weights alone %.4f; kernels only %.4f"
+          % (vs_ref, fro, weight_format, kernels_only))
+    assert vs_ref <= 0.9 * 2e-2
+    assert kernels_only <= 5e-3
