@@ -428,9 +428,9 @@ class Engine(object):
         assert(type(input_file) == str)
         self.config.input_file = input_file
         self.config.output_file = output_file
-        start_line = 0
+        start_line, offset = 0, 0     # lines and bytes of the output file that are known to be good
         while True:
-            failed, progress = self._run_once(input_file, output_file, start_line)
+            failed, progress = self._run_once(input_file, output_file, start_line, offset)
             if failed is None:
                 break
             name, code = failed
@@ -438,7 +438,10 @@ class Engine(object):
             dead = [g for g in gpus if name == "gpu%s" % g]
             if not (dead and len(gpus) > 1 and getattr(self.config, "resume_without_dead_gpu", True)):
                 raise RuntimeError("engine stage %s died with exit code %s; the run was stopped" % failed)
-            start_line, offset = int(progress[0]), int(progress[1])
+            # the writer publishes (lines, bytes) together after every flush; the pair starts at the
+            # previous attempt's values, so a replica that dies before the writer's first batch
+            # (e.g. at model load) leaves the file exactly as the previous attempt left it
+            start_line, offset = max(start_line, int(progress[0])), max(offset, int(progress[1]))
             with open(output_file, 'a', encoding='utf-8') as f:
                 f.truncate(offset if start_line else 0)
             self.config.gpu = [g for g in gpus if g not in dead]
@@ -446,10 +449,10 @@ class Engine(object):
                                 dead[0], code, start_line, self.config.gpu)
         self.logger.info("ALL JOBS DONE")
 
-    def _run_once(self, input_file, output_file, start_line):
+    def _run_once(self, input_file, output_file, start_line, offset=0):
         self._init()
         ctx = self._ctx
-        progress = ctx.Array('q', [start_line, 0])
+        progress = ctx.Array('q', [start_line, offset])
         procs = [("reader", ctx.Process(target=self._engine_preprocess, args=(input_file, start_line), daemon=True))]
         for num_gpu in self.config.gpu:
             procs.append(("gpu%s" % num_gpu, ctx.Process(target=self._engine_model, args=(num_gpu,), daemon=True)))

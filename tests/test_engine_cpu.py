@@ -139,6 +139,48 @@ def test_engine_resumes_without_a_dead_replica(tmp_path):
         assert got == "%s\t%d\t%d" % (raw, sum(toks), len(toks))
 
 
+class DyingTwiceReplica(FakeReplica):
+    """gpu 1 disappears in mid-run (after a few batches, so that lines are already written); gpu 2
+    disappears while the RESUMED run loads its model, before the writer has seen a batch."""
+    def __init__(self, id_gpu, config):
+        super().__init__(id_gpu, config)
+        self.calls = 0
+        if 1 not in config.gpu:          # a resumed run
+            if id_gpu == 2:
+                os._exit(9)
+            import time
+            time.sleep(1.0)              # the surviving replica is still loading when gpu 2 is found dead
+
+    def encode(self, tensor):
+        self.calls += 1
+        if self.id_gpu == 1 and self.calls == 4:
+            os._exit(7)
+        if self.id_gpu == 1:
+            import time
+            time.sleep(0.05)     # let the other replicas' lines reach the file first
+        return super().encode(tensor)
+
+
+def test_engine_keeps_written_lines_when_a_second_replica_dies_at_start_up(tmp_path):
+    """Two failures in a row: the second strikes before the resumed run's writer has written
+    anything.  The lines the first attempt wrote must survive, and the output must be complete."""
+    src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
+    lines = _write_input(src, 600)
+    cfg = _config([0, 1, 2])
+    eng = Engine(cfg)
+    eng.set_cuda_model(DyingTwiceReplica)
+    eng.set_finetune_layer(Head)
+    eng.set_tokenlizer_function(tokenize)
+    eng.set_output_function(output_line)
+    eng.run(src, dst)
+    assert cfg.gpu == [0]
+    out = open(dst).read().splitlines()
+    assert len(out) == len(lines)
+    for raw, got in zip(lines, out):
+        toks = [int(t) for t in raw.split()]
+        assert got == "%s\t%d\t%d" % (raw, sum(toks), len(toks))
+
+
 def test_engine_reports_a_dead_replica(tmp_path):
     src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
     _write_input(src, 200)
