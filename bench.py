@@ -1,18 +1,26 @@
 #!/usr/bin/env python
-"""Throughput of the BERT-encoder hot path on B200: sequences/s on the BERT-large, seq 200,
-batch 128 workload (the configuration the reference's README number is quoted on), with the
-pooler followed by the Linear(1024 -> 2) + Softmax head.
+"""Throughput of the BERT-encoder hot path on B200 in sequences/s.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--config 0|1|2|3|4] [--feed raw|engine]
 
-One step = one batch of 128 synthetic lines (valid lengths uniform in [16, 200], padded to
-200) through the whole path.  Prints ONE JSON line:
+--config picks one of the five workloads of the benchmark specification (cudabert_b200/synth.py:
+CONFIGS); the default, 1, is the headline: BERT-large, batch 128, seq 200, valid lengths uniform in
+[16, 200], pooler followed by the Linear(1024 -> 2) + Softmax head, 16-bit mode with bf16 weights.
+  0  BERT-base  fp32  batch 8    seq 128  lengths U[32,128]
+  2  BERT-base  bf16  batch 256  seq 128  lengths ~ N(60,25) clipped to [8,128]   (per GPU)
+  3  BERT-large bf16  batch 32   seq 512  every position valid
+  4  BERT-large fp8 weights  batch 1024  seq 64  lengths U[8,64]
+--feed raw (default): one step = one fixed [batch, seq] array of synthetic lines, as stated above.
+--feed engine: the same stream of lines first goes through the engine's length buckets and right-trim
+(the library's native batcher, what Engine's reader stage runs), one step = one such batch.
 
-  value      sequences/s with the batch already resident in HBM (device-side entry point),
+Prints ONE JSON line:
+  value      sequences/s with the batches already resident in HBM (device-side entry point),
              K steps timed with CUDA events on the replica's stream, max over ranks
-  e2e        the same through the reference-facing call (Cuda_Classify: host arrays in,
-             host probabilities out), copies inside the timed region
-  roofline   achieved TFLOP/s of the tcgen05 GEMM kernel (the kernel that holds ~97 % of the
+  e2e        the same through the reference-facing call (Cuda_Classify: host arrays in, host
+             probabilities out), copies inside the timed region
+  roofline   achieved TFLOP/s of the dense-projection GEMM kernel (the kernel that holds ~97 % of the
              FLOPs), from CUDA events recorded around every launch on the launching stream
   cpu_baseline  the CPU oracle (a restatement of the reference's bundled PyTorch model) on a
              bounded sample of the same workload, on this box's host cores; when a build of the
@@ -44,41 +52,72 @@ sys.path.insert(0, ROOT)
 
 from cudabert_b200 import synth  # noqa: E402
 
-CFG = 1
-WL = synth.CONFIGS[CFG]
-METRIC = "BERT-large seq200 sequences/sec"
 UNIT = "sequences/s"
-WORKLOAD = ("C1: BERT-large (L24 H1024 h16 F4096) bf16 weights fp32 accumulate, batch 128, seq 200, "
-            "valid lengths U[16,200] padded to 200, pooler + Linear(1024->2) + Softmax")
+L2_BYTES = 126e6
+
+
+def describe(cfg):
+    """(metric, workload description) of a configuration."""
+    wl = synth.CONFIGS[cfg]
+    d = synth.model_dims(wl["large"])
+    size = "BERT-large" if wl["large"] else "BERT-base"
+    prec = {"fp32": "fp32", "bf16": "bf16 weights, fp16 activations, fp32 accumulate",
+            "fp8": "FP8-E4M3 weights (per-tensor scale), fp16 activations, fp32 accumulate"}[wl["precision"]]
+    lens = {"full": "every position valid"}.get(wl["dist"], "valid lengths %s padded to %d" % (wl["dist"], wl["seq"]))
+    metric = "%s seq%d sequences/sec" % (size, wl["seq"])
+    work = ("C%d: %s (L%d H%d h%d F%d) %s, batch %d, seq %d, %s, pooler + Linear(%d->2) + Softmax"
+            % (cfg, size, d["layers"], d["hidden"], d["heads"], d["ffn"], prec, wl["batch"], wl["seq"], lens, d["hidden"]))
+    return metric, work
 
 
 def flops_per_step(batch, seq, dims):
-    """Executed FLOPs of one padded batch: per token per layer 24 H^2 dense + 4 S H attention,
-    plus the pooler (2 H^2 per sequence)."""
+    """FLOPs of one padded batch: per token per layer 24 H^2 dense + 4 S H attention, plus the
+    pooler (2 H^2 per sequence)."""
     H, L = dims["hidden"], dims["layers"]
     dense = batch * seq * L * 24 * H * H
     attn = batch * seq * L * 4 * seq * H
     return dense, attn, batch * 2 * H * H
 
 
-def gemm_flops(tokens, dims, sequences=None):
-    """FLOPs the tensor-core GEMMs execute for `tokens` rows (QKV, attention-output, FFN1, FFN2 of
-    every layer).  With the packed layout only the valid tokens of a batch are rows.  `sequences`:
-    the pass returns the pooler output only, so the last layer computes its attention-output and FFN
-    GEMMs for the first token of every sequence only (its QKV GEMM still takes every token)."""
+def short_last_layer(precision):
+    """Whether a pooler-only pass computes its last layer for the first token of each sequence only
+    (16-bit modes, unless CUDABERT_LAST_LAYER=full)."""
+    return precision != "fp32" and os.environ.get("CUDABERT_LAST_LAYER", "")[:1] != "f"
+
+
+def executed_work(lens, dims, precision, padded_seq=None):
+    """What one forward pass of a batch executes, given the rows each sequence has (`lens`: the live
+    rows per sequence in the packed layout, or the padded length for every sequence otherwise):
+    FLOPs of the dense-projection GEMMs, FLOPs of attention (4 * 64 per query-key pair and head),
+    and the rows each of the 2 L LayerNorm launches works on."""
     H, L, F = dims["hidden"], dims["layers"], dims["ffn"]
-    full = 2 * tokens * (3 * H * H + H * H + 2 * H * F)
-    if sequences is None or os.environ.get("CUDABERT_LAST_LAYER", "")[:1] == "f":
-        return L * full
-    return (L - 1) * full + 2 * tokens * 3 * H * H + 2 * sequences * (H * H + 2 * H * F)
+    rows, seqs = int(lens.sum()), len(lens)
+    keys = lens.astype(np.float64)
+    per_row = 2 * (3 * H * H + H * H + 2 * H * F)
+    pairs_full = float((keys * keys).sum())
+    if short_last_layer(precision):
+        gemm = (L - 1) * rows * per_row + rows * 2 * 3 * H * H + seqs * 2 * (H * H + 2 * H * F)
+        attn = 4 * H * ((L - 1) * pairs_full + float(keys.sum()))      # last layer: one query per sequence
+        ln_rows = [rows] * (2 * L - 2) + [seqs, seqs]
+    else:
+        gemm = L * rows * per_row
+        attn = 4 * H * L * pairs_full
+        ln_rows = [rows] * (2 * L)
+    return gemm, attn, ln_rows
+
+
+def layernorm_bytes_per_row(dims, precision):
+    """Algorithmic bytes the residual LayerNorm moves per row.  16-bit modes: fp16 dense output and fp32
+    residual in, fp16 GEMM operand and fp32 residual out (12 B per element).  fp32 mode: the GEMM
+    epilogue has added the residual; fp32 in, fp32 out (8 B per element)."""
+    return dims["hidden"] * (8 if precision == "fp32" else 12)
 
 
 def live_tokens(mask):
     """Rows the packed layout computes for a batch: per line 1 + index of its last valid position
     (a line with no valid position counts as the full padded length)."""
     S = mask.shape[1]
-    last = np.where(mask.any(1), S - np.argmax(mask[:, ::-1] != 0, axis=1), S)
-    return last
+    return np.where(mask.any(1), S - np.argmax(mask[:, ::-1] != 0, axis=1), S)
 
 
 def load_peaks():
@@ -92,8 +131,21 @@ def load_peaks():
     return dict(tensor=1590.0, hbm=6650.0, burst=1590.0, source="fallback")
 
 
+def measured_traffic(kernel, cfg):
+    """DRAM bytes (read + write) per launch of `kernel` on configuration `cfg` from an ncu capture, as
+    recorded in profiles/kernel_traffic.json ({kernel: {"c<cfg>": {"dram_bytes_per_launch": ...}}});
+    None when no capture is on record."""
+    p = os.path.join(ROOT, "profiles", "kernel_traffic.json")
+    try:
+        with open(p) as f:
+            rec = json.load(f)[kernel]["c%d" % cfg]
+        return float(rec["dram_bytes_per_launch"]), rec.get("source")
+    except (OSError, KeyError, ValueError, TypeError):
+        return None, None
+
+
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms while the timed and profiled regions run."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -106,7 +158,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -141,40 +193,85 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         busy = [c for c, p in zip(sm, power) if p > 0.5 * max(power)] or sm
         return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                "power_w_max": max(power), "samples": len(sm)}
+                "power_w_max": max(power), "samples": len(sm), "samples_under_load": len(busy),
+                "period_ms": 50}
 
 
-def make_batches(n_batches, rank):
+def engine_splits(seq):
+    """Bucket boundaries of the engine for a maximum length `seq`: the reference's defaults (first
+    inner boundary 50, last 180, step 2, for a maximum of 200; engine.py:225-232) scaled to `seq`."""
+    lo, hi = max(2, 50 * seq // 200), max(4, 180 * seq // 200)
+    inner = list(range(lo, hi + 1, 2))
+    return [0] + [b for b in inner if 0 < b < seq] + [seq]
+
+
+def make_batches(cfg, n_batches, rank, feed):
+    """Host batches (ids, seg, mask) of the workload.  raw: n_batches arrays of the stated shape.
+    engine: a stream of such lines pushed through the native batcher (length buckets, right-trim);
+    n_batches of the full batches it emits, evenly spaced over the stream, are kept."""
+    wl = synth.CONFIGS[cfg]
+    B, S = wl["batch"], wl["seq"]
+    if feed == "raw":
+        return [synth.make_inputs(synth.input_seed(cfg) + 1000 * rank + i, B, S, wl["dist"]) for i in range(n_batches)]
+    from ctypes import byref, c_int, c_longlong
+    from cudabert_b200.cuda_bert import pybert
+    bounds = np.ascontiguousarray(engine_splits(S), dtype=np.int32)
+    batcher = pybert.batcher_create(bounds, len(bounds), B, S)
+    if not batcher:
+        raise RuntimeError("batcher_create failed")
     out = []
-    for i in range(n_batches):
-        out.append(synth.make_inputs(synth.input_seed(CFG) + 1000 * rank + i, WL["batch"], WL["seq"], WL["dist"]))
+    line = 0
+    # enough lines for every bucket to fill about three times, so that the batches kept below are the
+    # engine's steady-state mix of lengths and not just its widest buckets
+    n_lines = 3 * (len(bounds) - 1) * B
+    try:
+        for i in range((n_lines + B - 1) // B):
+            ids, seg, mask = synth.make_inputs(synth.input_seed(cfg) + 1000 * rank + i, B, S, wl["dist"])
+            for r in range(B):
+                pybert.batcher_put(batcher, line, ids[r], seg[r], mask[r], S)
+                line += 1
+            while pybert.batcher_ready(batcher) > 0:
+                rows, seq, first = c_int(0), c_int(0), c_longlong(0)
+                pybert.batcher_next(batcher, byref(rows), byref(seq), byref(first))
+                idx = np.empty(rows.value, np.int64)
+                t = [np.empty((rows.value, seq.value), np.int32) for _ in range(3)]
+                pybert.batcher_pop(batcher, idx, t[0], t[1], t[2])
+                out.append(tuple(t))
+    finally:
+        pybert.batcher_destroy(batcher)
+    if not out:
+        raise RuntimeError("the batcher emitted no full batch")
+    if len(out) > n_batches:     # evenly spaced over the stream
+        out = [out[int(k * len(out) / n_batches)] for k in range(n_batches)]
     return out
 
 
-def weights_dir(rank_local, barrier):
-    """Seeded synthetic BERT-large weights in the reference's .npy layout, written once per box."""
-    d = os.path.join(tempfile.gettempdir(), "cudabert_bench_large_seed%d" % synth.weight_seed(CFG))
+def weights_dir(cfg, rank_local, barrier):
+    """Seeded synthetic weights of the configuration's model in the reference's .npy layout, written
+    once per box."""
+    large = synth.CONFIGS[cfg]["large"]
+    d = os.path.join(tempfile.gettempdir(), "cudabert_bench_%s_seed%d" % ("large" if large else "base", synth.weight_seed(cfg)))
     done = d + ".complete"   # beside the directory: the reference's loader parses every file inside it
     if rank_local == 0 and not os.path.exists(done):
-        synth.write_weight_dir(d, synth.make_weights(True, synth.weight_seed(CFG)))
+        synth.write_weight_dir(d, synth.make_weights(large, synth.weight_seed(cfg)))
         open(done, "w").close()
     barrier()
     return d
 
 
-def reference_cuda_library(wdir, batch):
+def reference_cuda_library(wdir, large, batch):
     """The reference's own CUDA library (fp32, cuBLAS), when oracle/_ref holds a build of it, on one
     batch of the workload on this GPU, in a process of its own: its sequences/s (host arrays in, pooler
     output out, like `e2e`) and its pooler output.  Reported beside the CPU baseline; never on the
     product path."""
-    lib = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "libcudaBERT_ref.so")
+    lib = os.path.join(ROOT, "oracle", "_ref", "libcudaBERT_ref.so")
     if not os.path.exists(lib):
         return None
     tmp = tempfile.mkdtemp(prefix="cudabert_ref_")
     inp, out = os.path.join(tmp, "in.npz"), os.path.join(tmp, "out.npy")
     np.savez(inp, ids=batch[0], seg=batch[1], mask=batch[2])
     try:
-        r = subprocess.run([sys.executable, os.path.join(os.path.dirname(lib), "..", "run_ref_cuda.py"), wdir, "1", inp,
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "oracle", "run_ref_cuda.py"), wdir, str(int(large)), inp,
                             out, "5"], capture_output=True, text=True, timeout=300)
         if r.returncode != 0:
             why = (r.stderr.strip().splitlines() or r.stdout.strip().splitlines() or [""])[-1][:200]
@@ -188,15 +285,16 @@ def reference_cuda_library(wdir, batch):
 
 
 # ------------------------------------------------------------------ CPU baseline / reference arm
-def oracle_seq_per_s(n_seq, threads, repeats=1, weights=None):
-    """Time the CPU oracle on n_seq sequences of the workload; returns (seq/s, seconds)."""
+def oracle_seq_per_s(cfg, n_seq, threads, repeats=1, weights=None):
+    """Time the CPU oracle on n_seq sequences of the workload; returns (seq/s, seconds, weights)."""
     import torch
     from oracle import bert_oracle
+    wl = synth.CONFIGS[cfg]
     torch.set_num_threads(threads)
-    dims = synth.model_dims(True)
+    dims = synth.model_dims(wl["large"])
     if weights is None:
-        weights = bert_oracle.Weights(synth.make_weights(True, synth.weight_seed(CFG)))
-    ids, seg, mask = synth.make_inputs(synth.input_seed(CFG), n_seq, WL["seq"], WL["dist"])
+        weights = bert_oracle.Weights(synth.make_weights(wl["large"], synth.weight_seed(cfg)))
+    ids, seg, mask = synth.make_inputs(synth.input_seed(cfg), n_seq, wl["seq"], wl["dist"])
     best = None
     for _ in range(repeats):
         t0 = time.perf_counter()
@@ -212,26 +310,29 @@ def run_reference(args, rank, world):
     model is not shipped to this box, so its restatement in oracle/ stands in: kind "port")."""
     if rank != 0:
         return
+    cfg = args.config
+    wl = synth.CONFIGS[cfg]
+    metric, work = describe(cfg)
     threads = os.cpu_count() or 1
     # size the per-step sample so that warmup + steps stay within about two minutes
-    rate, dt, w = oracle_seq_per_s(2, threads)
+    rate, dt, w = oracle_seq_per_s(cfg, 2, threads)
     budget = 120.0 / max(args.steps + args.warmup, 1)
-    n_seq = int(max(1, min(WL["batch"], rate * budget)))
+    n_seq = int(max(1, min(wl["batch"], rate * budget)))
     for _ in range(args.warmup):
-        oracle_seq_per_s(n_seq, threads, weights=w)
+        oracle_seq_per_s(cfg, n_seq, threads, weights=w)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle_seq_per_s(n_seq, threads, weights=w)
+        oracle_seq_per_s(cfg, n_seq, threads, weights=w)
     total = time.perf_counter() - t0
     value = n_seq * args.steps / total
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": metric, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample_sequences_per_step": n_seq},
+        "config": {"workload": work, "sample_sequences_per_step": n_seq, "batch_of_the_workload": wl["batch"]},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": "%d sequences of the workload per step (seq 200, lengths U[16,200]), fp32, "
-                                   "torch CPU ops, %d threads" % (n_seq, threads)},
+                         "sample": "%d sequences of the workload per step (seq %d, lengths %s), fp32, "
+                                   "torch CPU ops, %d threads" % (n_seq, wl["seq"], wl["dist"], threads)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -244,46 +345,50 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     from cudabert_b200.cuda_bert import pybert
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the hot path has no CPU fallback")
+    cfg = args.config
+    wl = synth.CONFIGS[cfg]
+    metric, work = describe(cfg)
+    precision, large = wl["precision"], wl["large"]
     dev = local_rank % torch.cuda.device_count()
     torch.cuda.set_device(dev)
-    dims = synth.model_dims(True)
-    B, S = WL["batch"], WL["seq"]
-    wdir = weights_dir(local_rank, barrier)
-    n_pool = 4
-    host = make_batches(n_pool, rank)
+    dims = synth.model_dims(large)
+    B, S = wl["batch"], wl["seq"]
+    wdir = weights_dir(cfg, local_rank, barrier)
+    n_pool = 4 if args.feed == "raw" else 48
+    host = make_batches(cfg, n_pool, rank, args.feed)
+    n_pool = len(host)
     ref_cuda = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.layers:
-        ref_cuda = reference_cuda_library(wdir, host[0])   # before this process takes device memory
+        ref_cuda = reference_cuda_library(wdir, large, host[0])   # before this process takes device memory
     t_load = time.perf_counter()
-    model = pybert.load_model(True, wdir, dev, B, S, precision="bf16", num_layers=args.layers)
-    load_seconds = time.perf_counter() - t_load   # .npy directory -> device-resident bf16 K-major weights
+    model = pybert.load_model(large, wdir, dev, B, S, precision=precision, num_layers=args.layers)
+    load_seconds = time.perf_counter() - t_load   # .npy directory -> device-resident K-major operands
     if args.layers:
         dims = dict(dims, layers=min(args.layers, dims["layers"]))
     C = pybert.num_classes(model)
     stream = torch.cuda.ExternalStream(pybert.stream(model), device=dev)
 
     devb = [tuple(torch.from_numpy(a).to("cuda:%d" % dev) for a in hb) for hb in host]
-    probs = np.zeros((B, C), np.float32)
+    probs = [np.zeros((hb[0].shape[0], C), np.float32) for hb in host]
+    rows_of = [hb[0].shape[0] for hb in host]
 
     def step_dev(i):
         ids, seg, mask = devb[i % n_pool]
-        rc = pybert.classify_dev(model, ids.data_ptr(), seg.data_ptr(), mask.data_ptr(), B, S)
+        rc = pybert.classify_dev(model, ids.data_ptr(), seg.data_ptr(), mask.data_ptr(), ids.shape[0], ids.shape[1])
         if rc:
             raise RuntimeError("forward failed: " + pybert.last_error(model))
 
     def step_e2e(i):
         ids, seg, mask = host[i % n_pool]
-        pybert.classify(model, probs, ids, seg, B, S, C, mask)
+        pybert.classify(model, probs[i % n_pool], ids, seg, ids.shape[0], ids.shape[1], C, mask)
 
     def timed(fn, steps, sync_after):
         barrier()
         torch.cuda.synchronize(dev)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        t_host = time.perf_counter()
         for i in range(steps):
             fn(i)
-        timed.host_ms = (time.perf_counter() - t_host) * 1e3 / steps
         e1.record(stream)
         if sync_after:
             rc = pybert.sync(model)
@@ -293,7 +398,10 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
         barrier()
         return allmax(e0.elapsed_time(e1))
 
-    for i in range(args.warmup):
+    # warm-up: W steps as asked, and at least three passes over every pooled batch, after which each of
+    # them replays as a CUDA graph (a pass is captured the third time its arguments are seen)
+    warm_steps = max(args.warmup, 3 * n_pool)
+    for i in range(warm_steps):
         step_dev(i)
     pybert.sync(model)
     pybert.check(model)
@@ -310,15 +418,15 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     pybert.sync(model)
     ms_total = timed(step_dev, args.steps, True)
     launches = pybert.launch_count(model) * args.steps
+    seqs_timed = sum(rows_of[i % n_pool] for i in range(args.steps))
     # end to end through the reference-facing call, host buffers in and out
-    for i in range(min(args.warmup, 3)):
+    for i in range(max(min(args.warmup, 3), 3)):
         step_e2e(i)
     ms_e2e = timed(step_e2e, args.steps, False)
-    clocks = sampler.stop() if rank == 0 else None
     pybert.check(model)
 
-    value = world * args.steps * B / (ms_total / 1e3)
-    e2e_value = world * args.steps * B / (ms_e2e / 1e3)
+    value = world * seqs_timed / (ms_total / 1e3)
+    e2e_value = world * seqs_timed / (ms_e2e / 1e3)
 
     # per-kernel device times: CUDA events around every launch on the launching stream, over steps
     # enqueued back to back right after the timed regions (one synchronisation at the end), so the
@@ -332,88 +440,112 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
     pybert.profile_enable(model, 0)
     prof = pybert.profile_get(model)
     pybert.check(model)
+    clocks = sampler.stop() if rank == 0 else None
 
     if rank != 0:
         pybert.unload_model(model)
         return
     peaks = load_peaks()
-    gemm_ms = sum(prof[k][0] for k in prof if k.startswith("gemm"))
-    gemm_n = sum(prof[k][1] for k in prof if k.startswith("gemm"))
+    gemm_ms = sum(prof[k][0] for k in prof if k.startswith("gemm") and k != "gemm_pooler")
+    gemm_n = sum(prof[k][1] for k in prof if k.startswith("gemm") and k != "gemm_pooler")
     packed = os.environ.get("CUDABERT_PACK", "1") != "0"
-    lens = [live_tokens(hb[2]) if packed else np.full(B, S) for hb in host]
-    prof_lens = [lens[i % n_pool] for i in range(prof_steps)]
-    gflops = sum(gemm_flops(int(l.sum()), dims, sequences=B) for l in prof_lens)
-    attn_exec = sum(dims["layers"] * 4 * dims["hidden"] * float((l.astype(np.float64) ** 2).sum()) for l in prof_lens)
-    ln_rows = sum(int(l.sum()) for l in prof_lens) / prof_steps
+    lens = [live_tokens(hb[2]) if packed else np.full(hb[0].shape[0], hb[0].shape[1]) for hb in host]
+    work_of = [executed_work(l, dims, precision) for l in lens]
+    prof_idx = [i % n_pool for i in range(prof_steps)]
+    gflops = sum(work_of[i][0] for i in prof_idx)
+    attn_exec = sum(work_of[i][1] for i in prof_idx)
+    ln_row_launches = sum(sum(work_of[i][2]) for i in prof_idx)    # rows summed over all LayerNorm launches
+    live_rows = sum(int(lens[i].sum()) for i in prof_idx) / prof_steps
     achieved = gflops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
     dense, attn, pool = flops_per_step(B, S, dims)
     total_ms = sum(v[0] for v in prof.values())
     kernels = {k: {"ms_per_step": v[0] / prof_steps, "launches_per_step": v[1] / prof_steps,
                    "share": (v[0] / total_ms if total_ms else 0)} for k, v in prof.items()}
     attn_ms = prof["attention"][0]
-    ln_ms, ln_n = prof["layernorm"]
-    # LayerNorm: read fp16 dense output + fp32 residual, write the bf16 GEMM copy + the fp32 residual copy
-    ln_bytes = ln_rows * dims["hidden"] * 12
+    ln_ms = prof["layernorm"][0]
+    ln_bytes = ln_row_launches * layernorm_bytes_per_row(dims, precision)
 
     if ref_cuda and ref_cuda.get("pooled") is not None:
-        # the reference's own fp32 pooler output for batch 0 against this library's bf16 mode, full size
+        # the reference's own fp32 pooler output for batch 0 against this library's output, full size
         from oracle import bert_oracle
-        ours = np.zeros((B, dims["hidden"]), np.float32)
-        pybert.bert(model, ours, host[0][0], host[0][1], B, S, host[0][2])
+        b0 = host[0]
+        ours = np.zeros((b0[0].shape[0], dims["hidden"]), np.float32)
+        pybert.bert(model, ours, b0[0], b0[1], b0[0].shape[0], b0[0].shape[1], b0[2])
         pybert.check(model)
         ref = ref_cuda.pop("pooled")
-        # max |a - b| / max |b| (the measure the parity tests bound by 2e-2 on their cases) and the
-        # relative Frobenius norm, over all 128 x 1024 pooler outputs of the batch
-        ref_cuda["rel_err_of_this_library_bf16"] = float(bert_oracle.rel_err(ours, ref))
-        ref_cuda["rel_fro_err_of_this_library_bf16"] = float(np.linalg.norm(ours - ref) / np.linalg.norm(ref))
+        # max |a - b| / max |b| (the measure the parity tests bound by 2e-2 in the 16-bit mode) and the
+        # relative Frobenius norm, over all pooler outputs of the batch
+        ref_cuda["rel_err_of_this_library_%s" % precision] = float(bert_oracle.rel_err(ours, ref))
+        ref_cuda["rel_fro_err_of_this_library_%s" % precision] = float(np.linalg.norm(ours - ref) / np.linalg.norm(ref))
+        ref_cuda["max_abs_err_of_this_library_%s" % precision] = float(np.abs(ours - ref).max())
     elif ref_cuda:
         ref_cuda.pop("pooled", None)
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        n_seq = 16
-        rate, dt, _ = oracle_seq_per_s(n_seq, threads)
+        n_seq = min(16 if large else 64, B)
+        rate, dt, _ = oracle_seq_per_s(cfg, n_seq, threads)
         cpu = {"value": rate, "unit": UNIT, "cores": threads, "kind": "port",
-               "sample": "%d sequences of the workload (seq 200, lengths U[16,200]) in one batch, fp32, "
-                         "torch CPU ops, %.1f s" % (n_seq, dt)}
+               "sample": "%d sequences of the workload (seq %d, lengths %s) in one batch, fp32, "
+                         "torch CPU ops, %.1f s" % (n_seq, S, wl["dist"], dt)}
         if ref_cuda:
             cpu["reference_cuda_library_on_this_gpu"] = ref_cuda
 
+    lowp = precision != "fp32"
+    gemm_kernel = "gemm_tcgen05_pair_kernel" if lowp else "gemm_f32_kernel"
+    traffic, traffic_source = (None, None) if args.layers else measured_traffic(gemm_kernel, cfg)
+    act_bytes = live_rows * (dims["hidden"] * (4 + 4 + 2 + 2 + 2 + 2 + 6) + dims["ffn"] * 2) if lowp else \
+        live_rows * 4 * (dims["hidden"] * 7 + dims["ffn"])
+    mean_rows = seqs_timed / args.steps
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_total / args.steps, "host_enqueue_ms_per_step": host_enqueue_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "batch_per_gpu": B, "seq_len": S, "global_batch": B * world,
+        "metric": metric, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_total / args.steps, "host_enqueue_ms_per_step": host_enqueue_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": {"fp32": "f32", "bf16": "bf16", "fp8": "fp8"}[precision], "data": "synthetic",
+        "config": {"workload": work, "feed": args.feed, "batch_per_gpu": B, "seq_len": S,
+                   "global_batch": B * world, "sample_sequences_per_step": mean_rows,
+                   "operands": ("fp32 on CUDA cores" if not lowp else
+                                "dense weights rounded to %s and held in fp16; activations fp16; both tensor-core "
+                                "operands fp16 (tcgen05 kind::f16), fp32 accumulation, fp32 residual stream"
+                                % ("bf16" if precision == "bf16" else "FP8-E4M3 with a per-tensor scale")),
                    "parallelism": "replicas x%d (batch sharding, no collective)" % world,
-                   "l2": "working set per step (577 MB of activations, 604 MB of weights) is larger than L2",
+                   "untimed_warmup_steps_run": warm_steps,
+                   "l2": "activations written and re-read per step (%.0f MB) %s the 126 MB L2; %d batches alternate"
+                         % (act_bytes / 1e6, "exceed" if act_bytes > L2_BYTES else "DO NOT exceed", n_pool),
                    "tflops_per_step_padded": (dense + attn + pool) / 1e12,
-                   "layout": ("packed: padding tokens are not computed (%.0f live of %d token slots per step)"
-                              % (ln_rows, B * S)) if packed else "padded",
-                   "last_layer": ("every token" if os.environ.get("CUDABERT_LAST_LAYER", "")[:1] == "f" else
-                                  "attention-output, FFN and LayerNorm for the first token of each sequence "
-                                  "only (all the pooler reads; same bits out as the full layer)"),
+                   "layout": ("packed: padding tokens are not computed (%.0f live of %.0f token slots per step)"
+                              % (live_rows, sum(h[0].size for h in host) / n_pool)) if packed else "padded",
+                   "last_layer": ("attention-output, FFN and LayerNorm for the first token of each sequence "
+                                  "only (all the pooler reads; same bits out as the full layer)"
+                                  if short_last_layer(precision) else "every token"),
                    "tflops_per_step_executed_gemm": gflops / prof_steps / 1e12},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e / args.steps,
-                "h2d_bytes_per_step": 3 * B * S * 4, "d2h_bytes_per_step": B * C * 4 + 4},
+                "h2d_bytes_per_step": int(sum(3 * h[0].size * 4 for h in host) / n_pool),
+                "d2h_bytes_per_step": int(mean_rows * C * 4 + 4)},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel (QKV, attention-output, FFN1, FFN2)",
+        "roofline": {"bound": "tensor", "kernel": gemm_kernel + " (QKV, attention-output, FFN1, FFN2)",
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tensor"] if peaks["tensor"] else None, "peak_source": peaks["source"],
                      # the same against the measured burst figure and the nominal dense bf16 peak of the part
                      "frac_of_measured_burst": achieved / peaks["burst"] if peaks.get("burst") else None,
                      "frac_of_nominal_2250": achieved / 2250.0,
                      "launches": gemm_n / prof_steps, "avg_launch_ms": gemm_ms / gemm_n if gemm_n else None,
-                     # mean DRAM bytes (read + write) per GEMM launch from the ncu capture summarised in
-                     # profiles/gemm_tcgen05_c1_2layers.md (QKV 70, attention-output 32, FFN1 99, FFN2 139 MB)
-                     "traffic": 85.0e6 if not args.layers else None, "traffic_unit": "bytes per launch (ncu, mean of the four GEMMs of a layer)"},
+                     "traffic": traffic, "traffic_unit": "DRAM bytes per launch (ncu, mean over the four GEMMs of a layer)",
+                     "traffic_source": traffic_source},
         "kernels": kernels,
+        "attention_kernel": pybert.attention_kernel_name(S) if lowp else "attention_f32_kernel",
         "attention_tflops": (attn_exec / (attn_ms / 1e3) / 1e12) if attn_ms else None,
-        "layernorm_gbs": (ln_bytes * ln_n / (ln_ms / 1e3) / 1e9) if ln_ms else None,
+        "layernorm_gbs": (ln_bytes / (ln_ms / 1e3) / 1e9) if ln_ms else None,
+        "layernorm_frac_of_hbm_peak": (ln_bytes / (ln_ms / 1e3) / 1e9 / peaks["hbm"]) if ln_ms else None,
         "weight_load_seconds": round(load_seconds, 3),
+        "graph_replays": int(pybert.graph_replays(model)),
         "cpu_baseline": cpu,
     }
+    if not lowp:
+        line["roofline"]["note"] = ("the fp32 mode runs on the CUDA cores (FFMA): the tensor-core peak is the "
+                                    "denominator only because the contract asks for one")
     if args.layers:
         line["profiling_only"] = "first %d encoder layers only: not a benchmark result" % dims["layers"]
     print(json.dumps(line), flush=True)
@@ -447,6 +579,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=1, choices=sorted(synth.CONFIGS))
+    ap.add_argument("--feed", default="raw", choices=["raw", "engine"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=0,
                     help="profiling only: run the first N encoder layers (the printed line is then not a "

@@ -189,6 +189,8 @@ const char* cudabert_last_error(void* model) {
   return as_model(model)->error().c_str();
 }
 
+int cudabert_attention_kernel_for(int seq_length) { return cb::attention_kernel_for(seq_length); }
+
 int cudabert_hidden_size(void* model) { return model ? as_model(model)->hidden() : 0; }
 int cudabert_num_classes(void* model) { return model ? as_model(model)->num_classes() : 0; }
 
@@ -221,6 +223,13 @@ int cudabert_sync(void* model) {
   return m->sync() ? 0 : m->status();
 }
 
+int cudabert_test_wait_timeout(void* model, int limit_us) {
+  Model* m = as_model(model);
+  if (!m || limit_us <= 0) return 1;
+  begin_call(m);
+  return m->probe_wait_timeout(static_cast<unsigned long long>(limit_us) * 1000ull);
+}
+
 float* cudabert_pooled_dev(void* model) { return model ? as_model(model)->pooled_dev() : nullptr; }
 void* cudabert_stream(void* model) { return model ? static_cast<void*>(as_model(model)->stream()) : nullptr; }
 long cudabert_launch_count(void* model) { return model ? as_model(model)->launches_last_forward() : 0; }
@@ -244,7 +253,11 @@ int cudabert_k_gemm_tcgen05(const void* A_dev, long lda, const void* W_dev, int 
   if (!A_dev || !W_dev || !out_dev || M <= 0 || N <= 0 || K <= 0 || lda < K) return 1;
   CUtensorMap tmA, tmW;
   if (!cb::make_tmap_16bit_kmajor(&tmA, A_dev, M, K, static_cast<uint64_t>(lda) * 2, 128)) return 2;
-  if (!cb::make_tmap_16bit_kmajor(&tmW, W_dev, N, K, static_cast<uint64_t>(K) * 2, cb::gemm_w_box_rows(N))) return 2;
+  if (flags & cb::EPI_W_FP8) {
+    if (!cb::make_tmap_u8_kmajor(&tmW, W_dev, N, K)) return 2;
+  } else if (!cb::make_tmap_16bit_kmajor(&tmW, W_dev, N, K, static_cast<uint64_t>(K) * 2, cb::gemm_w_box_rows(N))) {
+    return 2;
+  }
   static thread_local DevErr scratch;
   int* err = err_dev;
   if (!err) {

@@ -403,34 +403,54 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 //               on the empty barrier (and, per tile, the accumulator-full barrier) of BOTH CTAs.
 //   both CTAs   warps 2-9: epilogue of the CTA's own 128 accumulator rows; every epilogue warp
 //               of the pair arrives on the leader's accumulator-empty barrier (count 16).
-template <int BN>
+//
+// W8 (FP8-weight mode): W lives in HBM as E4M3 bytes [N, K].  The producer's TMA brings the CTA's
+// 128 x 64 bytes of a k-block into a raw buffer beside the stage's A tile; four converter warps
+// (10-13) widen them to fp16 (cvt.rn.f16x2.e4m3x2, exact) into one of three W operand buffers in
+// the layout the MMA reads (128-byte rows, 16-byte chunk c of row r at position c ^ (r & 7)) and
+// arrive on the leader's "converted" barrier of that buffer.  The weights cross HBM, L2 and the
+// TMA at one byte per element; the tensor core sees fp16.  Two rings instead of one because the two
+// latencies differ: what TMA fetches (A tiles, raw bytes) needs six stages in flight to cover the
+// memory latency, as in the 16-bit kernel, while the converted tiles are made on the SM a few
+// hundred cycles before their MMA and need only three buffers -- six stages of A + raw + converted
+// W would not fit in shared memory.
+constexpr int CONV_WARPS = 4;
+template <int BN, bool W8>
 struct PairCfg {
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = W8 ? 5 : 6;
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = (BN / 2) * BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int RAW_BYTES = W8 ? (BN / 2) * BK : 0;  // E4M3 bytes of the CTA's W half per k-block
+  // 16-bit kernel: a stage is A | W.  W8: a stage is A | raw bytes, and W operand tiles live in their own ring.
+  static constexpr int STAGE_BYTES = A_BYTES + (W8 ? RAW_BYTES : B_BYTES);
+  static constexpr int WBUFS = W8 ? 5 : 0;
+  static constexpr int THREADS = GEMM_THREADS + (W8 ? CONV_WARPS * 32 : 0);
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + WBUFS * B_BYTES + EPI_STAGE_BYTES + BAR_BYTES + 1024;
 };
 
-template <int BN, int FLAGS>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+template <int BN, int FLAGS, bool W8>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN, W8>::THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, int M,
                          int N, int K, void* __restrict__ out, int ldo, int flags, const float* __restrict__ bias,
                          const void* __restrict__ residual, const float* __restrict__ colscale, int* err,
                          const int* __restrict__ m_dev) {
-  using C = PairCfg<BN>;
+  using C = PairCfg<BN, W8>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;
+  uint8_t* wbuf = smem + C::STAGES * C::STAGE_BYTES;  // W8: WBUFS converted W operand tiles
+  uint8_t* epi_stage = wbuf + C::WBUFS * C::B_BYTES;
   float* sbias = reinterpret_cast<float*>(epi_stage + EPI_WARPS * EPI_WARP_BYTES);
   float* sscale = sbias + 256;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + EPI_STAGE_BYTES);
   uint64_t* empty_bar = full_bar + C::STAGES;
   uint64_t* tfull_bar = empty_bar + C::STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* raw_full_bar = tempty_bar + 2;           // W8: this CTA's raw W bytes of a stage have landed
+  uint64_t* wfull_bar = raw_full_bar + C::STAGES;    // W8 [3]: both CTAs' halves of a W operand tile are converted (leader's copy)
+  uint64_t* wempty_bar = wfull_bar + 5;              // W8 [3]: the MMAs that read a W operand buffer have completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wempty_bar + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -442,6 +462,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(full_bar + s, 1);   // the leader's producer arrives; only the leader's copy is used
       mbar_init(empty_bar + s, 1);  // one commit arrival from the leader's MMA thread, in each CTA
+      mbar_init(raw_full_bar + s, 1);
+    }
+    for (int b = 0; b < 5; ++b) {
+      mbar_init(wfull_bar + b, 2 * CONV_WARPS);  // the converter warps of both CTAs
+      mbar_init(wempty_bar + b, 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar + a, 1);
@@ -482,10 +507,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         for (int kb = 0; kb < kblocks; ++kb) {
           mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, err, SITE_EMPTY);
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
-          if (leader) mbar_arrive_expect_tx(full_bar + stage, 2 * C::STAGE_BYTES);
+          if (leader) mbar_arrive_expect_tx(full_bar + stage, W8 ? 2 * C::A_BYTES : 2 * C::STAGE_BYTES);
           const uint32_t leader_full = mapa_u32(smem_u32(full_bar + stage), 0);
           tma_load_2d_pair(sa, &tmA, leader_full, kb * BK, m0);
-          tma_load_2d_pair(sa + C::A_BYTES, &tmW, leader_full, kb * BK, n0);
+          if (W8) {  // E4M3 bytes -> the stage's raw buffer; the converter warps take it from there
+            mbar_arrive_expect_tx(raw_full_bar + stage, C::RAW_BYTES);
+            tma_load_2d(sa + C::A_BYTES, &tmW, raw_full_bar + stage, kb * BK, n0);
+          } else {
+            tma_load_2d_pair(sa + C::A_BYTES, &tmW, leader_full, kb * BK, n0);
+          }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -494,8 +524,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (lane == 0 && leader) {
       const uint32_t idesc =
           (((FLAGS >= 0) ? FLAGS : flags) & EPI_IN_F16) ? umma_idesc_f16(2 * BM, BN) : umma_idesc_bf16(2 * BM, BN);
-      int stage = 0;
-      uint32_t phase = 0;
+      int stage = 0, wb = 0;
+      uint32_t phase = 0, wphase = 0;
       int it = 0;
       for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
         const int acc = it & 1;
@@ -505,16 +535,62 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kblocks; ++kb) {
           mbar_wait(full_bar + stage, phase, abort_flag, err, SITE_FULL);
+          if (W8) mbar_wait(wfull_bar + wb, wphase, abort_flag, err, SITE_FULL);
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
           const uint64_t da = umma_desc_sw128(sa);
-          const uint64_t db = umma_desc_sw128(sa + C::A_BYTES);
+          const uint64_t db = umma_desc_sw128(W8 ? smem_u32(wbuf + wb * C::B_BYTES) : sa + C::A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) umma_f16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
           umma_commit_pair(empty_bar + stage, 3);
+          if (W8) {
+            umma_commit_pair(wempty_bar + wb, 3);
+            if (++wb == 5) { wb = 0; wphase ^= 1; }
+          }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
         umma_commit_pair(tfull_bar + acc, 3);
+      }
+    }
+  } else if (W8 && warp >= 2 + EPI_WARPS) {
+    // converter warps: E4M3 bytes of the stage -> fp16 W operand tile.  Per pass a thread takes 16
+    // consecutive bytes (a warp reads 512 contiguous bytes: rows r .. r + 7, four 16-element pieces
+    // each) and writes the two 16-byte chunks they widen to at their swizzled places; the 32
+    // stores of one instruction fall on all 32 banks four times over, the minimum for 512 bytes.
+    const int t = threadIdx.x - (2 + EPI_WARPS) * 32;  // 0 .. 127
+    const uint32_t leader_wfull0 = mapa_u32(smem_u32(wfull_bar), 0);
+    int stage = 0, wb = 0;
+    uint32_t phase = 0, wphase = 0;
+    for (int tile = pair_id; tile < num_tiles; tile += num_pairs) {
+      for (int kb = 0; kb < kblocks; ++kb) {
+        mbar_wait(raw_full_bar + stage, phase, abort_flag, err, SITE_FULL);       // the bytes have landed
+        mbar_wait(wempty_bar + wb, wphase ^ 1, abort_flag, err, SITE_EMPTY);      // the buffer's last readers are done
+        const uint8_t* src = smem + stage * C::STAGE_BYTES + C::A_BYTES;
+        uint8_t* dst = wbuf + wb * C::B_BYTES;
+#pragma unroll
+        for (int i = 0; i < C::RAW_BYTES / (CONV_WARPS * 32 * 16); ++i) {
+          const int idx = i * (CONV_WARPS * 32) + t;
+          const int row = idx >> 2, q = idx & 3;
+          const uint4 v = *reinterpret_cast<const uint4*>(src + idx * 16);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+          uint32_t h[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            h[2 * j] = e4m3x2_to_f16x2(static_cast<uint16_t>(w[j] & 0xffffu));
+            h[2 * j + 1] = e4m3x2_to_f16x2(static_cast<uint16_t>(w[j] >> 16));
+          }
+          uint8_t* drow = dst + row * 128;
+          *reinterpret_cast<uint4*>(drow + (((2 * q) ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<uint4*>(drow + (((2 * q + 1) ^ (row & 7)) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+        }
+        fence_proxy_async_smem();  // the tensor core reads the tile through the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) mbar_arrive(wfull_bar + wb);
+          else mbar_arrive_remote(leader_wfull0 + wb * 8);
+        }
+        if (++wb == 5) { wb = 0; wphase ^= 1; }
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else {
@@ -530,7 +606,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                                (warp - 2) >> 2, lane, m0, n0, M, out, ldo, flags, residual);
       if (lane == 0) {
         if (leader) mbar_arrive(tempty_bar + acc);
-        else mbar_arrive_cluster(mapa_u32(smem_u32(tempty_bar + acc), 0));
+        else mbar_arrive_remote(mapa_u32(smem_u32(tempty_bar + acc), 0));
       }
     }
   }
@@ -546,6 +622,20 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     __syncwarp();
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// One thread waits, with the pipeline's own bounded wait, on an mbarrier that nobody ever arrives
+// on: the wait gives up after `limit_ns`, records the time-out in `err` exactly as a broken GEMM
+// pipeline would, and the kernel returns.  Used to check the host's handling of that status.
+__global__ void wait_timeout_probe_kernel(int* err, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+    mbar_wait(&bar, 0, &abort_flag, err, SITE_FULL, limit_ns);
   }
 }
 
@@ -570,7 +660,7 @@ EncodeTiledFn get_encode_fn() {
 // also with the FP8 column scale); everything else runs the FLAGS = -1 instantiation.
 constexpr int F_LIN = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_WSCALE;                  // QKV, attention-output, FFN2
 constexpr int F_FFN1 = F_LIN | EPI_GELU;
-constexpr int F_LIN8 = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_COLSCALE;               // the same in FP8-weight mode
+constexpr int F_LIN8 = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_COLSCALE | EPI_W_FP8;   // the same in FP8-weight mode
 constexpr int F_FFN18 = F_LIN8 | EPI_GELU;
 
 template <int BN, int FLAGS>
@@ -605,17 +695,17 @@ int launch(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, 
 
 // Number of CTA pairs that can be resident at once on this device (pairs need two SMs of one
 // GPC); a persistent grid larger than that would run its last pairs after all the others.
-template <int FLAGS>
+template <int FLAGS, bool W8>
 int max_resident_pairs(int dev) {
   static std::atomic<int> cached[64] = {};  // per device; racing threads compute the same value
   if (dev >= 0 && dev < 64 && cached[dev].load(std::memory_order_acquire) > 0) return cached[dev].load();
-  using C = PairCfg<256>;
-  if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<256, FLAGS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  using C = PairCfg<256, W8>;
+  if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<256, FLAGS, W8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            C::SMEM_BYTES) != cudaSuccess)
     return -1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * 148, 1, 1);
-  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.blockDim = dim3(C::THREADS, 1, 1);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -625,7 +715,7 @@ int max_resident_pairs(int dev) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<256, FLAGS>, &cfg) != cudaSuccess || n <= 0) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<256, FLAGS, W8>, &cfg) != cudaSuccess || n <= 0) {
     cudaGetLastError();
     return -1;
   }
@@ -633,17 +723,17 @@ int max_resident_pairs(int dev) {
   return n;
 }
 
-template <int FLAGS>
+template <int FLAGS, bool W8 = false>
 int launch_pair_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
                     const GemmEpilogue& epi, int* err_flag, const int* m_dev, cudaStream_t stream) {
-  using C = PairCfg<256>;
+  using C = PairCfg<256, W8>;
   int dev = 0;
   cudaGetDevice(&dev);
-  const int pairs = max_resident_pairs<FLAGS>(dev);
+  const int pairs = max_resident_pairs<FLAGS, W8>(dev);
   if (pairs <= 0) return -2;
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * (N / 256);
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  return launch_pdl(gemm_tcgen05_pair_kernel<256, FLAGS>, dim3(grid), dim3(GEMM_THREADS), C::SMEM_BYTES, stream, *tmA,
+  return launch_pdl(gemm_tcgen05_pair_kernel<256, FLAGS, W8>, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, stream, *tmA,
                     *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev) ==
                  cudaSuccess ? 1 : -3;
 }
@@ -653,9 +743,11 @@ int launch_pair(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, in
   switch (epi.flags) {
     case F_LIN: return launch_pair_one<F_LIN>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_FFN1: return launch_pair_one<F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    case F_LIN8: return launch_pair_one<F_LIN8>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    case F_FFN18: return launch_pair_one<F_FFN18>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    default: return launch_pair_one<-1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_LIN8: return launch_pair_one<F_LIN8, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_FFN18: return launch_pair_one<F_FFN18, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    default:
+      if (epi.flags & EPI_W_FP8) return launch_pair_one<-1, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+      return launch_pair_one<-1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   }
 }
 
@@ -668,6 +760,12 @@ bool pair_enabled() {
 }
 
 }  // namespace
+
+int wait_timeout_probe(int* err_flag, unsigned long long limit_ns, cudaStream_t stream) {
+  if (!err_flag || limit_ns == 0 || limit_ns > WAIT_LIMIT_NS) return -1;
+  wait_timeout_probe_kernel<<<1, 32, 0, stream>>>(err_flag, limit_ns);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
 
 int gemm_block_n(int N) { return (N % 256 == 0) ? 256 : 128; }
 
@@ -701,6 +799,21 @@ bool make_tmap_16bit_kmajor(CUtensorMap* out, const void* base, uint64_t rows, u
   return r == CUDA_SUCCESS;
 }
 
+bool make_tmap_u8_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (cols & 15)) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols};
+  const cuuint32_t box[2] = {BK, 128};  // 64 bytes x the 128 rows one CTA of a pair converts per k-block
+  const CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_NONE;
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
                       const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (N % 128) != 0 || (K % BK) != 0 || (ldo % 8) != 0) return -1;
@@ -716,6 +829,11 @@ int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, i
   // compares (waves of tiles) x (tensor-pipe time of one tile's k loop) for the two shapes and takes
   // the small tiles only for a clear win.  The pair's W map has 128-row boxes, which is what the
   // 128 x 128 kernel loads too.
+  if (epi.flags & EPI_W_FP8) {
+    // E4M3 weight bytes: the CTA-pair kernel with converter warps is the one kernel that reads them
+    if (N % 256 != 0 || !(epi.flags & EPI_IN_F16)) return -1;
+    return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+  }
   if (small_tiles_enabled() && gemm_uses_pairs(N) && gemm_w_box_rows(N) == 128) {
     const long pairs = num_sms / 2 > 0 ? num_sms / 2 : 1;
     const long tiles_p = static_cast<long>((M + 2 * BM - 1) / (2 * BM)) * (N / 256);

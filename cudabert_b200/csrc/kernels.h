@@ -66,7 +66,9 @@ enum EpiFlags : int {
   EPI_COLSCALE = 32, // multiply the accumulator by colscale[n] (FP8 weight de-quantisation)
   EPI_OUT_F16 = 64,  // write fp16 instead of bf16 (tcgen05 GEMM only)
   EPI_WSCALE = 128,  // multiply the accumulator by 1 / W_CONTAINER_SCALE (weights held as scaled fp16, below)
-  EPI_IN_F16 = 256   // A and W are fp16 (tcgen05 GEMM only; bf16 otherwise)
+  EPI_IN_F16 = 256,  // A and W are fp16 (tcgen05 GEMM only; bf16 otherwise)
+  EPI_W_FP8 = 512    // W is E4M3 bytes [N, K] (map from make_tmap_u8_kmajor), widened to fp16 inside the
+                     // kernel; needs EPI_IN_F16 and N % 256 == 0
 };
 
 // The encoder's dense weights are ROUNDED to bf16 (8 significand bits: the weight format of the bf16
@@ -93,6 +95,10 @@ struct GemmEpilogue {
 int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
                       const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream);
 int gemm_block_n(int N);
+// Launches one thread that runs the pipelines' bounded mbarrier wait on a barrier nobody arrives on,
+// with a limit of `limit_ns` (<= the pipelines' own 2 s): after the limit it sets bit 0 of *err_flag
+// (and the wait site in bits 8..) and the kernel ends.  For testing the host side of a time-out.
+int wait_timeout_probe(int* err_flag, unsigned long long limit_ns, cudaStream_t stream);
 // Box rows the W tensor map must be encoded with for the kernel variant that gemm_tcgen05
 // will pick for this N (128 when CTA pairs each load half of a 256-row tile, else gemm_block_n).
 int gemm_w_box_rows(int N);
@@ -100,6 +106,10 @@ int gemm_w_box_rows(int N);
 // `row_stride_bytes` between rows, box = 64 columns (128 bytes, 128-byte swizzle) x `box_rows` rows.
 bool make_tmap_16bit_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                            uint64_t row_stride_bytes, uint32_t box_rows);
+
+// Map over a row-major matrix of bytes [rows, cols] (the E4M3 weights of the FP8 mode), box = 64 bytes x
+// 128 rows, no swizzle.
+bool make_tmap_u8_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols);
 
 // ---- fp32 CUDA-core GEMM: out[M, N] = A[M, K] (fp32, row stride lda) x W[K, N] (fp32, the
 // on-disk [in, out] layout).  N % 4 == 0, K % 4 == 0.
@@ -173,11 +183,9 @@ int classify_softmax(const float* pooled, const float* W, const float* bias, flo
 // dst[n, k] = bf16-rounded src[k, n] held as fp16 x W_CONTAINER_SCALE (on-disk [in, out] -> K-contiguous
 // [out, in]); dst row offset lets Q, K, V be packed into one [3H, H] operand.
 int transpose_round_bf16(const float* src, __half* dst, int K, int N, cudaStream_t stream);
-// FP8 weights: q[n, k] = e4m3(src[k, n] / scale) stored as bytes, and the same values widened
-// exactly to fp16 for the tensor-core operand; scale = maxabs / 448 is computed on the device
-// and written to *scale_out.
-int quantize_fp8_weight(const float* src, uint8_t* dst_q, __half* dst_op, float* scale_out, int K, int N,
-                        cudaStream_t stream);
+// FP8 weights: q[n, k] = e4m3(src[k, n] / scale) stored as bytes (what the GEMM reads); scale =
+// maxabs / 448 is computed on the device and written to *scale_out.
+int quantize_fp8_weight(const float* src, uint8_t* dst_q, float* scale_out, int K, int N, cudaStream_t stream);
 int fill_f32(float* dst, float value, size_t n, cudaStream_t stream);
 
 // Message that cudabert_last_error(NULL) returns on the calling thread.

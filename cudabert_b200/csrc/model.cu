@@ -167,11 +167,13 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
     d->K = K;
     d->N = n_total;
     const size_t elems = static_cast<size_t>(K) * n_total;
-    if (!check(cudaMalloc(&d->w, elems * esize), "cudaMalloc")) return false;
-    owned_.push_back(d->w);
+    if (prec != PREC_FP8) {
+      if (!check(cudaMalloc(&d->w, elems * esize), "cudaMalloc")) return false;
+      owned_.push_back(d->w);
+    }
     if (!check(cudaMalloc(&d->bias, n_total * sizeof(float)), "cudaMalloc")) return false;
     owned_.push_back(d->bias);
-    if (prec == PREC_FP8) {
+    if (prec == PREC_FP8) {  // the E4M3 bytes are the only copy of the weights; the GEMM reads them
       if (!check(cudaMalloc(&d->w_fp8, elems), "cudaMalloc")) return false;
       owned_.push_back(d->w_fp8);
       if (!check(cudaMalloc(&d->colscale, n_total * sizeof(float)), "cudaMalloc")) return false;
@@ -194,9 +196,7 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
       return fail(2, "transpose launch failed");
   } else {
     float* scale_dev = d->colscale + n_off;  // first element of the segment doubles as the scalar slot
-    if (quantize_fp8_weight(stage_f32_, d->w_fp8 + static_cast<size_t>(n_off) * K,
-                            static_cast<__half*>(d->w) + static_cast<size_t>(n_off) * K, scale_dev, K, N,
-                            stream_) < 0)
+    if (quantize_fp8_weight(stage_f32_, d->w_fp8 + static_cast<size_t>(n_off) * K, scale_dev, K, N, stream_) < 0)
       return fail(2, "quantise launch failed");
     float scale = 0.f;
     if (!check(cudaMemcpyAsync(&scale, scale_dev, sizeof(float), cudaMemcpyDeviceToHost, stream_), "scale")) return false;
@@ -214,6 +214,12 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
 
 bool Model::finish_dense(DenseWeight* d, int prec) {
   if (prec == PREC_FP32) return true;
+  if (prec == PREC_FP8) {
+    if (d->N % 256 != 0) return fail(1, "FP8 mode needs dense widths that are multiples of 256");
+    if (!make_tmap_u8_kmajor(&d->tmap, d->w_fp8, d->N, d->K))
+      return fail(2, "cuTensorMapEncodeTiled failed for an FP8 weight matrix");
+    return true;
+  }
   if (!make_tmap_16bit_kmajor(&d->tmap, d->w, d->N, d->K, static_cast<uint64_t>(d->K) * 2, gemm_w_box_rows(d->N)))
     return fail(2, "cuTensorMapEncodeTiled failed for a weight matrix");
   return true;
@@ -413,7 +419,7 @@ bool Model::dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, i
     // FP8 de-quantisation scale comes out in the epilogue
     epi.flags |= EPI_IN_F16 | EPI_OUT_F16;
     if (prec_ == PREC_FP8) {
-      epi.flags |= EPI_COLSCALE;
+      epi.flags |= EPI_COLSCALE | EPI_W_FP8;
       epi.colscale = w.colscale;
     } else {
       epi.flags |= EPI_WSCALE;
@@ -437,16 +443,31 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
   if (!ensure_capacity(B, S, want_hidden_f32)) return false;
   if (!graphs_enabled_ || profiling_) return enqueue_forward(d_ids, d_seg, d_mask, B, S, want_hidden_f32, want_probs);
 
-  // The first pass with a given argument set runs kernel by kernel (it also does every one-time
-  // set-up a launcher may need); the second is captured into a CUDA graph; from then on the pass is
-  // one graph launch, which takes the per-kernel launch cost off the host for small batches.
+  // The first passes with a given argument set run kernel by kernel (the very first also does every
+  // one-time set-up a launcher may need); pass number GRAPH_CAPTURE_AT is captured into a CUDA graph;
+  // from then on the pass is one graph launch, which takes the per-kernel launch cost off the host
+  // for small batches.  A caller whose shapes rarely repeat (the engine trims every batch to its own
+  // longest line) thus pays for few captures, and a full cache drops only its least recently used
+  // entry.
   const GraphKey key{d_ids, d_seg, d_mask, B, S, (want_hidden_f32 ? 1 : 0) | (want_probs ? 2 : 0)};
   auto it = graphs_.find(key);
   if (it == graphs_.end()) {
-    if (graphs_.size() >= 32) drop_graphs();
-    graphs_[key] = GraphEntry();
-    return enqueue_forward(d_ids, d_seg, d_mask, B, S, want_hidden_f32, want_probs);
+    if (graphs_.size() >= GRAPH_CACHE_MAX) {
+      auto lru = graphs_.begin();
+      for (auto g = graphs_.begin(); g != graphs_.end(); ++g)
+        if (g->second.last_use < lru->second.last_use) lru = g;
+      if (lru->second.exec) {
+        // the graph may still be executing: it is the stream's most recent work at the earliest
+        if (!check(cudaStreamSynchronize(stream_), "sync before dropping a graph")) return false;
+        cudaGraphExecDestroy(lru->second.exec);
+      }
+      graphs_.erase(lru);
+    }
+    it = graphs_.emplace(key, GraphEntry()).first;
   }
+  it->second.last_use = ++graph_tick_;
+  if (!it->second.exec && ++it->second.seen < GRAPH_CAPTURE_AT)
+    return enqueue_forward(d_ids, d_seg, d_mask, B, S, want_hidden_f32, want_probs);
   GraphEntry& entry = it->second;
   if (!entry.exec) {
     if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
@@ -591,6 +612,16 @@ bool Model::sync() {
     return fail(4, "input ids or segment ids out of range (clamped); results of this call are suspect");
   }
   return true;
+}
+
+int Model::probe_wait_timeout(unsigned long long limit_ns) {
+  if (!check(cudaSetDevice(dev_), "cudaSetDevice")) return status_;
+  if (wait_timeout_probe(err_dev_, limit_ns, stream_) < 0) {
+    fail(1, "wait probe: the limit must be between 1 ns and 2 s");
+    return status_;
+  }
+  sync();
+  return status_;
 }
 
 bool Model::run_host(const int* ids, const int* seg, const int* mask, int B, int S, float* pooled_out,

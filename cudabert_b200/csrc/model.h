@@ -61,6 +61,9 @@ class Model {
   bool forward_device(const int* d_ids, const int* d_seg, const int* d_mask, int B, int S, bool want_hidden_f32,
                       bool want_probs);
   bool sync();
+  // Enqueues the bounded-wait probe (kernels.h: wait_timeout_probe) on the handle's stream with this
+  // handle's device error word, then synchronises: returns status() afterwards (4 after the time-out).
+  int probe_wait_timeout(unsigned long long limit_ns);
   // CUDA graphs replayed / captured so far (a forward pass is captured the second time its exact
   // arguments are seen; CUDABERT_GRAPH=0 turns this off)
   long graph_replays() const { return graph_replays_; }
@@ -122,7 +125,12 @@ class Model {
   struct GraphEntry {
     cudaGraphExec_t exec = nullptr;
     long launches = 0;
+    int seen = 0;             // passes with this key so far; it is captured on pass GRAPH_CAPTURE_AT
+    unsigned long long last_use = 0;
   };
+  static constexpr int GRAPH_CAPTURE_AT = 3;     // a key seen once or twice is not worth a capture + instantiate
+  static constexpr size_t GRAPH_CACHE_MAX = 64;  // beyond this the least recently used entry goes
+  unsigned long long graph_tick_ = 0;
   std::map<GraphKey, GraphEntry> graphs_;
   bool graphs_enabled_ = true;
   bool cls_last_ = true;  // pooler-only passes compute the last layer for the first token of every sequence only

@@ -66,15 +66,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` lives in shared memory (one per CTA); `err` in global memory.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* err, int site) {
+                                          int* err, int site, unsigned long long limit_ns = WAIT_LIMIT_NS) {
+  // The clock is read only every 1024 polls, and for the first time after the first 1024: reading
+  // %globaltimer takes on the order of a microsecond, which a waiter that merely arrived a little
+  // early (the common case in a running pipeline) must not pay before it polls again.
   if (mbar_try_wait(bar, parity)) return true;
-  if (*abort_flag) return false;
-  const unsigned long long t0 = globaltimer_ns();
+  if (*abort_flag) return false;  // a wait of this CTA has given up before: do not wait again
   uint32_t spins = 0;
+  unsigned long long t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicOr(err, 1 | (site << 8));
         return false;
@@ -113,8 +119,15 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t smem_addr, uint32_t rank) 
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+// Arrive on an mbarrier of another CTA of the cluster (address from mapa_u32), with the default
+// CTA-scope release.  What these arrivals publish is either nothing in memory (an accumulator in TMEM
+// has been read: tcgen05.wait::ld and a tcgen05 fence come first) or shared-memory writes of the
+// arriving CTA that a fence.proxy.async has already handed to the tensor core's proxy.  A
+// `.release.cluster` arrival here cost about a microsecond each (it waits for every earlier store of
+// the thread, global ones included, to be visible cluster-wide) and halved the rate of the FP8
+// kernel, whose converter warps arrive once per k-block.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // Tile load into THIS CTA's shared memory whose completion bytes are counted on an mbarrier of
 // the pair's leader CTA (`bar_cluster_addr` from mapa_u32); used by both CTAs of a pair.
@@ -271,6 +284,13 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   uint32_t v;
   asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(v) : "f"(hi), "f"(lo));
   return v;
+}
+
+// Two E4M3 bytes (low byte first) -> packed fp16, exact.
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint16_t v) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+  return r;
 }
 
 // 2^x by the hardware approximation (relative error 2^-22; results below 2^-126 flush to zero)

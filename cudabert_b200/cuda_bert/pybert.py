@@ -179,6 +179,17 @@ reader_lines = lib.cudabert_reader_lines
 reader_lines.argtypes = [c_void_p]
 reader_lines.restype = _c_ll
 
+attention_kernel_for = lib.cudabert_attention_kernel_for
+attention_kernel_for.argtypes = [c_int]
+attention_kernel_for.restype = c_int
+
+
+def attention_kernel_name(seq_length):
+    """Name of the attention kernel a 16-bit forward pass of this padded length runs."""
+    return {1: "attention_f16_kernel", 2: "attention_tc_kernel",
+            3: "attention_f16_persist_kernel"}.get(attention_kernel_for(int(seq_length)), "unknown")
+
+
 hidden_size = lib.cudabert_hidden_size
 hidden_size.argtypes = [c_void_p]
 hidden_size.restype = c_int
@@ -202,6 +213,11 @@ probs_dev.restype = c_void_p
 sync = lib.cudabert_sync
 sync.argtypes = [c_void_p]
 sync.restype = c_int
+
+# test hook: makes one bounded device-side wait run out (limit in microseconds) and returns the status
+test_wait_timeout = lib.cudabert_test_wait_timeout
+test_wait_timeout.argtypes = [c_void_p, c_int]
+test_wait_timeout.restype = c_int
 
 pooled_dev = lib.cudabert_pooled_dev
 pooled_dev.argtypes = [c_void_p]

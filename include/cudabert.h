@@ -82,6 +82,11 @@ CUDABERT_API int cudabert_status(void* model);
  * init_model on this thread failed.                                                          */
 CUDABERT_API const char* cudabert_last_error(void* model);
 CUDABERT_API int cudabert_hidden_size(void* model);
+/* Which attention kernel a 16-bit forward pass of this padded sequence length runs (the lengths of the
+ * sequences live on the device, so the choice depends on the padded length alone; environment
+ * CUDABERT_ATTENTION=tc|persist|mma forces one): 1 = mma.sync, one CTA per sequence and head;
+ * 2 = tcgen05; 3 = mma.sync, persistent.                                                             */
+CUDABERT_API int cudabert_attention_kernel_for(int seq_length);
 CUDABERT_API int cudabert_num_classes(void* model);
 
 /* Forward pass on inputs that already live in device memory (int32 [batchsize, seq_length];
@@ -94,6 +99,14 @@ CUDABERT_API int cudabert_forward_dev(void* model, const int* ids_dev, const int
 CUDABERT_API int cudabert_classify_dev(void* model, const int* ids_dev, const int* seg_dev, const int* mask_dev,
                                        int batchsize, int seq_length);
 CUDABERT_API int cudabert_sync(void* model);
+/* Test hook for the failure path of the device-side pipelines (no counterpart in the reference, whose
+ * kernels have no waits).  Every mbarrier wait in the GEMM and attention kernels gives up after 2 s, sets
+ * an error word and lets the kernel finish; the host then reports status 4.  This call runs that same wait,
+ * in a one-thread kernel on the handle's stream, on a barrier nobody arrives on, with a limit of limit_us
+ * microseconds (at most 2 000 000), waits for it and returns the handle's status: 4, with the wait site
+ * in cudabert_last_error.  The handle stays usable; the next call clears the status.  Nothing faults or
+ * hangs: the kernel returns by itself when the limit has passed.                                       */
+CUDABERT_API int cudabert_test_wait_timeout(void* model, int limit_us);
 CUDABERT_API float* cudabert_pooled_dev(void* model);
 CUDABERT_API float* cudabert_probs_dev(void* model);
 /* Blocking device-to-host copy, so that a ctypes caller can read what Retval points to. */
@@ -104,7 +117,7 @@ CUDABERT_API void* cudabert_stream(void* model);
 /* Kernels launched by the last forward pass of this handle. */
 CUDABERT_API long cudabert_launch_count(void* model);
 /* A forward pass is enqueued kernel by kernel the first time its exact arguments (input addresses,
- * batch, sequence length) are seen, captured into a CUDA graph the second time and replayed as one
+ * batch, sequence length) are seen (and the second), captured into a CUDA graph the third time and replayed as one
  * graph launch from then on (environment CUDABERT_GRAPH=0: never).  These count the captures and the
  * replays of this handle so far. */
 CUDABERT_API long cudabert_graph_captures(void* model);

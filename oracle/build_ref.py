@@ -28,9 +28,16 @@ SOURCES = ["utils/bert.cu", "utils/common.cc", "utils/load_model.cc", "utils/man
            "ops/batch_matmul.cu", "cuda_bert.cu", "ops/crossEntropyLoss.cu"]
 
 
+def default_reference_dir():
+    env = os.environ.get("CUDABERT_REFERENCE")
+    return env if env else os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=default_reference_dir(),
+                    help="checkout of the reference project (default: $CUDABERT_REFERENCE, else the "
+                         "directory 'reference' beside this repository)")
     args = ap.parse_args()
     src_root = os.path.join(args.reference, "cuda_bert")
     if not os.path.isdir(src_root):

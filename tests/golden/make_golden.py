@@ -71,7 +71,10 @@ def to_state_dict(weights, layers):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("CUDABERT_REFERENCE") or os.path.join(
+        os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference"),
+                    help="checkout of the reference project (default: $CUDABERT_REFERENCE, else the directory "
+                         "'reference' beside this repository)")
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     BertConfig, BertModel = load_reference_model(args.reference)

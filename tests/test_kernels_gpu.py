@@ -11,7 +11,9 @@ from oracle import bert_oracle
 pytestmark = pytest.mark.gpu
 
 EPI_BIAS, EPI_GELU, EPI_RESIDUAL, EPI_TANH, EPI_OUT_F32, EPI_COLSCALE, EPI_OUT_F16 = 1, 2, 4, 8, 16, 32, 64
-EPI_WSCALE, EPI_IN_F16 = 128, 256
+EPI_WSCALE, EPI_IN_F16, EPI_W_FP8 = 128, 256, 512
+# what they pass in FP8-weight mode: E4M3 weight bytes widened inside the kernel, per-column scale
+ENCODER_LINEAR_FP8 = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_COLSCALE | EPI_W_FP8
 W_CONTAINER_SCALE = 4096.0
 # what the encoder's dense layers pass in bf16 mode: fp16 operands and output, weights held scaled
 ENCODER_LINEAR = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_WSCALE
@@ -63,13 +65,18 @@ def test_gemm_tcgen05(pybert, M, N, K, flags):
     in_dt = torch.float16 if flags & EPI_IN_F16 else torch.bfloat16
     A = (torch.randn(M, K, device="cuda", generator=g) * 0.5).to(in_dt)
     W = torch.randn(N, K, device="cuda", generator=g) * 0.05
-    if flags & EPI_WSCALE:   # bf16-rounded weights held as fp16 numbers times the container scale
+    if flags & EPI_W_FP8:    # E4M3 bytes (values up to +-448), widened to fp16 inside the kernel
+        W8 = (W * 2000.0).to(torch.float8_e4m3fn)
+        W, Wref = W8.view(torch.uint8), W8.float()
+    elif flags & EPI_WSCALE:   # bf16-rounded weights held as fp16 numbers times the container scale
         W = (W.bfloat16().float() * W_CONTAINER_SCALE).half()
         assert torch.equal(W.float() / W_CONTAINER_SCALE, (W.float() / W_CONTAINER_SCALE).bfloat16().float())
     else:
         W = W.to(in_dt)
     bias = torch.randn(N, device="cuda", generator=g) * 0.1
     colscale = torch.rand(N, device="cuda", generator=g) + 0.5
+    if flags & EPI_W_FP8:
+        colscale = (colscale / 2000.0).contiguous()      # undoes the quantisation scale, as the model's per-tensor scale does
     out_f32 = bool(flags & EPI_OUT_F32)
     resid = torch.randn(M, N, device="cuda", generator=g)
     resid = resid if out_f32 else resid.bfloat16()
@@ -79,7 +86,9 @@ def test_gemm_tcgen05(pybert, M, N, K, flags):
     rc = pybert.k_gemm_tcgen05(A.data_ptr(), K, W.data_ptr(), M, N, K, out.data_ptr(), flags, bias.data_ptr(),
                             resid.data_ptr(), colscale.data_ptr(), err.data_ptr())
     assert rc == 0, "k_gemm_tcgen05 rc=%d err=%d" % (rc, int(err.item()))
-    ref = _ref_epilogue(A.float() @ W.float().t(), flags, bias, resid, colscale)
+    if not flags & EPI_W_FP8:
+        Wref = W.float()
+    ref = _ref_epilogue(A.float() @ Wref.t(), flags, bias, resid, colscale)
     got = out.float()
     assert torch.isfinite(got).all()
     rel = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
