@@ -116,7 +116,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int i = 0; i < 14; ++i) mbar_init(bars + i, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 4);  // one arrival per softmax warp
     mbar_init(o_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -362,7 +362,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_proxy_async_smem();  // the tensor core reads P through the async proxy
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();              // every lane's rows are written and fenced: one arrival for the warp
+      if (lane == 0) mbar_arrive(p_full);
       if (j != it.nblocks - 1) continue;
 
       // last block of the item: O / l -> bf16 -> this warp's staging rows -> coalesced stores

@@ -662,6 +662,8 @@ constexpr int F_LIN = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_WSCALE;         
 constexpr int F_FFN1 = F_LIN | EPI_GELU;
 constexpr int F_LIN8 = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_COLSCALE | EPI_W_FP8;   // the same in FP8-weight mode
 constexpr int F_FFN18 = F_LIN8 | EPI_GELU;
+constexpr int F_LIN8W = F_LIN8 & ~EPI_W_FP8;    // FP8-weight mode with the weights widened to fp16 at load
+constexpr int F_FFN18W = F_FFN18 & ~EPI_W_FP8;
 
 template <int BN, int FLAGS>
 int launch_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
@@ -745,6 +747,8 @@ int launch_pair(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, in
     case F_FFN1: return launch_pair_one<F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_LIN8: return launch_pair_one<F_LIN8, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_FFN18: return launch_pair_one<F_FFN18, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_LIN8W: return launch_pair_one<F_LIN8W>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_FFN18W: return launch_pair_one<F_FFN18W>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     default:
       if (epi.flags & EPI_W_FP8) return launch_pair_one<-1, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
       return launch_pair_one<-1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);

@@ -183,9 +183,11 @@ int classify_softmax(const float* pooled, const float* W, const float* bias, flo
 // dst[n, k] = bf16-rounded src[k, n] held as fp16 x W_CONTAINER_SCALE (on-disk [in, out] -> K-contiguous
 // [out, in]); dst row offset lets Q, K, V be packed into one [3H, H] operand.
 int transpose_round_bf16(const float* src, __half* dst, int K, int N, cudaStream_t stream);
-// FP8 weights: q[n, k] = e4m3(src[k, n] / scale) stored as bytes (what the GEMM reads); scale =
-// maxabs / 448 is computed on the device and written to *scale_out.
-int quantize_fp8_weight(const float* src, uint8_t* dst_q, float* scale_out, int K, int N, cudaStream_t stream);
+// FP8 weights: q[n, k] = e4m3(src[k, n] / scale), written as bytes to dst_q (what the GEMM reads with
+// EPI_W_FP8) and / or widened exactly to fp16 to dst_wide (either may be null); scale = maxabs / 448 is
+// computed on the device and written to *scale_out.
+int quantize_fp8_weight(const float* src, uint8_t* dst_q, __half* dst_wide, float* scale_out, int K, int N,
+                        cudaStream_t stream);
 int fill_f32(float* dst, float value, size_t n, cudaStream_t stream);
 
 // Message that cudabert_last_error(NULL) returns on the calling thread.

@@ -30,7 +30,7 @@ enum KernelClass : int {
 
 struct DenseWeight {      // one projection
   void* w = nullptr;      // fp32 [K, N] (fp32 mode); else fp16 [N, K] holding the bf16-rounded (x 4096) or e4m3 weights
-  uint8_t* w_fp8 = nullptr;  // fp8 mode: e4m3 bytes [N, K] (the stored quantised weights)
+  uint8_t* w_fp8 = nullptr;  // fp8 mode: e4m3 bytes [N, K], the weights the GEMM reads (null when they were widened at load)
   float* bias = nullptr;     // [N]
   float* colscale = nullptr; // fp8 mode: [N] de-quantisation scale per output column
   int K = 0, N = 0;
@@ -133,6 +133,7 @@ class Model {
   unsigned long long graph_tick_ = 0;
   std::map<GraphKey, GraphEntry> graphs_;
   bool graphs_enabled_ = true;
+  bool fp8_widened_ = false;  // FP8 mode: weights expanded to fp16 at load (CUDABERT_FP8_OPERAND=widened)
   bool cls_last_ = true;  // pooler-only passes compute the last layer for the first token of every sequence only
   static constexpr int PDL_MAX_TOKENS = 4096;  // forward passes up to this many token slots use dependent launch
   long graph_replays_ = 0, graph_captures_ = 0;

@@ -250,8 +250,9 @@ __global__ void finish_scale_kernel(float* scale_io) {
   *scale_io = (m > 0.f) ? m / 448.0f : 1.0f;
 }
 
+// dst_q (may be null): the E4M3 bytes; dst_wide (may be null): the same values widened exactly to fp16
 __global__ void quantize_fp8_kernel(const float* __restrict__ src, uint8_t* __restrict__ dst_q,
-                                    const float* __restrict__ scale, int K, int N) {
+                                    __half* __restrict__ dst_wide, const float* __restrict__ scale, int K, int N) {
   __shared__ float tile[32][33];
   const float inv = 1.0f / *scale;
   const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
@@ -264,7 +265,9 @@ __global__ void quantize_fp8_kernel(const float* __restrict__ src, uint8_t* __re
     const int n = n0 + r, k = k0 + threadIdx.x;
     if (n < N && k < K) {
       const __nv_fp8_e4m3 q(tile[threadIdx.x][r] * inv);
-      dst_q[static_cast<size_t>(n) * K + k] = q.__x;
+      const size_t o = static_cast<size_t>(n) * K + k;
+      if (dst_q) dst_q[o] = q.__x;
+      if (dst_wide) dst_wide[o] = __float2half_rn(static_cast<float>(q));  // every E4M3 value is an fp16 value
     }
   }
 }
@@ -425,12 +428,13 @@ int transpose_round_bf16(const float* src, __half* dst, int K, int N, cudaStream
   return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
-int quantize_fp8_weight(const float* src, uint8_t* dst_q, float* scale_out, int K, int N, cudaStream_t stream) {
+int quantize_fp8_weight(const float* src, uint8_t* dst_q, __half* dst_wide, float* scale_out, int K, int N,
+                        cudaStream_t stream) {
   if (cudaMemsetAsync(scale_out, 0, sizeof(float), stream) != cudaSuccess) return -3;
   maxabs_kernel<<<296, 256, 0, stream>>>(src, static_cast<size_t>(K) * N, reinterpret_cast<unsigned int*>(scale_out));
   finish_scale_kernel<<<1, 1, 0, stream>>>(scale_out);
   dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
-  quantize_fp8_kernel<<<grid, block, 0, stream>>>(src, dst_q, scale_out, K, N);
+  quantize_fp8_kernel<<<grid, block, 0, stream>>>(src, dst_q, dst_wide, scale_out, K, N);
   return cudaGetLastError() == cudaSuccess ? 3 : -3;
 }
 

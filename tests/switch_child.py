@@ -23,7 +23,7 @@ def main():
         cfg.is_large = bool(int(large))
         cfg.model_npy_pth = weight_dir
         cfg.batch_size = cfg.max_seq_length = 0
-        cfg.precision = "bf16"
+        cfg.precision = os.environ.get("SWITCH_CHILD_PRECISION", "bf16")
         model = Cuda_BERT(0, cfg)
         for name in names.split(","):
             ids, seg, mask = cases.case_inputs(name)

@@ -16,7 +16,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BASE_CASES = ["c0_affine", "c2_small", "edge_s17", "edge_b1s1", "edge_nomask", "edge_zero_row", "edge_holes"]
 LARGE_CASES = ["c1_small", "c3_small", "c4_small"]
 SWITCHES = ("CUDABERT_PACK", "CUDABERT_GRAPH", "CUDABERT_PDL", "CUDABERT_LAST_LAYER", "CUDABERT_ATTENTION",
-            "CUDABERT_GEMM_PAIR", "CUDABERT_GEMM_SMALL_TILES", "CUDABERT_PRECISION", "CUDABERT_LN")
+            "CUDABERT_GEMM_PAIR", "CUDABERT_GEMM_SMALL_TILES", "CUDABERT_PRECISION", "CUDABERT_LN",
+            "CUDABERT_FP8_OPERAND", "SWITCH_CHILD_PRECISION")
 
 
 @pytest.fixture(scope="module")
@@ -72,3 +73,13 @@ def test_kernel_choice_switches_stay_close(run_with, switch):
     for case, (to_gold, to_default) in worst.items():
         assert to_gold <= 2e-2, "%s, case %s vs golden: %g" % (switch, case, to_gold)
         assert to_default <= 1.5e-2, "%s, case %s vs default: %g" % (switch, case, to_default)
+
+
+def test_fp8_operand_switch_keeps_every_bit(run_with):
+    """FP8 mode reads the E4M3 weight bytes in the GEMM (converter warps widen them to fp16 in shared
+    memory); CUDABERT_FP8_OPERAND=widened expands them to fp16 once at load instead.  Both feed the
+    tensor core the same fp16 values in the same order: not a bit may differ."""
+    in_kernel = run_with(SWITCH_CHILD_PRECISION="fp8")
+    widened = run_with(SWITCH_CHILD_PRECISION="fp8", CUDABERT_FP8_OPERAND="widened")
+    for case in BASE_CASES + LARGE_CASES:
+        np.testing.assert_array_equal(widened[case], in_kernel[case], err_msg=case)
