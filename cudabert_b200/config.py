@@ -1,7 +1,7 @@
 """Engine configuration.  ``Engin_Config`` offers the attribute names callers of the reference set
 (config.py:3-39) so that their scripts run unchanged; defaults and their meaning are listed in
-``_DEFAULTS`` below.  Additions: ``precision``, ``native_batcher``, ``resume_without_dead_gpu`` and
-``mp_start_method``."""
+``_DEFAULTS`` below.  Additions: ``precision``, ``native_batcher``, ``native_reader``, ``reader_threads``, ``replica_mode``,
+``resume_without_dead_gpu`` and ``mp_start_method``."""
 import os
 
 _PACKAGE_DIR = os.path.dirname(os.path.abspath(__file__))
@@ -24,6 +24,8 @@ _DEFAULTS = {
     "native_batcher": (True, "bucket and trim in the library's batcher; False = the Python classes"),
     "native_reader": (True, "with a tokenizer.Tokenlizer as tokenizer function: read, tokenise and bucket in native threads"),
     "reader_threads": (0, "tokenizer threads of the native reader; 0 = up to 16, one core left free"),
+    "replica_mode": ("auto", '"process": one OS process per replica (the reference\'s way); "thread": one thread per replica '
+                             'inside this process (needs a tokenizer.Tokenlizer); "auto": threads for more than two GPUs when possible'),
     "resume_without_dead_gpu": (True, "if a replica's process dies, resume after the last written line on the rest"),
     "mp_start_method": (None, 'multiprocessing start method; use "spawn" when the parent already holds a CUDA context'),
 }

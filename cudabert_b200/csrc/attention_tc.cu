@@ -281,28 +281,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       tmem_ld32(t_s + 32, v[1]);
       tmem_ld_wait();
       // four independent chains for the maximum (and below for the sum): a single chain of 64
-      // dependent operations would leave the two warps an SM sub-partition holds mostly stalled
+      // dependent operations would leave the two warps an SM sub-partition holds mostly stalled.
+      // The softmax warps are bound by their issue slots, so the loops below use the three-input
+      // maximum and packed pairs for the multiply-adds and the sums (half the instructions each).
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (plain) {
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[ch][i]));
+          for (int i = 0; i < 32; i += 8)
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              mx4[q] = max3(mx4[q], __uint_as_float(v[ch][i + 2 * q]), __uint_as_float(v[ch][i + 2 * q + 1]));
 #pragma unroll
         for (int q = 0; q < 4; ++q) mx4[q] *= scale;  // the scale itself is folded into the exponential below
       } else {
+        const uint64_t sc2 = pack_f32x2(scale, scale);
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch)
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const float4 b4 = *reinterpret_cast<const float4*>(bias + ch * 32 + i);
-            const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float x = fmaf(__uint_as_float(v[ch][i + q]), scale, bb[q]);
-              v[ch][i + q] = __float_as_uint(x);
-              mx4[q] = fmaxf(mx4[q], x);
-            }
+            float x0, x1, x2, x3;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1])), sc2,
+                                   pack_f32x2(b4.x, b4.y)), x0, x1);
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[ch][i + 2]), __uint_as_float(v[ch][i + 3])), sc2,
+                                   pack_f32x2(b4.z, b4.w)), x2, x3);
+            v[ch][i] = __float_as_uint(x0); v[ch][i + 1] = __float_as_uint(x1);
+            v[ch][i + 2] = __float_as_uint(x2); v[ch][i + 3] = __float_as_uint(x3);
+            mx4[(i >> 2) & 1] = max3(mx4[(i >> 2) & 1], x0, x1);
+            mx4[2 + ((i >> 2) & 1)] = max3(mx4[2 + ((i >> 2) & 1)], x2, x3);
           }
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
@@ -338,16 +346,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
           tmem_st_wait();
         }
       }
-      // P = exp2(x - max) -> bf16 -> swizzled A-operand tile
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      // P = exp2(x - max) -> fp16 -> swizzled A-operand tile
+      uint64_t l2[2] = {0ull, 0ull};  // two packed pairs of partial sums
       const float e_scale = plain ? scale : 1.0f;  // plain blocks still hold the raw dot products
+      const uint64_t es2 = pack_f32x2(e_scale, e_scale), nm2 = pack_f32x2(-m_new, -m_new);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         float p[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          p[i] = ex2_approx(fmaf(__uint_as_float(v[ch][i]), e_scale, -m_new));
-          l4[i & 3] += p[i];
+        for (int i = 0; i < 32; i += 2) {
+          float a, b;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1])), es2, nm2), a, b);
+          p[i] = ex2_approx(a);
+          p[i + 1] = ex2_approx(b);
+          l2[(i >> 1) & 1] = add_f32x2(l2[(i >> 1) & 1], pack_f32x2(p[i], p[i + 1]));
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -359,6 +371,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
           *reinterpret_cast<uint4*>(my_p + (((ch * 4 + q) ^ (r & 7)) << 4)) = t;
         }
       }
+      float l4[4];
+      unpack_f32x2(l2[0], l4[0], l4[1]);
+      unpack_f32x2(l2[1], l4[2], l4[3]);
       l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_proxy_async_smem();  // the tensor core reads P through the async proxy
       tc_fence_before();

@@ -16,6 +16,12 @@ sharding, no collective: workers pull whole batches from a shared queue); a writ
 the input order in a sliding window and applies back-pressure through ``alert_size``
 (engine.py:303-375).
 
+With a ``tokenizer.Tokenlizer`` as tokenizer function and more than two GPUs (or
+``config.replica_mode = "thread"``) the same pipeline runs inside ONE process instead: the native
+reader's tokenizer threads fill the buckets, one host thread per GPU drives its replica (the
+library call releases the GIL), and the writer takes finished batches from an in-process queue --
+no pickling and no pipes, which is what lets eight replicas be fed at their own rate (``_run_threads``).
+
 Differences from the reference, on purpose: workers block on the queue instead of busy-polling
 ``empty()`` (engine.py:253-264); every stage is joined and a stage that dies is detected by the
 parent instead of being waited for forever on a sentinel count (engine.py:312, 401): a dead replica
@@ -428,6 +434,13 @@ class Engine(object):
         assert(type(input_file) == str)
         self.config.input_file = input_file
         self.config.output_file = output_file
+        assert(self.cuda_model is not None and self.finetune_layer is not None)
+        assert(self.tokenlizer_line is not None and self.output_line is not None)
+        assert(self.config.gpu != [])
+        if self._wants_threads():
+            self._run_threads(input_file, output_file)
+            self.logger.info("ALL JOBS DONE")
+            return
         start_line, offset = 0, 0     # lines and bytes of the output file that are known to be good
         while True:
             failed, progress = self._run_once(input_file, output_file, start_line, offset)
@@ -448,6 +461,167 @@ class Engine(object):
             self.logger.warning("replica on gpu %s died with exit code %s: resuming at line %d on gpus %s",
                                 dead[0], code, start_line, self.config.gpu)
         self.logger.info("ALL JOBS DONE")
+
+    # ------------------------------------------------------------------ one process, one thread per replica
+    def _wants_threads(self):
+        """ Whether run() uses the in-process pipeline: config.replica_mode "thread" / "process", or
+        "auto" (default): threads when the native reader can do the tokenising (the tokenizer function
+        is a tokenizer.Tokenlizer and config.native_reader is on) and more than two replicas have to
+        be fed, which is where one reader process and its pipes become the limit. """
+        from .tokenizer import Tokenlizer
+        mode = getattr(self.config, "replica_mode", "auto")
+        native = getattr(self.config, "native_reader", True) and isinstance(self.tokenlizer_line, Tokenlizer)
+        if mode == "thread":
+            if not native:
+                raise ValueError('replica_mode "thread" needs a tokenizer.Tokenlizer as tokenizer function '
+                                 "(a Python tokenizer would hold the interpreter lock that the replicas need)")
+            return True
+        return mode == "auto" and native and len(self.config.gpu) > 2
+
+    def _run_threads(self, input_file, output_file):
+        """ The pipeline inside one process.  Threads: the native reader's tokenizer threads (no
+        interpreter lock), a feeder that turns finished buckets into Batch_Blobs, one thread per
+        replica, and the caller's thread as the writer.  A replica whose model fails to load or whose
+        call raises is dropped and its batch goes to another replica; the run fails only when no
+        replica is left.  (A replica that crashes the process -- not an exception -- takes the run with
+        it: that isolation is what the process-per-replica mode is for.) """
+        import threading
+        from ctypes import byref, c_int, c_longlong, create_string_buffer
+        import numpy as np
+        from .cuda_bert import pybert
+        self.generate_splits()
+        config, tok, log = self.config, self.tokenlizer_line, self.logger
+        gpus = list(config.gpu)
+        tok._native()
+        bounds = np.ascontiguousarray(self.seq_length_split, dtype=np.int32)
+        threads = int(getattr(config, "reader_threads", 0)) or max(1, min(4 * len(gpus), (os.cpu_count() or 2) - 1))
+        reader = pybert.reader_create(input_file.encode("utf-8"), tok._handle, config.max_seq_length, bounds,
+                                      len(bounds), config.batch_size, threads, 1 if config.skip_first_line else 0, 0)
+        if not reader:
+            raise RuntimeError("native reader: cannot open %r" % (input_file,))
+        batches = pyqueue.Queue(maxsize=max(4, 3 * len(gpus)))   # feeder -> replicas
+        results = pyqueue.Queue()                                 # replicas -> writer
+        stop = threading.Event()
+        state = {"issued": 0, "fed": False}
+
+        def put_until_stopped(q, item):
+            while not stop.is_set():
+                try:
+                    q.put(item, timeout=0.2)
+                    return True
+                except pyqueue.Full:
+                    pass
+            return False
+
+        def feeder():
+            try:
+                rows, seq, first = c_int(0), c_int(0), c_longlong(0)
+                while not stop.is_set() and pybert.reader_next(reader, byref(rows), byref(seq), byref(first)) == 1:
+                    index = np.empty(rows.value, np.int64)
+                    offsets = np.empty(rows.value + 1, np.int64)
+                    tensor = [np.empty((rows.value, seq.value), np.int32) for _ in range(3)]
+                    got = pybert.reader_pop(reader, index, tensor[0], tensor[1], tensor[2], offsets)
+                    assert got == rows.value
+                    raw = create_string_buffer(int(offsets[-1]) + 1)
+                    pybert.reader_raw(reader, raw, int(offsets[-1]))
+                    state["issued"] += 1
+                    if not put_until_stopped(batches, Batch_Blob(index, raw.raw[:int(offsets[-1])], offsets, tensor)):
+                        return
+                state["fed"] = True
+                results.put(("fed", None, None, None))
+            except BaseException as e:       # the writer must not wait for batches that will never come
+                results.put(("feeder_failed", None, None, e))
+
+        def replica(gpu):
+            try:
+                layer = self.finetune_layer(config.is_large)
+                layer.init_finetune_layer(gpu)
+                model = self.cuda_model(gpu, config)
+            except BaseException as e:
+                results.put(("replica_failed", gpu, None, e))
+                return
+            done, t0 = 0, time.time()
+            while True:
+                batch = batches.get()
+                if batch is None:
+                    break
+                try:
+                    batch.output = layer.run(model.encode(batch.tensor))
+                except BaseException as e:
+                    results.put(("replica_failed", gpu, batch, e))
+                    return
+                done += batch.tensor[0].shape[0]
+                batch.drop_tensor()
+                results.put(("done", gpu, batch, None))
+            close = getattr(model, "close", None)
+            if close:
+                close()
+            log.info("replica thread on gpu %s done: %d lines in %.2f s", gpu, done, time.time() - t0)
+
+        workers = [threading.Thread(target=replica, args=(g,), daemon=True, name="replica-gpu%s" % g) for g in gpus]
+        feed = threading.Thread(target=feeder, daemon=True, name="feeder")
+        for t in workers + [feed]:
+            t.start()
+        alive, completed, next_line, window = len(gpus), 0, 0, {}
+        failure = None
+        t_first, lines_at_first = None, 0     # steady-state rate: from the first finished batch on
+        try:
+            with open(output_file, 'w', encoding='utf-8') as f:
+                while not (state["fed"] and completed == state["issued"]):
+                    kind, gpu, batch, exc = results.get()
+                    if kind == "fed":
+                        continue
+                    if kind == "feeder_failed":
+                        raise RuntimeError("engine reader failed: %r" % (exc,))
+                    if kind == "replica_failed":
+                        alive -= 1
+                        log.warning("replica on gpu %s failed (%r): %d replicas left", gpu, exc, alive)
+                        if gpu in self.config.gpu:
+                            self.config.gpu = [g for g in self.config.gpu if g != gpu]
+                        if alive == 0:
+                            raise RuntimeError("engine: the last replica (gpu %s) failed: %r" % (gpu, exc))
+                        if batch is not None:      # another replica takes the batch
+                            batch.output = None
+                            threading.Thread(target=put_until_stopped, args=(batches, batch), daemon=True).start()
+                        continue
+                    completed += 1
+                    if t_first is None:
+                        t_first, lines_at_first = time.time(), len(batch.index)
+                    for num_line, line_data, output in batch.results():
+                        if num_line in window or num_line < next_line:
+                            raise RuntimeError("Line Index {} is written twice!".format(num_line))
+                        window[num_line] = self.output_line(line_data, output)
+                    while next_line in window:
+                        f.write(window.pop(next_line) + '\n')
+                        next_line += 1
+                    if len(window) > config.alert_size:
+                        pybert.reader_flush(reader)    # too many lines wait for a slow bucket
+                if window:
+                    raise RuntimeError("%d lines never received their predecessors" % len(window))
+        except BaseException as e:
+            failure = e
+            raise
+        finally:
+            stop.set()
+            for _ in workers:
+                try:
+                    batches.put_nowait(None)
+                except pyqueue.Full:
+                    try:
+                        batches.get_nowait()
+                        batches.put_nowait(None)
+                    except (pyqueue.Empty, pyqueue.Full):
+                        pass
+            if failure is None:
+                for t in workers:
+                    t.join()
+            feed.join(5)
+            pybert.reader_destroy(reader)
+        steady = time.time() - t_first if t_first else 0.0
+        self.last_run = {"lines": next_line, "replicas_left": alive, "steady_seconds": steady,
+                         "steady_lines_per_s": (next_line - lines_at_first) / steady if steady > 0 else 0.0}
+        log.info("engine (threads): %d lines written; %.0f lines/s from the first finished batch on (%d replicas)",
+                 next_line, self.last_run["steady_lines_per_s"], alive)
 
     def _run_once(self, input_file, output_file, start_line, offset=0):
         self._init()

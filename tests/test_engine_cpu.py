@@ -288,3 +288,103 @@ def test_native_batcher_rejects_bad_arguments():
     assert pybert.batcher_pop(b, idx, *out) == 1 and pybert.batcher_pop(b, idx, *out) == 0
     assert pybert.batcher_pending(b) == 0
     pybert.batcher_destroy(b)
+
+
+# ---------------------------------------------------------------- one process, one thread per replica
+def _word_vocab(tmp_path):
+    words = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]"] + ["w%d" % i for i in range(200)]
+    path = tmp_path / "vocab.txt"
+    path.write_text("\n".join(words) + "\n", encoding="utf-8")
+    return str(path), words
+
+
+def _text_lines(path, n_lines, words, seed=3):
+    rng = np.random.default_rng(seed)
+    lines = []
+    for _ in range(n_lines):
+        a = " ".join(words[5 + int(x)] for x in rng.integers(0, 200, int(rng.integers(1, 30))))
+        b = " ".join(words[5 + int(x)] for x in rng.integers(0, 200, int(rng.integers(0, 30))))
+        lines.append(a + ("\t" + b if b else ""))
+    with open(path, "w", encoding="utf-8") as f:
+        f.write("\n".join(lines) + "\n")
+    return lines
+
+
+class FlakyReplica(FakeReplica):
+    """gpu 1 cannot load its model; gpu 2 fails at its third batch: exceptions, not crashes."""
+    def __init__(self, id_gpu, config):
+        super().__init__(id_gpu, config)
+        self.calls = 0
+        if id_gpu == 1:
+            raise RuntimeError("no such device")
+
+    def encode(self, tensor):
+        self.calls += 1
+        if self.id_gpu == 2 and self.calls == 3:
+            raise RuntimeError("replica lost")
+        return super().encode(tensor)
+
+
+@pytest.mark.parametrize("replica,gpus,left", [(FakeReplica, [0, 1, 2, 3], [0, 1, 2, 3]), (FlakyReplica, [0, 1, 2], [0]),
+                                               (FakeReplica, [5], [5])])
+def test_engine_thread_mode(tmp_path, replica, gpus, left):
+    """replica_mode "thread": native reader -> one thread per replica -> writer, all in this process.
+    Every line comes out once, in order, with what the replica computes for its own tokens, also
+    when a replica fails to start and another fails in mid-run (their batches go to the survivors)."""
+    from cudabert_b200.tokenizer import Tokenlizer
+    vocab, words = _word_vocab(tmp_path)
+    src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
+    lines = _text_lines(src, 700, words)
+    cfg = _config(gpus)
+    cfg.replica_mode = "thread"
+    cfg.alert_size = 64            # also exercises the flush request
+    tok = Tokenlizer(vocab)
+    eng = Engine(cfg)
+    eng.set_cuda_model(replica)
+    eng.set_finetune_layer(Head)
+    eng.set_tokenlizer_function(tok)
+    eng.set_output_function(output_line)
+    eng.run(src, dst)
+    assert cfg.gpu == left
+    out = open(dst, encoding="utf-8").read().splitlines()
+    assert len(out) == len(lines)
+    for i, (raw, got) in enumerate(zip(lines, out)):
+        _, raw_line, ids, mask, _ = tok(MAX_SEQ, raw, i)
+        assert got == "%s\t%d\t%d" % (raw_line, int((ids * mask).sum()), int(mask.sum()))
+
+
+def test_engine_thread_mode_stops_when_no_replica_is_left(tmp_path):
+    from cudabert_b200.tokenizer import Tokenlizer
+    vocab, words = _word_vocab(tmp_path)
+    src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
+    _text_lines(src, 200, words)
+    cfg = _config([1])
+    cfg.replica_mode = "thread"
+    eng = Engine(cfg)
+    eng.set_cuda_model(FlakyReplica)
+    eng.set_finetune_layer(Head)
+    eng.set_tokenlizer_function(Tokenlizer(vocab))
+    eng.set_output_function(output_line)
+    with pytest.raises(RuntimeError, match="last replica"):
+        eng.run(src, dst)
+
+
+def test_engine_mode_selection(tmp_path):
+    """Threads need the native reader (a Python tokenizer would hold the interpreter lock); "auto"
+    takes them from three replicas on."""
+    from cudabert_b200.tokenizer import Tokenlizer
+    vocab, _ = _word_vocab(tmp_path)
+    eng = Engine(_config([0, 1, 2]))
+    eng.set_tokenlizer_function(tokenize)
+    assert not eng._wants_threads()
+    eng.config.replica_mode = "thread"
+    with pytest.raises(ValueError):
+        eng._wants_threads()
+    eng.config.replica_mode = "auto"
+    eng.set_tokenlizer_function(Tokenlizer(vocab))
+    assert eng._wants_threads()
+    eng.config.gpu = [0, 1]
+    assert not eng._wants_threads()
+    eng.config.replica_mode = "process"
+    eng.config.gpu = [0, 1, 2, 3]
+    assert not eng._wants_threads()

@@ -117,3 +117,49 @@ def test_replica_pool_in_one_process(weight_dirs, gpus):
     finally:
         pool.close()
         single.close()
+
+
+@pytest.mark.parametrize("gpus", [[0], [0, 0], [0, 1]])
+def test_engine_thread_mode_matches_direct_calls(tmp_path, weight_dirs, gpus):
+    """replica_mode "thread": native reader and tokenizer, one thread per replica, writer, all in this
+    process (two replicas may share a GPU).  Every output line carries what a direct call on that
+    line alone returns."""
+    import torch
+    from cudabert_b200.tokenizer import Tokenlizer
+    if torch.cuda.device_count() <= max(gpus):
+        pytest.skip("needs %d GPUs" % (max(gpus) + 1))
+    words = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]"] + ["w%d" % i for i in range(1200)]
+    vocab = tmp_path / "vocab.txt"
+    vocab.write_text("\n".join(words) + "\n", encoding="utf-8")
+    rng = np.random.default_rng(5)
+    lines = []
+    for _ in range(300):
+        a = " ".join(words[5 + int(x)] for x in rng.integers(0, 1200, int(rng.integers(1, 20))))
+        b = " ".join(words[5 + int(x)] for x in rng.integers(0, 1200, int(rng.integers(1, 20))))
+        lines.append(a + "\t" + b)
+    src, dst = str(tmp_path / "in.tsv"), str(tmp_path / "out.tsv")
+    with open(src, "w", encoding="utf-8") as f:
+        f.write("\n".join(lines) + "\n")
+    cfg = _config(gpus, weight_dirs("base_affine"))
+    cfg.replica_mode = "thread"
+    tok = Tokenlizer(str(vocab))
+    eng = Engine(cfg)
+    eng.set_cuda_model(Cuda_BERT)
+    eng.set_finetune_layer(Head)
+    eng.set_tokenlizer_function(tok)
+    eng.set_output_function(output_line)
+    eng.run(src, dst)
+    out = open(dst, encoding="utf-8").read().splitlines()
+    assert len(out) == len(lines)
+    direct = Cuda_BERT(0, cfg)
+    try:
+        for i in list(range(0, 300, 11)) + [299]:
+            _, raw, ids, mask, seg = tok(MAX_SEQ, lines[i], i)
+            n = int(mask.sum())
+            want = direct.encode([ids[None, :n], seg[None, :n], mask[None, :n]])[0, :N_OUT]
+            raw_out, vals = out[i].rsplit("\t", 1)
+            assert raw_out == raw
+            got = np.array([float(v) for v in vals.split()], np.float32)
+            np.testing.assert_allclose(got, want, rtol=2e-6, atol=1e-7)
+    finally:
+        direct.close()
