@@ -8,7 +8,10 @@
 //   raw text kept for the writer = the same fields joined by tabs again.
 // Lines reach the buckets in slightly shuffled order (whichever thread finishes first), which changes
 // nothing downstream: batches still leave by smallest first line number and the writer restores
-// the input order.  Unlike Python's text mode, only '\n' ends a line (a lone '\r' does not).
+// the input order.  Lines end as in Python's text mode (universal newlines): at "\n", at "\r\n" and at
+// a lone "\r", so both readers number the lines of any file alike.  A line the tokenizer or the
+// buckets refuse is counted and stops the stream (cudabert_reader_next returns -1) instead of
+// leaving a hole in the line numbers that the writer would only notice at the end.
 #include "../../include/cudabert.h"
 
 #include <condition_variable>
@@ -69,24 +72,37 @@ struct Reader {
   int threads_running = 0;
   bool stop = false;
   long long lines_read = 0;
+  long long rejected = 0, first_rejected = -1;
+
+  // Next line of the file without its terminator ("\n", "\r\n" or a lone "\r") and without NUL
+  // bytes; false at the end of the file.  Called under file_mu.
+  bool read_line(std::string& line) {
+    line.clear();
+    int c = getc_unlocked(file);
+    if (c == EOF) return false;
+    for (; c != EOF; c = getc_unlocked(file)) {
+      if (c == '\n') break;
+      if (c == '\r') {
+        const int next = getc_unlocked(file);
+        if (next != '\n' && next != EOF) ungetc(next, file);
+        break;
+      }
+      if (c != '\0') line.push_back(static_cast<char>(c));
+    }
+    return true;
+  }
 
   std::vector<std::thread> threads;
 
   void work() {
     std::vector<int> ids(max_seq), mask(max_seq), seg(max_seq);
-    char* buf = nullptr;
-    size_t cap = 0;
+    std::string line;
     for (;;) {
       long long index;
-      std::string line;
       {
         std::lock_guard<std::mutex> lk(file_mu);
-        const ssize_t n = getline(&buf, &cap, file);
-        if (n < 0) break;
+        if (!read_line(line)) break;
         index = next_index++;
-        line.reserve(static_cast<size_t>(n));
-        for (ssize_t i = 0; i < n; ++i)
-          if (buf[i] != '\0') line.push_back(buf[i]);
       }
       line.resize(rstrip_len(line));
       const size_t tab = line.find('\t');
@@ -101,12 +117,14 @@ struct Reader {
       room.wait(lk, [&] { return stop || static_cast<size_t>(cudabert_batcher_ready(batcher)) < max_ready; });
       if (stop) break;
       if (n_tok >= 0 && cudabert_batcher_put(batcher, index, ids.data(), seg.data(), mask.data(), max_seq) >= 0) {
-        raw[index] = std::move(line);
+        raw[index] = line;
         ++lines_read;
+      } else {
+        if (rejected++ == 0) first_rejected = index;
+        batch_ready.notify_all();
       }
       if (cudabert_batcher_ready(batcher) > 0) batch_ready.notify_all();
     }
-    std::free(buf);
     std::lock_guard<std::mutex> lk(mu);
     if (--threads_running == 0) {
       cudabert_batcher_flush(batcher);  // end of input: the partly filled buckets leave too
@@ -132,11 +150,9 @@ void* cudabert_reader_create(const char* input_path, void* tokenizer, int max_se
     return nullptr;
   }
   {
-    char* buf = nullptr;
-    size_t cap = 0;
+    std::string skipped;
     for (long long i = 0; i < skip_lines; ++i)
-      if (getline(&buf, &cap, r->file) < 0) break;  // fewer lines than asked: nothing left to read
-    std::free(buf);
+      if (!r->read_line(skipped)) break;  // fewer lines than asked: nothing left to read
   }
   r->next_index = first_index;
   r->tokenizer = tokenizer;
@@ -165,7 +181,10 @@ int cudabert_reader_next(void* reader, int* rows, int* seq, long long* first_lin
   Reader* r = static_cast<Reader*>(reader);
   if (!r) return -1;
   std::unique_lock<std::mutex> lk(r->mu);
-  r->batch_ready.wait(lk, [&] { return cudabert_batcher_ready(r->batcher) > 0 || r->threads_running == 0; });
+  r->batch_ready.wait(lk, [&] {
+    return cudabert_batcher_ready(r->batcher) > 0 || r->threads_running == 0 || r->rejected > 0;
+  });
+  if (r->rejected > 0) return -1;  // a line was refused: its number would be missing downstream
   int n_rows = 0, n_seq = 0;
   long long first = 0;
   if (cudabert_batcher_next(r->batcher, &n_rows, &n_seq, &first) != 1) return 0;  // every thread is done and nothing is left
@@ -229,6 +248,14 @@ int cudabert_reader_flush(void* reader) {
   const int n = cudabert_batcher_flush(r->batcher);
   if (n > 0) r->batch_ready.notify_all();
   return n;
+}
+
+long long cudabert_reader_rejected(void* reader, long long* first_index) {
+  Reader* r = static_cast<Reader*>(reader);
+  if (!r) return -1;
+  std::lock_guard<std::mutex> lk(r->mu);
+  if (first_index) *first_index = r->first_rejected;
+  return r->rejected;
 }
 
 long long cudabert_reader_lines(void* reader) {

@@ -175,6 +175,9 @@ reader_raw.restype = _c_ll
 reader_flush = lib.cudabert_reader_flush
 reader_flush.argtypes = [c_void_p]
 reader_flush.restype = c_int
+reader_rejected = lib.cudabert_reader_rejected
+reader_rejected.argtypes = [c_void_p, POINTER(_c_ll)]
+reader_rejected.restype = _c_ll
 reader_lines = lib.cudabert_reader_lines
 reader_lines.argtypes = [c_void_p]
 reader_lines.restype = _c_ll

@@ -355,6 +355,9 @@ class Engine(object):
                 raw = create_string_buffer(int(offsets[-1]) + 1)
                 pybert.reader_raw(reader, raw, int(offsets[-1]))
                 handle.input_queue.put(Batch_Blob(index, raw.raw[:int(offsets[-1])], offsets, tensor))
+            bad = c_longlong(-1)
+            if pybert.reader_rejected(reader, byref(bad)) > 0:
+                raise RuntimeError("native reader: line %d could not be tokenised or bucketed" % bad.value)
             total = pybert.reader_lines(reader)
         finally:
             stop.set()
@@ -527,6 +530,9 @@ class Engine(object):
                     state["issued"] += 1
                     if not put_until_stopped(batches, Batch_Blob(index, raw.raw[:int(offsets[-1])], offsets, tensor)):
                         return
+                bad = c_longlong(-1)
+                if pybert.reader_rejected(reader, byref(bad)) > 0:
+                    raise RuntimeError("line %d could not be tokenised or bucketed" % bad.value)
                 state["fed"] = True
                 results.put(("fed", None, None, None))
             except BaseException as e:       # the writer must not wait for batches that will never come

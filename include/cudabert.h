@@ -184,7 +184,9 @@ CUDABERT_API void* cudabert_reader_create(const char* input_path, void* tokenize
 CUDABERT_API void cudabert_reader_destroy(void* reader);
 /* Blocks until a batch is ready and takes it out of the buckets (1: its shape in rows / seq /
  * first_line; the batch waits inside the reader for cudabert_reader_pop), or until the file is
- * finished and every batch has been taken (0). */
+ * finished and every batch has been taken (0).  -1: a line was refused by the tokenizer or the buckets
+ * (cudabert_reader_rejected says which); the stream ends there.  Lines end at "\n", "\r\n" or a lone
+ * "\r", as in Python's text mode. */
 CUDABERT_API int cudabert_reader_next(void* reader, int* rows, int* seq, long long* first_line);
 /* Copies that batch out: line_index[rows], ids / seg / mask [rows, seq], raw_offsets[rows + 1] = where each
  * line's raw text (the line without NULs and trailing white space) starts in the text that
@@ -199,6 +201,8 @@ CUDABERT_API long long cudabert_reader_raw(void* reader, char* buf, long long ca
 CUDABERT_API int cudabert_reader_flush(void* reader);
 /* Lines tokenised so far. */
 CUDABERT_API long long cudabert_reader_lines(void* reader);
+/* Lines refused so far; *first_index (may be NULL) receives the number of the first one, -1 if none. */
+CUDABERT_API long long cudabert_reader_rejected(void* reader, long long* first_index);
 
 /* ---- single kernels on device buffers (stream 0, synchronous), for per-kernel parity tests ---- */
 

@@ -131,3 +131,38 @@ def test_engine_with_native_reader(tmp_path, golden, threads, native):
     for k, line in enumerate(body):
         _, raw, ids, mask, _ = fn(cfg.max_seq_length, line, k)
         assert out[k] == "%s\t%d\t%d" % (raw, int((ids * mask).sum()), int(mask.sum())), k
+
+
+def test_native_reader_ends_lines_like_python_text_mode(tmp_path, golden):
+    """"\\n", "\\r\\n" and a lone "\\r" all end a line, so the native reader numbers the lines of a file
+    exactly as the Python reader (text mode, universal newlines) does."""
+    from ctypes import byref, c_int, c_longlong, create_string_buffer
+    from cudabert_b200.cuda_bert import pybert
+    data = b"alpha one\tbeta\nsecond line\r\nthird\rfourth \t x\n\nlast without newline"
+    path = tmp_path / "mixed.tsv"
+    path.write_bytes(data)
+    with open(path, "r", encoding="utf-8") as f:
+        want = ["\t".join(l.replace("\0", "").rstrip().split("\t")) for l in f]
+    assert len(want) == 6
+    tok = Tokenlizer(golden["vocab_file"])
+    tok._native()
+    bounds = np.array([0, 8, 32], np.int32)
+    reader = pybert.reader_create(str(path).encode(), tok._handle, 32, bounds, 3, 4, 2, 0, 0)
+    assert reader
+    got = {}
+    rows, seq, first = c_int(0), c_int(0), c_longlong(0)
+    try:
+        while pybert.reader_next(reader, byref(rows), byref(seq), byref(first)) == 1:
+            index = np.empty(rows.value, np.int64)
+            offsets = np.empty(rows.value + 1, np.int64)
+            t = [np.empty((rows.value, seq.value), np.int32) for _ in range(3)]
+            assert pybert.reader_pop(reader, index, t[0], t[1], t[2], offsets) == rows.value
+            raw = create_string_buffer(int(offsets[-1]) + 1)
+            pybert.reader_raw(reader, raw, int(offsets[-1]))
+            for i, n in enumerate(index.tolist()):
+                got[n] = raw.raw[offsets[i]:offsets[i + 1]].decode("utf-8")
+        assert pybert.reader_rejected(reader, None) == 0
+        assert pybert.reader_lines(reader) == 6
+    finally:
+        pybert.reader_destroy(reader)
+    assert [got[i] for i in range(6)] == want
