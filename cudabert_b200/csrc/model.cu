@@ -5,6 +5,8 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "npy.h"
 
 namespace cb {
@@ -86,6 +88,8 @@ bool Model::init(bool large, int gpu, int max_batch, int max_seq, const std::str
     // 1024 x 64 batches of BERT-large 25.2 against 28.9 ms per pass).  Default: the GEMM reads the E4M3 bytes.
     const char* f8 = std::getenv("CUDABERT_FP8_OPERAND");
     fp8_widened_ = f8 && f8[0] == 'w';
+    const char* nv = std::getenv("CUDABERT_NVTX");
+    nvtx_ = nv && nv[0] == '1';
   }
   esize_ = (precision == PREC_FP32) ? 4 : 2;
   if (!check(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking), "cudaStreamCreate")) return false;
@@ -374,7 +378,16 @@ void Model::count(int kclass, int n) {
     prof_n_[kclass] += profiling_ ? n : 0;
   }
 }
+namespace {
+const char* const kKernelClassNames[KC_COUNT] = {"embed_layernorm", "gemm_qkv",  "attention",   "gemm_attn_out", "layernorm",
+                                                 "gemm_ffn1",       "gemm_ffn2", "gemm_pooler", "other"};
+}  // namespace
+
+// CUDABERT_NVTX=1: an NVTX range around every forward pass and, for passes enqueued kernel by kernel
+// (not graph replays), around each kernel's launch, named after its class.  The header-only NVTX
+// does nothing unless a tool is attached.
 void Model::prof_begin(int kclass) {
+  if (nvtx_) nvtxRangePushA(kKernelClassNames[kclass]);
   if (!profiling_) return;
   if (ev_used_ + 2 > ev_.size()) {
     for (int i = 0; i < 64; ++i) {
@@ -387,6 +400,7 @@ void Model::prof_begin(int kclass) {
   cudaEventRecord(ev_[ev_used_], stream_);
 }
 void Model::prof_end(int) {
+  if (nvtx_) nvtxRangePop();
   if (!profiling_) return;
   cudaEventRecord(ev_[ev_used_ + 1], stream_);
   ev_used_ += 2;
@@ -450,6 +464,13 @@ bool Model::forward_device(const int* d_ids, const int* d_seg, const int* d_mask
   if (want_probs && classes_ == 0) return fail(1, "the model directory has no classifier_kernel/bias");
   if (!check(cudaSetDevice(dev_), "cudaSetDevice")) return false;
   if (!ensure_capacity(B, S, want_hidden_f32)) return false;
+  struct NvtxScope {
+    bool on;
+    NvtxScope(bool enabled, int b, int s) : on(enabled) {
+      if (on) nvtxRangePushA(("cudabert forward " + std::to_string(b) + " x " + std::to_string(s)).c_str());
+    }
+    ~NvtxScope() { if (on) nvtxRangePop(); }
+  } nvtx_scope(nvtx_, B, S);
   if (!graphs_enabled_ || profiling_) return enqueue_forward(d_ids, d_seg, d_mask, B, S, want_hidden_f32, want_probs);
 
   // The first passes with a given argument set run kernel by kernel (the very first also does every

@@ -133,6 +133,7 @@ class Model {
   unsigned long long graph_tick_ = 0;
   std::map<GraphKey, GraphEntry> graphs_;
   bool graphs_enabled_ = true;
+  bool nvtx_ = false;         // CUDABERT_NVTX=1: NVTX ranges around passes and launches
   bool fp8_widened_ = false;  // FP8 mode: weights expanded to fp16 at load (CUDABERT_FP8_OPERAND=widened)
   bool cls_last_ = true;  // pooler-only passes compute the last layer for the first token of every sequence only
   static constexpr int PDL_MAX_TOKENS = 4096;  // forward passes up to this many token slots use dependent launch

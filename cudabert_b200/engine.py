@@ -306,7 +306,12 @@ class Engine(object):
             packed_batch.drop_tensor()       # the writer wants line numbers, raw lines and outputs only
             handle.output_queue.put(packed_batch)
         handle.output_queue.put(_DONE)
-        self.logger.info("engine_model on gpu %s done: %d lines in %.2f s", id_gpu, total_length, time.time() - start)
+        stats = ""
+        if getattr(model, "model", None) is not None and hasattr(getattr(model, "_pybert", None), "graph_replays"):
+            stats = "; CUDA graphs: %d captured, %d passes replayed" % (model._pybert.graph_captures(model.model),
+                                                                       model._pybert.graph_replays(model.model))
+        self.logger.info("engine_model on gpu %s done: %d lines in %.2f s%s", id_gpu, total_length,
+                         time.time() - start, stats)
 
     def _generate_tagged_line(self, user_output):
         return Tagged_line(
@@ -559,10 +564,16 @@ class Engine(object):
                 done += batch.tensor[0].shape[0]
                 batch.drop_tensor()
                 results.put(("done", gpu, batch, None))
+            stats = ""
+            handle = getattr(model, "model", None)
+            if handle is not None and hasattr(getattr(model, "_pybert", None), "graph_replays"):
+                # a caller whose batch shapes rarely repeat sees few replays: every pass then pays its launches
+                stats = "; CUDA graphs: %d captured, %d passes replayed" % (model._pybert.graph_captures(handle),
+                                                                           model._pybert.graph_replays(handle))
             close = getattr(model, "close", None)
             if close:
                 close()
-            log.info("replica thread on gpu %s done: %d lines in %.2f s", gpu, done, time.time() - t0)
+            log.info("replica thread on gpu %s done: %d lines in %.2f s%s", gpu, done, time.time() - t0, stats)
 
         workers = [threading.Thread(target=replica, args=(g,), daemon=True, name="replica-gpu%s" % g) for g in gpus]
         feed = threading.Thread(target=feeder, daemon=True, name="feeder")

@@ -63,8 +63,10 @@ def test_fp8_mode(models, name, record_property):
         to every dense kernel of 12 / 24 layers) moves the pooler output by 0.10 - 0.25 even when
         everything else is computed in fp32 on the CPU, so no implementation of this weight
         format can meet 5e-2 on these weights.  What is asserted is that the CUDA path adds
-        nothing on top: its distance to the fp32 path is within 1.25x + 0.02 of the distance the
-        CPU oracle shows for the same quantisation.  Both numbers are recorded."""
+        nothing on top: its distance to the fp32 path is at most the distance the CPU oracle shows
+        for the same quantisation plus the two kernel tolerances that separate them (2e-2 for the
+        16-bit kernels against the oracle, 1e-3 for the fp32 path against the golden output).  All
+        three numbers are recorded."""
     wname = cases.CASES[name]["weights"]
     ids, seg, mask = cases.case_inputs(name)
     p8 = models(wname, "fp8").encode([ids, seg, mask])
@@ -79,7 +81,7 @@ def test_fp8_mode(models, name, record_property):
     record_property("fp8_inherent_quantisation_error", inherent)
     print("fp8 %s: vs quantised-weight oracle %.4f, vs fp32 path %.4f, inherent %.4f" % (name, kernel_err, vs_fp32, inherent))
     assert kernel_err <= BF16_REL
-    assert vs_fp32 <= 1.25 * inherent + 0.02
+    assert vs_fp32 <= inherent + BF16_REL + FP32_MAXABS / max(float(np.abs(p32).max()), 1e-6)
 
 
 @pytest.mark.parametrize("name,precision", [("c1_small", "bf16"), ("c0", "fp32"), ("c4_small", "fp8")])
