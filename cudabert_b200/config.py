@@ -1,6 +1,6 @@
 """Engine configuration.  ``Engin_Config`` offers the attribute names callers of the reference set
 (config.py:3-39) so that their scripts run unchanged; defaults and their meaning are listed in
-``_DEFAULTS`` below.  Additions: ``precision``, ``native_batcher``, ``native_reader``, ``reader_threads``, ``replica_mode``,
+``_DEFAULTS`` below.  Additions: ``precision``, ``weight_cache_pth``, ``native_batcher``, ``native_reader``, ``reader_threads``, ``replica_mode``,
 ``resume_without_dead_gpu`` and ``mp_start_method``."""
 import os
 
@@ -21,6 +21,8 @@ _DEFAULTS = {
     "model_npy_pth": ("./model_npy", "directory of .npy weights: the encoder, the pooler, the fine-tune head"),
     "cubert_pth": (os.path.join(_PACKAGE_DIR, "cuda_bert"), "directory that holds pybert.py and libcudaBERT.so"),
     "precision": (None, '"fp32", "bf16" or "fp8"; None = environment CUDABERT_PRECISION, else bf16'),
+    "weight_cache_pth": (None, "directory for device-ready copies of the weights (one file per model directory and mode), "
+                               "written at the first load and read by later ones; None = environment CUDABERT_WEIGHT_CACHE, else no cache"),
     "native_batcher": (True, "bucket and trim in the library's batcher; False = the Python classes"),
     "native_reader": (True, "with a tokenizer.Tokenlizer as tokenizer function: read, tokenise and bucket in native threads"),
     "reader_threads": (0, "tokenizer threads of the native reader; 0 = up to 16, one core left free"),

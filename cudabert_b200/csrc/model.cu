@@ -1,5 +1,8 @@
 #include "model.h"
 
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -35,7 +38,7 @@ bool Model::check(cudaError_t e, const char* what) {
 Model::~Model() {
   cudaSetDevice(dev_);
   if (stream_) cudaStreamSynchronize(stream_);
-  for (void* p : owned_) cudaFree(p);
+  for (const Owned& o : owned_) cudaFree(o.p);
   if (arena_) cudaFree(arena_);
   if (stage_f32_) cudaFree(stage_f32_);
   if (hidden_unpacked_) cudaFree(hidden_unpacked_);
@@ -120,7 +123,21 @@ const std::string* Model::find_file(const std::vector<std::string>& keys) const 
   return nullptr;
 }
 
+bool Model::dev_alloc(void** p, size_t bytes) {
+  if (from_cache_) {
+    // the sizes were recorded when the cache was written; a difference means a stale or foreign file
+    const size_t i = owned_.size();
+    if (i >= cache_sizes_.size()) return fail(3, "weight cache " + cache_path_ + " does not match this model: delete it");
+    if (bytes == 0) bytes = cache_sizes_[i];
+    if (bytes != cache_sizes_[i]) return fail(3, "weight cache " + cache_path_ + " does not match this model: delete it");
+  }
+  if (!check(cudaMalloc(p, bytes), "cudaMalloc(weights)")) return false;
+  owned_.push_back(Owned{*p, bytes});
+  return true;
+}
+
 bool Model::read_tensor(const std::vector<std::string>& keys, size_t expect, NpyArray* arr) {
+  if (from_cache_) return find_file(keys) != nullptr || fail(3, "weight cache: a tensor's file has disappeared");
   const std::string* f = find_file(keys);
   if (!f) {
     std::string k;
@@ -147,10 +164,8 @@ bool Model::read_tensor(const std::vector<std::string>& keys, size_t expect, Npy
 bool Model::upload_vec(const std::vector<std::string>& keys, size_t n, float** dst) {
   NpyArray a;
   if (!read_tensor(keys, n, &a)) return false;
-  if (!*dst) {
-    if (!check(cudaMalloc(dst, n * sizeof(float)), "cudaMalloc")) return false;
-    owned_.push_back(*dst);
-  }
+  if (!*dst && !dev_alloc(reinterpret_cast<void**>(dst), n * sizeof(float))) return false;
+  if (from_cache_) return true;
   if (!check(cudaMemcpyAsync(*dst, stage_f32_, n * sizeof(float), cudaMemcpyDeviceToDevice, stream_), "copy"))
     return false;
   return check(cudaStreamSynchronize(stream_), "copy");
@@ -159,12 +174,16 @@ bool Model::upload_vec(const std::vector<std::string>& keys, size_t n, float** d
 bool Model::upload_table(const std::vector<std::string>& keys, size_t min_rows, float** dst, int* rows_out) {
   NpyArray a;
   if (!read_tensor(keys, 0, &a)) return false;
+  if (from_cache_) {  // the size comes from the cache's record; the shape was checked when it was written
+    if (!dev_alloc(reinterpret_cast<void**>(dst), 0)) return false;
+    if (rows_out) *rows_out = static_cast<int>(owned_.back().bytes / (sizeof(float) * H_));
+    return true;
+  }
   if (a.shape.size() != 2 || a.shape[1] != static_cast<size_t>(H_) || a.shape[0] < min_rows)
     return fail(3, "embedding table has the wrong shape");
   if (rows_out) *rows_out = static_cast<int>(a.shape[0]);
   const size_t n = a.numel();
-  if (!check(cudaMalloc(dst, n * sizeof(float)), "cudaMalloc")) return false;
-  owned_.push_back(*dst);
+  if (!dev_alloc(reinterpret_cast<void**>(dst), n * sizeof(float))) return false;
   if (!check(cudaMemcpyAsync(*dst, stage_f32_, n * 4, cudaMemcpyDeviceToDevice, stream_), "copy")) return false;
   return check(cudaStreamSynchronize(stream_), "table copy");
 }
@@ -176,23 +195,17 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
     d->K = K;
     d->N = n_total;
     const size_t elems = static_cast<size_t>(K) * n_total;
-    if (prec != PREC_FP8 || fp8_widened_) {
-      if (!check(cudaMalloc(&d->w, elems * esize), "cudaMalloc")) return false;
-      owned_.push_back(d->w);
-    }
-    if (!check(cudaMalloc(&d->bias, n_total * sizeof(float)), "cudaMalloc")) return false;
-    owned_.push_back(d->bias);
+    if ((prec != PREC_FP8 || fp8_widened_) && !dev_alloc(&d->w, elems * esize)) return false;
+    if (!dev_alloc(reinterpret_cast<void**>(&d->bias), n_total * sizeof(float))) return false;
     if (prec == PREC_FP8) {
-      if (!fp8_widened_) {  // the E4M3 bytes are the only copy of the weights; the GEMM reads them
-        if (!check(cudaMalloc(&d->w_fp8, elems), "cudaMalloc")) return false;
-        owned_.push_back(d->w_fp8);
-      }
-      if (!check(cudaMalloc(&d->colscale, n_total * sizeof(float)), "cudaMalloc")) return false;
-      owned_.push_back(d->colscale);
+      // without widening the E4M3 bytes are the only copy of the weights; the GEMM reads them
+      if (!fp8_widened_ && !dev_alloc(reinterpret_cast<void**>(&d->w_fp8), elems)) return false;
+      if (!dev_alloc(reinterpret_cast<void**>(&d->colscale), n_total * sizeof(float))) return false;
     }
   }
   NpyArray a;
   if (!read_tensor(keys_kernel, static_cast<size_t>(K) * N, &a)) return false;
+  if (from_cache_) return true;
   if (a.shape.size() != 2 || a.shape[0] != static_cast<size_t>(K) || a.shape[1] != static_cast<size_t>(N))
     return fail(3, "dense kernel is not stored [in, out]");
   if (prec == PREC_FP32) {
@@ -242,6 +255,7 @@ bool Model::load_weights(const std::string& dir) {
   std::string err;
   if (!list_npy_files(dir, &files_, &err)) return fail(3, err);
   if (files_.empty()) return fail(3, "no .npy files in " + dir);
+  from_cache_ = cache_probe();
   const size_t H = H_;
   // embeddings: key pairs as in ops/embedding.cuh:12-20
   if (!upload_table({"embeddings", "word"}, 2, &word_, &vocab_rows_)) return false;
@@ -281,14 +295,24 @@ bool Model::load_weights(const std::string& dir) {
   if (find_file({"classifier_kernel"}) && find_file({"classifier_bias"})) {
     NpyArray k;
     if (!read_tensor({"classifier_kernel"}, 0, &k)) return false;
-    if (k.shape.size() == 2 && k.shape[0] == H && k.shape[1] >= 1 && k.shape[1] <= MAX_CLASSES) {
+    if (from_cache_) {
+      if (owned_.size() < cache_sizes_.size()) {  // the cache holds a head: kernel [H, C], then bias [C]
+        if (!dev_alloc(reinterpret_cast<void**>(&cls_w_), 0)) return false;
+        classes_ = static_cast<int>(owned_.back().bytes / (sizeof(float) * H));
+        if (!upload_vec({"classifier_bias"}, classes_, &cls_b_)) return false;
+      }
+    } else if (k.shape.size() == 2 && k.shape[0] == H && k.shape[1] >= 1 && k.shape[1] <= MAX_CLASSES) {
       classes_ = static_cast<int>(k.shape[1]);
-      if (!check(cudaMalloc(&cls_w_, k.numel() * sizeof(float)), "cudaMalloc")) return false;
-      owned_.push_back(cls_w_);
+      if (!dev_alloc(reinterpret_cast<void**>(&cls_w_), k.numel() * sizeof(float))) return false;
       if (!check(cudaMemcpy(cls_w_, stage_f32_, k.numel() * sizeof(float), cudaMemcpyDeviceToDevice), "copy"))
         return false;
       if (!upload_vec({"classifier_bias"}, classes_, &cls_b_)) return false;
     }
+  }
+  if (from_cache_) {
+    if (!cache_fill()) return false;
+  } else if (!cache_path_.empty()) {
+    cache_write();
   }
   if (stage_f32_) {
     cudaFree(stage_f32_);
@@ -296,6 +320,102 @@ bool Model::load_weights(const std::string& dir) {
     stage_elems_ = 0;
   }
   return true;
+}
+
+// ------------------------------------------------------------------ weight cache
+namespace {
+constexpr char CACHE_MAGIC[8] = {'C', 'B', 'W', 'C', 'A', 'C', 'H', '2'};
+
+uint64_t fnv1a(const std::string& s) {
+  uint64_t h = 1469598103934665603ull;
+  for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
+  return h;
+}
+}  // namespace
+
+bool Model::cache_probe() {
+  cache_path_.clear();
+  cache_sizes_.clear();
+  const char* e = std::getenv("CUDABERT_WEIGHT_CACHE");
+  if (!e || !*e) return false;
+  cache_dir_ = e;
+  // what the device-ready weights depend on: every file of the directory and how this handle lays them out
+  std::string sig = "layout 2|large " + std::to_string(large_) + "|prec " + std::to_string(prec_) + "|layers " +
+                    std::to_string(L_) + "|fp8 widened " + std::to_string(fp8_widened_) + "|scale " +
+                    std::to_string(W_CONTAINER_SCALE) + "\n";
+  for (const std::string& f : files_) {
+    struct stat st;
+    if (stat((dir_ + "/" + f).c_str(), &st) != 0) return false;
+    sig += f + ":" + std::to_string(static_cast<long long>(st.st_size)) + ":" +
+           std::to_string(static_cast<long long>(st.st_mtim.tv_sec)) + "." + std::to_string(st.st_mtim.tv_nsec) + "\n";
+  }
+  cache_signature_ = sig;
+  char name[64];
+  std::snprintf(name, sizeof(name), "/cudabert_%016llx.weights", static_cast<unsigned long long>(fnv1a(dir_ + "\n" + sig)));
+  cache_path_ = cache_dir_ + name;
+  std::FILE* fp = std::fopen(cache_path_.c_str(), "rb");
+  if (!fp) return false;
+  bool ok = false;
+  char magic[8];
+  uint64_t sig_len = 0, n = 0;
+  if (std::fread(magic, 1, 8, fp) == 8 && std::memcmp(magic, CACHE_MAGIC, 8) == 0 &&
+      std::fread(&sig_len, sizeof(sig_len), 1, fp) == 1 && sig_len == sig.size()) {
+    std::string stored(sig_len, '\0');
+    if (std::fread(&stored[0], 1, sig_len, fp) == sig_len && stored == sig &&
+        std::fread(&n, sizeof(n), 1, fp) == 1 && n > 0 && n < (1u << 20)) {
+      std::vector<uint64_t> sizes(n);
+      if (std::fread(sizes.data(), sizeof(uint64_t), n, fp) == n) {
+        cache_sizes_.assign(sizes.begin(), sizes.end());
+        ok = true;
+      }
+    }
+  }
+  std::fclose(fp);
+  if (!ok) cache_sizes_.clear();
+  return ok;
+}
+
+bool Model::cache_fill() {
+  if (owned_.size() != cache_sizes_.size())
+    return fail(3, "weight cache " + cache_path_ + " does not match this model: delete it");
+  std::FILE* fp = std::fopen(cache_path_.c_str(), "rb");
+  if (!fp) return fail(3, "cannot reopen weight cache " + cache_path_);
+  const long header = 8 + 8 + static_cast<long>(cache_signature_.size()) + 8 + 8 * static_cast<long>(cache_sizes_.size());
+  bool ok = std::fseek(fp, header, SEEK_SET) == 0;
+  size_t biggest = 0;
+  for (const Owned& o : owned_) biggest = std::max(biggest, o.bytes);
+  void* host = nullptr;
+  if (ok && cudaMallocHost(&host, biggest) != cudaSuccess) { ok = false; host = nullptr; }
+  for (size_t i = 0; ok && i < owned_.size(); ++i) {
+    ok = std::fread(host, 1, owned_[i].bytes, fp) == owned_[i].bytes &&
+         cudaMemcpyAsync(owned_[i].p, host, owned_[i].bytes, cudaMemcpyHostToDevice, stream_) == cudaSuccess &&
+         cudaStreamSynchronize(stream_) == cudaSuccess;
+  }
+  if (host) cudaFreeHost(host);
+  std::fclose(fp);
+  return ok || fail(3, "weight cache " + cache_path_ + " is truncated or unreadable: delete it");
+}
+
+void Model::cache_write() {
+  // written under a temporary name and renamed, so that a reader never sees half a file
+  const std::string tmp = cache_path_ + ".tmp" + std::to_string(static_cast<long long>(getpid()));
+  std::FILE* fp = std::fopen(tmp.c_str(), "wb");
+  if (!fp) return;
+  const uint64_t sig_len = cache_signature_.size(), n = owned_.size();
+  bool ok = std::fwrite(CACHE_MAGIC, 1, 8, fp) == 8 && std::fwrite(&sig_len, sizeof(sig_len), 1, fp) == 1 &&
+            std::fwrite(cache_signature_.data(), 1, sig_len, fp) == sig_len && std::fwrite(&n, sizeof(n), 1, fp) == 1;
+  size_t biggest = 0;
+  for (const Owned& o : owned_) {
+    const uint64_t b = o.bytes;
+    ok = ok && std::fwrite(&b, sizeof(b), 1, fp) == 1;
+    biggest = std::max(biggest, o.bytes);
+  }
+  std::vector<char> host(biggest);
+  for (size_t i = 0; ok && i < owned_.size(); ++i)
+    ok = cudaMemcpy(host.data(), owned_[i].p, owned_[i].bytes, cudaMemcpyDeviceToHost) == cudaSuccess &&
+         std::fwrite(host.data(), 1, owned_[i].bytes, fp) == owned_[i].bytes;
+  ok = (std::fclose(fp) == 0) && ok;
+  if (!ok || std::rename(tmp.c_str(), cache_path_.c_str()) != 0) std::remove(tmp.c_str());
 }
 
 // ------------------------------------------------------------------ arena

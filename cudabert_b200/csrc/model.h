@@ -155,7 +155,21 @@ class Model {
   float *cls_w_ = nullptr, *cls_b_ = nullptr;
   float* stage_f32_ = nullptr;  // device staging for load-time conversion
   size_t stage_elems_ = 0;
-  std::vector<void*> owned_;    // every cudaMalloc'ed weight pointer
+  struct Owned { void* p; size_t bytes; };
+  std::vector<Owned> owned_;    // every cudaMalloc'ed weight buffer, in allocation order
+  bool dev_alloc(void** p, size_t bytes);  // cudaMalloc + owned_
+
+  // Weight cache (CUDABERT_WEIGHT_CACHE=<directory>): the device-ready weights of one (model directory,
+  // mode) pair as one file, written after the first load and read back by later ones instead of
+  // parsing, uploading and transposing some four hundred .npy files.  A cache file is used only if
+  // its recorded signature (every .npy file's name, size and modification time, the mode and the
+  // layout version) equals the directory's current one.
+  std::string cache_dir_, cache_path_, cache_signature_;
+  bool from_cache_ = false;             // this load fills the buffers from the cache file
+  std::vector<size_t> cache_sizes_;     // from_cache_: size of every buffer, in allocation order
+  bool cache_probe();                   // sets cache_path_ / cache_signature_; true if a valid file exists
+  bool cache_fill();                    // file -> owned_ buffers
+  void cache_write();                   // owned_ buffers -> file (failures are not errors)
 
   // activation arena
   size_t cap_tokens_ = 0;

@@ -33,6 +33,10 @@ class Cuda_BERT(object):
         else:
             self.hidden_size = 768
 
+        if getattr(config, "weight_cache_pth", None):
+            import os
+            os.makedirs(config.weight_cache_pth, exist_ok=True)
+            os.environ["CUDABERT_WEIGHT_CACHE"] = str(config.weight_cache_pth)   # read by the library at every load
         self.model = self._pybert.load_model(config.is_large, config.model_npy_pth, id_gpu,
                                              config.batch_size, config.max_seq_length,
                                              precision=getattr(config, "precision", None))

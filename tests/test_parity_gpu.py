@@ -173,6 +173,55 @@ def test_full_size_properties(models, cfg, wname, precision):
     assert bert_oracle.rel_err(full[:2], ref) <= BF16_REL
 
 
+@pytest.mark.parametrize("precision", ["bf16", "fp8", "fp32"])
+def test_weight_cache_gives_the_same_model(weight_dirs, tmp_path, monkeypatch, precision):
+    """CUDABERT_WEIGHT_CACHE: the first load writes the device-ready weights as one file, the second
+    reads it instead of the .npy files: same pooler and classifier bits.  A change to any weight file
+    (here: its modification time) makes the old cache file irrelevant and a new one is written."""
+    import os
+    import shutil
+    from cudabert_b200.cuda_bert import pybert
+    src = weight_dirs("base_affine")
+    wdir = str(tmp_path / "weights")
+    shutil.copytree(src, wdir)
+    cache = tmp_path / "cache"
+    cache.mkdir()
+    ids, seg, mask = cases.case_inputs("edge_s17")
+    B, S = ids.shape
+
+    def run():
+        model = pybert.load_model(False, wdir, 0, 0, 0, precision=precision)
+        out = np.zeros((B, pybert.hidden_size(model)), np.float32)
+        probs = np.zeros((B, pybert.num_classes(model)), np.float32)
+        pybert.bert(model, out, ids, seg, B, S, mask)
+        pybert.classify(model, probs, ids, seg, B, S, probs.shape[1], mask)
+        pybert.check(model)
+        pybert.unload_model(model)
+        return out, probs
+
+    plain = run()
+    monkeypatch.setenv("CUDABERT_WEIGHT_CACHE", str(cache))
+    first = run()
+    files = sorted(os.listdir(cache))
+    assert len(files) == 1 and files[0].endswith(".weights")
+    assert os.path.getsize(cache / files[0]) > 100e6 / (1 if precision == "fp32" else 2) * 0.8
+    second = run()
+    assert sorted(os.listdir(cache)) == files
+    for a, b, c in zip(plain, first, second):
+        assert np.array_equal(a, b) and np.array_equal(a, c)
+    victim = os.path.join(wdir, "bert_pooler_dense_bias.npy")
+    os.utime(victim, ns=(1, 1))
+    third = run()
+    assert len(os.listdir(cache)) == 2
+    assert np.array_equal(third[0], plain[0])
+    # a cache file that was cut short is refused with a message, not read
+    newest = max((cache / f for f in os.listdir(cache)), key=os.path.getmtime)
+    with open(newest, "r+b") as f:
+        f.truncate(os.path.getsize(newest) // 2)
+    with pytest.raises(RuntimeError, match="truncated or unreadable"):
+        run()
+
+
 def test_a_device_side_wait_that_runs_out_is_reported_and_survived(models):
     """Every mbarrier wait of the GEMM and attention pipelines is bounded: when it runs out the
     kernel records the site and finishes, and the host reports status 4.  The hook runs that same
