@@ -60,29 +60,32 @@ def _oracle_full_batch(weights, ids, seg, mask, dims):
 
 
 @pytest.mark.skipif(not os.path.exists(REF_LIB), reason="oracle/_ref is not built")
-def test_full_c1_bf16_against_reference_cuda(tmp_path, record_property):
-    """The headline workload at FULL size (BERT-large, 128 x 200, lengths U[16, 200], the benchmark's
-    own weights and first batch): this library's bf16 mode against the reference's CUDA library
-    (fp32, cuBLAS) on the same GPU, all 128 x 1024 pooler outputs in the maximum.
+@pytest.mark.parametrize("cfg", [1, 2, 3])
+def test_full_size_bf16_against_reference_cuda(tmp_path, record_property, cfg):
+    """The bf16-mode workloads at FULL size with the benchmark's own weights and first batch
+    (1: BERT-large 128 x 200, lengths U[16, 200] -- the headline; 2: BERT-base 256 x 128, lengths
+    ~ N(60, 25); 3: BERT-large 32 x 512, every position valid): this library against the reference's
+    CUDA library (fp32, cuBLAS) on the same GPU, every pooler output of the batch in the maximum.
 
     Bar: max|a-b| / max|b| <= 2e-2, asserted with a 10 % margin.  Rounding the dense weights to
-    bf16 -- the mode's weight format -- moves the pooler by 1.66e-2 on this batch when everything
-    else is computed in fp32; that part is measured here on the CPU oracle and recorded, and the
-    rest (this library against the oracle on the SAME rounded weights: what the kernels add) must
-    stay below a quarter of the bar."""
+    bf16 -- the mode's weight format -- alone moves the pooler by 1.66e-2 on the headline batch when
+    everything else is computed in fp32; that part is measured here on the CPU oracle and recorded,
+    and the rest (this library against the oracle on the SAME rounded weights: what the kernels
+    add) must stay below a quarter of the bar."""
     import torch
     from cudabert_b200 import synth
     from cudabert_b200.cuda_bert import pybert
     from oracle import bert_oracle
-    cfg = 1
     wl = synth.CONFIGS[cfg]
-    dims = synth.model_dims(True)
-    weights = synth.make_weights(True, synth.weight_seed(cfg))
+    assert wl["precision"] == "bf16"
+    large = wl["large"]
+    dims = synth.model_dims(large)
+    weights = synth.make_weights(large, synth.weight_seed(cfg))
     ids, seg, mask = synth.make_inputs(synth.input_seed(cfg), wl["batch"], wl["seq"], wl["dist"])
     wdir = str(tmp_path / "w")
     synth.write_weight_dir(wdir, weights)
-    ref = _run_reference(wdir, True, ids, seg, mask, tmp_path)
-    model = pybert.load_model(True, wdir, 0, wl["batch"], wl["seq"], precision="bf16")
+    ref = _run_reference(wdir, large, ids, seg, mask, tmp_path)
+    model = pybert.load_model(large, wdir, 0, wl["batch"], wl["seq"], precision="bf16")
     ours = np.zeros((wl["batch"], dims["hidden"]), np.float32)
     pybert.bert(model, ours, ids, seg, wl["batch"], wl["seq"], mask)
     pybert.check(model)
@@ -96,8 +99,8 @@ def test_full_c1_bf16_against_reference_cuda(tmp_path, record_property):
     fro = float(np.linalg.norm(ours - ref) / np.linalg.norm(ref))
     for k, v in (("vs_reference_cuda", vs_ref), ("bf16_weights_alone", weight_format), ("kernels_only", kernels_only),
                  ("vs_reference_cuda_frobenius", fro)):
-        record_property("full_c1_" + k, v)
-    print("full C1 bf16: vs reference CUDA library %.4f (Frobenius %.4f); bf16 weights alone %.4f; kernels only %.4f"
-          % (vs_ref, fro, weight_format, kernels_only))
+        record_property("full_c%d_%s" % (cfg, k), v)
+    print("full C%d bf16: vs reference CUDA library %.4f (Frobenius %.4f); bf16 weights alone %.4f; kernels only %.4f"
+          % (cfg, vs_ref, fro, weight_format, kernels_only))
     assert vs_ref <= 0.9 * 2e-2
     assert kernels_only <= 5e-3
