@@ -28,7 +28,7 @@ constexpr int HD = 64;  // head size
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int ATT_MAX_WARPS = 8;
 
-// Shared-memory rows are 128 bytes (64 bf16); the 16-byte chunk c of row r lives at position
+// Shared-memory rows are 128 bytes (64 fp16); the 16-byte chunk c of row r lives at position
 // c ^ (r & 7), which makes ldmatrix (8 consecutive rows, one chunk column) conflict-free without
 // padding.
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
@@ -790,7 +790,7 @@ int row_layout(const int* mask, int* kv_len, int* row_start, int* sched, int B, 
 // library holds CUDABERT_NOALLOC_MAX_BATCH * 4 bytes (16 KiB) of it until the process exits.
 static __device__ __align__(256) int g_noalloc_kv_len[CUDABERT_NOALLOC_MAX_BATCH];
 
-extern "C" int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B,
+extern "C" int cudabert_k_attention_noalloc(int kernel_code, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B,
                                             int S, int heads) {
   // Everything is validated before the first launch: a kernel number this entry point cannot serve
   // must not fall through to another kernel that would write a differently shaped output.
@@ -798,8 +798,8 @@ extern "C" int cudabert_k_attention_noalloc(int bf16, const void* qkv_dev, const
     cb::set_thread_error("cudabert_k_attention_noalloc: null buffer or non-positive size");
     return 1;
   }
-  const int cls_only = (bf16 & 16) ? 1 : 0;  // + 16: first query of every sequence only, ctx is [B, H]
-  const int kernel = bf16 & ~16;
+  const int cls_only = (kernel_code & 16) ? 1 : 0;  // + 16: first query of every sequence only, ctx is [B, H]
+  const int kernel = kernel_code & ~16;
   if (kernel != 0 && kernel != 1) {
     cb::set_thread_error("cudabert_k_attention_noalloc: only kernels 0 (fp32) and 1 (16-bit mma.sync, optionally + 16) "
                          "are served; kernels 2 and 3 need scheduling and error scratch beyond the built-in array");

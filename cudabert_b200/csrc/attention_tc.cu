@@ -1,4 +1,4 @@
-// Fused masked attention on the tcgen05 tensor cores (bf16 / fp8 modes).  Same contract as
+// Fused masked attention on the tcgen05 tensor cores (16-bit modes: fp16 Q, K, V in, fp16 context out).  Same contract as
 // attention_f16 in attention.cu (which stays as the `mma.sync` variant): QK^T, 1/8 scale, additive
 // key mask, softmax, P.V in one kernel, keys at or beyond kv_len[b] never touched.  Replaces
 // Query_Key::forward (ops/batch_matmul.cu:24-82), cuApplySoftmax (ops/softmax.cu:86-143) and
@@ -16,8 +16,8 @@
 //                      rows, O in TMEM columns [128, 192).
 //   warps 0-3          thread = query row = TMEM lane: scale + mask bias, row max (no shuffles: the
 //                      whole row belongs to the thread), online-softmax correction of O in TMEM
-//                      when a later key block raises the max, P = exp2(x - max) as bf16 into the
-//                      swizzled A-operand tile in shared memory; at the end O / sum -> bf16 ->
+//                      when a later key block raises the max, P = exp2(x - max) as fp16 into the
+//                      swizzled A-operand tile in shared memory; at the end O / sum -> fp16 ->
 //                      coalesced stores.
 // Every wait is bounded (ptx.cuh): a broken pipeline ends with an error flag, not a hang.
 #include "kernels.h"
@@ -34,9 +34,9 @@ constexpr int TQ = 128;  // queries per item
 constexpr int TK = 64;   // keys per block
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int ATC_THREADS = 192;
-constexpr int Q_BYTES = TQ * 128;   // 128 query rows x 128 bytes (64 bf16)
+constexpr int Q_BYTES = TQ * 128;   // 128 query rows x 128 bytes (64 fp16)
 constexpr int KV_BYTES = TK * 128;  // 64 key rows x 128 bytes
-constexpr int P_BYTES = TQ * 128;   // 128 query rows x 64 keys (bf16)
+constexpr int P_BYTES = TQ * 128;   // 128 query rows x 64 keys (fp16)
 // Q, K and V are double-buffered so that the loads and the QK^T of the next block (or item) run
 // while the softmax warps work on the current one.
 constexpr int SMEM_Q = 0, SMEM_K = 2 * Q_BYTES, SMEM_V = SMEM_K + 2 * KV_BYTES, SMEM_P = SMEM_V + 2 * KV_BYTES;
@@ -61,7 +61,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Shared-memory descriptor of an MN-major bf16 operand stored as rows of 64 elements (128 bytes,
+// Shared-memory descriptor of an MN-major 16-bit operand stored as rows of 64 elements (128 bytes,
 // 128-byte swizzle), one row per K index: 8-row groups are 1024 bytes apart (stride byte offset);
 // the leading byte offset (distance between 64-element groups along MN) is unused for N = 64.
 __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr) {
@@ -317,7 +317,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       // Reference point of the exponentials.  It only has to keep exp2 in range, so it follows the
       // running maximum lazily: it moves (and O is rescaled in TMEM, a round trip) only when a block
       // exceeds it by more than 8 in the log2 domain; until then probabilities may reach 2^8, which
-      // bf16 and the fp32 sums hold without loss.  The first block of an item sets it exactly.
+      // fp16 and the fp32 sums hold without loss.  The first block of an item sets it exactly.
       float alpha = 1.0f;
       if (j == 0) {
         m_run = mx;  // finite: key 0 of block 0 is never masked with -inf
@@ -381,7 +381,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       if (lane == 0) mbar_arrive(p_full);
       if (j != it.nblocks - 1) continue;
 
-      // last block of the item: O / l -> bf16 -> this warp's staging rows -> coalesced stores
+      // last block of the item: O / l -> fp16 -> this warp's staging rows -> coalesced stores
       mbar_wait(o_full, o_waits & 1, abort_flag, err, SITE_ATT_O);
       ++o_waits;
       tc_fence_after();
@@ -434,7 +434,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
 
 }  // namespace
 
-// Which bf16 attention kernel a forward pass of padded length S uses.  The tcgen05 kernel works on
+// Which 16-bit attention kernel a forward pass of padded length S uses.  The tcgen05 kernel works on
 // 128-query tiles of 64-key blocks whatever the number of live rows in them, so it wins where the
 // tiles are full and loses where a batch's rows are much shorter than the tile grid.  Measured per
 // layer, BERT-large unless noted, in microseconds for tcgen05 / persistent mma.sync / mma.sync with

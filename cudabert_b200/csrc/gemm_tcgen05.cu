@@ -1,6 +1,6 @@
 // Dense projection GEMM for sm_100a: out[M, N] = A[M, K] x W[N, K]^T with a fused epilogue.
 //
-// It replaces, for the bf16 / FP8-weight modes, the reference's cuBLAS SGEMM calls and the
+// It replaces, for the 16-bit modes (bf16 or FP8 weights, fp16 activations), the reference's cuBLAS SGEMM calls and the
 // kernels around them: the bias pre-fill `MemoryCpyLinear` (ops/linear.cu:23-27), the GEMMs
 // of `op_BatchedLinear::forward` (ops/linear.cu:241-319) and `op_Linear::forward`
 // (ops/linear.cu:91-148), the GELU sweep (ops/elementwise.cu:38-51), the residual add that
@@ -17,7 +17,7 @@
 //   warp 0, one lane   TMA producer: per k-block one 128x64 tile of A and one BNx64 tile of W
 //                      (128-byte swizzle) into a ring of shared-memory stages guarded by
 //                      full/empty mbarriers.
-//   warp 1, one lane   issues tcgen05.mma (128 x BN x 16, bf16 in, fp32 accumulate in TMEM);
+//   warp 1, one lane   issues tcgen05.mma (128 x BN x 16, fp16 or bf16 in, fp32 accumulate in TMEM);
 //                      tcgen05.commit releases a stage back to the producer and, after the
 //                      last k-block, hands the accumulator to the epilogue.
 //   warps 2-9          epilogue: tcgen05.ld of the accumulator (a warp can reach the TMEM lane
@@ -61,7 +61,7 @@ struct Cfg {
 };
 
 // erf-GELU x * 0.5 * (1 + erf(x / sqrt 2)) evaluated as 0.5 x (1 + tanh(x (c0 + c1 x^2 + c2 x^4))) with
-// coefficients fitted to the erf form (max abs deviation 2.5e-5 over the reals, below one bf16
+// coefficients fitted to the erf form (max abs deviation 2.5e-5 over the reals, below one 16-bit
 // rounding of the result everywhere) and the hardware tanh (relative error 2^-11), instead of ~45
 // instructions per element for erff, which otherwise makes the FFN1 epilogue slower than its main loop.
 // Two values at a time with the packed fp32 instructions of sm_100 (mul / fma .f32x2: one issue
