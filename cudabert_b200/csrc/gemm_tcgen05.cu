@@ -404,16 +404,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 //   both CTAs   warps 2-9: epilogue of the CTA's own 128 accumulator rows; every epilogue warp
 //               of the pair arrives on the leader's accumulator-empty barrier (count 16).
 //
-// W8 (FP8-weight mode): W lives in HBM as E4M3 bytes [N, K].  The producer's TMA brings the CTA's
-// 128 x 64 bytes of a k-block into a raw buffer beside the stage's A tile; four converter warps
-// (10-13) widen them to fp16 (cvt.rn.f16x2.e4m3x2, exact) into one of three W operand buffers in
-// the layout the MMA reads (128-byte rows, 16-byte chunk c of row r at position c ^ (r & 7)) and
-// arrive on the leader's "converted" barrier of that buffer.  The weights cross HBM, L2 and the
-// TMA at one byte per element; the tensor core sees fp16.  Two rings instead of one because the two
-// latencies differ: what TMA fetches (A tiles, raw bytes) needs six stages in flight to cover the
-// memory latency, as in the 16-bit kernel, while the converted tiles are made on the SM a few
-// hundred cycles before their MMA and need only three buffers -- six stages of A + raw + converted
-// W would not fit in shared memory.
+// W8 (FP8-weight mode): W lives in HBM as E4M3 bytes [N, K] and in no wider form.  The producer's TMA
+// brings the CTA's 128 x 64 bytes of a k-block into a raw buffer beside the stage's A tile; four
+// converter warps (10-13) widen them to fp16 (cvt.rn.f16x2.e4m3x2, exact) into one of five W operand
+// tiles in the layout the MMA reads (128-byte rows, 16-byte chunk c of row r at position
+// c ^ (r & 7)), fence them for the async proxy and arrive on the leader's "converted" barrier of that
+// tile.  The weights cross HBM, L2 and the TMA at one byte per element; the tensor core sees fp16.
+// Two rings (five stages of A + raw bytes, five converted tiles) instead of one of six: six stages of
+// all three do not fit in shared memory.  Ring depths of 6 + 3 and 4 + 6 run at the same speed: what
+// bounds this variant is shared-memory bandwidth (TMA writes, converter loads and stores, and the
+// tensor core's operand reads come to 80 KB per k-block against 64 KB in the 16-bit kernel).
 constexpr int CONV_WARPS = 4;
 template <int BN, bool W8>
 struct PairCfg {
