@@ -299,7 +299,7 @@ int cudabert_k_attention(int kernel, const void* qkv_dev, const int* mask_dev, v
   int* kv = nullptr;
   if (cudaMalloc(&kv, (3 * static_cast<size_t>(B) + 1) * sizeof(int)) != cudaSuccess) return 2;
   int* err = kv + B;
-  int* sched = kernel == 3 ? kv + B + 1 : nullptr;  // 2 B entries
+  int* sched = (kernel == 2 || kernel == 3) ? kv + B + 1 : nullptr;  // 2 B entries
   cudaMemset(err, 0, sizeof(int));
   int rc = 0;
   if (cb::row_layout(mask_dev, kv, nullptr, sched, B, S, nullptr) < 0) rc = 3;
@@ -315,8 +315,8 @@ int cudabert_k_attention(int kernel, const void* qkv_dev, const int* mask_dev, v
         return 2;
       }
       if (kernel == 2)
-        n = cb::attention_f16_tc(&tm, mask_dev, kv, nullptr, static_cast<__half*>(ctx_dev), B, S, heads, sms,
-                                  cls_only, err, nullptr);
+        n = cb::attention_f16_tc(&tm, mask_dev, kv, nullptr, sched, static_cast<__half*>(ctx_dev), B, S, heads,
+                                 sms, cls_only, err, nullptr);
       else
         n = cb::attention_f16_persist(&tm, mask_dev, kv, nullptr, sched, static_cast<__half*>(ctx_dev), B, S,
                                        heads, sms, cls_only, err, nullptr);

@@ -41,9 +41,13 @@ constexpr int P_BYTES = TQ * 128;   // 128 query rows x 64 keys (fp16)
 // while the softmax warps work on the current one.
 constexpr int SMEM_Q = 0, SMEM_K = 2 * Q_BYTES, SMEM_V = SMEM_K + 2 * KV_BYTES, SMEM_P = SMEM_V + 2 * KV_BYTES;
 constexpr int SMEM_BIAS = SMEM_P + P_BYTES;
-constexpr int SMEM_BAR = SMEM_BIAS + 512 * 4 + 16;  // bias of up to 512 keys + one flag word
-constexpr int ATC_SMEM = SMEM_BAR + 256 + 1024;  // + barriers + alignment slack: 83 KB, two CTAs per SM
-constexpr uint32_t TMEM_COLS = 256;  // S buffers in columns [0, 64) and [64, 128), O in [128, 192)
+constexpr int SMEM_STAGE = SMEM_BIAS + 512 * 4 + 1024;  // bias of up to 512 keys + one flag word, padded
+constexpr int STAGE_BYTES = TQ * 128;                   // output staging: 128 rows x 64 fp16
+constexpr int SMEM_BAR = SMEM_STAGE + STAGE_BYTES;
+constexpr int ATC_SMEM = SMEM_BAR + 256 + 1024;  // + barriers + alignment slack: 100 KB, two CTAs per SM
+// S buffers in columns [0, 64) and [64, 128); two O accumulators in [128, 192) and [192, 256), used by
+// alternate items so that the output of one item is read while the next one accumulates
+constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t S_COL = 0, O_COL = 128;
 
 enum { SITE_ATT_Q = 10, SITE_ATT_K, SITE_ATT_V, SITE_ATT_S, SITE_ATT_P, SITE_ATT_O, SITE_ATT_E };
@@ -75,20 +79,22 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16_bmn(int m, int n) {
 
 struct ItemInfo {
   int b, h, q0, first, nq, klen, nblocks;
-  bool use_mask, live;
+  bool use_mask, live;  // use_mask: some key below klen may be masked, the mask row has to be read
 };
 
 // cls_only: only the first query of every sequence is wanted (the last encoder layer of a call that
 // returns the pooler output alone); its result goes to output row b instead of the sequence's first row.
-__device__ __forceinline__ ItemInfo decode_item(int item, int QT, int heads, int S, const int* __restrict__ kv_len,
-                                                const int* __restrict__ row_start, const int* __restrict__ mask,
+__device__ __forceinline__ ItemInfo decode_item(int item, int QT, int heads, int S, int B,
+                                                const int* __restrict__ kv_len, const int* __restrict__ row_start,
+                                                const int* __restrict__ mask, const int* __restrict__ sched,
                                                 int cls_only) {
   ItemInfo it;
   const int qt = item % QT;
   it.h = (item / QT) % heads;
   it.b = item / (QT * heads);
   int klen = kv_len[it.b];
-  it.use_mask = (klen > 0) && (mask != nullptr);
+  // with `sched` (from row_layout) the mask is read only for rows flagged as having holes
+  it.use_mask = (klen > 0) && (mask != nullptr) && (!sched || sched[B + it.b] != 0);
   if (klen <= 0) klen = S;
   it.klen = klen;
   it.first = row_start ? row_start[it.b] : it.b * S;
@@ -102,7 +108,8 @@ __device__ __forceinline__ ItemInfo decode_item(int item, int QT, int heads, int
 __global__ void __launch_bounds__(ATC_THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __restrict__ mask,
                     const int* __restrict__ kv_len, const int* __restrict__ row_start,
-                    __half* __restrict__ ctx, int B, int S, int heads, int cls_only, int* err) {
+                    const int* __restrict__ sched, __half* __restrict__ ctx, int B, int S, int heads, int cls_only,
+                    int* err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* sBias = reinterpret_cast<float*>(smem + SMEM_BIAS);
@@ -147,7 +154,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
   auto cursor_seek = [&](Cursor& c) {  // position on the first live item at or after c.item
     c.valid = false;
     while (c.item < num_items) {
-      c.it = decode_item(c.item, QT, heads, S, kv_len, row_start, mask, cls_only);
+      c.it = decode_item(c.item, QT, heads, S, B, kv_len, row_start, mask, sched, cls_only);
       if (c.it.live) { c.valid = true; break; }
       c.item += gridDim.x;
     }
@@ -214,7 +221,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
         for (int k = 0; k < TK / 16; ++k) {
           const uint64_t da = umma_desc_sw128(sp) + 2 * k;
           const uint64_t db = umma_desc_sw128_mn(sv + vb * KV_BYTES) + static_cast<uint64_t>(k) * (2048 >> 4);
-          umma_f16(tmem_base + O_COL, da, db, idesc_o, (c.j | k) != 0);
+          umma_f16(tmem_base + O_COL + (c.items_done & 1) * HD, da, db, idesc_o, (c.j | k) != 0);
         }
         umma_commit(o_full);
         umma_commit(v_empty + vb);
@@ -240,11 +247,51 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
     // softmax warps 0-3: thread r owns query row r of the tile and TMEM lane r
     const int r = threadIdx.x;  // 0..127
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    uint8_t* my_p = smem + SMEM_P + r * 128;       // this row's 64 probabilities of the block
-    uint8_t* stage = smem + SMEM_P + warp * 4096;  // output staging: this warp's 32 rows x 128 B
+    uint8_t* my_p = smem + SMEM_P + r * 128;           // this row's 64 probabilities of the block
+    uint8_t* stage = smem + SMEM_STAGE + warp * 4096;  // output staging: this warp's 32 rows x 128 B
     const float scale = 0.125f * LOG2E;
     uint32_t o_waits = 0;  // completions of o_full consumed so far
     float m_run = -INFINITY, l_run = 0.f;
+    // The output of an item is written one step late: its last P.V runs while these warps already
+    // work on the first key block of the next item (the two items accumulate in different TMEM
+    // columns), and the finished accumulator is read, normalised and stored right after that block's
+    // probabilities have been handed to the tensor core.  Per item this takes the P.V latency, the
+    // TMEM read and the stores off the path the next MMA waits on.
+    bool prev = false;  // an item's output is pending
+    float prev_inv = 0.f;
+    int prev_row0 = 0, prev_h = 0, prev_q0 = 0, prev_nq = 0;
+    uint32_t prev_ocol = 0;
+    auto finish_prev = [&]() {  // its last P.V has completed (o_full waited for): O / l -> fp16 -> staging -> stores
+      uint8_t* my_row = stage + lane * 128;
+      uint32_t ov[2][32];
+      tmem_ld32(t_lane + prev_ocol, ov[0]);
+      tmem_ld32(t_lane + prev_ocol + 32, ov[1]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int ch = 0; ch < HD / 32; ++ch) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 t;
+          t.x = pack_f16(__uint_as_float(ov[ch][8 * q]) * prev_inv, __uint_as_float(ov[ch][8 * q + 1]) * prev_inv);
+          t.y = pack_f16(__uint_as_float(ov[ch][8 * q + 2]) * prev_inv, __uint_as_float(ov[ch][8 * q + 3]) * prev_inv);
+          t.z = pack_f16(__uint_as_float(ov[ch][8 * q + 4]) * prev_inv, __uint_as_float(ov[ch][8 * q + 5]) * prev_inv);
+          t.w = pack_f16(__uint_as_float(ov[ch][8 * q + 6]) * prev_inv, __uint_as_float(ov[ch][8 * q + 7]) * prev_inv);
+          *reinterpret_cast<uint4*>(my_row + (((ch * 4 + q) ^ (lane & 7)) << 4)) = t;
+        }
+      }
+      tc_fence_before();  // the accumulator's next writer (an MMA two items on) comes after these reads
+      __syncwarp();
+      __half* out_base = ctx + static_cast<size_t>(prev_row0) * H + prev_h * HD;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + (lane >> 3), p2 = lane & 7;
+        const int qrow = prev_q0 + warp * 32 + rr;
+        const uint4 t = *reinterpret_cast<const uint4*>(stage + rr * 128 + (p2 << 4));
+        if (qrow < prev_nq)
+          *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(qrow) * H + ((p2 ^ (rr & 7)) << 3)) = t;
+      }
+      __syncwarp();  // the staging rows are free for the next item
+    };
     Cursor c{};
     c.item = static_cast<int>(blockIdx.x);
     for (cursor_seek(c); c.valid; cursor_next(c)) {
@@ -253,10 +300,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       const int* mrow = mask ? mask + static_cast<size_t>(it.b) * S : nullptr;
       if (j == 0) { m_run = -INFINITY; l_run = 0.f; }
       const uint32_t t_s = t_lane + S_COL + (c.blocks_done & 1) * TK;
-      if (j == 0) {
-        // once per item: additive bias (log2 domain) of every key of the sequence, and one flag bit
-        // per 64-key block that has any non-zero bias (masked key or tail beyond the last key)
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone is done with the previous item's bias
+      const uint32_t t_o = t_lane + O_COL + (c.items_done & 1) * HD;
+      if (j == 0 && it.use_mask) {
+        // a sequence with masked keys below its last valid one (rare): additive bias (log2 domain) of
+        // every key, staged once per item, and one flag bit per 64-key block that has any
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone is done with the previous such item's bias
         if (r == 0) *sFlags = 0u;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int kend = it.nblocks * TK;
@@ -264,14 +312,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
         for (int key = r; key < kend; key += 128) {
           float bv = 0.f;
           if (key >= it.klen) bv = -INFINITY;
-          else if (it.use_mask && __ldg(mrow + key) == 0) bv = -10000.0f * LOG2E;
+          else if (__ldg(mrow + key) == 0) bv = -10000.0f * LOG2E;
           sBias[key] = bv;
           if (bv != 0.f) bits |= 1u << (key / TK);
         }
         if (bits) atomicOr(sFlags, bits);
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      const bool plain = ((*sFlags >> j) & 1u) == 0u;  // every key of the block is valid
+      // plain: every key of the block is valid.  Without a mask to read, only the last block of a
+      // sequence can hold keys beyond its length, and which ones follows from the length alone.
+      const int tail = it.klen - j * TK;  // keys of this block that exist (>= 64: all)
+      const bool plain = it.use_mask ? ((*sFlags >> j) & 1u) == 0u : tail >= TK;
       const float* bias = sBias + j * TK;
       mbar_wait(s_full + (c.blocks_done & 1), (c.blocks_done >> 1) & 1, abort_flag, err, SITE_ATT_S);
       tc_fence_after();
@@ -281,9 +332,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       tmem_ld32(t_s + 32, v[1]);
       tmem_ld_wait();
       // four independent chains for the maximum (and below for the sum): a single chain of 64
-      // dependent operations would leave the two warps an SM sub-partition holds mostly stalled.
-      // The softmax warps are bound by their issue slots, so the loops below use the three-input
-      // maximum and packed pairs for the multiply-adds and the sums (half the instructions each).
+      // dependent operations would leave the two warps an SM sub-partition holds mostly stalled;
+      // three-input maxima and packed pairs for the multiply-adds and the sums
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (plain) {
 #pragma unroll
@@ -295,7 +345,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
               mx4[q] = max3(mx4[q], __uint_as_float(v[ch][i + 2 * q]), __uint_as_float(v[ch][i + 2 * q + 1]));
 #pragma unroll
         for (int q = 0; q < 4; ++q) mx4[q] *= scale;  // the scale itself is folded into the exponential below
-      } else {
+      } else if (it.use_mask) {
         const uint64_t sc2 = pack_f32x2(scale, scale);
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch)
@@ -312,6 +362,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
             mx4[(i >> 2) & 1] = max3(mx4[(i >> 2) & 1], x0, x1);
             mx4[2 + ((i >> 2) & 1)] = max3(mx4[2 + ((i >> 2) & 1)], x2, x3);
           }
+      } else {
+        // last block of a sequence without masked keys: keys at or beyond `tail` do not exist
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = (ch * 32 + i < tail) ? __uint_as_float(v[ch][i]) * scale : -INFINITY;
+            v[ch][i] = __float_as_uint(x);
+            mx4[i & 3] = fmaxf(mx4[i & 3], x);
+          }
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // Reference point of the exponentials.  It only has to keep exp2 in range, so it follows the
@@ -327,29 +387,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       }
       const float m_new = m_run;
       l_run *= alpha;
-      if (j > 0) {
-        // the previous block's P.V must have landed before P is overwritten (and O rescaled)
-        mbar_wait(o_full, o_waits & 1, abort_flag, err, SITE_ATT_O);
-        ++o_waits;
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-          uint32_t o[2][32];
-          tmem_ld32(t_lane + O_COL, o[0]);
-          tmem_ld32(t_lane + O_COL + 32, o[1]);
-          tmem_ld_wait();
-#pragma unroll
-          for (int ch = 0; ch < 2; ++ch) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[ch][i] = __float_as_uint(__uint_as_float(o[ch][i]) * alpha);
-            tmem_st32(t_lane + O_COL + ch * 32, o[ch]);
-          }
-          tmem_st_wait();
-        }
-      }
-      // P = exp2(x - max) -> fp16 -> swizzled A-operand tile
+      // P = exp2(x - max) in registers first: nothing below depends on the previous P.V yet
       uint64_t l2[2] = {0ull, 0ull};  // two packed pairs of partial sums
       const float e_scale = plain ? scale : 1.0f;  // plain blocks still hold the raw dot products
       const uint64_t es2 = pack_f32x2(e_scale, e_scale), nm2 = pack_f32x2(-m_new, -m_new);
+      uint4 pk[8];
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         float p[32];
@@ -363,58 +405,60 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          uint4 t;
-          t.x = pack_f16(p[8 * q], p[8 * q + 1]);
-          t.y = pack_f16(p[8 * q + 2], p[8 * q + 3]);
-          t.z = pack_f16(p[8 * q + 4], p[8 * q + 5]);
-          t.w = pack_f16(p[8 * q + 6], p[8 * q + 7]);
-          *reinterpret_cast<uint4*>(my_p + (((ch * 4 + q) ^ (r & 7)) << 4)) = t;
+          pk[ch * 4 + q].x = pack_f16(p[8 * q], p[8 * q + 1]);
+          pk[ch * 4 + q].y = pack_f16(p[8 * q + 2], p[8 * q + 3]);
+          pk[ch * 4 + q].z = pack_f16(p[8 * q + 4], p[8 * q + 5]);
+          pk[ch * 4 + q].w = pack_f16(p[8 * q + 6], p[8 * q + 7]);
         }
       }
       float l4[4];
       unpack_f32x2(l2[0], l4[0], l4[1]);
       unpack_f32x2(l2[1], l4[2], l4[3]);
       l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      // The P tile (and, for a rescale, O) may be touched only after the P.V that last read it has
+      // completed: the previous block's, or the last block's of the previous item.
+      if (j > 0 || prev) {
+        mbar_wait(o_full, o_waits & 1, abort_flag, err, SITE_ATT_O);
+        ++o_waits;
+        tc_fence_after();
+      }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+        uint32_t o[2][32];
+        tmem_ld32(t_o, o[0]);
+        tmem_ld32(t_o + 32, o[1]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[ch][i] = __float_as_uint(__uint_as_float(o[ch][i]) * alpha);
+          tmem_st32(t_o + ch * 32, o[ch]);
+        }
+        tmem_st_wait();
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(my_p + ((q ^ (r & 7)) << 4)) = pk[q];
       fence_proxy_async_smem();  // the tensor core reads P through the async proxy
       tc_fence_before();
       __syncwarp();              // every lane's rows are written and fenced: one arrival for the warp
       if (lane == 0) mbar_arrive(p_full);
-      if (j != it.nblocks - 1) continue;
-
-      // last block of the item: O / l -> fp16 -> this warp's staging rows -> coalesced stores
+      if (j == 0 && prev) {      // the previous item's accumulator is complete (waited for above)
+        finish_prev();
+        prev = false;
+      }
+      if (j == it.nblocks - 1) {
+        prev = true;
+        prev_inv = 1.0f / l_run;
+        prev_row0 = cls_only ? it.b : it.first;
+        prev_h = it.h;
+        prev_q0 = it.q0;
+        prev_nq = it.nq;
+        prev_ocol = O_COL + (c.items_done & 1) * HD;
+      }
+    }
+    if (prev) {
       mbar_wait(o_full, o_waits & 1, abort_flag, err, SITE_ATT_O);
-      ++o_waits;
       tc_fence_after();
-      const float inv = 1.0f / l_run;
-      uint8_t* my_row = stage + lane * 128;
-      uint32_t ov[2][32];
-      tmem_ld32(t_lane + O_COL, ov[0]);
-      tmem_ld32(t_lane + O_COL + 32, ov[1]);
-      tmem_ld_wait();
-#pragma unroll
-      for (int ch = 0; ch < HD / 32; ++ch) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 t;
-          t.x = pack_f16(__uint_as_float(ov[ch][8 * q]) * inv, __uint_as_float(ov[ch][8 * q + 1]) * inv);
-          t.y = pack_f16(__uint_as_float(ov[ch][8 * q + 2]) * inv, __uint_as_float(ov[ch][8 * q + 3]) * inv);
-          t.z = pack_f16(__uint_as_float(ov[ch][8 * q + 4]) * inv, __uint_as_float(ov[ch][8 * q + 5]) * inv);
-          t.w = pack_f16(__uint_as_float(ov[ch][8 * q + 6]) * inv, __uint_as_float(ov[ch][8 * q + 7]) * inv);
-          *reinterpret_cast<uint4*>(my_row + (((ch * 4 + q) ^ (lane & 7)) << 4)) = t;
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      __half* out_base = ctx + static_cast<size_t>(cls_only ? it.b : it.first) * H + it.h * HD;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rr = i * 4 + (lane >> 3), p2 = lane & 7;
-        const int qrow = it.q0 + warp * 32 + rr;
-        const uint4 t = *reinterpret_cast<const uint4*>(stage + rr * 128 + (p2 << 4));
-        if (qrow < it.nq)
-          *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(qrow) * H + ((p2 ^ (rr & 7)) << 3)) = t;
-      }
-      __syncwarp();  // the staging rows are this warp's P rows of the next block
+      finish_prev();
     }
   }
 
@@ -468,8 +512,8 @@ bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H) {
 }
 
 int attention_f16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                      __half* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
-                      cudaStream_t stream) {
+                     const int* sched, __half* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
+                     cudaStream_t stream) {
   if (B <= 0 || S <= 0 || S > 512 || heads <= 0) return -1;
   static std::atomic<bool> attr_set[64] = {};  // per device; a repeated set by a racing thread is harmless
   int dev = 0;
@@ -482,7 +526,7 @@ int attention_f16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_l
   const long long items = static_cast<long long>(B) * heads * ((S + TQ - 1) / TQ);
   const int grid = static_cast<int>(items < 2LL * num_sms ? items : 2LL * num_sms);
   return launch_pdl(attention_tc_kernel, dim3(grid), dim3(ATC_THREADS), ATC_SMEM, stream, *tm_qkv, mask, kv_len,
-                    row_start, ctx, B, S, heads, cls_only, err_flag) == cudaSuccess ? 1 : -3;
+                    row_start, sched, ctx, B, S, heads, cls_only, err_flag) == cudaSuccess ? 1 : -3;
 }
 
 }  // namespace cb

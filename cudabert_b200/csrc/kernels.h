@@ -149,9 +149,10 @@ int attention_f16_persist(const CUtensorMap* tm_qkv, const int* mask, const int*
 enum AttentionKernel : int { ATT_KERNEL_MMA = 1, ATT_KERNEL_TC = 2, ATT_KERNEL_PERSIST = 3 };
 int attention_kernel_for(int S);
 bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H);
+// `sched` (may be null) as above: only its mask flags are used, the items keep their natural order.
 int attention_f16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
-                      __half* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
-                      cudaStream_t stream);
+                     const int* sched, __half* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
+                     cudaStream_t stream);
 // kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none); mask null => S.
 // row_start (may be null): exclusive prefix sum of the sequence lengths (a length of 0 counts as S),
 // B + 1 entries, the last one being the number of packed rows.

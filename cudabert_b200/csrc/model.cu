@@ -674,7 +674,7 @@ bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mas
   const int* live = packed_ ? row_start_ + B : nullptr;     // live row count (device)
   const bool lowp = prec_ != PREC_FP32;
   const int att_kernel = lowp ? attention_kernel_for(S) : ATT_KERNEL_MMA;
-  int* sched = att_kernel == ATT_KERNEL_PERSIST ? att_sched_ : nullptr;
+  int* sched = att_kernel != ATT_KERNEL_MMA ? att_sched_ : nullptr;  // work order and mask flags
   CB_LAUNCH(KC_OTHER, row_layout(d_mask, kv_len_, packed_ ? row_start_ : nullptr, sched, B, S, stream_));
   __half* xa = static_cast<__half*>(xa_);
   __half* x1a = static_cast<__half*>(x1a_);
@@ -697,8 +697,8 @@ bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mas
       // so the pooler output has the same bits as after a full last layer.
       const int cls = (cls_last_ && !want_hidden_f32 && l == L_ - 1) ? 1 : 0;
       if (att_kernel == ATT_KERNEL_TC) {
-        CB_LAUNCH(KC_ATTENTION, attention_f16_tc(&tm_qkv_, d_mask, kv_len_, rs, static_cast<__half*>(ctx_), B, S,
-                                                  heads_, num_sms_, cls, err_dev_, stream_));
+        CB_LAUNCH(KC_ATTENTION, attention_f16_tc(&tm_qkv_, d_mask, kv_len_, rs, sched, static_cast<__half*>(ctx_), B,
+                                                 S, heads_, num_sms_, cls, err_dev_, stream_));
       } else if (att_kernel == ATT_KERNEL_PERSIST) {
         CB_LAUNCH(KC_ATTENTION, attention_f16_persist(&tm_qkv_, d_mask, kv_len_, rs, sched,
                                                        static_cast<__half*>(ctx_), B, S, heads_, num_sms_, cls,
