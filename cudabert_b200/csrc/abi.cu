@@ -294,15 +294,18 @@ int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, 
 int cudabert_k_attention(int kernel, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads) {
   if (!qkv_dev || !ctx_dev || B <= 0 || S <= 0 || heads <= 0) return 1;
   const int cls_only = (kernel & 16) ? 1 : 0;  // + 16: first query of every sequence only, ctx is [B, H]
+  const bool packed = (kernel & 32) != 0;      // + 32: the sequences' valid rows lie back to back
   kernel &= 15;
-  if (cls_only && kernel == 0) return 1;
-  int* kv = nullptr;
-  if (cudaMalloc(&kv, (3 * static_cast<size_t>(B) + 1) * sizeof(int)) != cudaSuccess) return 2;
+  if (kernel > 3 || (cls_only && kernel == 0)) return 1;
+  const size_t tiles = (static_cast<size_t>(B) * S + 127) / 128;
+  int* kv = nullptr;  // kv_len [B] | error word | row_start [B + 1] | sched [2 B + tiles]
+  if (cudaMalloc(&kv, (4 * static_cast<size_t>(B) + 2 + tiles) * sizeof(int)) != cudaSuccess) return 2;
   int* err = kv + B;
-  int* sched = (kernel == 2 || kernel == 3) ? kv + B + 1 : nullptr;  // 2 B entries
+  int* rs = packed ? kv + B + 1 : nullptr;
+  int* sched = (kernel == 2 || kernel == 3) ? kv + 2 * B + 2 : nullptr;
   cudaMemset(err, 0, sizeof(int));
   int rc = 0;
-  if (cb::row_layout(mask_dev, kv, nullptr, sched, B, S, nullptr) < 0) rc = 3;
+  if (cb::row_layout(mask_dev, kv, rs, sched, B, S, nullptr) < 0) rc = 3;
   if (!rc) {
     int n;
     if (kernel == 2 || kernel == 3) {  // tcgen05 kernel, persistent mma.sync kernel: both read K and V by TMA
@@ -315,16 +318,16 @@ int cudabert_k_attention(int kernel, const void* qkv_dev, const int* mask_dev, v
         return 2;
       }
       if (kernel == 2)
-        n = cb::attention_f16_tc(&tm, mask_dev, kv, nullptr, sched, static_cast<__half*>(ctx_dev), B, S, heads,
+        n = cb::attention_f16_tc(&tm, mask_dev, kv, rs, sched, static_cast<__half*>(ctx_dev), B, S, heads,
                                  sms, cls_only, err, nullptr);
       else
-        n = cb::attention_f16_persist(&tm, mask_dev, kv, nullptr, sched, static_cast<__half*>(ctx_dev), B, S,
+        n = cb::attention_f16_persist(&tm, mask_dev, kv, rs, sched, static_cast<__half*>(ctx_dev), B, S,
                                        heads, sms, cls_only, err, nullptr);
     } else if (kernel) {
-      n = cb::attention_f16(static_cast<const __half*>(qkv_dev), mask_dev, kv, nullptr,
+      n = cb::attention_f16(static_cast<const __half*>(qkv_dev), mask_dev, kv, rs,
                              static_cast<__half*>(ctx_dev), B, S, heads, cls_only, nullptr);
     } else {
-      n = cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, nullptr, static_cast<float*>(ctx_dev), B,
+      n = cb::attention_f32(static_cast<const float*>(qkv_dev), mask_dev, kv, rs, static_cast<float*>(ctx_dev), B,
                             S, heads, nullptr);
     }
     if (n < 0) rc = 3;

@@ -620,10 +620,13 @@ attention_f32_kernel(const float* __restrict__ qkv, const int* __restrict__ mask
 // mask is null).  With `row_start` (B + 1 entries) it also lays the sequences out back to back:
 // row_start[b] = sum of the lengths of the rows before b, a row of length 0 (no valid key: it
 // attends to everything) counting as S; row_start[B] is the number of packed rows.  With `sched`
-// (2 B entries) it also prepares the persistent attention kernel's work order: sched[r] = the
-// sequence of rank r when sequences are sorted by descending length (counting sort; the order
-// among equal lengths is arbitrary and only affects scheduling), and sched[B + b] = 1 if row b
-// has a masked key below its last valid one (only then does attention have to read the mask).
+// it also prepares the persistent attention kernel's work order: sched[r] = the sequence of rank r
+// when sequences are sorted by descending length (counting sort; the order among equal lengths is
+// arbitrary and only affects scheduling), and sched[B + b] = 1 if row b has a masked key below its
+// last valid one (only then does attention have to read the mask).
+// With both, sched[2 B + t] = the sequence that packed row 128 t belongs to, for every t with
+// 128 t < row_start[B] (the tcgen05 attention kernel's tiles); `sched` then holds
+// 2 B + ceil(B S / 128) entries.
 __global__ void __launch_bounds__(1024)
 row_layout_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int* __restrict__ row_start,
                   int* __restrict__ sched, int B, int S) {
@@ -719,6 +722,14 @@ row_layout_kernel(const int* __restrict__ mask, int* __restrict__ kv_len, int* _
     __syncthreads();
   }
   if (tid == 0) row_start[B] = carry;
+  if (sched) {
+    // tile table: the sequence that row 128 t of the packed layout belongs to
+    __syncthreads();  // row_start, written above by other threads of this block, is read below
+    for (int b = tid; b < B; b += 1024) {
+      const int lo = row_start[b], hi = row_start[b + 1];
+      for (int t = (lo + 127) / 128; t * 128 < hi; ++t) sched[2 * B + t] = b;
+    }
+  }
 }
 
 }  // namespace

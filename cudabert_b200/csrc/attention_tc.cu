@@ -40,14 +40,14 @@ constexpr int P_BYTES = TQ * 128;   // 128 query rows x 64 keys (fp16)
 // Q, K and V are double-buffered so that the loads and the QK^T of the next block (or item) run
 // while the softmax warps work on the current one.
 constexpr int SMEM_Q = 0, SMEM_K = 2 * Q_BYTES, SMEM_V = SMEM_K + 2 * KV_BYTES, SMEM_P = SMEM_V + 2 * KV_BYTES;
-constexpr int SMEM_BIAS = SMEM_P + P_BYTES;
-constexpr int SMEM_STAGE = SMEM_BIAS + 512 * 4 + 1024;  // bias of up to 512 keys + one flag word, padded
-constexpr int STAGE_BYTES = TQ * 128;                   // output staging: 128 rows x 64 fp16
+constexpr int SMEM_STAGE = SMEM_P + P_BYTES;
+constexpr int STAGE_BYTES = TQ * 128;  // output staging: 128 rows x 64 fp16
 constexpr int SMEM_BAR = SMEM_STAGE + STAGE_BYTES;
-constexpr int ATC_SMEM = SMEM_BAR + 256 + 1024;  // + barriers + alignment slack: 100 KB, two CTAs per SM
+constexpr int ATC_SMEM = SMEM_BAR + 256 + 1024;  // + barriers + alignment slack: 97 KB, two CTAs per SM
 // S buffers in columns [0, 64) and [64, 128); two O accumulators in [128, 192) and [192, 256), used by
 // alternate items so that the output of one item is read while the next one accumulates
 constexpr uint32_t TMEM_COLS = 256;
+constexpr int ATC_PACKED_MAX_S = 80;  // padded lengths up to this use packed tiles (see attention_kernel_for)
 constexpr uint32_t S_COL = 0, O_COL = 128;
 
 enum { SITE_ATT_Q = 10, SITE_ATT_K, SITE_ATT_V, SITE_ATT_S, SITE_ATT_P, SITE_ATT_O, SITE_ATT_E };
@@ -77,34 +77,28 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16_bmn(int m, int n) {
   return umma_idesc_f16(m, n) | (1u << 16);
 }
 
-struct ItemInfo {
-  int b, h, q0, first, nq, klen, nblocks;
-  bool use_mask, live;  // use_mask: some key below klen may be masked, the mask row has to be read
+// Position of one role (loader, MMA issuer, softmax warps) in this CTA's work: an item is a tile of
+// 128 query rows of one head, a step is a block of up to 64 keys of ONE sequence.
+//   per-sequence items (MULTI = false): (sequence, head, 128-query tile); the tile's rows all belong
+//     to the sequence and its steps are that sequence's key blocks.  Used when the rows are not
+//     packed and for the pass that wants only the first query of every sequence.
+//   packed tiles (MULTI = true): (tile of 128 consecutive packed rows, head); the tile may hold rows
+//     of several sequences, and its steps are the key blocks of every sequence it cuts, in order.  A
+//     row takes part only in the steps of its own sequence (its probabilities are zero in the
+//     others), so it sees exactly the blocks, in the order and with the contents, that it sees in a
+//     per-sequence item: the results are the same bits, whatever the other rows of the batch are.
+struct Cursor {
+  int item, items_done, blocks_done;
+  bool valid;
+  // item
+  int h, q_row, out_row, n_out, q_end, ji;  // head; first query row in the QKV buffer; first output row; rows to
+                                            // store; (MULTI) end of the tile's rows; step index within the item
+  // sequence of the current step
+  int seq, ks, ke, nb, jb;  // its rows (= keys) [ks, ke) in the QKV buffer, its key blocks, the current one
+  bool use_mask;            // some key below its last valid one is masked: the mask row has to be read
 };
 
-// cls_only: only the first query of every sequence is wanted (the last encoder layer of a call that
-// returns the pooler output alone); its result goes to output row b instead of the sequence's first row.
-__device__ __forceinline__ ItemInfo decode_item(int item, int QT, int heads, int S, int B,
-                                                const int* __restrict__ kv_len, const int* __restrict__ row_start,
-                                                const int* __restrict__ mask, const int* __restrict__ sched,
-                                                int cls_only) {
-  ItemInfo it;
-  const int qt = item % QT;
-  it.h = (item / QT) % heads;
-  it.b = item / (QT * heads);
-  int klen = kv_len[it.b];
-  // with `sched` (from row_layout) the mask is read only for rows flagged as having holes
-  it.use_mask = (klen > 0) && (mask != nullptr) && (!sched || sched[B + it.b] != 0);
-  if (klen <= 0) klen = S;
-  it.klen = klen;
-  it.first = row_start ? row_start[it.b] : it.b * S;
-  it.nq = cls_only ? 1 : (row_start ? klen : S);
-  it.q0 = qt * TQ;
-  it.live = it.q0 < it.nq;
-  it.nblocks = (klen + TK - 1) / TK;
-  return it;
-}
-
+template <bool MULTI>
 __global__ void __launch_bounds__(ATC_THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __restrict__ mask,
                     const int* __restrict__ kv_len, const int* __restrict__ row_start,
@@ -112,8 +106,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
                     int* err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* sBias = reinterpret_cast<float*>(smem + SMEM_BIAS);
-  unsigned int* sFlags = reinterpret_cast<unsigned int*>(smem + SMEM_BIAS + 512 * 4);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BAR);
   uint64_t *q_full = bars, *q_empty = bars + 2, *k_full = bars + 4, *k_empty = bars + 6, *v_full = bars + 8,
            *v_empty = bars + 10, *s_full = bars + 12, *p_full = bars + 14, *o_full = bars + 15;  // [2] each but the last two
@@ -141,28 +133,73 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
   griddep_launch();
 
   const int H = heads * HD;
-  const int QT = (S + TQ - 1) / TQ;
-  const int num_items = B * heads * QT;
+  const int QT = (S + TQ - 1) / TQ;                                     // query tiles of a sequence
+  const int R = MULTI ? row_start[B] : 0;                               // packed rows (written by row_layout)
+  const int tiles = (R + TQ - 1) / TQ;                                  // (MULTI) tiles of 128 packed rows
+  const int num_items = MULTI ? tiles * heads : B * heads * QT;
 
-  // Walks the key blocks of this CTA's live items in order: (item, block j), counting items and
-  // blocks so that every role derives buffer indices and barrier parities the same way.
-  struct Cursor {
-    int item, j, items_done, blocks_done;
-    ItemInfo it;
-    bool valid;
-  };
+  // Every role walks the same steps and derives buffer indices and barrier parities from the same
+  // counters (items_done, blocks_done).
   auto cursor_seek = [&](Cursor& c) {  // position on the first live item at or after c.item
     c.valid = false;
-    while (c.item < num_items) {
-      c.it = decode_item(c.item, QT, heads, S, B, kv_len, row_start, mask, sched, cls_only);
-      if (c.it.live) { c.valid = true; break; }
-      c.item += gridDim.x;
+    c.ji = 0;
+    c.jb = 0;
+    if constexpr (MULTI) {
+      // tiles run fastest: neighbouring CTAs work on neighbouring tiles of one head, which share the
+      // keys and values of the sequence cut between them
+      if (c.item >= num_items) return;
+      const int t = c.item % tiles;
+      c.h = c.item / tiles;
+      c.q_row = c.out_row = t * TQ;
+      c.n_out = R - t * TQ;
+      c.q_end = min(t * TQ + TQ, R);
+      c.seq = sched[2 * B + t];  // the sequence the tile's first row belongs to
+      c.ks = row_start[c.seq];
+      c.ke = row_start[c.seq + 1];
+      c.nb = (c.ke - c.ks + TK - 1) / TK;
+      c.use_mask = mask != nullptr && sched[B + c.seq] != 0;
+      c.valid = true;
+    } else {
+      while (c.item < num_items) {
+        const int q0 = (c.item % QT) * TQ, b = c.item / (QT * heads);
+        int klen = kv_len[b];
+        // with `sched` (from row_layout) the mask is read only for rows flagged as having holes
+        c.use_mask = klen > 0 && mask != nullptr && (!sched || sched[B + b] != 0);
+        if (klen <= 0) klen = S;  // no valid key: the row attends to everything
+        const int nq = cls_only ? 1 : (row_start ? klen : S);
+        if (q0 < nq) {
+          c.h = (c.item / QT) % heads;
+          c.seq = b;
+          c.ks = row_start ? row_start[b] : b * S;
+          c.ke = c.ks + klen;
+          c.nb = (klen + TK - 1) / TK;
+          c.q_row = c.ks + q0;
+          c.out_row = cls_only ? b : c.q_row;  // first queries alone: one output row per sequence
+          c.n_out = nq - q0;
+          c.q_end = c.ke;
+          c.valid = true;
+          break;
+        }
+        c.item += gridDim.x;
+      }
     }
-    c.j = 0;
+  };
+  auto cursor_last = [&](const Cursor& c) {  // the step under c is the last one of its item
+    return c.jb == c.nb - 1 && (!MULTI || c.ke >= c.q_end);
   };
   auto cursor_next = [&](Cursor& c) {
     ++c.blocks_done;
-    if (++c.j < c.it.nblocks) return;
+    ++c.ji;
+    if (++c.jb < c.nb) return;
+    if (MULTI && c.ke < c.q_end) {  // the tile goes on into the next sequence
+      ++c.seq;
+      c.ks = c.ke;
+      c.ke = row_start[c.seq + 1];
+      c.nb = (c.ke - c.ks + TK - 1) / TK;
+      c.use_mask = mask != nullptr && sched[B + c.seq] != 0;
+      c.jb = 0;
+      return;
+    }
     ++c.items_done;
     c.item += gridDim.x;
     cursor_seek(c);
@@ -173,22 +210,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       Cursor c{};
       c.item = static_cast<int>(blockIdx.x);
       for (cursor_seek(c); c.valid; cursor_next(c)) {
-        if (c.j == 0) {
+        if (c.ji == 0) {
           const int qb = c.items_done & 1;
           mbar_wait(q_empty + qb, ((c.items_done >> 1) & 1) ^ 1, abort_flag, err, SITE_ATT_E);
           mbar_arrive_expect_tx(q_full + qb, Q_BYTES);  // two 64-row boxes
-          tma_load_2d(smem + SMEM_Q + qb * Q_BYTES, &tmQKV, q_full + qb, c.it.h * HD, c.it.first + c.it.q0);
-          tma_load_2d(smem + SMEM_Q + qb * Q_BYTES + Q_BYTES / 2, &tmQKV, q_full + qb, c.it.h * HD,
-                      c.it.first + c.it.q0 + 64);
+          tma_load_2d(smem + SMEM_Q + qb * Q_BYTES, &tmQKV, q_full + qb, c.h * HD, c.q_row);
+          tma_load_2d(smem + SMEM_Q + qb * Q_BYTES + Q_BYTES / 2, &tmQKV, q_full + qb, c.h * HD, c.q_row + 64);
         }
         const int kb = c.blocks_done & 1;
         const uint32_t par = ((c.blocks_done >> 1) & 1) ^ 1;
         mbar_wait(k_empty + kb, par, abort_flag, err, SITE_ATT_E);
         mbar_arrive_expect_tx(k_full + kb, KV_BYTES);
-        tma_load_2d(smem + SMEM_K + kb * KV_BYTES, &tmQKV, k_full + kb, H + c.it.h * HD, c.it.first + c.j * TK);
+        tma_load_2d(smem + SMEM_K + kb * KV_BYTES, &tmQKV, k_full + kb, H + c.h * HD, c.ks + c.jb * TK);
         mbar_wait(v_empty + kb, par, abort_flag, err, SITE_ATT_E);
         mbar_arrive_expect_tx(v_full + kb, KV_BYTES);
-        tma_load_2d(smem + SMEM_V + kb * KV_BYTES, &tmQKV, v_full + kb, 2 * H + c.it.h * HD, c.it.first + c.j * TK);
+        tma_load_2d(smem + SMEM_V + kb * KV_BYTES, &tmQKV, v_full + kb, 2 * H + c.h * HD, c.ks + c.jb * TK);
       }
     }
   } else if (warp == 5) {
@@ -201,7 +237,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       // the softmax of block blocks_done - 2, whose p_full this thread has already waited for.
       auto issue_s = [&](const Cursor& c) {
         const int qb = c.items_done & 1, kb = c.blocks_done & 1;
-        if (c.j == 0) mbar_wait(q_full + qb, (c.items_done >> 1) & 1, abort_flag, err, SITE_ATT_Q);
+        if (c.ji == 0) mbar_wait(q_full + qb, (c.items_done >> 1) & 1, abort_flag, err, SITE_ATT_Q);
         mbar_wait(k_full + kb, (c.blocks_done >> 1) & 1, abort_flag, err, SITE_ATT_K);
         tc_fence_after();
         const uint64_t da = umma_desc_sw128(sq + qb * Q_BYTES), db = umma_desc_sw128(sk + kb * KV_BYTES);
@@ -209,7 +245,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
         for (int k = 0; k < HD / 16; ++k) umma_f16(tmem_base + S_COL + kb * TK, da + 2 * k, db + 2 * k, idesc_s, k != 0);
         umma_commit(s_full + kb);
         umma_commit(k_empty + kb);
-        if (c.j == c.it.nblocks - 1) umma_commit(q_empty + qb);
+        if (cursor_last(c)) umma_commit(q_empty + qb);
       };
       // O (+)= P V over the block's 64 keys: A = P (K-major over the keys), B = V rows (MN-major)
       auto issue_pv = [&](const Cursor& c) {
@@ -221,7 +257,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
         for (int k = 0; k < TK / 16; ++k) {
           const uint64_t da = umma_desc_sw128(sp) + 2 * k;
           const uint64_t db = umma_desc_sw128_mn(sv + vb * KV_BYTES) + static_cast<uint64_t>(k) * (2048 >> 4);
-          umma_f16(tmem_base + O_COL + (c.items_done & 1) * HD, da, db, idesc_o, (c.j | k) != 0);
+          umma_f16(tmem_base + O_COL + (c.items_done & 1) * HD, da, db, idesc_o, (c.ji | k) != 0);
         }
         umma_commit(o_full);
         umma_commit(v_empty + vb);
@@ -259,7 +295,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
     // TMEM read and the stores off the path the next MMA waits on.
     bool prev = false;  // an item's output is pending
     float prev_inv = 0.f;
-    int prev_row0 = 0, prev_h = 0, prev_q0 = 0, prev_nq = 0;
+    int prev_n = 0;
+    __half* prev_out = nullptr;
     uint32_t prev_ocol = 0;
     auto finish_prev = [&]() {  // its last P.V has completed (o_full waited for): O / l -> fp16 -> staging -> stores
       uint8_t* my_row = stage + lane * 128;
@@ -281,51 +318,35 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       }
       tc_fence_before();  // the accumulator's next writer (an MMA two items on) comes after these reads
       __syncwarp();
-      __half* out_base = ctx + static_cast<size_t>(prev_row0) * H + prev_h * HD;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int rr = i * 4 + (lane >> 3), p2 = lane & 7;
-        const int qrow = prev_q0 + warp * 32 + rr;
+        const int row = warp * 32 + rr;  // row of the tile
         const uint4 t = *reinterpret_cast<const uint4*>(stage + rr * 128 + (p2 << 4));
-        if (qrow < prev_nq)
-          *reinterpret_cast<uint4*>(out_base + static_cast<size_t>(qrow) * H + ((p2 ^ (rr & 7)) << 3)) = t;
+        if (row < prev_n)
+          *reinterpret_cast<uint4*>(prev_out + static_cast<size_t>(row) * H + ((p2 ^ (rr & 7)) << 3)) = t;
       }
       __syncwarp();  // the staging rows are free for the next item
     };
     Cursor c{};
     c.item = static_cast<int>(blockIdx.x);
     for (cursor_seek(c); c.valid; cursor_next(c)) {
-      const ItemInfo& it = c.it;
-      const int j = c.j;
-      const int* mrow = mask ? mask + static_cast<size_t>(it.b) * S : nullptr;
-      if (j == 0) { m_run = -INFINITY; l_run = 0.f; }
       const uint32_t t_s = t_lane + S_COL + (c.blocks_done & 1) * TK;
       const uint32_t t_o = t_lane + O_COL + (c.items_done & 1) * HD;
-      if (j == 0 && it.use_mask) {
-        // a sequence with masked keys below its last valid one (rare): additive bias (log2 domain) of
-        // every key, staged once per item, and one flag bit per 64-key block that has any
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // everyone is done with the previous such item's bias
-        if (r == 0) *sFlags = 0u;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int kend = it.nblocks * TK;
-        uint32_t bits = 0u;
-        for (int key = r; key < kend; key += 128) {
-          float bv = 0.f;
-          if (key >= it.klen) bv = -INFINITY;
-          else if (__ldg(mrow + key) == 0) bv = -10000.0f * LOG2E;
-          sBias[key] = bv;
-          if (bv != 0.f) bits |= 1u << (key / TK);
-        }
-        if (bits) atomicOr(sFlags, bits);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
-      // plain: every key of the block is valid.  Without a mask to read, only the last block of a
-      // sequence can hold keys beyond its length, and which ones follows from the length alone.
-      const int tail = it.klen - j * TK;  // keys of this block that exist (>= 64: all)
-      const bool plain = it.use_mask ? ((*sFlags >> j) & 1u) == 0u : tail >= TK;
-      const float* bias = sBias + j * TK;
+      // In a packed tile a row takes part only in the steps of its own sequence; elsewhere its
+      // probabilities are zero and its running maximum and sum stay as they are.
+      const bool member = !MULTI || (c.q_row + r >= c.ks && c.q_row + r < c.ke);
+      const bool warp_in = !MULTI || __any_sync(0xffffffffu, member);
+      // plain: every key of the block is valid.  Only the last block of a sequence can hold keys
+      // beyond its length, and which ones follows from the length alone.  A sequence with masked keys
+      // below its last valid one (rare) takes the mask row from global memory, every lane the same word.
+      const int tail = c.ke - c.ks - c.jb * TK;  // keys of this block that exist (>= 64: all)
+      const bool plain = !c.use_mask && tail >= TK;
       mbar_wait(s_full + (c.blocks_done & 1), (c.blocks_done >> 1) & 1, abort_flag, err, SITE_ATT_S);
       tc_fence_after();
+      float alpha = 1.0f;
+      uint4 pk[8];
+      if (warp_in) {
       // the 64 scores of the row: one TMEM round trip, kept in registers for both steps
       uint32_t v[2][32];
       tmem_ld32(t_s, v[0]);
@@ -345,22 +366,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
               mx4[q] = max3(mx4[q], __uint_as_float(v[ch][i + 2 * q]), __uint_as_float(v[ch][i + 2 * q + 1]));
 #pragma unroll
         for (int q = 0; q < 4; ++q) mx4[q] *= scale;  // the scale itself is folded into the exponential below
-      } else if (it.use_mask) {
-        const uint64_t sc2 = pack_f32x2(scale, scale);
+      } else if (c.use_mask) {
+        const int* mk = mask + static_cast<size_t>(c.seq) * S + c.jb * TK;
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch)
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 b4 = *reinterpret_cast<const float4*>(bias + ch * 32 + i);
-            float x0, x1, x2, x3;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[ch][i]), __uint_as_float(v[ch][i + 1])), sc2,
-                                   pack_f32x2(b4.x, b4.y)), x0, x1);
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[ch][i + 2]), __uint_as_float(v[ch][i + 3])), sc2,
-                                   pack_f32x2(b4.z, b4.w)), x2, x3);
-            v[ch][i] = __float_as_uint(x0); v[ch][i + 1] = __float_as_uint(x1);
-            v[ch][i + 2] = __float_as_uint(x2); v[ch][i + 3] = __float_as_uint(x3);
-            mx4[(i >> 2) & 1] = max3(mx4[(i >> 2) & 1], x0, x1);
-            mx4[2 + ((i >> 2) & 1)] = max3(mx4[2 + ((i >> 2) & 1)], x2, x3);
+          for (int i = 0; i < 32; ++i) {
+            float bias = -INFINITY;  // additive, log2 domain
+            if (ch * 32 + i < tail) bias = __ldg(mk + ch * 32 + i) == 0 ? -10000.0f * LOG2E : 0.f;
+            const float x = fmaf(__uint_as_float(v[ch][i]), scale, bias);
+            v[ch][i] = __float_as_uint(x);
+            mx4[i & 3] = fmaxf(mx4[i & 3], x);
           }
       } else {
         // last block of a sequence without masked keys: keys at or beyond `tail` do not exist
@@ -377,21 +393,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       // Reference point of the exponentials.  It only has to keep exp2 in range, so it follows the
       // running maximum lazily: it moves (and O is rescaled in TMEM, a round trip) only when a block
       // exceeds it by more than 8 in the log2 domain; until then probabilities may reach 2^8, which
-      // fp16 and the fp32 sums hold without loss.  The first block of an item sets it exactly.
-      float alpha = 1.0f;
-      if (j == 0) {
-        m_run = mx;  // finite: key 0 of block 0 is never masked with -inf
+      // fp16 and the fp32 sums hold without loss.  The first block of a sequence sets it exactly.
+      float m_new = m_run, l_new = l_run;
+      if (c.jb == 0) {
+        m_new = mx;  // finite: key 0 of block 0 is never masked with -inf
+        l_new = 0.f;
       } else if (mx > m_run + 8.0f) {
         alpha = ex2_approx(m_run - mx);
-        m_run = mx;
+        m_new = mx;
+        l_new *= alpha;
       }
-      const float m_new = m_run;
-      l_run *= alpha;
       // P = exp2(x - max) in registers first: nothing below depends on the previous P.V yet
       uint64_t l2[2] = {0ull, 0ull};  // two packed pairs of partial sums
       const float e_scale = plain ? scale : 1.0f;  // plain blocks still hold the raw dot products
       const uint64_t es2 = pack_f32x2(e_scale, e_scale), nm2 = pack_f32x2(-m_new, -m_new);
-      uint4 pk[8];
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         float p[32];
@@ -414,15 +429,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       float l4[4];
       unpack_f32x2(l2[0], l4[0], l4[1]);
       unpack_f32x2(l2[1], l4[2], l4[3]);
-      l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      l_new += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      if (member) {
+        m_run = m_new;
+        l_run = l_new;
+      } else {  // a row of another sequence: what was computed from its scores is dropped
+        alpha = 1.0f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) pk[q] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) pk[q] = make_uint4(0u, 0u, 0u, 0u);
+      }
       // The P tile (and, for a rescale, O) may be touched only after the P.V that last read it has
-      // completed: the previous block's, or the last block's of the previous item.
-      if (j > 0 || prev) {
+      // completed: the previous step's, or the last step's of the previous item.
+      if (c.ji > 0 || prev) {
         mbar_wait(o_full, o_waits & 1, abort_flag, err, SITE_ATT_O);
         ++o_waits;
         tc_fence_after();
       }
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+      if (c.ji > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
         uint32_t o[2][32];
         tmem_ld32(t_o, o[0]);
         tmem_ld32(t_o + 32, o[1]);
@@ -441,17 +468,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
       tc_fence_before();
       __syncwarp();              // every lane's rows are written and fenced: one arrival for the warp
       if (lane == 0) mbar_arrive(p_full);
-      if (j == 0 && prev) {      // the previous item's accumulator is complete (waited for above)
+      if (c.ji == 0 && prev) {   // the previous item's accumulator is complete (waited for above)
         finish_prev();
         prev = false;
       }
-      if (j == it.nblocks - 1) {
+      if (cursor_last(c)) {
         prev = true;
         prev_inv = 1.0f / l_run;
-        prev_row0 = cls_only ? it.b : it.first;
-        prev_h = it.h;
-        prev_q0 = it.q0;
-        prev_nq = it.nq;
+        prev_out = ctx + static_cast<size_t>(c.out_row) * H + c.h * HD;
+        prev_n = c.n_out;
         prev_ocol = O_COL + (c.items_done & 1) * HD;
       }
     }
@@ -479,16 +504,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
 }  // namespace
 
 // Which 16-bit attention kernel a forward pass of padded length S uses.  The tcgen05 kernel works on
-// 128-query tiles of 64-key blocks whatever the number of live rows in them, so it wins where the
-// tiles are full and loses where a batch's rows are much shorter than the tile grid.  Measured per
-// layer, BERT-large unless noted, in microseconds for tcgen05 / persistent mma.sync / mma.sync with
-// one CTA per item:  S = 512 full rows 95 / - / 165;  S = 512 lengths 64..512: 137 / - / 176;
-// S = 128 full rows 42 / 51 / 59;  BERT-base S = 128 lengths ~N(60, 25): 50 / 42 / 57;
-// S = 200 lengths 16..200: 88 / 57 / 74;  S = 64 lengths 8..64: 185 / 132 / 125.
-// The lengths live on the device, so the choice uses S alone: tcgen05 for long sequences or an S
-// of at least 96 that fills its last query tile to 85 % or more, the persistent kernel otherwise
-// (the per-item kernel beyond the length the persistent one can hold).
-// CUDABERT_ATTENTION=tc / persist / mma forces one kernel.
+// 128-query tiles of 64-key blocks whatever the number of live rows in them.  With one sequence per
+// tile it wins where the tiles are full and loses where a batch's rows are much shorter than the
+// tile grid; with packed tiles (rows of several sequences in one tile, every tile walking the key
+// blocks of each sequence it cuts) the tiles are full but a sequence cut by two tiles is walked
+// twice, which pays for short sequences only.  Measured per layer, BERT-large (16 heads), in
+// microseconds for tcgen05 packed tiles / tcgen05 one sequence per tile / persistent mma.sync:
+//   1024 x 64 full rows 123 / 150 / 151;   1024 x 64 lengths 8..64: 133 / 167 / 142;
+//   2048 x 32 lengths 4..32: 216 / 332 / 278;   800 x 80 lengths 8..80: 132 / 150 / 137;
+//   512 x 96 lengths 8..96: 105 / 106 / 100;   512 x 96 full rows 154 / 129 / 157;
+//   256 x 128 lengths 16..128: 77 / 72 / 77;   110 x 128 full rows 31 / 33 / 45;
+//   128 x 200 lengths 16..200: 60 / 79 / 60;   110 x 192 full rows 60 / 65 / 75;
+//   55 x 256 full rows 44 / 48 / 68;   32 x 512 full rows 92 / 84 / 200 (one CTA per item);
+//   32 x 512 lengths 64..512: 70 / 74 / 106 (one CTA per item).
+// The lengths live on the device, so the choice uses S alone: tcgen05 with packed tiles up to S = 80;
+// beyond, tcgen05 with one sequence per tile for long sequences (S >= 384) or an S that fills its
+// last query tile to 85 % or more, the persistent kernel otherwise (the per-item kernel beyond the
+// length the persistent one can hold).
+// CUDABERT_ATTENTION=tc / persist / mma forces one kernel; CUDABERT_ATTENTION_TILES=packed / sequence
+// forces the tcgen05 kernel's tiles (both give the same bits).
 int attention_kernel_for(int S) {
   static const int forced = []() -> int {
     const char* e = std::getenv("CUDABERT_ATTENTION");
@@ -501,7 +535,8 @@ int attention_kernel_for(int S) {
   int k = forced;
   if (k < 0) {
     const int tiles = (S + TQ - 1) / TQ;
-    k = (S >= 384 || (S >= 96 && S * 100 >= tiles * TQ * 85)) ? ATT_KERNEL_TC : ATT_KERNEL_PERSIST;
+    k = (S <= ATC_PACKED_MAX_S || S >= 384 || (S >= 96 && S * 100 >= tiles * TQ * 85)) ? ATT_KERNEL_TC
+                                                                                         : ATT_KERNEL_PERSIST;
   }
   if (k == ATT_KERNEL_PERSIST && !attention_persist_fits(S)) k = ATT_KERNEL_MMA;
   return k;
@@ -519,14 +554,31 @@ int attention_f16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_l
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr_set[dev].load(std::memory_order_acquire)) {
-    if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM) !=
+            cudaSuccess)
       return -2;
     if (dev >= 0 && dev < 64) attr_set[dev].store(true, std::memory_order_release);
   }
-  const long long items = static_cast<long long>(B) * heads * ((S + TQ - 1) / TQ);
+  // Short sequences in packed rows (with the tile table of row_layout): tiles of 128 consecutive
+  // rows, whatever sequences they belong to.  Otherwise one sequence per tile.
+  static const int tiles_forced = []() {  // CUDABERT_ATTENTION_TILES=packed / sequence forces one (same bits)
+    const char* e = std::getenv("CUDABERT_ATTENTION_TILES");
+    return !e ? -1 : e[0] == 'p' ? 1 : e[0] == 's' ? 0 : -1;
+  }();
+  const bool want_multi = tiles_forced >= 0 ? tiles_forced == 1 : S <= ATC_PACKED_MAX_S;
+  const bool multi = row_start != nullptr && sched != nullptr && !cls_only && want_multi;
+  const long long tiles = multi ? (static_cast<long long>(B) * S + TQ - 1) / TQ
+                                : static_cast<long long>(B) * ((S + TQ - 1) / TQ);
+  const long long items = tiles * heads;
   const int grid = static_cast<int>(items < 2LL * num_sms ? items : 2LL * num_sms);
-  return launch_pdl(attention_tc_kernel, dim3(grid), dim3(ATC_THREADS), ATC_SMEM, stream, *tm_qkv, mask, kv_len,
-                    row_start, sched, ctx, B, S, heads, cls_only, err_flag) == cudaSuccess ? 1 : -3;
+  const cudaError_t e =
+      multi ? launch_pdl(attention_tc_kernel<true>, dim3(grid), dim3(ATC_THREADS), ATC_SMEM, stream, *tm_qkv, mask,
+                         kv_len, row_start, sched, ctx, B, S, heads, cls_only, err_flag)
+            : launch_pdl(attention_tc_kernel<false>, dim3(grid), dim3(ATC_THREADS), ATC_SMEM, stream, *tm_qkv, mask,
+                         kv_len, row_start, sched, ctx, B, S, heads, cls_only, err_flag);
+  return e == cudaSuccess ? 1 : -3;
 }
 
 }  // namespace cb

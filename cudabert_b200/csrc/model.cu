@@ -446,7 +446,7 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   const size_t o_ints = slot(3 * ct * sizeof(int));
   const size_t o_kv = slot(static_cast<size_t>(cbatch) * sizeof(int));
   const size_t o_rs = slot((static_cast<size_t>(cbatch) + 1) * sizeof(int));
-  const size_t o_sched = slot(2 * static_cast<size_t>(cbatch) * sizeof(int));
+  const size_t o_sched = slot((2 * static_cast<size_t>(cbatch) + ct / 128 + 2) * sizeof(int));  // + tile table
   const size_t o_xf = slot(ct * H_ * sizeof(float));
   const size_t o_x1f = slot(ct * H_ * sizeof(float));
   const size_t o_y = slot(ct * H_ * (lowp ? 2 : 4));

@@ -176,7 +176,7 @@ class Model {
   int cap_batch_ = 0;
   void* arena_ = nullptr;
   int *ids_ = nullptr, *kv_len_ = nullptr, *err_dev_ = nullptr;  // ids_: 3 * cap_tokens ints (ids | seg | mask)
-  int* att_sched_ = nullptr;  // 2 * cap_batch: work order and mask flags for the TMA-fed attention kernels
+  int* att_sched_ = nullptr;  // work order, mask flags (cap_batch each) and tile table (cap_tokens / 128) of the TMA-fed attention kernels
   // packed layout: padding tokens get no rows; row_start_[b] is the first row of sequence b and
   // row_start_[B] the live row count, all computed on the device (no host round trip)
   bool packed_ = true;

@@ -85,7 +85,9 @@ CUDABERT_API int cudabert_hidden_size(void* model);
 /* Which attention kernel a 16-bit forward pass of this padded sequence length runs (the lengths of the
  * sequences live on the device, so the choice depends on the padded length alone; environment
  * CUDABERT_ATTENTION=tc|persist|mma forces one): 1 = mma.sync, one CTA per sequence and head;
- * 2 = tcgen05; 3 = mma.sync, persistent.                                                             */
+ * 2 = tcgen05 (padded lengths up to 80 with 128-row tiles that hold rows of several sequences,
+ * CUDABERT_ATTENTION_TILES=packed|sequence forces either; the bits do not depend on it);
+ * 3 = mma.sync, persistent.                                                                          */
 CUDABERT_API int cudabert_attention_kernel_for(int seq_length);
 CUDABERT_API int cudabert_num_classes(void* model);
 
@@ -221,7 +223,10 @@ CUDABERT_API int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W
  * out), 1 = 16-bit mma.sync kernel (one CTA per sequence and head), 2 = 16-bit tcgen05 kernel, 3 = 16-bit
  * mma.sync kernel, persistent (S <= 256); the 16-bit kernels take fp16 Q, K, V and write fp16.  Adding 16
  * to a 16-bit kernel's number computes only the first query of every sequence and writes it to row b of
- * ctx_dev, then [B, H] (the last encoder layer of a pooler-only pass). */
+ * ctx_dev, then [B, H] (the last encoder layer of a pooler-only pass).  Adding 32 takes qkv_dev, and
+ * writes ctx_dev, in the packed layout of a forward pass: the valid rows of the sequences back to back
+ * (a sequence without a valid key counting as S rows), in buffers that still hold B * S rows; the
+ * tcgen05 kernel then works on tiles of 128 consecutive rows whatever sequences they belong to. */
 CUDABERT_API int cudabert_k_attention(int kernel, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads);
 /* No counterpart in the reference.  cudabert_k_attention for callers that must not allocate device
  * memory: code that runs where cudaMalloc is not allowed (inside another framework's memory pool

@@ -217,6 +217,42 @@ def test_attention_first_query_only(pybert, kernel, B, S, heads, mode):
     assert torch.equal(first, full.view(B, S, H)[:, 0])
 
 
+@pytest.mark.parametrize("kernel", [2, 1, 3, 0])
+@pytest.mark.parametrize("B,S,heads,mode", [(37, 200, 16, "prefix"), (300, 64, 12, "prefix"), (300, 64, 12, "holes"),
+                                            (9, 256, 16, "zero_row"), (5, 512, 16, "prefix"), (64, 17, 12, "none"),
+                                            (700, 8, 12, "prefix"), (3, 130, 16, "full"), (128, 128, 12, "holes")])
+def test_attention_packed_rows(pybert, kernel, B, S, heads, mode):
+    """A forward pass keeps only the valid rows, back to back.  Every attention kernel must give a
+    row the same bits in that layout as with one padded block of S rows per sequence; for the
+    tcgen05 kernel this is the case where a tile of 128 query rows holds rows of several sequences
+    (up to 128 of them) and walks the key blocks of each."""
+    if kernel == 3 and S > 256:
+        pytest.skip("the persistent kernel holds sequences of up to 256 tokens")
+    g = torch.Generator(device="cuda").manual_seed(B * 17 + S)
+    H = heads * 64
+    x = torch.randn(B * S, 3 * H, device="cuda", generator=g)
+    x = x.half() if kernel else x
+    mask = _mask(B, S, mode, g)
+    mptr = None if mask is None else mask.data_ptr()
+    if mask is None:
+        lens = torch.full((B,), S, dtype=torch.long)
+    else:
+        pos = torch.arange(1, S + 1, device="cuda")[None, :]
+        lens = (mask.long() * pos).max(dim=1).values.cpu()
+        lens[lens == 0] = S      # no valid key: the sequence keeps all its rows
+    rows = torch.cat([torch.arange(b * S, b * S + int(lens[b])) for b in range(B)]).cuda()
+    padded = torch.full((B * S, H), float("nan"), device="cuda", dtype=x.dtype)
+    assert pybert.k_attention(kernel, x.data_ptr(), mptr, padded.data_ptr(), B, S, heads) == 0
+    xp = torch.zeros_like(x)
+    xp[: rows.numel()] = x[rows]
+    packed = torch.full((B * S, H), float("nan"), device="cuda", dtype=x.dtype)
+    assert pybert.k_attention(kernel + 32, xp.data_ptr(), mptr, packed.data_ptr(), B, S, heads) == 0
+    got = packed[: rows.numel()]
+    assert torch.isfinite(got.float()).all()
+    assert torch.equal(got, padded[rows])
+    assert torch.isnan(packed[rows.numel():].float()).all()      # nothing is written beyond the packed rows
+
+
 @pytest.mark.parametrize("bf16", [1, 0])
 @pytest.mark.parametrize("H", [768, 1024])
 def test_embed_layernorm_and_layernorm(pybert, bf16, H):

@@ -17,7 +17,7 @@ BASE_CASES = ["c0_affine", "c2_small", "edge_s17", "edge_b1s1", "edge_nomask", "
 LARGE_CASES = ["c1_small", "c3_small", "c4_small"]
 SWITCHES = ("CUDABERT_PACK", "CUDABERT_GRAPH", "CUDABERT_PDL", "CUDABERT_LAST_LAYER", "CUDABERT_ATTENTION",
             "CUDABERT_GEMM_PAIR", "CUDABERT_GEMM_SMALL_TILES", "CUDABERT_PRECISION", "CUDABERT_LN",
-            "CUDABERT_FP8_OPERAND", "SWITCH_CHILD_PRECISION")
+            "CUDABERT_FP8_OPERAND", "CUDABERT_ATTENTION_TILES", "SWITCH_CHILD_PRECISION")
 
 
 @pytest.fixture(scope="module")
@@ -73,6 +73,18 @@ def test_kernel_choice_switches_stay_close(run_with, switch):
     for case, (to_gold, to_default) in worst.items():
         assert to_gold <= 2e-2, "%s, case %s vs golden: %g" % (switch, case, to_gold)
         assert to_default <= 1.5e-2, "%s, case %s vs default: %g" % (switch, case, to_default)
+
+
+def test_attention_tile_switch_keeps_every_bit(run_with):
+    """The tcgen05 attention kernel either gives every sequence its own 128-query tiles or cuts the
+    packed rows into tiles that hold rows of several sequences.  A row walks the key blocks of its
+    own sequence in the same order either way: with the kernel forced for every length, the two
+    must agree in every bit (sequences of one and of several key blocks, masks with holes, a row
+    without valid key)."""
+    packed = run_with(CUDABERT_ATTENTION="tc", CUDABERT_ATTENTION_TILES="packed")
+    sequence = run_with(CUDABERT_ATTENTION="tc", CUDABERT_ATTENTION_TILES="sequence")
+    for case in BASE_CASES + LARGE_CASES:
+        np.testing.assert_array_equal(packed[case], sequence[case], err_msg=case)
 
 
 def test_fp8_operand_switch_keeps_every_bit(run_with):
