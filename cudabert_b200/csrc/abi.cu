@@ -251,6 +251,7 @@ int cudabert_profile_get(void* model, int kernel_class, double* total_ms, long* 
 int cudabert_k_gemm_tcgen05(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev, int flags,
                          const float* bias_dev, const void* residual_dev, const float* colscale_dev, int* err_dev) {
   if (!A_dev || !W_dev || !out_dev || M <= 0 || N <= 0 || K <= 0 || lda < K) return 1;
+  if (flags & cb::EPI_SPLIT3) return 1;  // operands of three planes: cudabert_k_gemm_f32_tensor builds them
   CUtensorMap tmA, tmW;
   if (!cb::make_tmap_16bit_kmajor(&tmA, A_dev, M, K, static_cast<uint64_t>(lda) * 2, 128)) return 2;
   if (flags & cb::EPI_W_FP8) {
@@ -289,6 +290,44 @@ int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, 
   const int n = cb::gemm_f32(A_dev, lda, W_dev, M, N, K, out_dev, N, epi, nullptr, nullptr);
   if (n < 0) return 3;
   return cudaDeviceSynchronize() == cudaSuccess ? 0 : 4;
+}
+
+int cudabert_k_gemm_f32_tensor(const float* A_dev, int lda, const float* W_dev, int M, int N, int K, float* out_dev,
+                               int flags, const float* bias_dev, const float* residual_dev) {
+  if (!A_dev || !W_dev || !out_dev || M <= 0 || N <= 0 || K <= 0 || lda < K || (N % 128) || (K % 64) || (lda % 4))
+    return 1;
+  // the bf16 planes of both operands, then the tcgen05 GEMM over them
+  __nv_bfloat16 *a3 = nullptr, *w3 = nullptr;
+  int* err = nullptr;
+  int rc = 0;
+  if (cudaMalloc(&a3, static_cast<size_t>(M) * K * 6) != cudaSuccess ||
+      cudaMalloc(&w3, static_cast<size_t>(N) * K * 6) != cudaSuccess || cudaMalloc(&err, sizeof(int)) != cudaSuccess)
+    rc = 2;
+  CUtensorMap tmA, tmW;
+  if (!rc && (!cb::make_tmap_16bit_kmajor(&tmA, a3, M, 3ull * K, 6ull * K, 128) ||
+              !cb::make_tmap_16bit_kmajor(&tmW, w3, N, 3ull * K, 6ull * K, cb::gemm_split_w_box_rows(N))))
+    rc = 2;
+  if (!rc) {
+    cudaMemset(err, 0, sizeof(int));
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cb::GemmEpilogue epi;
+    epi.flags = (flags & (cb::EPI_BIAS | cb::EPI_GELU | cb::EPI_RESIDUAL | cb::EPI_TANH)) | cb::EPI_OUT_F32 | cb::EPI_SPLIT3;
+    epi.bias = bias_dev;
+    epi.residual = residual_dev;
+    if (cb::transpose_split_bf16x3(W_dev, w3, K, N, nullptr) < 0 ||
+        cb::split_bf16x3(A_dev, lda, a3, M, K, nullptr, nullptr) < 0 ||
+        cb::gemm_tcgen05(&tmA, &tmW, M, N, K, out_dev, N, epi, err, sms, nullptr, nullptr) < 0)
+      rc = 3;
+    if (cudaDeviceSynchronize() != cudaSuccess) rc = 4;
+    int herr = 0;
+    if (!rc && (cudaMemcpy(&herr, err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess || herr)) rc = 5;
+  }
+  cudaFree(a3);
+  cudaFree(w3);
+  cudaFree(err);
+  return rc;
 }
 
 int cudabert_k_attention(int kernel, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads) {

@@ -263,6 +263,23 @@ __device__ __forceinline__ void stage_tile_vectors(float* __restrict__ sbias, fl
   asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
 }
 
+// The k-blocks a tile walks.  Plain: K / BK blocks at columns 0, BK, ... of both operands.  EPI_SPLIT3
+// (operands of three bf16 planes of K columns each): six passes over K, one per cross term, the
+// smallest terms first so that the fp32 accumulator keeps them: (A plane, W plane) = (2, 0), (0, 2),
+// (1, 1), (1, 0), (0, 1), (0, 0).
+struct KWalk {
+  int per, kblocks, K;
+  bool split;
+  __device__ KWalk(int K_, bool split_) : per(K_ / BK), kblocks(split_ ? 6 * (K_ / BK) : K_ / BK), K(K_), split(split_) {}
+  __device__ __forceinline__ int col(int kb, uint32_t planes) const {
+    if (!split) return kb * BK;
+    const int pass = kb / per;
+    return static_cast<int>((planes >> (4 * pass)) & 15u) * K + (kb - pass * per) * BK;
+  }
+  __device__ __forceinline__ int a_col(int kb) const { return col(kb, 0x001102u); }
+  __device__ __forceinline__ int w_col(int kb) const { return col(kb, 0x010120u); }
+};
+
 template <int BN, int FLAGS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, int M, int N,
@@ -315,7 +332,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int tiles_n = N / BN;
   const int tiles_m = (M + BM - 1) / BM;
   const int num_tiles = tiles_m * tiles_n;
-  const int kblocks = K / BK;
+  const KWalk kw(K, (((FLAGS >= 0) ? FLAGS : flags) & EPI_SPLIT3) != 0);
+  const int kblocks = kw.kblocks;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -328,8 +346,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           mbar_wait(empty_bar + stage, phase ^ 1, abort_flag, err, SITE_EMPTY);
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
           mbar_arrive_expect_tx(full_bar + stage, C::STAGE_BYTES);
-          tma_load_2d(sa, &tmA, full_bar + stage, kb * BK, m0);
-          tma_load_2d(sa + C::A_BYTES, &tmW, full_bar + stage, kb * BK, n0);
+          tma_load_2d(sa, &tmA, full_bar + stage, kw.a_col(kb), m0);
+          tma_load_2d(sa + C::A_BYTES, &tmW, full_bar + stage, kw.w_col(kb), n0);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -493,7 +511,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int tiles_n = N / BN;
   const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
   const int num_tiles = tiles_m * tiles_n;
-  const int kblocks = K / BK;
+  const KWalk kw(K, !W8 && (((FLAGS >= 0) ? FLAGS : flags) & EPI_SPLIT3) != 0);
+  const int kblocks = kw.kblocks;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
@@ -509,12 +528,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
           if (leader) mbar_arrive_expect_tx(full_bar + stage, W8 ? 2 * C::A_BYTES : 2 * C::STAGE_BYTES);
           const uint32_t leader_full = mapa_u32(smem_u32(full_bar + stage), 0);
-          tma_load_2d_pair(sa, &tmA, leader_full, kb * BK, m0);
+          tma_load_2d_pair(sa, &tmA, leader_full, kw.a_col(kb), m0);
           if (W8) {  // E4M3 bytes -> the stage's raw buffer; the converter warps take it from there
             mbar_arrive_expect_tx(raw_full_bar + stage, C::RAW_BYTES);
             tma_load_2d(sa + C::A_BYTES, &tmW, raw_full_bar + stage, kb * BK, n0);
           } else {
-            tma_load_2d_pair(sa + C::A_BYTES, &tmW, leader_full, kb * BK, n0);
+            tma_load_2d_pair(sa + C::A_BYTES, &tmW, leader_full, kw.w_col(kb), n0);
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
@@ -664,6 +683,9 @@ constexpr int F_LIN8 = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_COLSCALE | EPI_
 constexpr int F_FFN18 = F_LIN8 | EPI_GELU;
 constexpr int F_LIN8W = F_LIN8 & ~EPI_W_FP8;    // FP8-weight mode with the weights widened to fp16 at load
 constexpr int F_FFN18W = F_FFN18 & ~EPI_W_FP8;
+constexpr int F_S3 = EPI_BIAS | EPI_OUT_F32 | EPI_SPLIT3;   // fp32 mode on the tensor cores: QKV
+constexpr int F_S3_RES = F_S3 | EPI_RESIDUAL;               // attention-output, FFN2 (+ fp32 residual)
+constexpr int F_S3_FFN1 = F_S3 | EPI_GELU;
 
 template <int BN, int FLAGS>
 int launch_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
@@ -697,12 +719,12 @@ int launch(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, 
 
 // Number of CTA pairs that can be resident at once on this device (pairs need two SMs of one
 // GPC); a persistent grid larger than that would run its last pairs after all the others.
-template <int FLAGS, bool W8>
+template <int FLAGS, bool W8, int BN>
 int max_resident_pairs(int dev) {
   static std::atomic<int> cached[64] = {};  // per device; racing threads compute the same value
   if (dev >= 0 && dev < 64 && cached[dev].load(std::memory_order_acquire) > 0) return cached[dev].load();
-  using C = PairCfg<256, W8>;
-  if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<256, FLAGS, W8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  using C = PairCfg<BN, W8>;
+  if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN, FLAGS, W8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            C::SMEM_BYTES) != cudaSuccess)
     return -1;
   cudaLaunchConfig_t cfg = {};
@@ -717,7 +739,7 @@ int max_resident_pairs(int dev) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<256, FLAGS, W8>, &cfg) != cudaSuccess || n <= 0) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<BN, FLAGS, W8>, &cfg) != cudaSuccess || n <= 0) {
     cudaGetLastError();
     return -1;
   }
@@ -725,17 +747,17 @@ int max_resident_pairs(int dev) {
   return n;
 }
 
-template <int FLAGS, bool W8 = false>
+template <int FLAGS, bool W8 = false, int BN = 256>
 int launch_pair_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
                     const GemmEpilogue& epi, int* err_flag, const int* m_dev, cudaStream_t stream) {
-  using C = PairCfg<256, W8>;
+  using C = PairCfg<BN, W8>;
   int dev = 0;
   cudaGetDevice(&dev);
-  const int pairs = max_resident_pairs<FLAGS, W8>(dev);
+  const int pairs = max_resident_pairs<FLAGS, W8, BN>(dev);
   if (pairs <= 0) return -2;
-  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * (N / 256);
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * (N / BN);
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  return launch_pdl(gemm_tcgen05_pair_kernel<256, FLAGS, W8>, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, stream, *tmA,
+  return launch_pdl(gemm_tcgen05_pair_kernel<BN, FLAGS, W8>, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, stream, *tmA,
                     *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev) ==
                  cudaSuccess ? 1 : -3;
 }
@@ -749,7 +771,21 @@ int launch_pair(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, in
     case F_FFN18: return launch_pair_one<F_FFN18, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_LIN8W: return launch_pair_one<F_LIN8W>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_FFN18W: return launch_pair_one<F_FFN18W>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_S3:
+      if (gemm_split_block_n(N) == 128)
+        return launch_pair_one<F_S3, false, 128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+      return launch_pair_one<F_S3>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_S3_RES:
+      if (gemm_split_block_n(N) == 128)
+        return launch_pair_one<F_S3_RES, false, 128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+      return launch_pair_one<F_S3_RES>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_S3_FFN1:
+      if (gemm_split_block_n(N) == 128)
+        return launch_pair_one<F_S3_FFN1, false, 128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+      return launch_pair_one<F_S3_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     default:
+      if ((epi.flags & EPI_SPLIT3) && gemm_split_block_n(N) == 128)
+        return launch_pair_one<-1, false, 128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
       if (epi.flags & EPI_W_FP8) return launch_pair_one<-1, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
       return launch_pair_one<-1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   }
@@ -772,6 +808,12 @@ int wait_timeout_probe(int* err_flag, unsigned long long limit_ns, cudaStream_t 
 }
 
 int gemm_block_n(int N) { return (N % 256 == 0) ? 256 : 128; }
+
+// Tile width of the three-plane (fp32) GEMM.  Its k loop is six times as long, so with few rows the
+// tiles of a narrow output are few and long; 256 x 128 tiles double their number.  The choice goes by N
+// alone: what a row's result is must not depend on how many rows share its batch.
+int gemm_split_block_n(int N) { return (N % 256 == 0 && N > 1024) ? 256 : 128; }
+int gemm_split_w_box_rows(int N) { return gemm_split_block_n(N) / 2; }
 
 static bool small_tiles_enabled() {
   static const bool on = [] {
@@ -824,6 +866,7 @@ int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, i
   if ((epi.flags & EPI_BIAS) && !epi.bias) return -1;
   if ((epi.flags & EPI_RESIDUAL) && !epi.residual) return -1;
   if ((epi.flags & EPI_COLSCALE) && !epi.colscale) return -1;
+  if ((epi.flags & EPI_SPLIT3) && (epi.flags & (EPI_IN_F16 | EPI_W_FP8))) return -1;  // the planes are bf16
   // Few rows: a CTA pair's 256 x 256 tiles are too few to occupy the SMs, and the k loop of one
   // tile is then the whole run time.  Single CTAs with 128 x 128 tiles have a k loop half as long
   // and four times as many tiles (BERT-base, 8 x 128 tokens: 0.80 against 0.88 ms per pass; one
@@ -838,6 +881,8 @@ int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, i
     if (N % 256 != 0 || !(epi.flags & EPI_IN_F16)) return -1;
     return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   }
+  if (epi.flags & EPI_SPLIT3)  // always CTA pairs, tile width by N alone (gemm_split_block_n)
+    return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   if (small_tiles_enabled() && gemm_uses_pairs(N) && gemm_w_box_rows(N) == 128) {
     const long pairs = num_sms / 2 > 0 ? num_sms / 2 : 1;
     const long tiles_p = static_cast<long>((M + 2 * BM - 1) / (2 * BM)) * (N / 256);

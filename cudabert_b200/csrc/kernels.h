@@ -67,9 +67,18 @@ enum EpiFlags : int {
   EPI_OUT_F16 = 64,  // write fp16 instead of bf16 (tcgen05 GEMM only)
   EPI_WSCALE = 128,  // multiply the accumulator by 1 / W_CONTAINER_SCALE (weights held as scaled fp16, below)
   EPI_IN_F16 = 256,  // A and W are fp16 (tcgen05 GEMM only; bf16 otherwise)
-  EPI_W_FP8 = 512    // W is E4M3 bytes [N, K] (map from make_tmap_u8_kmajor), widened to fp16 inside the
+  EPI_W_FP8 = 512,   // W is E4M3 bytes [N, K] (map from make_tmap_u8_kmajor), widened to fp16 inside the
                      // kernel; needs EPI_IN_F16 and N % 256 == 0
+  EPI_SPLIT3 = 1024  // fp32 product on the tensor cores: A [M, 3 K] and W [N, 3 K] each hold three bf16 planes
+                     // side by side (see split_bf16x3); the kernel sums the six leading cross terms over K
 };
+
+// fp32 on the 16-bit tensor-core path.  An fp32 number is the sum of three bf16 numbers, x = x0 + x1 +
+// x2 with x0 = bf16(x), x1 = bf16(x - x0), x2 = bf16(x - x0 - x1) (the subtractions are exact; bf16 has
+// fp32's exponent range, so nothing needs scaling); what is left is below 2^-24 |x|.  A product of two
+// bf16 numbers is exact in the tensor core's fp32 accumulator, so
+//   a . w = a2 w0 + a0 w2 + a1 w1 + a1 w0 + a0 w1 + a0 w0  (+ terms below 2^-24 |a| |w|, dropped)
+// is a GEMM over 6 K with bf16 operands and fp32 accumulation, the small terms first.
 
 // The encoder's dense weights are ROUNDED to bf16 (8 significand bits: the weight format of the bf16
 // mode) and HELD as fp16 numbers, multiplied by this power of two so that even the smallest of them
@@ -102,6 +111,10 @@ int wait_timeout_probe(int* err_flag, unsigned long long limit_ns, cudaStream_t 
 // Box rows the W tensor map must be encoded with for the kernel variant that gemm_tcgen05
 // will pick for this N (128 when CTA pairs each load half of a 256-row tile, else gemm_block_n).
 int gemm_w_box_rows(int N);
+// The same for the W operand of an EPI_SPLIT3 GEMM ([N, 3 K] bf16 planes): always CTA pairs, with tiles
+// 256 wide for N > 1024 and 128 wide otherwise.
+int gemm_split_block_n(int N);
+int gemm_split_w_box_rows(int N);
 // Encode a 2-D tiled map over a row-major matrix of 16-bit elements [rows, cols] with
 // `row_stride_bytes` between rows, box = 64 columns (128 bytes, 128-byte swizzle) x `box_rows` rows.
 bool make_tmap_16bit_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
@@ -190,6 +203,13 @@ int transpose_round_bf16(const float* src, __half* dst, int K, int N, cudaStream
 int quantize_fp8_weight(const float* src, uint8_t* dst_q, __half* dst_wide, float* scale_out, int K, int N,
                         cudaStream_t stream);
 int fill_f32(float* dst, float value, size_t n, cudaStream_t stream);
+// The three bf16 planes of an fp32 weight matrix, K-contiguous: dst[n, p K + k] = plane p of src[k, n]
+// (dst rows of 3 K elements; the row offset lets Q, K, V be packed into one operand).
+int transpose_split_bf16x3(const float* src, __nv_bfloat16* dst, int K, int N, cudaStream_t stream);
+// The three bf16 planes of fp32 activations: dst[m, p K + k] = plane p of src[m * lds + k] for the
+// first `rows` rows (at most *rows_dev of them when rows_dev is given).
+int split_bf16x3(const float* src, int lds, __nv_bfloat16* dst, int rows, int K, const int* rows_dev,
+                 cudaStream_t stream);
 
 // Message that cudabert_last_error(NULL) returns on the calling thread.
 void set_thread_error(const std::string& msg);

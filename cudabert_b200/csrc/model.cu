@@ -91,6 +91,10 @@ bool Model::init(bool large, int gpu, int max_batch, int max_seq, const std::str
     // 1024 x 64 batches of BERT-large 25.2 against 28.9 ms per pass).  Default: the GEMM reads the E4M3 bytes.
     const char* f8 = std::getenv("CUDABERT_FP8_OPERAND");
     fp8_widened_ = f8 && f8[0] == 'w';
+    // CUDABERT_FP32_GEMM=cuda: fp32 mode multiplies on the CUDA cores (gemm_f32) instead of splitting
+    // both operands into three bf16 planes for the tensor cores
+    const char* f32 = std::getenv("CUDABERT_FP32_GEMM");
+    f32_tensor_ = !(f32 && f32[0] == 'c');
     const char* nv = std::getenv("CUDABERT_NVTX");
     nvtx_ = nv && nv[0] == '1';
   }
@@ -190,7 +194,7 @@ bool Model::upload_table(const std::vector<std::string>& keys, size_t min_rows, 
 
 bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::vector<std::string>& keys_bias, int K,
                        int N, DenseWeight* d, int n_off, int n_total, int prec) {
-  const size_t esize = (prec == PREC_FP32) ? 4 : 2;
+  const size_t esize = (prec == PREC_FP32) ? 4 : (prec == PREC_FP32_SPLIT) ? 6 : 2;  // bytes per weight
   if (n_off == 0) {
     d->K = K;
     d->N = n_total;
@@ -214,6 +218,10 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
     if (!check(cudaMemcpy2DAsync(base, static_cast<size_t>(n_total) * 4, stage_f32_, static_cast<size_t>(N) * 4,
                                  static_cast<size_t>(N) * 4, K, cudaMemcpyDeviceToDevice, stream_), "pack"))
       return false;
+  } else if (prec == PREC_FP32_SPLIT) {
+    if (transpose_split_bf16x3(stage_f32_, static_cast<__nv_bfloat16*>(d->w) + static_cast<size_t>(n_off) * 3 * K, K, N,
+                               stream_) < 0)
+      return fail(2, "transpose launch failed");
   } else if (prec == PREC_BF16) {
     if (transpose_round_bf16(stage_f32_, static_cast<__half*>(d->w) + static_cast<size_t>(n_off) * K, K, N,
                           stream_) < 0)
@@ -240,6 +248,13 @@ bool Model::load_dense(const std::vector<std::string>& keys_kernel, const std::v
 
 bool Model::finish_dense(DenseWeight* d, int prec) {
   if (prec == PREC_FP32) return true;
+  if (prec == PREC_FP32_SPLIT) {
+    if (d->N % 128 != 0 || d->K % 64 != 0) return fail(1, "the tensor-core fp32 GEMM needs widths in multiples of 128 and depths of 64");
+    if (!make_tmap_16bit_kmajor(&d->tmap, d->w, d->N, 3 * static_cast<uint64_t>(d->K), static_cast<uint64_t>(d->K) * 6,
+                                gemm_split_w_box_rows(d->N)))
+      return fail(2, "cuTensorMapEncodeTiled failed for a weight matrix");
+    return true;
+  }
   if (prec == PREC_FP8 && !fp8_widened_) {
     if (d->N % 256 != 0) return fail(1, "FP8 mode needs dense widths that are multiples of 256");
     if (!make_tmap_u8_kmajor(&d->tmap, d->w_fp8, d->N, d->K))
@@ -264,6 +279,7 @@ bool Model::load_weights(const std::string& dir) {
   if (!upload_vec({"embeddings_LayerNorm_gamma"}, H, &emb_g_)) return false;
   if (!upload_vec({"embeddings_LayerNorm_beta"}, H, &emb_b_)) return false;
   layer_.resize(L_);
+  const int lprec = (prec_ == PREC_FP32 && f32_tensor_) ? PREC_FP32_SPLIT : prec_;  // layout of the layers' dense weights
   for (int i = 0; i < L_; ++i) {
     // per-layer keys "_<i>_" + suffix, as in utils/bert.cu:17-61
     const std::string p = "_" + std::to_string(i) + "_";
@@ -271,19 +287,19 @@ bool Model::load_weights(const std::string& dir) {
     const char* qkv_names[3] = {"query", "key", "value"};
     for (int j = 0; j < 3; ++j) {
       const std::string s = p + "attention_self_" + qkv_names[j];
-      if (!load_dense({s + "_kernel"}, {s + "_bias"}, H_, H_, &lw.qkv, j * H_, 3 * H_, prec_)) return false;
+      if (!load_dense({s + "_kernel"}, {s + "_bias"}, H_, H_, &lw.qkv, j * H_, 3 * H_, lprec)) return false;
     }
-    if (!finish_dense(&lw.qkv, prec_)) return false;
+    if (!finish_dense(&lw.qkv, lprec)) return false;
     if (!load_dense({p + "attention_output_dense_kernel"}, {p + "attention_output_dense_bias"}, H_, H_, &lw.attn_out,
-                    0, H_, prec_) || !finish_dense(&lw.attn_out, prec_))
+                    0, H_, lprec) || !finish_dense(&lw.attn_out, lprec))
       return false;
     if (!upload_vec({p + "attention_output_LayerNorm_gamma"}, H, &lw.ln1_g)) return false;
     if (!upload_vec({p + "attention_output_LayerNorm_beta"}, H, &lw.ln1_b)) return false;
-    if (!load_dense({p + "intermediate_dense_kernel"}, {p + "intermediate_dense_bias"}, H_, F_, &lw.ffn1, 0, F_, prec_) ||
-        !finish_dense(&lw.ffn1, prec_))
+    if (!load_dense({p + "intermediate_dense_kernel"}, {p + "intermediate_dense_bias"}, H_, F_, &lw.ffn1, 0, F_, lprec) ||
+        !finish_dense(&lw.ffn1, lprec))
       return false;
-    if (!load_dense({p + "output_dense_kernel"}, {p + "output_dense_bias"}, F_, H_, &lw.ffn2, 0, H_, prec_) ||
-        !finish_dense(&lw.ffn2, prec_))
+    if (!load_dense({p + "output_dense_kernel"}, {p + "output_dense_bias"}, F_, H_, &lw.ffn2, 0, H_, lprec) ||
+        !finish_dense(&lw.ffn2, lprec))
       return false;
     if (!upload_vec({p + "output_LayerNorm_gamma"}, H, &lw.ln2_g)) return false;
     if (!upload_vec({p + "output_LayerNorm_beta"}, H, &lw.ln2_b)) return false;
@@ -341,7 +357,7 @@ bool Model::cache_probe() {
   cache_dir_ = e;
   // what the device-ready weights depend on: every file of the directory and how this handle lays them out
   std::string sig = "layout 2|large " + std::to_string(large_) + "|prec " + std::to_string(prec_) + "|layers " +
-                    std::to_string(L_) + "|fp8 widened " + std::to_string(fp8_widened_) + "|scale " +
+                    std::to_string(L_) + "|fp8 widened " + std::to_string(fp8_widened_) + "|fp32 planes " + std::to_string(f32_tensor_) + "|scale " +
                     std::to_string(W_CONTAINER_SCALE) + "\n";
   for (const std::string& f : files_) {
     struct stat st;
@@ -455,6 +471,8 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   const size_t o_ctx = slot(ct * H_ * esize_);
   const size_t o_qkv = slot(ct * 3 * H_ * esize_);
   const size_t o_z = slot(ct * F_ * esize_);
+  const bool planes = !lowp && f32_tensor_;
+  const size_t o_split = planes ? slot(ct * F_ * 6) : 0;  // three bf16 planes of the widest GEMM input
   const size_t o_pool = slot(static_cast<size_t>(cbatch) * H_ * sizeof(float));
   const size_t o_probs = slot(static_cast<size_t>(cbatch) * MAX_CLASSES * sizeof(float));
   if (!check(cudaMalloc(&arena_, off), "cudaMalloc(activation arena)")) return false;
@@ -479,6 +497,13 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
               make_tmap_16bit_kmajor(&tm_z_, z_, rows, F_, static_cast<uint64_t>(F_) * 2, 128) &&
               make_tmap_qkv(&tm_qkv_, qkv_, rows, H_);
     if (!ok) return fail(2, "cuTensorMapEncodeTiled failed for an activation buffer");
+  }
+  if (planes) {
+    split_ = base + o_split;
+    const uint64_t rows = ct;
+    if (!make_tmap_16bit_kmajor(&tm_splitH_, split_, rows, 3 * static_cast<uint64_t>(H_), static_cast<uint64_t>(H_) * 6, 128) ||
+        !make_tmap_16bit_kmajor(&tm_splitF_, split_, rows, 3 * static_cast<uint64_t>(F_), static_cast<uint64_t>(F_) * 6, 128))
+      return fail(2, "cuTensorMapEncodeTiled failed for an activation buffer");
   }
   if (h_in_) cudaFreeHost(h_in_);
   if (h_out_) cudaFreeHost(h_out_);
@@ -554,7 +579,16 @@ bool Model::dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, i
   epi.residual = residual;
   int n;
   prof_begin(kclass);
-  if (prec_ == PREC_FP32) {
+  if (prec_ == PREC_FP32 && f32_tensor_) {
+    // fp32 on the tensor cores: the input's three bf16 planes, then one GEMM over 6 K (kernels.h)
+    n = split_bf16x3(static_cast<const float*>(A), lda, static_cast<__nv_bfloat16*>(split_), M, w.K, m_dev_cur_, stream_);
+    if (n > 0) {
+      epi.flags |= EPI_OUT_F32 | EPI_SPLIT3;
+      const int g = gemm_tcgen05(w.K == H_ ? &tm_splitH_ : &tm_splitF_, &w.tmap, M, w.N, w.K, out, w.N, epi, err_dev_,
+                                 num_sms_, m_dev_cur_, stream_);
+      n = g < 0 ? g : n + g;
+    }
+  } else if (prec_ == PREC_FP32) {
     n = gemm_f32(static_cast<const float*>(A), lda, static_cast<const float*>(w.w), M, w.N, w.K,
                  static_cast<float*>(out), w.N, epi, m_dev_cur_, stream_);
   } else {

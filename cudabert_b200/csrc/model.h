@@ -22,6 +22,8 @@
 namespace cb {
 
 enum Precision : int { PREC_FP32 = 0, PREC_BF16 = 1, PREC_FP8 = 2 };
+// how load_dense lays a weight out when an fp32 handle multiplies on the tensor cores: three bf16 planes
+constexpr int PREC_FP32_SPLIT = 100;
 
 enum KernelClass : int {
   KC_EMBED = 0, KC_GEMM_QKV, KC_ATTENTION, KC_GEMM_ATTN_OUT, KC_LAYERNORM, KC_GEMM_FFN1, KC_GEMM_FFN2,
@@ -135,6 +137,7 @@ class Model {
   bool graphs_enabled_ = true;
   bool nvtx_ = false;         // CUDABERT_NVTX=1: NVTX ranges around passes and launches
   bool fp8_widened_ = false;  // FP8 mode: weights expanded to fp16 at load (CUDABERT_FP8_OPERAND=widened)
+  bool f32_tensor_ = true;    // fp32 mode: dense layers on the tensor cores as sums of bf16 planes (CUDABERT_FP32_GEMM=cuda: CUDA cores)
   bool cls_last_ = true;  // pooler-only passes compute the last layer for the first token of every sequence only
   static constexpr int PDL_MAX_TOKENS = 4096;  // forward passes up to this many token slots use dependent launch
   long graph_replays_ = 0, graph_captures_ = 0;
@@ -192,6 +195,8 @@ class Model {
   void *xa_ = nullptr, *x1a_ = nullptr, *ctx_ = nullptr, *qkv_ = nullptr, *z_ = nullptr;
   float *pooled_ = nullptr, *probs_ = nullptr;
   CUtensorMap tm_x_, tm_x1_, tm_ctx_, tm_z_, tm_qkv_;
+  void* split_ = nullptr;          // fp32 mode on the tensor cores: the bf16 planes of the current GEMM's input, [tokens, 3 K]
+  CUtensorMap tm_splitH_, tm_splitF_;  // ... viewed with K = H and K = F
 
   // pinned staging
   int* h_in_ = nullptr;

@@ -235,6 +235,59 @@ __global__ void transpose_round_bf16_kernel(const float* __restrict__ src, __hal
   }
 }
 
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& b0, __nv_bfloat16& b1, __nv_bfloat16& b2) {
+  b0 = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(b0);  // exact
+  b1 = __float2bfloat16_rn(r1);
+  b2 = __float2bfloat16_rn(r1 - __bfloat162float(b1));
+}
+
+// dst[n, p K + k] = bf16 plane p of src[k, n], through a 32x33 shared tile
+__global__ void transpose_split_bf16x3_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int K,
+                                              int N) {
+  __shared__ float tile[32][33];
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int k = k0 + r, n = n0 + threadIdx.x;
+    tile[r][threadIdx.x] = (k < K && n < N) ? src[static_cast<size_t>(k) * N + n] : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < K) {
+      __nv_bfloat16 b0, b1, b2;
+      split3(tile[threadIdx.x][r], b0, b1, b2);
+      __nv_bfloat16* row = dst + static_cast<size_t>(n) * 3 * K;
+      row[k] = b0;
+      row[K + k] = b1;
+      row[2 * K + k] = b2;
+    }
+  }
+}
+
+// dst[m, p K + k] = bf16 plane p of src[m, k]; a thread takes four consecutive k (K % 4 == 0)
+__global__ void __launch_bounds__(256)
+split_bf16x3_kernel(const float* __restrict__ src, int lds, __nv_bfloat16* __restrict__ dst, int rows, int K,
+                    const int* __restrict__ rows_dev) {
+  griddep_wait();
+  griddep_launch();
+  if (rows_dev) rows = min(rows, __ldg(rows_dev));
+  const int quads = K >> 2;
+  const long long total = static_cast<long long>(rows) * quads;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int m = static_cast<int>(i / quads), k = static_cast<int>(i % quads) << 2;
+    const float4 x = *reinterpret_cast<const float4*>(src + static_cast<size_t>(m) * lds + k);
+    const float xs[4] = {x.x, x.y, x.z, x.w};
+    __nv_bfloat16 p[3][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) split3(xs[j], p[0][j], p[1][j], p[2][j]);
+    __nv_bfloat16* row = dst + static_cast<size_t>(m) * 3 * K + k;
+#pragma unroll
+    for (int q = 0; q < 3; ++q) *reinterpret_cast<uint2*>(row + q * K) = *reinterpret_cast<const uint2*>(p[q]);
+  }
+}
+
 __global__ void maxabs_kernel(const float* __restrict__ src, size_t n, unsigned int* __restrict__ out_bits) {
   float m = 0.f;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
@@ -436,6 +489,22 @@ int quantize_fp8_weight(const float* src, uint8_t* dst_q, __half* dst_wide, floa
   dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
   quantize_fp8_kernel<<<grid, block, 0, stream>>>(src, dst_q, dst_wide, scale_out, K, N);
   return cudaGetLastError() == cudaSuccess ? 3 : -3;
+}
+
+int transpose_split_bf16x3(const float* src, __nv_bfloat16* dst, int K, int N, cudaStream_t stream) {
+  dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
+  transpose_split_bf16x3_kernel<<<grid, block, 0, stream>>>(src, dst, K, N);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
+}
+
+int split_bf16x3(const float* src, int lds, __nv_bfloat16* dst, int rows, int K, const int* rows_dev,
+                 cudaStream_t stream) {
+  if (rows <= 0 || K <= 0 || (K & 3) || (lds & 3)) return -1;
+  const long long total = static_cast<long long>(rows) * (K >> 2);
+  const long long want = (total + 255) / 256;
+  const int grid = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
+  return launch_pdl(split_bf16x3_kernel, dim3(grid), dim3(256), 0, stream, src, lds, dst, rows, K, rows_dev) ==
+                 cudaSuccess ? 1 : -3;
 }
 
 int fill_f32(float* dst, float value, size_t n, cudaStream_t stream) {

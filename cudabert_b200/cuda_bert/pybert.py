@@ -276,6 +276,9 @@ k_gemm_tcgen05.restype = c_int
 k_gemm_f32 = lib.cudabert_k_gemm_f32
 k_gemm_f32.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
 k_gemm_f32.restype = c_int
+k_gemm_f32_tensor = lib.cudabert_k_gemm_f32_tensor
+k_gemm_f32_tensor.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
+k_gemm_f32_tensor.restype = c_int
 k_attention = lib.cudabert_k_attention
 k_attention.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]
 k_attention.restype = c_int

@@ -211,14 +211,21 @@ CUDABERT_API long long cudabert_reader_rejected(void* reader, long long* first_i
 /* out[M,N] = epilogue(A[M,K] (row stride lda elements) x W[N,K]^T), A and W both bf16, or both fp16 with
  * flag 256; flags: 1 bias, 2 GELU, 4 residual, 8 tanh, 16 fp32 output, 32 per-column scale, 64 fp16 output
  * (bf16 otherwise), 128 accumulator x 1/4096 (the encoder holds its bf16-rounded weights as fp16 numbers
- * times 4096), 256 fp16 operands.  err_dev: device int, set non-zero if a pipeline wait timed out.
- * N % 128 == 0, K % 64 == 0.                                                                  */
+ * times 4096), 256 fp16 operands, 512 W given as E4M3 bytes (with 256 and 32; N % 256 == 0).  err_dev:
+ * device int, set non-zero if a pipeline wait timed out.  N % 128 == 0, K % 64 == 0.  (Flag 1024, operands
+ * of three bf16 planes, is refused here: cudabert_k_gemm_f32_tensor prepares such operands itself.)  */
 CUDABERT_API int cudabert_k_gemm_tcgen05(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev,
                          int flags, const float* bias_dev, const void* residual_dev, const float* colscale_dev,
                          int* err_dev);
 /* out[M,N] = epilogue(A[M,K] fp32 (row stride lda) x W[K,N] fp32). */
 CUDABERT_API int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W_dev, int M, int N, int K, float* out_dev,
                         int flags, const float* bias_dev, const float* residual_dev);
+/* The same product on the tensor cores, as fp32 mode computes it by default: both operands are split
+ * into three bf16 planes (x = x0 + x1 + x2, each the bf16 rounding of what the ones before leave) and
+ * the tcgen05 GEMM sums the six leading cross terms with fp32 accumulation; what is dropped is below
+ * 2^-24 of |a| |w|.  Same arguments as cudabert_k_gemm_f32; N % 128 == 0, K % 64 == 0, lda % 4 == 0. */
+CUDABERT_API int cudabert_k_gemm_f32_tensor(const float* A_dev, int lda, const float* W_dev, int M, int N, int K,
+                                            float* out_dev, int flags, const float* bias_dev, const float* residual_dev);
 /* ctx[T,H] = attention(qkv[T,3H]); mask_dev int32 [B,S] or NULL; kernel: 0 = fp32 kernel (fp32 in and
  * out), 1 = 16-bit mma.sync kernel (one CTA per sequence and head), 2 = 16-bit tcgen05 kernel, 3 = 16-bit
  * mma.sync kernel, persistent (S <= 256); the 16-bit kernels take fp16 Q, K, V and write fp16.  Adding 16

@@ -127,6 +127,39 @@ def test_gemm_f32(pybert, M, N, K, flags):
     assert (out - ref).abs().max().item() <= FP32_ABS_TOL
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 768, 768), (1024, 2304, 768), (333, 3072, 768), (130, 1024, 4096),
+                                   (657, 768, 3072), (2000, 4096, 1024)])
+@pytest.mark.parametrize("flags", [EPI_BIAS, EPI_BIAS | EPI_GELU, EPI_BIAS | EPI_RESIDUAL, 0])
+def test_gemm_f32_on_tensor_cores(pybert, M, N, K, flags):
+    """fp32 mode's default GEMM: both operands as three bf16 planes, six cross terms on the tcgen05
+    pipeline.  Against float64 it has to be at the level of an fp32 GEMM (within 2e-6 of the sum of
+    |a||w|, element by element; two bf16 planes alone would leave 2^-16 = 1.5e-5), not merely within the
+    mode's budget; the rows of A span ten binary orders of magnitude."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K + flags)
+    A = torch.randn(M, K, device="cuda", generator=g) * torch.exp2(torch.randint(-6, 4, (M, 1), device="cuda",
+                                                                                 generator=g).float())
+    W = torch.randn(K, N, device="cuda", generator=g) * 0.05
+    bias = torch.randn(N, device="cuda", generator=g) * 0.1
+    resid = torch.randn(M, N, device="cuda", generator=g)
+    out = torch.full((M, N), float("nan"), device="cuda")
+    rc = pybert.k_gemm_f32_tensor(A.data_ptr(), K, W.data_ptr(), M, N, K, out.data_ptr(), flags, bias.data_ptr(),
+                                  resid.data_ptr())
+    assert rc == 0
+    exact = A.double() @ W.double()
+    ref = _ref_epilogue(exact.float(), flags, bias, resid, None)
+    err = (out - ref).abs()
+    # element-wise against sum_k |a||w|: the planes drop less than 2^-22 of it, and the tensor core's
+    # fp32 accumulator adds its own rounding per 16-product step (up to 1 536 steps); GELU (slope <= 1.13)
+    # passes that on and adds the 2.5e-5 of its polynomial
+    scale = (A.abs().double() @ W.abs().double()).float()
+    bound = 2e-6 * scale + 2e-7 * ref.abs() + 1e-9 + (5e-5 if flags & EPI_GELU else 0.0)
+    worst = (err / bound).max().item()
+    assert worst <= 1.0, "error is %.2f x the bound" % worst
+    if not flags & EPI_GELU:
+        plain = (A @ W)          # torch's own fp32 GEMM on the same inputs, for scale
+        print("max err %.3g (torch fp32 GEMM: %.3g)" % (err.max().item(), (plain - exact.float()).abs().max().item()))
+
+
 def _attention_ref(qkv, mask, B, S, heads):
     # float64: in fp32 a row whose keys are all masked loses score bits to the -10000 offset
     H = heads * 64

@@ -17,7 +17,7 @@ BASE_CASES = ["c0_affine", "c2_small", "edge_s17", "edge_b1s1", "edge_nomask", "
 LARGE_CASES = ["c1_small", "c3_small", "c4_small"]
 SWITCHES = ("CUDABERT_PACK", "CUDABERT_GRAPH", "CUDABERT_PDL", "CUDABERT_LAST_LAYER", "CUDABERT_ATTENTION",
             "CUDABERT_GEMM_PAIR", "CUDABERT_GEMM_SMALL_TILES", "CUDABERT_PRECISION", "CUDABERT_LN",
-            "CUDABERT_FP8_OPERAND", "CUDABERT_ATTENTION_TILES", "SWITCH_CHILD_PRECISION")
+            "CUDABERT_FP8_OPERAND", "CUDABERT_ATTENTION_TILES", "CUDABERT_FP32_GEMM", "SWITCH_CHILD_PRECISION")
 
 
 @pytest.fixture(scope="module")
@@ -85,6 +85,25 @@ def test_attention_tile_switch_keeps_every_bit(run_with):
     sequence = run_with(CUDABERT_ATTENTION="tc", CUDABERT_ATTENTION_TILES="sequence")
     for case in BASE_CASES + LARGE_CASES:
         np.testing.assert_array_equal(packed[case], sequence[case], err_msg=case)
+
+
+def test_fp32_gemm_switch_stays_at_fp32_level(run_with):
+    """fp32 mode multiplies on the tensor cores (operands split into three bf16 planes, fp32
+    accumulation) unless CUDABERT_FP32_GEMM=cuda sends the products to the CUDA cores.  Both are fp32
+    computations of the same model; the tensor core's fp32 accumulator rounds less carefully than
+    an FFMA chain, which shows as about 1e-4 on the pooler output, a tenth of the mode's budget of 1e-3.
+    Both meet that budget against the golden output."""
+    tensor = run_with(SWITCH_CHILD_PRECISION="fp32")
+    cuda = run_with(SWITCH_CHILD_PRECISION="fp32", CUDABERT_FP32_GEMM="cuda")
+    worst = {}
+    for case in BASE_CASES + LARGE_CASES:
+        gold = cases.load_golden(case)["pooled"]
+        worst[case] = (float(np.abs(tensor[case] - cuda[case]).max()), float(np.abs(tensor[case] - gold).max()),
+                       float(np.abs(cuda[case] - gold).max()))
+    print({k: tuple("%.2g" % x for x in v) for k, v in worst.items()})
+    for case, (between, t_gold, c_gold) in worst.items():
+        assert between <= 4e-4, "%s: tensor-core and CUDA-core fp32 GEMMs differ by %g" % (case, between)
+        assert t_gold <= 1e-3 and c_gold <= 1e-3, "%s: %g / %g against the golden output" % (case, t_gold, c_gold)
 
 
 def test_fp8_operand_switch_keeps_every_bit(run_with):
