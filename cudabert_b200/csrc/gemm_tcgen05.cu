@@ -711,6 +711,12 @@ template <int BN>
 int launch(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int K, void* out, int ldo,
            const GemmEpilogue& epi, int* err_flag, int num_sms, const int* m_dev, cudaStream_t stream) {
   switch (epi.flags) {
+    case F_S3_RES:
+      if (BN == 128) return launch_one<128, F_S3_RES>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
+      break;
+    default: break;
+  }
+  switch (epi.flags) {
     case F_LIN: return launch_one<BN, F_LIN>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
     case F_FFN1: return launch_one<BN, F_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
     default: return launch_one<BN, -1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
@@ -771,21 +777,10 @@ int launch_pair(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, in
     case F_FFN18: return launch_pair_one<F_FFN18, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_LIN8W: return launch_pair_one<F_LIN8W>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_FFN18W: return launch_pair_one<F_FFN18W>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    case F_S3:
-      if (gemm_split_block_n(N) == 128)
-        return launch_pair_one<F_S3, false, 128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-      return launch_pair_one<F_S3>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    case F_S3_RES:
-      if (gemm_split_block_n(N) == 128)
-        return launch_pair_one<F_S3_RES, false, 128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-      return launch_pair_one<F_S3_RES>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-    case F_S3_FFN1:
-      if (gemm_split_block_n(N) == 128)
-        return launch_pair_one<F_S3_FFN1, false, 128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
-      return launch_pair_one<F_S3_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_S3: return launch_pair_one<F_S3>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_S3_RES: return launch_pair_one<F_S3_RES>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_S3_FFN1: return launch_pair_one<F_S3_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     default:
-      if ((epi.flags & EPI_SPLIT3) && gemm_split_block_n(N) == 128)
-        return launch_pair_one<-1, false, 128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
       if (epi.flags & EPI_W_FP8) return launch_pair_one<-1, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
       return launch_pair_one<-1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   }
@@ -809,11 +804,12 @@ int wait_timeout_probe(int* err_flag, unsigned long long limit_ns, cudaStream_t 
 
 int gemm_block_n(int N) { return (N % 256 == 0) ? 256 : 128; }
 
-// Tile width of the three-plane (fp32) GEMM.  Its k loop is six times as long, so with few rows the
-// tiles of a narrow output are few and long; 256 x 128 tiles double their number.  The choice goes by N
-// alone: what a row's result is must not depend on how many rows share its batch.
+// Tiles of the three-plane (fp32) GEMM.  Its k loop is six times as long, so with few rows the tiles of
+// a narrow output are few and long: outputs of up to 1024 columns take single CTAs with 128 x 128
+// tiles (four times as many, each half as long as a pair's), wider ones CTA pairs with 256 x 256.  The
+// choice goes by N alone: what a row's result is must not depend on how many rows share its batch.
 int gemm_split_block_n(int N) { return (N % 256 == 0 && N > 1024) ? 256 : 128; }
-int gemm_split_w_box_rows(int N) { return gemm_split_block_n(N) / 2; }
+int gemm_split_w_box_rows(int N) { return 128; }  // half of a pair's 256-row tile, or all of a 128-row one
 
 static bool small_tiles_enabled() {
   static const bool on = [] {
@@ -881,8 +877,10 @@ int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, i
     if (N % 256 != 0 || !(epi.flags & EPI_IN_F16)) return -1;
     return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
   }
-  if (epi.flags & EPI_SPLIT3)  // always CTA pairs, tile width by N alone (gemm_split_block_n)
-    return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+  if (epi.flags & EPI_SPLIT3) {  // tile shape by N alone (gemm_split_block_n)
+    if (gemm_split_block_n(N) == 256) return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
+  }
   if (small_tiles_enabled() && gemm_uses_pairs(N) && gemm_w_box_rows(N) == 128) {
     const long pairs = num_sms / 2 > 0 ? num_sms / 2 : 1;
     const long tiles_p = static_cast<long>((M + 2 * BM - 1) / (2 * BM)) * (N / 256);

@@ -111,8 +111,8 @@ int wait_timeout_probe(int* err_flag, unsigned long long limit_ns, cudaStream_t 
 // Box rows the W tensor map must be encoded with for the kernel variant that gemm_tcgen05
 // will pick for this N (128 when CTA pairs each load half of a 256-row tile, else gemm_block_n).
 int gemm_w_box_rows(int N);
-// The same for the W operand of an EPI_SPLIT3 GEMM ([N, 3 K] bf16 planes): always CTA pairs, with tiles
-// 256 wide for N > 1024 and 128 wide otherwise.
+// The same for the W operand of an EPI_SPLIT3 GEMM ([N, 3 K] bf16 planes): CTA pairs with 256 x 256
+// tiles for N > 1024, single CTAs with 128 x 128 tiles otherwise.
 int gemm_split_block_n(int N);
 int gemm_split_w_box_rows(int N);
 // Encode a 2-D tiled map over a row-major matrix of 16-bit elements [rows, cols] with
