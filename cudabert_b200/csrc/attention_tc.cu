@@ -47,7 +47,7 @@ constexpr int ATC_SMEM = SMEM_BAR + 256 + 1024;  // + barriers + alignment slack
 // S buffers in columns [0, 64) and [64, 128); two O accumulators in [128, 192) and [192, 256), used by
 // alternate items so that the output of one item is read while the next one accumulates
 constexpr uint32_t TMEM_COLS = 256;
-constexpr int ATC_PACKED_MAX_S = 80;  // padded lengths up to this use packed tiles (see attention_kernel_for)
+constexpr int ATC_PACKED_MAX_S = 80;  // padded lengths up to this prefer packed tiles to the persistent kernel
 constexpr uint32_t S_COL = 0, O_COL = 128;
 
 enum { SITE_ATT_Q = 10, SITE_ATT_K, SITE_ATT_V, SITE_ATT_S, SITE_ATT_P, SITE_ATT_O, SITE_ATT_E };
@@ -515,14 +515,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQKV, const int* __rest
 //   512 x 96 lengths 8..96: 105 / 106 / 100;   512 x 96 full rows 154 / 129 / 157;
 //   256 x 128 lengths 16..128: 77 / 72 / 77;   110 x 128 full rows 31 / 33 / 45;
 //   128 x 200 lengths 16..200: 60 / 79 / 60;   110 x 192 full rows 60 / 65 / 75;
-//   55 x 256 full rows 44 / 48 / 68;   32 x 512 full rows 92 / 84 / 200 (one CTA per item);
-//   32 x 512 lengths 64..512: 70 / 74 / 106 (one CTA per item).
-// The lengths live on the device, so the choice uses S alone: tcgen05 with packed tiles up to S = 80;
-// beyond, tcgen05 with one sequence per tile for long sequences (S >= 384) or an S that fills its
-// last query tile to 85 % or more, the persistent kernel otherwise (the per-item kernel beyond the
-// length the persistent one can hold).
+//   160 x 160 lengths 16..160: 59 / 74 / 54;   160 x 160 full rows 85 / 96 / 95;
+//   55 x 256 full rows 44 / 48 / 68;   and, beyond the 256 positions the persistent kernel holds
+//   (third figure: mma.sync with one CTA per item):   85 x 300 lengths 32..300: 80 / 87 / 98;
+//   85 x 300 full rows 140 / 119 / 166;   64 x 400 lengths 32..400: 78 / 116 / 124;
+//   64 x 400 full rows 155 / 165 / 275;   32 x 512 full rows 92 / 84 / 200;
+//   32 x 512 lengths 64..512: 70 / 74 / 106.
+// The lengths live on the device, so the choice uses S alone.  An S of at least 96 that fills its
+// last 128-query tile to 85 % or more: tcgen05, one sequence per tile.  Otherwise: tcgen05 with
+// packed tiles up to S = 80 and beyond S = 256, the persistent kernel in between.
 // CUDABERT_ATTENTION=tc / persist / mma forces one kernel; CUDABERT_ATTENTION_TILES=packed / sequence
 // forces the tcgen05 kernel's tiles (both give the same bits).
+static bool tiles_fill_well(int S) {  // a sequence of S rows fills its last 128-query tile to 85 % or more
+  const int tiles = (S + TQ - 1) / TQ;
+  return S >= 96 && S * 100 >= tiles * TQ * 85;
+}
+
 int attention_kernel_for(int S) {
   static const int forced = []() -> int {
     const char* e = std::getenv("CUDABERT_ATTENTION");
@@ -534,9 +542,7 @@ int attention_kernel_for(int S) {
   }();
   int k = forced;
   if (k < 0) {
-    const int tiles = (S + TQ - 1) / TQ;
-    k = (S <= ATC_PACKED_MAX_S || S >= 384 || (S >= 96 && S * 100 >= tiles * TQ * 85)) ? ATT_KERNEL_TC
-                                                                                         : ATT_KERNEL_PERSIST;
+    k = (tiles_fill_well(S) || S <= ATC_PACKED_MAX_S || !attention_persist_fits(S)) ? ATT_KERNEL_TC : ATT_KERNEL_PERSIST;
   }
   if (k == ATT_KERNEL_PERSIST && !attention_persist_fits(S)) k = ATT_KERNEL_MMA;
   return k;
@@ -567,7 +573,7 @@ int attention_f16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_l
     const char* e = std::getenv("CUDABERT_ATTENTION_TILES");
     return !e ? -1 : e[0] == 'p' ? 1 : e[0] == 's' ? 0 : -1;
   }();
-  const bool want_multi = tiles_forced >= 0 ? tiles_forced == 1 : S <= ATC_PACKED_MAX_S;
+  const bool want_multi = tiles_forced >= 0 ? tiles_forced == 1 : !tiles_fill_well(S);
   const bool multi = row_start != nullptr && sched != nullptr && !cls_only && want_multi;
   const long long tiles = multi ? (static_cast<long long>(B) * S + TQ - 1) / TQ
                                 : static_cast<long long>(B) * ((S + TQ - 1) / TQ);

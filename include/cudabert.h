@@ -85,8 +85,9 @@ CUDABERT_API int cudabert_hidden_size(void* model);
 /* Which attention kernel a 16-bit forward pass of this padded sequence length runs (the lengths of the
  * sequences live on the device, so the choice depends on the padded length alone; environment
  * CUDABERT_ATTENTION=tc|persist|mma forces one): 1 = mma.sync, one CTA per sequence and head;
- * 2 = tcgen05 (padded lengths up to 80 with 128-row tiles that hold rows of several sequences,
- * CUDABERT_ATTENTION_TILES=packed|sequence forces either; the bits do not depend on it);
+ * 2 = tcgen05 (with 128-row tiles that hold rows of several sequences unless the padded length fills
+ * its last tile of 128 rows to 85 %; CUDABERT_ATTENTION_TILES=packed|sequence forces either, and the bits
+ * do not depend on it);
  * 3 = mma.sync, persistent.                                                                          */
 CUDABERT_API int cudabert_attention_kernel_for(int seq_length);
 CUDABERT_API int cudabert_num_classes(void* model);
