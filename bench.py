@@ -529,7 +529,9 @@ def run_ours(args, rank, local_rank, world, barrier, allmax):
                 "h2d_bytes_per_step": int(sum(3 * h[0].size * 4 for h in host) / n_pool),
                 "d2h_bytes_per_step": int(mean_rows * C * 4 + 4)},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "tensor", "kernel": gemm_kernel + " (QKV, attention-output, FFN1, FFN2)",
+        "roofline": {"bound": "tensor",
+                     "kernel": (gemm_kernel + " (QKV, attention-output, FFN1, FFN2)" if lowp or f32_cuda else
+                                "gemm_tcgen05_pair_kernel (QKV, FFN1), gemm_tcgen05_kernel (attention-output, FFN2)"),
                      "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tensor"] if peaks["tensor"] else None, "peak_source": peaks["source"],
                      # the same against the measured burst figure and the nominal dense bf16 peak of the part
