@@ -286,6 +286,51 @@ def test_attention_packed_rows(pybert, kernel, B, S, heads, mode):
     assert torch.isnan(packed[rows.numel():].float()).all()      # nothing is written beyond the packed rows
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_attention_packed_tiles_random_shapes(pybert, seed):
+    """Random batch sizes, padded lengths and length distributions (many one-row sequences, a few long
+    ones, holes, rows without valid key): the tcgen05 kernel on packed rows, whichever way it cuts its
+    tiles for that length, gives every valid row the bits it gives it in the padded layout, and stays
+    within the 16-bit tolerance of the float64 reference."""
+    rng = np.random.default_rng(1000 + seed)
+    S = int(rng.choice([5, 24, 64, 80, 100, 130, 160, 200, 300, 400, 512]))
+    B = int(rng.integers(1, max(2, min(600, 40000 // S))))
+    heads = int(rng.choice([12, 16]))
+    H = heads * 64
+    style = seed % 4
+    if style == 0:
+        lens = rng.integers(1, S + 1, B)
+    elif style == 1:
+        lens = np.where(rng.random(B) < 0.8, rng.integers(1, 4, B), rng.integers(1, S + 1, B))
+    elif style == 2:
+        lens = np.full(B, S)
+    else:
+        lens = rng.integers(max(1, S // 2), S + 1, B)
+    mask = (np.arange(S)[None, :] < lens[:, None]).astype(np.int32)
+    if seed % 3 == 0:                                       # holes below the last valid key
+        holes = rng.random((B, S)) < 0.2
+        holes[:, 0] = False
+        holes[np.arange(B), lens - 1] = False
+        mask = mask * (~holes)
+    if seed % 5 == 0:
+        mask[rng.integers(0, B)] = 0                        # a row without valid key keeps all S rows
+    lens = np.where(mask.any(1), S - np.argmax(mask[:, ::-1], axis=1), S)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(B * S, 3 * H, device="cuda", generator=g).half()
+    m = torch.from_numpy(np.ascontiguousarray(mask)).cuda()
+    rows = torch.cat([torch.arange(b * S, b * S + int(lens[b])) for b in range(B)]).cuda()
+    padded = torch.full((B * S, H), float("nan"), device="cuda", dtype=torch.float16)
+    assert pybert.k_attention(2, x.data_ptr(), m.data_ptr(), padded.data_ptr(), B, S, heads) == 0
+    xp = torch.zeros_like(x)
+    xp[: rows.numel()] = x[rows]
+    packed = torch.full((B * S, H), float("nan"), device="cuda", dtype=torch.float16)
+    assert pybert.k_attention(2 + 32, xp.data_ptr(), m.data_ptr(), packed.data_ptr(), B, S, heads) == 0
+    assert torch.equal(packed[: rows.numel()], padded[rows]), "B %d S %d heads %d" % (B, S, heads)
+    assert torch.isnan(packed[rows.numel():].float()).all()
+    ref = _attention_ref(x.float(), m, B, S, heads)
+    assert (padded.float()[rows] - ref[rows]).abs().max().item() <= 4e-3
+
+
 @pytest.mark.parametrize("bf16", [1, 0])
 @pytest.mark.parametrize("H", [768, 1024])
 def test_embed_layernorm_and_layernorm(pybert, bf16, H):
