@@ -46,7 +46,7 @@ constexpr int EPI_WARPS = 8;                         // two per lane quarter, ea
 constexpr int EPI_THREADS = EPI_WARPS * 32;
 constexpr int GEMM_THREADS = 64 + EPI_THREADS;
 constexpr int EPI_WARP_BYTES = 32 * 64;              // one 32-row x 64-byte piece per epilogue warp
-constexpr int EPI_VEC_BYTES = 2 * 256 * 4;           // bias and column scale of one tile
+constexpr int EPI_VEC_BYTES = 5 * 256 * 4;           // bias, column scale and three LayerNorm vectors of one tile
 constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_WARP_BYTES + EPI_VEC_BYTES;
 
 template <int BN>
@@ -108,11 +108,149 @@ __device__ __forceinline__ void gelu_erf2(float& a, float& b) {
 // stores are full-sector, row-contiguous accesses.  Bias and column scale of the tile are staged
 // in shared memory once per tile.  A residual (tests only: the model adds its residual in the
 // LayerNorm kernel) is read by the row's own thread in phase 1.
+// Row statistics of a LayerNorm input from its per-slice partials (LnFold): mean and 1 / sqrt(var + eps)
+__device__ __forceinline__ void ln_row_stats(const float* __restrict__ stats, int row, int slots, int n, float& mu,
+                                             float& rstd) {
+  const float2* p = reinterpret_cast<const float2*>(stats) + static_cast<size_t>(row) * slots;
+  float sum = 0.f, sq = 0.f;
+  for (int i = 0; i < slots; ++i) {
+    const float2 t = __ldg(p + i);
+    sum += t.x;
+    sq += t.y;
+  }
+  const float inv_n = 1.0f / static_cast<float>(n);
+  mu = sum * inv_n;
+  const float var = fmaxf(sq * inv_n - mu * mu, 0.f);
+  rstd = 1.0f / sqrtf(var + LN_EPS_F);
+}
+
+// Epilogue of the GEMM in front of a folded LayerNorm (EPI_LN_SUM): s = acc * scale + bias + residual.
+// The accumulator leaves TMEM with a thread per row; everything that touches global memory happens after
+// the transposition through the staging piece, where 4 lanes cover 64 contiguous bytes of a row: the fp32
+// residual is read, s written in fp32 and s * gamma in fp16, all in full sectors, and a lane keeps the
+// partial sum and sum of squares of the 4 rows it serves (rows i * 8 + lane / 4).  The residual of a
+// 32-column chunk is in flight while the chunk before it is worked on; the first chunk's is requested
+// before this warp waits for the accumulator (`tfull`).
+template <int BN, int FLAGS>
+__device__ __forceinline__ void epilogue_tile_sum(uint32_t t_acc, uint8_t* __restrict__ stage, const float* __restrict__ sbias,
+                                                  const float* __restrict__ sscale, int warp, int half, int lane, int m0,
+                                                  int n0, int M, int N, void* __restrict__ out, int ldo, int flags,
+                                                  const void* __restrict__ residual, const LnFold& ln, uint64_t* tfull,
+                                                  uint32_t tfull_phase, volatile int* abort_flag, int* err) {
+  const int fl = (FLAGS >= 0) ? FLAGS : flags;
+  const int quarter = warp & 3;
+  const int row_base = m0 + quarter * 32;
+  const uint32_t t_row = t_acc + (static_cast<uint32_t>(quarter * 32) << 16);
+  const float* sv2 = sscale + 256;  // gamma of the LayerNorm this GEMM feeds
+  const float* sv3 = sscale + 512;  // EPI_RES_LN: gamma and ...
+  const float* sv4 = sscale + 768;  // ... beta of the residual's LayerNorm
+  const int r2 = lane >> 2, p2 = lane & 3;
+  uint8_t* my_row = stage + lane * 64;
+  float* outf = static_cast<float*>(out);
+  __half* outh = static_cast<__half*>(ln.out16);
+  const float* resf = static_cast<const float*>(residual);
+  const int c_begin = half * (BN / 64), c_end = c_begin + BN / 64;
+  // the lane's 4 columns of pass h of a chunk, for its row i * 8 + r2
+  auto cc_of = [&](int col, int h, int i) { return col + 16 * h + ((p2 ^ (((i * 8 + r2) >> 1) & 3)) << 2); };
+  auto load_res = [&](int col, float4 (&q)[2][4]) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = row_base + i * 8 + r2;
+        q[h][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if ((fl & EPI_RESIDUAL) && row < M)
+          q[h][i] = __ldg(reinterpret_cast<const float4*>(resf + static_cast<size_t>(row) * ldo + n0 + cc_of(col, h, i)));
+      }
+  };
+  float4 q[2][4], qn[2][4];
+  load_res(c_begin * 32, q);
+  float rmu[4] = {0.f, 0.f, 0.f, 0.f}, rrs[4] = {1.f, 1.f, 1.f, 1.f}, ssum[4] = {0.f, 0.f, 0.f, 0.f},
+        ssq[4] = {0.f, 0.f, 0.f, 0.f};
+  if (fl & EPI_RES_LN) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (row_base + i * 8 + r2 < M) ln_row_stats(ln.res_stats, row_base + i * 8 + r2, N / 128, N, rmu[i], rrs[i]);
+  }
+  mbar_wait(tfull, tfull_phase, abort_flag, err, SITE_TMEM_FULL);
+  tc_fence_after();
+#pragma unroll
+  for (int c = c_begin; c < c_end; ++c) {
+    const int col = c * 32;
+    if (c + 1 < c_end) load_res(col + 32, qn);
+    uint32_t v[32];
+    tmem_ld32(t_row + col, v);
+    tmem_ld_wait();
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      f[j] = __uint_as_float(v[j]);
+      if (fl & EPI_COLSCALE) f[j] *= sscale[col + j];
+      if (fl & EPI_WSCALE) f[j] *= (1.0f / W_CONTAINER_SCALE);
+      if (fl & EPI_BIAS) f[j] += sbias[col + j];
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<float4*>(my_row + ((j ^ ((lane >> 1) & 3)) << 4)) =
+            make_float4(f[16 * h + 4 * j], f[16 * h + 4 * j + 1], f[16 * h + 4 * j + 2], f[16 * h + 4 * j + 3]);
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = i * 8 + r2;
+        const int row = row_base + r;
+        float4 t = *reinterpret_cast<const float4*>(stage + r * 64 + (p2 << 4));
+        const int cc = cc_of(col, h, i);
+        if (row < M) {
+          if (fl & EPI_RESIDUAL) {
+            float4 x = q[h][i];
+            if (fl & EPI_RES_LN) {
+              x.x = (x.x - rmu[i]) * rrs[i] * sv3[cc] + sv4[cc];
+              x.y = (x.y - rmu[i]) * rrs[i] * sv3[cc + 1] + sv4[cc + 1];
+              x.z = (x.z - rmu[i]) * rrs[i] * sv3[cc + 2] + sv4[cc + 2];
+              x.w = (x.w - rmu[i]) * rrs[i] * sv3[cc + 3] + sv4[cc + 3];
+            }
+            t.x += x.x; t.y += x.y; t.z += x.z; t.w += x.w;
+          }
+          ssum[i] += (t.x + t.y) + (t.z + t.w);
+          ssq[i] += (t.x * t.x + t.y * t.y) + (t.z * t.z + t.w * t.w);
+          const size_t o = static_cast<size_t>(row) * ldo + n0 + cc;
+          *reinterpret_cast<float4*>(outf + o) = t;
+          uint2 g;
+          g.x = pack_f16(t.x * sv2[cc], t.y * sv2[cc + 1]);
+          g.y = pack_f16(t.z * sv2[cc + 2], t.w * sv2[cc + 3]);
+          *reinterpret_cast<uint2*>(outh + o) = g;
+        }
+      }
+      __syncwarp();
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q[h][i] = qn[h][i];
+  }
+  // a row's 4 lanes -> one partial per row and 128-column slice (BN = 256: one slice per warp of a row)
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    ssum[i] += __shfl_xor_sync(0xffffffffu, ssum[i], 1);
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 1);
+    ssum[i] += __shfl_xor_sync(0xffffffffu, ssum[i], 2);
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 2);
+    const int row = row_base + i * 8 + r2;
+    if (p2 == 0 && row < M)
+      reinterpret_cast<float2*>(ln.stats_out)[static_cast<size_t>(row) * (N / 128) + (n0 + half * (BN / 2)) / 128] =
+          make_float2(ssum[i], ssq[i]);
+  }
+  tc_fence_before();
+  __syncwarp();
+}
+
 template <int BN, int FLAGS>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restrict__ stage, const float* __restrict__ sbias,
                                               const float* __restrict__ sscale, int warp, int half, int lane, int m0, int n0,
-                                              int M, void* __restrict__ out, int ldo, int flags,
-                                              const void* __restrict__ residual) {
+                                              int M, int N, int K, void* __restrict__ out, int ldo, int flags,
+                                              const void* __restrict__ residual, const LnFold& ln, float mu, float rstd) {
   const int fl = (FLAGS >= 0) ? FLAGS : flags;
   tc_fence_after();
   const int quarter = warp & 3;
@@ -120,14 +258,23 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restric
   const int my_grow = row_base + lane;
   const uint32_t t_row = t_acc + (static_cast<uint32_t>(quarter * 32) << 16);
   const bool has_res = (fl & EPI_RESIDUAL) != 0 && my_grow < M;
+  const float* sv2 = sscale + 256;  // gamma of the LayerNorm this GEMM feeds (EPI_LN_SUM) or gamma W (EPI_LN_APPLY)
+  const float* sv3 = sscale + 512;  // EPI_RES_LN: gamma and ...
+  const float* sv4 = sscale + 768;  // ... beta of the residual's LayerNorm
+  const int r2 = lane >> 2, p2 = lane & 3;
+  uint8_t* my_row = stage + lane * 64;
+  // the residual's folded LayerNorm (without EPI_LN_SUM: the last GEMM before an ordinary LayerNorm)
+  float rmu = 0.f, rrstd = 1.f;
+  if ((fl & EPI_RES_LN) && has_res) ln_row_stats(ln.res_stats, my_grow, N / 128, N, rmu, rrstd);
 
-  // acc * scale + bias (+ residual) -> activation, for the 32 columns starting at n0 + col
+  // acc * scale (normalised) + bias (+ residual) -> activation, for the 32 columns starting at n0 + col
   auto finish32 = [&](const uint32_t (&v)[32], float (&f)[32], int col) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       f[j] = __uint_as_float(v[j]);
       if (fl & EPI_COLSCALE) f[j] *= sscale[col + j];
       if (fl & EPI_WSCALE) f[j] *= (1.0f / W_CONTAINER_SCALE);  // fuses with the bias add into one FMA
+      if (fl & EPI_LN_APPLY) f[j] = rstd * (f[j] - mu * sv2[col + j]);
       if (fl & EPI_BIAS) f[j] += sbias[col + j];
     }
     if (fl & EPI_RESIDUAL) {
@@ -137,7 +284,13 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restric
                                                             static_cast<size_t>(my_grow) * ldo + n0 + col);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            const float4 t = __ldg(r + j);
+            float4 t = __ldg(r + j);
+            if (fl & EPI_RES_LN) {
+              t.x = (t.x - rmu) * rrstd * sv3[col + 4 * j] + sv4[col + 4 * j];
+              t.y = (t.y - rmu) * rrstd * sv3[col + 4 * j + 1] + sv4[col + 4 * j + 1];
+              t.z = (t.z - rmu) * rrstd * sv3[col + 4 * j + 2] + sv4[col + 4 * j + 2];
+              t.w = (t.w - rmu) * rrstd * sv3[col + 4 * j + 3] + sv4[col + 4 * j + 3];
+            }
             f[4 * j] += t.x; f[4 * j + 1] += t.y; f[4 * j + 2] += t.z; f[4 * j + 3] += t.w;
           }
         } else {
@@ -167,98 +320,99 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restric
     }
   };
 
-  // this warp's share of the tile: chunks of 32 columns in [half * BN / 2, (half + 1) * BN / 2)
-  const int c_begin = half * (BN / 64), c_end = c_begin + BN / 64;
-  const int r2 = lane >> 2, p2 = lane & 3;
-  uint8_t* my_row = stage + lane * 64;
-  if (fl & EPI_OUT_F32) {
-    // two passes of 16 fp32 columns = 64 bytes per row; phase 2: 4 lanes per row, 8 rows per instruction
-    float* outf = static_cast<float*>(out);
+  // 32 fp32 columns of this warp's 32 rows -> dst[row][n0 + col ..]: two passes of 16 columns = 64 bytes
+  // per row through the staging piece; phase 2: 4 lanes per row, 8 rows per instruction
+  auto store_f32 = [&](const float (&f)[32], int col, float* dst) {
 #pragma unroll
-    for (int c = c_begin; c < c_end; ++c) {
-      const int col = c * 32;
-      uint32_t v[32];
-      tmem_ld32(t_row + col, v);
-      tmem_ld_wait();
-      float f[32];
-      finish32(v, f, col);
+    for (int h = 0; h < 2; ++h) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<float4*>(my_row + ((j ^ ((lane >> 1) & 3)) << 4)) =
-              make_float4(f[16 * h + 4 * j], f[16 * h + 4 * j + 1], f[16 * h + 4 * j + 2], f[16 * h + 4 * j + 3]);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = i * 8 + r2;
-          const int row = row_base + r;
-          const float4 t = *reinterpret_cast<const float4*>(stage + r * 64 + (p2 << 4));
-          if (row < M)
-            *reinterpret_cast<float4*>(outf + static_cast<size_t>(row) * ldo + n0 + col + 16 * h +
-                                       ((p2 ^ ((r >> 1) & 3)) << 2)) = t;
-        }
-        __syncwarp();
-      }
-    }
-  } else {
-    // 32 16-bit columns (bf16, or fp16 with EPI_OUT_F16) = 64 bytes per row; phase 2: 4 lanes per
-    // row, 8 rows per instruction
-    uint16_t* outh = static_cast<uint16_t*>(out);
-#pragma unroll
-    for (int c = c_begin; c < c_end; ++c) {
-      const int col = c * 32;
-      uint32_t v[32];
-      tmem_ld32(t_row + col, v);
-      tmem_ld_wait();
-      float f[32];
-      finish32(v, f, col);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 t;
-        if (fl & EPI_OUT_F16) {
-          t.x = pack_f16(f[8 * j], f[8 * j + 1]);
-          t.y = pack_f16(f[8 * j + 2], f[8 * j + 3]);
-          t.z = pack_f16(f[8 * j + 4], f[8 * j + 5]);
-          t.w = pack_f16(f[8 * j + 6], f[8 * j + 7]);
-        } else {
-          t.x = pack_bf16(f[8 * j], f[8 * j + 1]);
-          t.y = pack_bf16(f[8 * j + 2], f[8 * j + 3]);
-          t.z = pack_bf16(f[8 * j + 4], f[8 * j + 5]);
-          t.w = pack_bf16(f[8 * j + 6], f[8 * j + 7]);
-        }
-        *reinterpret_cast<uint4*>(my_row + ((j ^ ((lane >> 1) & 3)) << 4)) = t;
-      }
+      for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<float4*>(my_row + ((j ^ ((lane >> 1) & 3)) << 4)) =
+            make_float4(f[16 * h + 4 * j], f[16 * h + 4 * j + 1], f[16 * h + 4 * j + 2], f[16 * h + 4 * j + 3]);
       __syncwarp();
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int r = i * 8 + r2;
         const int row = row_base + r;
-        const uint4 t = *reinterpret_cast<const uint4*>(stage + r * 64 + (p2 << 4));
+        const float4 t = *reinterpret_cast<const float4*>(stage + r * 64 + (p2 << 4));
         if (row < M)
-          *reinterpret_cast<uint4*>(outh + static_cast<size_t>(row) * ldo + n0 + col + ((p2 ^ ((r >> 1) & 3)) << 3)) = t;
+          *reinterpret_cast<float4*>(dst + static_cast<size_t>(row) * ldo + n0 + col + 16 * h +
+                                     ((p2 ^ ((r >> 1) & 3)) << 2)) = t;
       }
       __syncwarp();
+    }
+  };
+  // 32 16-bit columns (bf16, or fp16 when `f16`) = 64 bytes per row, one pass
+  auto store_16 = [&](const float (&f)[32], int col, uint16_t* dst, bool f16) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 t;
+      if (f16) {
+        t.x = pack_f16(f[8 * j], f[8 * j + 1]);
+        t.y = pack_f16(f[8 * j + 2], f[8 * j + 3]);
+        t.z = pack_f16(f[8 * j + 4], f[8 * j + 5]);
+        t.w = pack_f16(f[8 * j + 6], f[8 * j + 7]);
+      } else {
+        t.x = pack_bf16(f[8 * j], f[8 * j + 1]);
+        t.y = pack_bf16(f[8 * j + 2], f[8 * j + 3]);
+        t.z = pack_bf16(f[8 * j + 4], f[8 * j + 5]);
+        t.w = pack_bf16(f[8 * j + 6], f[8 * j + 7]);
+      }
+      *reinterpret_cast<uint4*>(my_row + ((j ^ ((lane >> 1) & 3)) << 4)) = t;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i * 8 + r2;
+      const int row = row_base + r;
+      const uint4 t = *reinterpret_cast<const uint4*>(stage + r * 64 + (p2 << 4));
+      if (row < M)
+        *reinterpret_cast<uint4*>(dst + static_cast<size_t>(row) * ldo + n0 + col + ((p2 ^ ((r >> 1) & 3)) << 3)) = t;
+    }
+    __syncwarp();
+  };
+
+  // this warp's share of the tile: chunks of 32 columns in [half * BN / 2, (half + 1) * BN / 2)
+  const int c_begin = half * (BN / 64), c_end = c_begin + BN / 64;
+#pragma unroll
+  for (int c = c_begin; c < c_end; ++c) {
+    const int col = c * 32;
+    uint32_t v[32];
+    tmem_ld32(t_row + col, v);
+    tmem_ld_wait();
+    float f[32];
+    finish32(v, f, col);
+    if (fl & EPI_OUT_F32) {
+      store_f32(f, col, static_cast<float*>(out));
+    } else {
+      store_16(f, col, static_cast<uint16_t*>(out), (fl & EPI_OUT_F16) != 0);
     }
   }
   tc_fence_before();
   __syncwarp();
 }
 
-// The epilogue warps (EPI_THREADS threads, named barrier 1) stage bias / column scale of the tile's BN
-// columns in shared memory.  The first barrier keeps a fast warp from overwriting values a slow
-// warp still reads for the previous tile.
+// The epilogue warps (EPI_THREADS threads, named barrier 1) stage the per-column vectors of the tile's BN
+// columns in shared memory: bias, column scale and, for folded LayerNorms, gamma (or gamma W) and the
+// residual LayerNorm's gamma and beta.  The first barrier keeps a fast warp from overwriting values a
+// slow warp still reads for the previous tile.
 template <int BN, int FLAGS>
 __device__ __forceinline__ void stage_tile_vectors(float* __restrict__ sbias, float* __restrict__ sscale, int flags,
                                                    const float* __restrict__ bias, const float* __restrict__ colscale,
-                                                   int n0) {
+                                                   const LnFold& ln, int n0) {
   const int fl = (FLAGS >= 0) ? FLAGS : flags;
-  if (!(fl & (EPI_BIAS | EPI_COLSCALE))) return;
+  if (!(fl & (EPI_BIAS | EPI_COLSCALE | EPI_LN_SUM | EPI_LN_APPLY | EPI_RES_LN))) return;
   const int t = threadIdx.x - 64;  // 0..EPI_THREADS-1
   asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
   for (int i = t; i < BN; i += EPI_THREADS) {
     if (fl & EPI_BIAS) sbias[i] = __ldg(bias + n0 + i);
     if (fl & EPI_COLSCALE) sscale[i] = __ldg(colscale + n0 + i);
+    if (fl & EPI_LN_SUM) sscale[256 + i] = __ldg(ln.gamma + n0 + i);
+    if (fl & EPI_LN_APPLY) sscale[256 + i] = __ldg(ln.c + n0 + i);
+    if (fl & EPI_RES_LN) {
+      sscale[512 + i] = __ldg(ln.res_gamma + n0 + i);
+      sscale[768 + i] = __ldg(ln.res_beta + n0 + i);
+    }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
 }
@@ -285,7 +439,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, int M, int N,
                     int K, void* __restrict__ out, int ldo, int flags, const float* __restrict__ bias,
                     const void* __restrict__ residual, const float* __restrict__ colscale, int* err,
-                    const int* __restrict__ m_dev) {
+                    const int* __restrict__ m_dev, const LnFold ln) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -388,10 +542,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t acc_phase = (it >> 1) & 1;
       const int n0 = (tile % tiles_n) * BN;
       const int m0 = (tile / tiles_n) * BM;
-      stage_tile_vectors<BN, FLAGS>(sbias, sscale, flags, bias, colscale, n0);
+      stage_tile_vectors<BN, FLAGS>(sbias, sscale, flags, bias, colscale, ln, n0);
+      if (((FLAGS >= 0) ? FLAGS : flags) & EPI_LN_SUM) {
+        epilogue_tile_sum<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp - 2) * EPI_WARP_BYTES, sbias, sscale, warp,
+                                     (warp - 2) >> 2, lane, m0, n0, M, N, out, ldo, flags, residual, ln, tfull_bar + acc,
+                                     acc_phase, abort_flag, err);
+        if (lane == 0) mbar_arrive(tempty_bar + acc);
+        continue;
+      }
+      float mu = 0.f, rstd = 1.f;  // a folded LayerNorm in front of this GEMM: the statistics of this thread's row
+      if ((((FLAGS >= 0) ? FLAGS : flags) & EPI_LN_APPLY) && m0 + (warp & 3) * 32 + lane < M)
+        ln_row_stats(ln.stats_in, m0 + (warp & 3) * 32 + lane, K / 128, K, mu, rstd);
       mbar_wait(tfull_bar + acc, acc_phase, abort_flag, err, SITE_TMEM_FULL);
       epilogue_tile<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp - 2) * EPI_WARP_BYTES, sbias, sscale, warp,
-                               (warp - 2) >> 2, lane, m0, n0, M, out, ldo, flags, residual);
+                               (warp - 2) >> 2, lane, m0, n0, M, N, K, out, ldo, flags, residual, ln, mu, rstd);
       if (lane == 0) mbar_arrive(tempty_bar + acc);
     }
   }
@@ -453,7 +617,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN, W8>::THR
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, int M,
                          int N, int K, void* __restrict__ out, int ldo, int flags, const float* __restrict__ bias,
                          const void* __restrict__ residual, const float* __restrict__ colscale, int* err,
-                         const int* __restrict__ m_dev) {
+                         const int* __restrict__ m_dev, const LnFold ln) {
   using C = PairCfg<BN, W8>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -619,10 +783,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const uint32_t acc_phase = (it >> 1) & 1;
       const int n0 = (tile % tiles_n) * BN;
       const int m0 = (tile / tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
-      stage_tile_vectors<BN, FLAGS>(sbias, sscale, flags, bias, colscale, n0);
+      stage_tile_vectors<BN, FLAGS>(sbias, sscale, flags, bias, colscale, ln, n0);
+      if (((FLAGS >= 0) ? FLAGS : flags) & EPI_LN_SUM) {
+        epilogue_tile_sum<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp - 2) * EPI_WARP_BYTES, sbias, sscale, warp,
+                                     (warp - 2) >> 2, lane, m0, n0, M, N, out, ldo, flags, residual, ln, tfull_bar + acc,
+                                     acc_phase, abort_flag, err);
+        if (lane == 0) {
+          if (leader) mbar_arrive(tempty_bar + acc);
+          else mbar_arrive_remote(mapa_u32(smem_u32(tempty_bar + acc), 0));
+        }
+        continue;
+      }
+      float mu = 0.f, rstd = 1.f;  // a folded LayerNorm in front of this GEMM: the statistics of this thread's row
+      if ((((FLAGS >= 0) ? FLAGS : flags) & EPI_LN_APPLY) && m0 + (warp & 3) * 32 + lane < M)
+        ln_row_stats(ln.stats_in, m0 + (warp & 3) * 32 + lane, K / 128, K, mu, rstd);
       mbar_wait(tfull_bar + acc, acc_phase, abort_flag, err, SITE_TMEM_FULL);
       epilogue_tile<BN, FLAGS>(tmem_base + acc * BN, epi_stage + (warp - 2) * EPI_WARP_BYTES, sbias, sscale, warp,
-                               (warp - 2) >> 2, lane, m0, n0, M, out, ldo, flags, residual);
+                               (warp - 2) >> 2, lane, m0, n0, M, N, K, out, ldo, flags, residual, ln, mu, rstd);
       if (lane == 0) {
         if (leader) mbar_arrive(tempty_bar + acc);
         else mbar_arrive_remote(mapa_u32(smem_u32(tempty_bar + acc), 0));
@@ -683,6 +860,11 @@ constexpr int F_LIN8 = EPI_BIAS | EPI_OUT_F16 | EPI_IN_F16 | EPI_COLSCALE | EPI_
 constexpr int F_FFN18 = F_LIN8 | EPI_GELU;
 constexpr int F_LIN8W = F_LIN8 & ~EPI_W_FP8;    // FP8-weight mode with the weights widened to fp16 at load
 constexpr int F_FFN18W = F_FFN18 & ~EPI_W_FP8;
+constexpr int F_LIN_LN = F_LIN | EPI_LN_APPLY;     // QKV after a folded LayerNorm
+constexpr int F_FFN1_LN = F_FFN1 | EPI_LN_APPLY;   // FFN1 after a folded LayerNorm
+// attention-output / FFN2 feeding a folded LayerNorm: fp32 sum out (+ fp16 operand, statistics), residual fp32 ...
+constexpr int F_SUM = EPI_BIAS | EPI_IN_F16 | EPI_WSCALE | EPI_OUT_F32 | EPI_RESIDUAL | EPI_LN_SUM;
+constexpr int F_SUM_RLN = F_SUM | EPI_RES_LN;      // ... or itself a folded LayerNorm's output
 constexpr int F_S3 = EPI_BIAS | EPI_OUT_F32 | EPI_SPLIT3;   // fp32 mode on the tensor cores: QKV
 constexpr int F_S3_RES = F_S3 | EPI_RESIDUAL;               // attention-output, FFN2 (+ fp32 residual)
 constexpr int F_S3_FFN1 = F_S3 | EPI_GELU;
@@ -703,7 +885,7 @@ int launch_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, int
   const int tiles = ((M + BM - 1) / BM) * (N / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   return launch_pdl(gemm_tcgen05_kernel<BN, FLAGS>, dim3(grid), dim3(GEMM_THREADS), C::SMEM_BYTES, stream, *tmA, *tmW, M,
-                    N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev) == cudaSuccess
+                    N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev, epi.ln) == cudaSuccess
              ? 1 : -3;
 }
 
@@ -764,7 +946,7 @@ int launch_pair_one(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * (N / BN);
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
   return launch_pdl(gemm_tcgen05_pair_kernel<BN, FLAGS, W8>, dim3(grid), dim3(C::THREADS), C::SMEM_BYTES, stream, *tmA,
-                    *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev) ==
+                    *tmW, M, N, K, out, ldo, epi.flags, epi.bias, epi.residual, epi.colscale, err_flag, m_dev, epi.ln) ==
                  cudaSuccess ? 1 : -3;
 }
 
@@ -777,6 +959,10 @@ int launch_pair(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, in
     case F_FFN18: return launch_pair_one<F_FFN18, true>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_LIN8W: return launch_pair_one<F_LIN8W>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_FFN18W: return launch_pair_one<F_FFN18W>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_LIN_LN: return launch_pair_one<F_LIN_LN>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_FFN1_LN: return launch_pair_one<F_FFN1_LN>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_SUM: return launch_pair_one<F_SUM>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
+    case F_SUM_RLN: return launch_pair_one<F_SUM_RLN>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_S3: return launch_pair_one<F_S3>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_S3_RES: return launch_pair_one<F_S3_RES>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     case F_S3_FFN1: return launch_pair_one<F_S3_FFN1>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
@@ -863,6 +1049,19 @@ int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, i
   if ((epi.flags & EPI_RESIDUAL) && !epi.residual) return -1;
   if ((epi.flags & EPI_COLSCALE) && !epi.colscale) return -1;
   if ((epi.flags & EPI_SPLIT3) && (epi.flags & (EPI_IN_F16 | EPI_W_FP8))) return -1;  // the planes are bf16
+  if (epi.flags & (EPI_LN_SUM | EPI_LN_APPLY | EPI_RES_LN)) {  // folded LayerNorm: see LnFold
+    const LnFold& ln = epi.ln;
+    if ((epi.flags & EPI_SPLIT3) || (K % 128) != 0) return -1;
+    if ((epi.flags & EPI_LN_APPLY) && (!ln.stats_in || !ln.c)) return -1;
+    if (epi.flags & EPI_LN_SUM) {
+      // one statistics slice per epilogue warp and row: 256-wide tiles, i.e. the CTA-pair kernel
+      if (!ln.out16 || !ln.gamma || !ln.stats_out || !(epi.flags & EPI_OUT_F32) || (N % 256) != 0 || ldo != N) return -1;
+      if (!gemm_uses_pairs(N) && gemm_block_n(N) != 256) return -1;
+    }
+    if ((epi.flags & EPI_RES_LN) &&
+        (!ln.res_stats || !ln.res_gamma || !ln.res_beta || !(epi.flags & EPI_RESIDUAL) || !(epi.flags & EPI_OUT_F32)))
+      return -1;
+  }
   // Few rows: a CTA pair's 256 x 256 tiles are too few to occupy the SMs, and the k loop of one
   // tile is then the whole run time.  Single CTAs with 128 x 128 tiles have a k loop half as long
   // and four times as many tiles (BERT-base, 8 x 128 tokens: 0.80 against 0.88 ms per pass; one
@@ -881,7 +1080,7 @@ int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, i
     if (gemm_split_block_n(N) == 256) return launch_pair(tmA, tmW, M, N, K, out, ldo, epi, err_flag, m_dev, stream);
     return launch<128>(tmA, tmW, M, N, K, out, ldo, epi, err_flag, num_sms, m_dev, stream);
   }
-  if (small_tiles_enabled() && gemm_uses_pairs(N) && gemm_w_box_rows(N) == 128) {
+  if (small_tiles_enabled() && gemm_uses_pairs(N) && gemm_w_box_rows(N) == 128 && !(epi.flags & EPI_LN_SUM)) {
     const long pairs = num_sms / 2 > 0 ? num_sms / 2 : 1;
     const long tiles_p = static_cast<long>((M + 2 * BM - 1) / (2 * BM)) * (N / 256);
     const long tiles_s = static_cast<long>((M + BM - 1) / BM) * (N / 128);

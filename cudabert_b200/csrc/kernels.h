@@ -69,9 +69,34 @@ enum EpiFlags : int {
   EPI_IN_F16 = 256,  // A and W are fp16 (tcgen05 GEMM only; bf16 otherwise)
   EPI_W_FP8 = 512,   // W is E4M3 bytes [N, K] (map from make_tmap_u8_kmajor), widened to fp16 inside the
                      // kernel; needs EPI_IN_F16 and N % 256 == 0
-  EPI_SPLIT3 = 1024  // fp32 product on the tensor cores: A [M, 3 K] and W [N, 3 K] each hold three bf16 planes
+  EPI_SPLIT3 = 1024, // fp32 product on the tensor cores: A [M, 3 K] and W [N, 3 K] each hold three bf16 planes
                      // side by side (see split_bf16x3); the kernel sums the six leading cross terms over K
+  EPI_LN_SUM = 2048,   // this GEMM's output is the input of a LayerNorm that is not run as a kernel (LnFold below)
+  EPI_LN_APPLY = 4096, // this GEMM's A operand is such an input, times gamma: normalise in the epilogue
+  EPI_RES_LN = 8192    // the residual is LayerNorm(residual) of such an input: recompute it
 };
+
+// LayerNorm folded into the GEMMs on either side of it.  With s the LayerNorm's input (a GEMM's
+// accumulator + bias + residual) and mu_r, rstd_r its row statistics,
+//   LN(s) W + b = rstd_r ((s * gamma) W - mu_r (gamma W)) + (beta W + b).
+// The GEMM that produces s (EPI_LN_SUM; CTA-pair kernel, N % 256 == 0) writes s in fp32 (`out`, it is the
+// residual stream), s * gamma in fp16 (`out16`, the next GEMM's A operand) and, per row and 128-column
+// slice, the partial sum and sum of squares of s (`stats_out`, float2 [M][N / 128]).  The GEMM that consumes
+// it (EPI_LN_APPLY) adds the partials of a row in slice order (deterministic), and applies the two row
+// scalars with the vectors c = gamma W and d = beta W + b (d is passed as the bias).  Where the
+// residual of a producing GEMM is itself LN(s') of an earlier such input (EPI_RES_LN), it is recomputed
+// from s' (`residual`, fp32), its partials and its gamma, beta.
+struct LnFold {
+  const float* stats_in = nullptr;   // EPI_LN_APPLY: partials of the rows of A's LayerNorm input, [M][K / 128] float2
+  const float* c = nullptr;          // EPI_LN_APPLY: gamma W, [N]
+  void* out16 = nullptr;             // EPI_LN_SUM: fp16 [M][N], s * gamma
+  const float* gamma = nullptr;      // EPI_LN_SUM: [N]
+  float* stats_out = nullptr;        // EPI_LN_SUM: [M][N / 128] float2
+  const float* res_stats = nullptr;  // EPI_RES_LN: partials of the residual's LayerNorm input, [M][N / 128] float2
+  const float* res_gamma = nullptr;  // EPI_RES_LN: [N]
+  const float* res_beta = nullptr;   // EPI_RES_LN: [N]
+};
+constexpr float LN_EPS_F = 1e-12f;
 
 // fp32 on the 16-bit tensor-core path.  An fp32 number is the sum of three bf16 numbers, x = x0 + x1 +
 // x2 with x0 = bf16(x), x1 = bf16(x - x0), x2 = bf16(x - x0 - x1) (the subtractions are exact; bf16 has
@@ -92,6 +117,7 @@ struct GemmEpilogue {
   const float* bias = nullptr;
   const void* residual = nullptr;
   const float* colscale = nullptr;
+  LnFold ln;
 };
 
 // ---- tcgen05 GEMM: out[M, N] = A[M, K] (K contiguous) x W[N, K]^T (K contiguous), both bf16, or both
@@ -111,6 +137,7 @@ int wait_timeout_probe(int* err_flag, unsigned long long limit_ns, cudaStream_t 
 // Box rows the W tensor map must be encoded with for the kernel variant that gemm_tcgen05
 // will pick for this N (128 when CTA pairs each load half of a 256-row tile, else gemm_block_n).
 int gemm_w_box_rows(int N);
+bool gemm_uses_pairs(int N);  // the CTA-pair kernel (256 x 256 tiles) serves this width
 // The same for the W operand of an EPI_SPLIT3 GEMM ([N, 3 K] bf16 planes): CTA pairs with 256 x 256
 // tiles for N > 1024, single CTAs with 128 x 128 tiles otherwise.
 int gemm_split_block_n(int N);
@@ -203,6 +230,10 @@ int transpose_round_bf16(const float* src, __half* dst, int K, int N, cudaStream
 int quantize_fp8_weight(const float* src, uint8_t* dst_q, __half* dst_wide, float* scale_out, int K, int N,
                         cudaStream_t stream);
 int fill_f32(float* dst, float value, size_t n, cudaStream_t stream);
+// LnFold's vectors for the GEMM with bf16-mode weights w ([N, K], fp16 container) that follows a LayerNorm
+// with gamma, beta: c = gamma W, d = beta W + bias.
+int ln_fold_vectors(const __half* w, const float* gamma, const float* beta, const float* bias, float* c, float* d, int N,
+                    int K, cudaStream_t stream);
 // The three bf16 planes of an fp32 weight matrix, K-contiguous: dst[n, p K + k] = plane p of src[k, n]
 // (dst rows of 3 K elements; the row offset lets Q, K, V be packed into one operand).
 int transpose_split_bf16x3(const float* src, __nv_bfloat16* dst, int K, int N, cudaStream_t stream);

@@ -39,6 +39,7 @@ Model::~Model() {
   cudaSetDevice(dev_);
   if (stream_) cudaStreamSynchronize(stream_);
   for (const Owned& o : owned_) cudaFree(o.p);
+  for (void* p : derived_) cudaFree(p);
   if (arena_) cudaFree(arena_);
   if (stage_f32_) cudaFree(stage_f32_);
   if (hidden_unpacked_) cudaFree(hidden_unpacked_);
@@ -95,6 +96,10 @@ bool Model::init(bool large, int gpu, int max_batch, int max_seq, const std::str
     // both operands into three bf16 planes for the tensor cores
     const char* f32 = std::getenv("CUDABERT_FP32_GEMM");
     f32_tensor_ = !(f32 && f32[0] == 'c');
+    // CUDABERT_LN_FOLD=1 (bf16 mode): the LayerNorms between the dense layers are not run as kernels;
+    // the GEMM before one writes its input and row statistics, the GEMM after it normalises in its epilogue
+    const char* lf = std::getenv("CUDABERT_LN_FOLD");
+    ln_fold_ = lf && lf[0] == '1' && precision == PREC_BF16;
     const char* nv = std::getenv("CUDABERT_NVTX");
     nvtx_ = nv && nv[0] == '1';
   }
@@ -335,7 +340,31 @@ bool Model::load_weights(const std::string& dir) {
     stage_f32_ = nullptr;
     stage_elems_ = 0;
   }
-  return true;
+  return prepare_ln_fold();
+}
+
+bool Model::prepare_ln_fold() {
+  // needs the 256-wide tiles of the CTA-pair GEMM for the GEMMs that write the statistics (N = H)
+  if (ln_fold_ && !(gemm_uses_pairs(H_) && H_ % 256 == 0 && L_ >= 2)) ln_fold_ = false;
+  if (!ln_fold_) return true;
+  auto vec = [&](float** p, int n) {
+    if (!check(cudaMalloc(p, static_cast<size_t>(n) * sizeof(float)), "cudaMalloc(LayerNorm vectors)")) return false;
+    derived_.push_back(*p);
+    return true;
+  };
+  for (int l = 0; l < L_; ++l) {
+    LayerWeights& lw = layer_[l];
+    if (!vec(&lw.c_ffn1, F_) || !vec(&lw.d_ffn1, F_)) return false;
+    if (ln_fold_vectors(static_cast<const __half*>(lw.ffn1.w), lw.ln1_g, lw.ln1_b, lw.ffn1.bias, lw.c_ffn1, lw.d_ffn1, F_,
+                        H_, stream_) < 0)
+      return fail(2, "launch failed");
+    if (l == 0) continue;
+    if (!vec(&lw.c_qkv, 3 * H_) || !vec(&lw.d_qkv, 3 * H_)) return false;
+    if (ln_fold_vectors(static_cast<const __half*>(lw.qkv.w), layer_[l - 1].ln2_g, layer_[l - 1].ln2_b, lw.qkv.bias,
+                        lw.c_qkv, lw.d_qkv, 3 * H_, H_, stream_) < 0)
+      return fail(2, "launch failed");
+  }
+  return check(cudaStreamSynchronize(stream_), "LayerNorm vectors");
 }
 
 // ------------------------------------------------------------------ weight cache
@@ -471,6 +500,8 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   const size_t o_ctx = slot(ct * H_ * esize_);
   const size_t o_qkv = slot(ct * 3 * H_ * esize_);
   const size_t o_z = slot(ct * F_ * esize_);
+  const size_t o_st1 = ln_fold_ ? slot(ct * (H_ / 128) * 2 * sizeof(float)) : 0;
+  const size_t o_st2 = ln_fold_ ? slot(ct * (H_ / 128) * 2 * sizeof(float)) : 0;
   const bool planes = !lowp && f32_tensor_;
   const size_t o_split = planes ? slot(ct * F_ * 6) : 0;  // three bf16 planes of the widest GEMM input
   const size_t o_pool = slot(static_cast<size_t>(cbatch) * H_ * sizeof(float));
@@ -487,6 +518,8 @@ bool Model::ensure_capacity(int B, int S, bool want_hidden_f32) {
   xa_ = base + o_xa; x1a_ = base + o_x1a; ctx_ = base + o_ctx; qkv_ = base + o_qkv; z_ = base + o_z;
   pooled_ = reinterpret_cast<float*>(base + o_pool);
   probs_ = reinterpret_cast<float*>(base + o_probs);
+  ln_stats1_ = ln_fold_ ? reinterpret_cast<float*>(base + o_st1) : nullptr;
+  ln_stats2_ = ln_fold_ ? reinterpret_cast<float*>(base + o_st2) : nullptr;
   // zero once so that tile rows beyond the live token count never hold NaN patterns
   if (!check(cudaMemsetAsync(arena_, 0, off, stream_), "cudaMemset(arena)")) return false;
   if (lowp) {
@@ -572,11 +605,12 @@ void Model::get_profile(int kclass, double* ms, long* launches) const {
 
 // ------------------------------------------------------------------ forward
 bool Model::dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, int lda, int M, void* out, int flags,
-                  const void* residual, int kclass) {
+                  const void* residual, int kclass, const LnFold* ln, const float* bias) {
   GemmEpilogue epi;
   epi.flags = flags;
-  epi.bias = w.bias;
+  epi.bias = bias ? bias : w.bias;  // a folded LayerNorm's beta W + bias takes the bias's place
   epi.residual = residual;
+  if (ln) epi.ln = *ln;
   int n;
   prof_begin(kclass);
   if (prec_ == PREC_FP32 && f32_tensor_) {
@@ -594,7 +628,7 @@ bool Model::dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, i
   } else {
     // 16-bit modes: fp16 operands and output; the weights' container scale (bf16 mode) or their
     // FP8 de-quantisation scale comes out in the epilogue
-    epi.flags |= EPI_IN_F16 | EPI_OUT_F16;
+    epi.flags |= EPI_IN_F16 | ((flags & EPI_OUT_F32) ? 0 : EPI_OUT_F16);
     if (prec_ == PREC_FP8) {
       epi.flags |= EPI_COLSCALE | (fp8_widened_ ? 0 : EPI_W_FP8);
       epi.colscale = w.colscale;
@@ -720,9 +754,22 @@ bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mas
                                                vocab_rows_, err_dev_, rs, stream_));
   }
   bool compact_out = false;  // the final hidden states hold one row per sequence (rows [0, B))
+  // Folded LayerNorms (LnFold): in layers 0 .. L-2 the first LayerNorm, in layers 0 .. L-3 the second one
+  // are not run as kernels.  The last layer runs unfolded (it may work on the first tokens only and
+  // ends in hidden states the pooler reads), so the layer before it ends in an ordinary LayerNorm.
+  const bool fold = lowp && ln_fold_;
   for (int l = 0; l < L_; ++l) {
     const LayerWeights& w = layer_[l];
-    if (!dense(w.qkv, xa_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) return false;
+    const bool fold1 = fold && l <= L_ - 2, fold2 = fold && l <= L_ - 3;
+    const bool in_folded = fold && l >= 1 && l - 1 <= L_ - 3;  // this layer's input is LN(sum) with sum in xf_, sum * gamma in xa_
+    if (in_folded) {
+      LnFold f;
+      f.stats_in = ln_stats2_;
+      f.c = w.c_qkv;
+      if (!dense(w.qkv, xa_, &tm_x_, H_, T, qkv_, EPI_BIAS | EPI_LN_APPLY, nullptr, KC_GEMM_QKV, &f, w.d_qkv)) return false;
+    } else if (!dense(w.qkv, xa_, &tm_x_, H_, T, qkv_, EPI_BIAS, nullptr, KC_GEMM_QKV)) {
+      return false;
+    }
     if (lowp) {
       // The pooler reads the first token of every sequence only.  When nothing else of the final
       // hidden states is wanted, the LAST layer therefore computes, after its K and V, only that
@@ -744,6 +791,48 @@ bool Model::enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mas
       const int rows = cls ? B : T;               // rows the rest of the layer works on
       const int* rows_live = cls ? nullptr : live;  // ... all of them live in the compact case
       if (cls) m_dev_cur_ = nullptr;
+      if (fold1) {
+        // s1 = ctx.Wo + bo + x in fp32 -> x1f_, s1 * gamma1 in fp16 -> x1a_, row statistics -> ln_stats1_;
+        // x is the materialised input (xf_) or LN(previous sum) recomputed from it
+        LnFold f;
+        f.out16 = x1a_;
+        f.gamma = w.ln1_g;
+        f.stats_out = ln_stats1_;
+        int fl = EPI_BIAS | EPI_OUT_F32 | EPI_RESIDUAL | EPI_LN_SUM;
+        if (in_folded) {
+          fl |= EPI_RES_LN;
+          f.res_stats = ln_stats2_;
+          f.res_gamma = layer_[l - 1].ln2_g;
+          f.res_beta = layer_[l - 1].ln2_b;
+        }
+        if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, rows, x1f_, fl, xf_, KC_GEMM_ATTN_OUT, &f)) return false;
+        // FFN1 normalises in its epilogue
+        LnFold g;
+        g.stats_in = ln_stats1_;
+        g.c = w.c_ffn1;
+        if (!dense(w.ffn1, x1a_, &tm_x1_, H_, rows, z_, EPI_BIAS | EPI_GELU | EPI_LN_APPLY, nullptr, KC_GEMM_FFN1, &g, w.d_ffn1))
+          return false;
+        // s2 = z.W2 + b2 + LN1(s1), the residual recomputed from s1 and its statistics
+        LnFold h;
+        h.res_stats = ln_stats1_;
+        h.res_gamma = w.ln1_g;
+        h.res_beta = w.ln1_b;
+        if (fold2) {  // -> xf_ (fp32), s2 * gamma2 -> xa_, statistics -> ln_stats2_: the next layer's folded input
+          h.out16 = xa_;
+          h.gamma = w.ln2_g;
+          h.stats_out = ln_stats2_;
+          if (!dense(w.ffn2, z_, &tm_z_, F_, rows, xf_, EPI_BIAS | EPI_OUT_F32 | EPI_RESIDUAL | EPI_RES_LN | EPI_LN_SUM, x1f_,
+                     KC_GEMM_FFN2, &h))
+            return false;
+        } else {      // the layer before the last: s2 in fp32 -> xf_, then an ordinary LayerNorm over it, in place
+          if (!dense(w.ffn2, z_, &tm_z_, F_, rows, xf_, EPI_BIAS | EPI_OUT_F32 | EPI_RESIDUAL | EPI_RES_LN, x1f_, KC_GEMM_FFN2, &h))
+            return false;
+          CB_LAUNCH(KC_LAYERNORM, (layernorm<float, __half>(xf_, nullptr, w.ln2_g, w.ln2_b, xa, xf_, rows, H_, rows_live,
+                                                            stream_)));
+        }
+        compact_out = false;
+        continue;
+      }
       // y = ctx.Wo + bo in fp16; x1 = LN(y + x) with the add in fp32 inside the LayerNorm kernel
       if (!dense(w.attn_out, ctx_, &tm_ctx_, H_, rows, y_, EPI_BIAS, nullptr, KC_GEMM_ATTN_OUT))
         return false;

@@ -42,6 +42,9 @@ struct DenseWeight {      // one projection
 struct LayerWeights {
   DenseWeight qkv, attn_out, ffn1, ffn2;
   float *ln1_g = nullptr, *ln1_b = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
+  // LayerNorms folded into the GEMMs around them (LnFold): gamma W and beta W + bias of the QKV GEMM (with the
+  // previous layer's second LayerNorm) and of the FFN1 GEMM (with this layer's first)
+  float *c_qkv = nullptr, *d_qkv = nullptr, *c_ffn1 = nullptr, *d_ffn1 = nullptr;
 };
 
 class Model {
@@ -108,7 +111,7 @@ class Model {
   void prof_end(int kclass);
   bool collect_profile();
   bool dense(const DenseWeight& w, const void* A, const CUtensorMap* tmA, int lda, int M, void* out, int flags,
-             const void* residual, int kclass);
+             const void* residual, int kclass, const LnFold* ln = nullptr, const float* bias = nullptr);
 
   // Enqueues the kernels of one forward pass on stream_ (directly, or into a stream capture).
   bool enqueue_forward(const int* d_ids, const int* d_seg, const int* d_mask, int B, int S, bool want_hidden_f32,
@@ -137,6 +140,9 @@ class Model {
   bool graphs_enabled_ = true;
   bool nvtx_ = false;         // CUDABERT_NVTX=1: NVTX ranges around passes and launches
   bool fp8_widened_ = false;  // FP8 mode: weights expanded to fp16 at load (CUDABERT_FP8_OPERAND=widened)
+  bool ln_fold_ = false;      // bf16 mode: LayerNorms folded into the GEMMs around them (CUDABERT_LN_FOLD=1)
+  float* ln_stats1_ = nullptr;  // per row and 128-column slice: partial sum and sum of squares of the first ...
+  float* ln_stats2_ = nullptr;  // ... and second LayerNorm's input of a layer
   bool f32_tensor_ = true;    // fp32 mode: dense layers on the tensor cores as sums of bf16 planes (CUDABERT_FP32_GEMM=cuda: CUDA cores)
   bool cls_last_ = true;  // pooler-only passes compute the last layer for the first token of every sequence only
   static constexpr int PDL_MAX_TOKENS = 4096;  // forward passes up to this many token slots use dependent launch
@@ -160,6 +166,8 @@ class Model {
   size_t stage_elems_ = 0;
   struct Owned { void* p; size_t bytes; };
   std::vector<Owned> owned_;    // every cudaMalloc'ed weight buffer, in allocation order
+  std::vector<void*> derived_;  // device buffers computed from the weights after loading (not part of the cache)
+  bool prepare_ln_fold();       // the folded LayerNorms' vectors
   bool dev_alloc(void** p, size_t bytes);  // cudaMalloc + owned_
 
   // Weight cache (CUDABERT_WEIGHT_CACHE=<directory>): the device-ready weights of one (model directory,

@@ -288,6 +288,31 @@ split_bf16x3_kernel(const float* __restrict__ src, int lds, __nv_bfloat16* __res
   }
 }
 
+// The vectors of a LayerNorm folded into the GEMM that follows it (LnFold): c[n] = sum_k gamma[k] W[k, n],
+// d[n] = sum_k beta[k] W[k, n] + bias[n], with W as the GEMM sees it (w[n, k] / W_CONTAINER_SCALE).  One warp per n.
+__global__ void ln_fold_vectors_kernel(const __half* __restrict__ w, const float* __restrict__ gamma,
+                                       const float* __restrict__ beta, const float* __restrict__ bias,
+                                       float* __restrict__ c, float* __restrict__ d, int N, int K) {
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (n >= N) return;
+  const __half* row = w + static_cast<size_t>(n) * K;
+  float sc = 0.f, sd = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float x = __half2float(row[k]);
+    sc = fmaf(gamma[k], x, sc);
+    sd = fmaf(beta[k], x, sd);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    sc += __shfl_xor_sync(0xffffffffu, sc, off);
+    sd += __shfl_xor_sync(0xffffffffu, sd, off);
+  }
+  if (lane == 0) {
+    c[n] = sc * (1.0f / W_CONTAINER_SCALE);
+    d[n] = sd * (1.0f / W_CONTAINER_SCALE) + bias[n];
+  }
+}
+
 __global__ void maxabs_kernel(const float* __restrict__ src, size_t n, unsigned int* __restrict__ out_bits) {
   float m = 0.f;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
@@ -505,6 +530,12 @@ int split_bf16x3(const float* src, int lds, __nv_bfloat16* dst, int rows, int K,
   const int grid = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
   return launch_pdl(split_bf16x3_kernel, dim3(grid), dim3(256), 0, stream, src, lds, dst, rows, K, rows_dev) ==
                  cudaSuccess ? 1 : -3;
+}
+
+int ln_fold_vectors(const __half* w, const float* gamma, const float* beta, const float* bias, float* c, float* d, int N,
+                    int K, cudaStream_t stream) {
+  ln_fold_vectors_kernel<<<(N + 7) / 8, 256, 0, stream>>>(w, gamma, beta, bias, c, d, N, K);
+  return cudaGetLastError() == cudaSuccess ? 1 : -3;
 }
 
 int fill_f32(float* dst, float value, size_t n, cudaStream_t stream) {

@@ -17,7 +17,7 @@ BASE_CASES = ["c0_affine", "c2_small", "edge_s17", "edge_b1s1", "edge_nomask", "
 LARGE_CASES = ["c1_small", "c3_small", "c4_small"]
 SWITCHES = ("CUDABERT_PACK", "CUDABERT_GRAPH", "CUDABERT_PDL", "CUDABERT_LAST_LAYER", "CUDABERT_ATTENTION",
             "CUDABERT_GEMM_PAIR", "CUDABERT_GEMM_SMALL_TILES", "CUDABERT_PRECISION", "CUDABERT_LN",
-            "CUDABERT_FP8_OPERAND", "CUDABERT_ATTENTION_TILES", "CUDABERT_FP32_GEMM", "SWITCH_CHILD_PRECISION")
+            "CUDABERT_FP8_OPERAND", "CUDABERT_ATTENTION_TILES", "CUDABERT_FP32_GEMM", "CUDABERT_LN_FOLD", "SWITCH_CHILD_PRECISION")
 
 
 @pytest.fixture(scope="module")
@@ -56,7 +56,7 @@ def test_scheduling_switches_keep_every_bit(run_with, switch):
 
 
 @pytest.mark.parametrize("switch", ["CUDABERT_ATTENTION=tc", "CUDABERT_ATTENTION=persist", "CUDABERT_ATTENTION=mma",
-                                    "CUDABERT_GEMM_PAIR=0", "CUDABERT_GEMM_SMALL_TILES=1"])
+                                    "CUDABERT_GEMM_PAIR=0", "CUDABERT_GEMM_SMALL_TILES=1", "CUDABERT_LN_FOLD=1"])
 def test_kernel_choice_switches_stay_close(run_with, switch):
     """Another attention kernel or GEMM tile shape rounds at other places, and twelve or twenty-four
     layers of bf16 activations amplify that: the output stays within the bf16 mode's budget against the
