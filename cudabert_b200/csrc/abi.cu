@@ -252,6 +252,7 @@ int cudabert_k_gemm_tcgen05(const void* A_dev, long lda, const void* W_dev, int 
                          const float* bias_dev, const void* residual_dev, const float* colscale_dev, int* err_dev) {
   if (!A_dev || !W_dev || !out_dev || M <= 0 || N <= 0 || K <= 0 || lda < K) return 1;
   if (flags & cb::EPI_SPLIT3) return 1;  // operands of three planes: cudabert_k_gemm_f32_tensor builds them
+  if (flags & (cb::EPI_LN_SUM | cb::EPI_LN_APPLY | cb::EPI_RES_LN)) return 1;  // folded LayerNorms need the model's buffers
   CUtensorMap tmA, tmW;
   if (!cb::make_tmap_16bit_kmajor(&tmA, A_dev, M, K, static_cast<uint64_t>(lda) * 2, 128)) return 2;
   if (flags & cb::EPI_W_FP8) {

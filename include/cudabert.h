@@ -214,7 +214,8 @@ CUDABERT_API long long cudabert_reader_rejected(void* reader, long long* first_i
  * (bf16 otherwise), 128 accumulator x 1/4096 (the encoder holds its bf16-rounded weights as fp16 numbers
  * times 4096), 256 fp16 operands, 512 W given as E4M3 bytes (with 256 and 32; N % 256 == 0).  err_dev:
  * device int, set non-zero if a pipeline wait timed out.  N % 128 == 0, K % 64 == 0.  (Flag 1024, operands
- * of three bf16 planes, is refused here: cudabert_k_gemm_f32_tensor prepares such operands itself.)  */
+ * of three bf16 planes, is refused here: cudabert_k_gemm_f32_tensor prepares such operands itself; so are
+ * 2048, 4096 and 8192, the folded LayerNorms of CUDABERT_LN_FOLD=1, which exist inside a forward pass only.) */
 CUDABERT_API int cudabert_k_gemm_tcgen05(const void* A_dev, long lda, const void* W_dev, int M, int N, int K, void* out_dev,
                          int flags, const float* bias_dev, const void* residual_dev, const float* colscale_dev,
                          int* err_dev);
