@@ -331,6 +331,57 @@ int cudabert_k_gemm_f32_tensor(const float* A_dev, int lda, const float* W_dev, 
   return rc;
 }
 
+int cudabert_k_gemm_ln_folded(const void* A1_dev, const void* W1_dev, const float* b1_dev, const float* res_dev,
+                              const float* gamma_dev, const float* beta_dev, const void* W2_dev, const float* b2_dev, int M,
+                              int H, int K1, int N2, int gelu, float* sum_dev, void* out_dev) {
+  if (!A1_dev || !W1_dev || !b1_dev || !res_dev || !gamma_dev || !beta_dev || !W2_dev || !b2_dev || !sum_dev || !out_dev)
+    return 1;
+  if (M <= 0 || H <= 0 || H % 256 != 0 || K1 % 64 != 0 || N2 % 128 != 0 || !cb::gemm_uses_pairs(H)) return 1;
+  // scratch: s * gamma (fp16 [M, H]) | statistics (float2 [M, H / 128]) | gamma W2 [N2] | beta W2 + b2 [N2] | error word
+  const size_t b_s16 = static_cast<size_t>(M) * H * 2, b_st = static_cast<size_t>(M) * (H / 128) * 8;
+  char* scratch = nullptr;
+  if (cudaMalloc(&scratch, b_s16 + b_st + 2 * static_cast<size_t>(N2) * 4 + 16) != cudaSuccess) return 2;
+  __half* s16 = reinterpret_cast<__half*>(scratch);
+  float* stats = reinterpret_cast<float*>(scratch + b_s16);
+  float* c = reinterpret_cast<float*>(scratch + b_s16 + b_st);
+  float* d = c + N2;
+  int* err = reinterpret_cast<int*>(d + N2);
+  cudaMemset(err, 0, sizeof(int));
+  int rc = 0;
+  CUtensorMap tmA1, tmW1, tmA2, tmW2;
+  if (!cb::make_tmap_16bit_kmajor(&tmA1, A1_dev, M, K1, static_cast<uint64_t>(K1) * 2, 128) ||
+      !cb::make_tmap_16bit_kmajor(&tmW1, W1_dev, H, K1, static_cast<uint64_t>(K1) * 2, cb::gemm_w_box_rows(H)) ||
+      !cb::make_tmap_16bit_kmajor(&tmA2, s16, M, H, static_cast<uint64_t>(H) * 2, 128) ||
+      !cb::make_tmap_16bit_kmajor(&tmW2, W2_dev, N2, H, static_cast<uint64_t>(H) * 2, cb::gemm_w_box_rows(N2)))
+    rc = 2;
+  if (!rc) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cb::GemmEpilogue p;  // the GEMM in front of the LayerNorm
+    p.flags = cb::EPI_BIAS | cb::EPI_IN_F16 | cb::EPI_WSCALE | cb::EPI_OUT_F32 | cb::EPI_RESIDUAL | cb::EPI_LN_SUM;
+    p.bias = b1_dev;
+    p.residual = res_dev;
+    p.ln.out16 = s16;
+    p.ln.gamma = gamma_dev;
+    p.ln.stats_out = stats;
+    cb::GemmEpilogue q;  // the GEMM behind it
+    q.flags = cb::EPI_BIAS | cb::EPI_IN_F16 | cb::EPI_WSCALE | cb::EPI_OUT_F16 | cb::EPI_LN_APPLY | (gelu ? cb::EPI_GELU : 0);
+    q.bias = d;
+    q.ln.stats_in = stats;
+    q.ln.c = c;
+    if (cb::ln_fold_vectors(static_cast<const __half*>(W2_dev), gamma_dev, beta_dev, b2_dev, c, d, N2, H, nullptr) < 0 ||
+        cb::gemm_tcgen05(&tmA1, &tmW1, M, H, K1, sum_dev, H, p, err, sms, nullptr, nullptr) < 0 ||
+        cb::gemm_tcgen05(&tmA2, &tmW2, M, N2, H, out_dev, N2, q, err, sms, nullptr, nullptr) < 0)
+      rc = 3;
+    if (cudaDeviceSynchronize() != cudaSuccess) rc = 4;
+    int herr = 0;
+    if (!rc && (cudaMemcpy(&herr, err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess || herr)) rc = 5;
+  }
+  cudaFree(scratch);
+  return rc;
+}
+
 int cudabert_k_attention(int kernel, const void* qkv_dev, const int* mask_dev, void* ctx_dev, int B, int S, int heads) {
   if (!qkv_dev || !ctx_dev || B <= 0 || S <= 0 || heads <= 0) return 1;
   const int cls_only = (kernel & 16) ? 1 : 0;  // + 16: first query of every sequence only, ctx is [B, H]

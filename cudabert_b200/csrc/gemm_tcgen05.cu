@@ -1051,8 +1051,8 @@ int gemm_tcgen05(const CUtensorMap* tmA, const CUtensorMap* tmW, int M, int N, i
   if ((epi.flags & EPI_SPLIT3) && (epi.flags & (EPI_IN_F16 | EPI_W_FP8))) return -1;  // the planes are bf16
   if (epi.flags & (EPI_LN_SUM | EPI_LN_APPLY | EPI_RES_LN)) {  // folded LayerNorm: see LnFold
     const LnFold& ln = epi.ln;
-    if ((epi.flags & EPI_SPLIT3) || (K % 128) != 0) return -1;
-    if ((epi.flags & EPI_LN_APPLY) && (!ln.stats_in || !ln.c)) return -1;
+    if (epi.flags & EPI_SPLIT3) return -1;
+    if ((epi.flags & EPI_LN_APPLY) && (!ln.stats_in || !ln.c || (K % 128) != 0)) return -1;  // one partial per 128 columns of A's LayerNorm input
     if (epi.flags & EPI_LN_SUM) {
       // one statistics slice per epilogue warp and row: 256-wide tiles, i.e. the CTA-pair kernel
       if (!ln.out16 || !ln.gamma || !ln.stats_out || !(epi.flags & EPI_OUT_F32) || (N % 256) != 0 || ldo != N) return -1;

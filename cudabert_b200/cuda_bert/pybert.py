@@ -279,6 +279,9 @@ k_gemm_f32.restype = c_int
 k_gemm_f32_tensor = lib.cudabert_k_gemm_f32_tensor
 k_gemm_f32_tensor.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
 k_gemm_f32_tensor.restype = c_int
+k_gemm_ln_folded = lib.cudabert_k_gemm_ln_folded
+k_gemm_ln_folded.argtypes = [c_void_p] * 8 + [c_int] * 5 + [c_void_p, c_void_p]
+k_gemm_ln_folded.restype = c_int
 k_attention = lib.cudabert_k_attention
 k_attention.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]
 k_attention.restype = c_int

@@ -228,6 +228,15 @@ CUDABERT_API int cudabert_k_gemm_f32(const float* A_dev, int lda, const float* W
  * 2^-24 of |a| |w|.  Same arguments as cudabert_k_gemm_f32; N % 128 == 0, K % 64 == 0, lda % 4 == 0. */
 CUDABERT_API int cudabert_k_gemm_f32_tensor(const float* A_dev, int lda, const float* W_dev, int M, int N, int K,
                                             float* out_dev, int flags, const float* bias_dev, const float* residual_dev);
+/* Two dense layers of bf16 mode with the LayerNorm between them folded into their epilogues, as a forward
+ * pass runs them with CUDABERT_LN_FOLD=1:  sum = A1 W1 + b1 + res (fp32 [M, H], written to sum_dev);
+ * out = act(LayerNorm(sum; gamma, beta) W2 + b2) in fp16 [M, N2], act = GELU if `gelu`.  A1 fp16 [M, K1]; W1
+ * [H, K1] and W2 [N2, H] as the encoder holds its weights (bf16 values times 4096 in fp16); res fp32 [M, H].
+ * H % 256 == 0, K1 % 64 == 0, N2 % 128 == 0. */
+CUDABERT_API int cudabert_k_gemm_ln_folded(const void* A1_dev, const void* W1_dev, const float* b1_dev, const float* res_dev,
+                                           const float* gamma_dev, const float* beta_dev, const void* W2_dev,
+                                           const float* b2_dev, int M, int H, int K1, int N2, int gelu, float* sum_dev,
+                                           void* out_dev);
 /* ctx[T,H] = attention(qkv[T,3H]); mask_dev int32 [B,S] or NULL; kernel: 0 = fp32 kernel (fp32 in and
  * out), 1 = 16-bit mma.sync kernel (one CTA per sequence and head), 2 = 16-bit tcgen05 kernel, 3 = 16-bit
  * mma.sync kernel, persistent (S <= 256); the 16-bit kernels take fp16 Q, K, V and write fp16.  Adding 16

@@ -160,6 +160,46 @@ def test_gemm_f32_on_tensor_cores(pybert, M, N, K, flags):
         print("max err %.3g (torch fp32 GEMM: %.3g)" % (err.max().item(), (plain - exact.float()).abs().max().item()))
 
 
+@pytest.mark.parametrize("M,H,K1,N2,gelu", [(300, 768, 768, 3072, 1), (1000, 1024, 4096, 3072, 0), (77, 1024, 1024, 4096, 1),
+                                            (2049, 768, 3072, 2304, 0), (1, 256, 64, 128, 0)])
+def test_layernorm_folded_into_its_gemms(pybert, M, H, K1, N2, gelu):
+    """The GEMM in front of a LayerNorm writes the sum (fp32), the sum times gamma (fp16) and per-row
+    partial statistics; the GEMM behind it normalises in its epilogue:
+    LN(s) W + b = rstd (s * gamma) W - rstd mu (gamma W) + (beta W + b).  Against the two layers with
+    an explicit LayerNorm in float64 on the same fp16 / bf16 inputs; the rows get offsets and scales so
+    that the means are not small against the spread."""
+    g = torch.Generator(device="cuda").manual_seed(M + H + K1 + N2)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    A1 = (rnd(M, K1) * 0.5).half()
+    W1 = (rnd(H, K1) * 0.05).bfloat16().float()
+    W2 = (rnd(N2, H) * 0.05).bfloat16().float()
+    b1, b2 = rnd(H) * 0.1, rnd(N2) * 0.1
+    res = rnd(M, H) * torch.exp2(torch.randint(-2, 3, (M, 1), device="cuda", generator=g).float()) + rnd(M, 1)
+    gamma, beta = 1.0 + 0.3 * rnd(H), 0.2 * rnd(H)
+    hold = lambda w: (w * W_CONTAINER_SCALE).half().contiguous()      # the encoder's weight container
+    s_out = torch.full((M, H), float("nan"), device="cuda")
+    out = torch.full((M, N2), float("nan"), device="cuda", dtype=torch.float16)
+    W1h, W2h, res = hold(W1), hold(W2), res.contiguous()
+    rc = pybert.k_gemm_ln_folded(A1.data_ptr(), W1h.data_ptr(), b1.data_ptr(), res.data_ptr(), gamma.data_ptr(),
+                                 beta.data_ptr(), W2h.data_ptr(), b2.data_ptr(), M, H, K1, N2, gelu, s_out.data_ptr(),
+                                 out.data_ptr())
+    assert rc == 0
+    s = A1.double() @ W1.double().t() + b1.double() + res.double()
+    # fp32 accumulation in the tensor core: within 2e-6 of sum |a||w|, element by element
+    s_bound = 2e-6 * (A1.double().abs() @ W1.double().abs().t()) + 1e-6 * s.abs() + 1e-6
+    assert ((s_out.double() - s).abs() / s_bound).max().item() <= 1.0
+    ln = bert_oracle.layer_norm(s, gamma.double(), beta.double())
+    ref = ln @ W2.double().t() + b2.double()
+    if gelu:
+        ref = bert_oracle.gelu(ref)
+    # the operand s * gamma is rounded to fp16 (2^-11 relative per element) and so is the output
+    scale = ((ln.abs() + (s.mean(-1, keepdim=True) / s.std(-1, keepdim=True)).abs()) @ W2.double().abs().t())
+    err = (out.double() - ref).abs()
+    bound = 2.0 ** -10 * scale / (H ** 0.5) * 4 + 2.0 ** -10 * ref.abs() + 1e-3
+    assert (err / bound).max().item() <= 1.0, "max err %.3g" % err.max().item()
+    assert torch.isfinite(out.float()).all()
+
+
 def _attention_ref(qkv, mask, B, S, heads):
     # float64: in fp32 a row whose keys are all masked loses score bits to the -10000 offset
     H = heads * 64
