@@ -4,21 +4,24 @@
 // Query_Key::forward (ops/batch_matmul.cu:24-82), cuApplySoftmax (ops/softmax.cu:86-143) and
 // Prob_Value::forward (ops/batch_matmul.cu:85-140) of the reference.
 //
-// Persistent CTAs (two per SM) walk over work items (sequence b, head h, 128-query tile).  Per
-// item, for every block of 64 keys:
+// Persistent CTAs (two per SM) walk over work items: a tile of 128 query rows of one head, either of
+// one sequence or, in the packed row layout, of whatever sequences 128 consecutive rows belong to (see
+// Cursor).  Per item, for every step (a block of up to 64 keys of one sequence):
 //   warp 4, one lane   TMA: Q tile (once per item), K block, V block -> shared memory (128-byte
 //                      swizzle), two buffers each; a buffer is re-filled as soon as the MMAs that
 //                      read it have completed (tcgen05.commit on its "empty" barrier).
 //   warp 5, one lane   S = Q K^T   tcgen05.mma 128 x 64 x 16 (x4 over d = 64) into one of two S
-//                      buffers in TMEM, issued one block AHEAD so that it runs while the softmax
+//                      buffers in TMEM, issued one step AHEAD so that it runs while the softmax
 //                      warps work; after they have written P: O (+)= P V, 128 x 64 x 16 (x4 over
 //                      the 64 keys), V used as an MN-major operand straight from its [key][d]
-//                      rows, O in TMEM columns [128, 192).
-//   warps 0-3          thread = query row = TMEM lane: scale + mask bias, row max (no shuffles: the
-//                      whole row belongs to the thread), online-softmax correction of O in TMEM
-//                      when a later key block raises the max, P = exp2(x - max) as fp16 into the
-//                      swizzled A-operand tile in shared memory; at the end O / sum -> fp16 ->
-//                      coalesced stores.
+//                      rows, O in TMEM columns [128, 192) or [192, 256), alternating between items.
+//   warps 0-3          thread = query row = TMEM lane: scale, keys beyond the sequence cut by index
+//                      (the mask row is read only for sequences with masked keys below their last
+//                      valid one), row max (no shuffles: the whole row belongs to the thread),
+//                      online-softmax correction of O in TMEM when a later key block raises the
+//                      max, P = exp2(x - max) as fp16 into the swizzled A-operand tile in shared
+//                      memory; O / sum -> fp16 -> coalesced stores one item late, while the next
+//                      item's first step is in the tensor core.
 // Every wait is bounded (ptx.cuh): a broken pipeline ends with an error flag, not a hang.
 #include "kernels.h"
 #include "ptx.cuh"
