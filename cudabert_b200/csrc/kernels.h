@@ -169,7 +169,7 @@ int pooler_f32(const float* x, int rows_per_seq, const int* row_start, const flo
 // row_start == null: sequence b occupies rows [b*S, (b+1)*S) (padded layout).  row_start != null
 // (B + 1 entries from row_layout): sequences are packed back to back, sequence b occupies rows
 // [row_start[b], row_start[b+1]) and has no rows for its padding.
-// cls_only != 0 (the three bf16 kernels): only the first query of every sequence is computed and its
+// cls_only != 0 (the three 16-bit kernels): only the first query of every sequence is computed and its
 // result is written to row b of ctx ([B, H]) -- what the last encoder layer needs when only the
 // pooler output is wanted; the arithmetic of that row is the same as in a full pass.
 int attention_f16(const __half* qkv, const int* mask, const int* kv_len, const int* row_start,
@@ -178,7 +178,7 @@ int attention_f32(const float* qkv, const int* mask, const int* kv_len, const in
                   int S, int heads, cudaStream_t stream);
 // tcgen05 variant of attention_f16 (attention_tc.cu): Q, K, V tiles arrive by TMA through `tm_qkv`,
 // a map over the [rows, 3H] projection output made by make_tmap_qkv.  attention_kernel_for says which
-// bf16 kernel a forward pass of padded length S takes (CUDABERT_ATTENTION=tc|persist|mma forces one).
+// 16-bit kernel a forward pass of padded length S takes (CUDABERT_ATTENTION=tc|persist|mma forces one).
 // Persistent variant of attention_f16 (one CTA per SM, TMA-fed K/V slots, query blocks drawn
 // dynamically).  `sched` (2 B entries from row_layout, may be null) orders the items by descending
 // length and says which rows need their mask read; S <= 256.
@@ -189,13 +189,18 @@ int attention_f16_persist(const CUtensorMap* tm_qkv, const int* mask, const int*
 enum AttentionKernel : int { ATT_KERNEL_MMA = 1, ATT_KERNEL_TC = 2, ATT_KERNEL_PERSIST = 3 };
 int attention_kernel_for(int S);
 bool make_tmap_qkv(CUtensorMap* out, const void* qkv, uint64_t rows, int H);
-// `sched` (may be null) as above: only its mask flags are used, the items keep their natural order.
+// `sched` (from row_layout, may be null): its mask flags say which rows need their mask read; with
+// row_start as well it holds the tile table (sched[2 B + t] = sequence of packed row 128 t), and the
+// kernel then cuts the packed rows into 128-row tiles across sequences where that pays (padded lengths
+// that would leave a sequence's last tile under 85 % full), with the same bits as per-sequence tiles.
 int attention_f16_tc(const CUtensorMap* tm_qkv, const int* mask, const int* kv_len, const int* row_start,
                      const int* sched, __half* ctx, int B, int S, int heads, int num_sms, int cls_only, int* err_flag,
                      cudaStream_t stream);
 // kv_len[b] = 1 + index of the last non-zero mask entry of row b (0 if none); mask null => S.
 // row_start (may be null): exclusive prefix sum of the sequence lengths (a length of 0 counts as S),
-// B + 1 entries, the last one being the number of packed rows.
+// B + 1 entries, the last one being the number of packed rows.  sched (may be null): 2 B entries (work
+// order by descending length; mask flags), followed, when row_start is given, by ceil(B S / 128) entries
+// of the tile table.
 int row_layout(const int* mask, int* kv_len, int* row_start, int* sched, int B, int S, cudaStream_t stream);
 
 // ---- row-wise kernels.  The residual stream is kept in fp32; TOut (float or __half) is
