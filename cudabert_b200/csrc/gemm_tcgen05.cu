@@ -1,7 +1,7 @@
 // Dense projection GEMM for sm_100a: out[M, N] = A[M, K] x W[N, K]^T with a fused epilogue.
 //
-// It replaces, for the 16-bit modes (bf16 or FP8 weights, fp16 activations), the reference's cuBLAS SGEMM calls and the
-// kernels around them: the bias pre-fill `MemoryCpyLinear` (ops/linear.cu:23-27), the GEMMs
+// It replaces, in every mode (bf16 or FP8 weights with fp16 activations; fp32 with both operands as three
+// bf16 planes, EPI_SPLIT3), the reference's cuBLAS SGEMM calls and the kernels around them: the bias pre-fill `MemoryCpyLinear` (ops/linear.cu:23-27), the GEMMs
 // of `op_BatchedLinear::forward` (ops/linear.cu:241-319) and `op_Linear::forward`
 // (ops/linear.cu:91-148), the GELU sweep (ops/elementwise.cu:38-51), the residual add that
 // `cuApplyLayerNorm` does in place (ops/layernorm.cu:152-158) and the pooler's tanh
@@ -96,18 +96,6 @@ __device__ __forceinline__ void gelu_erf2(float& a, float& b) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(x));
 }
 
-// Epilogue of one accumulator (128 TMEM lanes x BN columns at `t_acc`), run by the eight epilogue
-// warps; each owns the lane quarter warp % 4 and the column half `half`.  `m0` is the first output
-// row of THIS CTA's 128 rows.
-//
-// FLAGS >= 0 fixes the epilogue at compile time (the combinations the model uses); FLAGS < 0 takes
-// the run-time `flags`.  A thread reads one accumulator ROW from TMEM, but 32 threads storing to 32
-// different rows touch 32 cache lines per instruction, so each warp transposes 32-column chunks
-// through its own 2 KB of shared memory: phase 1, thread = row, writes 16-byte pieces at a swizzled
-// position (conflict-free); phase 2, consecutive lanes cover consecutive bytes of a row, so global
-// stores are full-sector, row-contiguous accesses.  Bias and column scale of the tile are staged
-// in shared memory once per tile.  A residual (tests only: the model adds its residual in the
-// LayerNorm kernel) is read by the row's own thread in phase 1.
 // Row statistics of a LayerNorm input from its per-slice partials (LnFold): mean and 1 / sqrt(var + eps)
 __device__ __forceinline__ void ln_row_stats(const float* __restrict__ stats, int row, int slots, int n, float& mu,
                                              float& rstd) {
@@ -246,6 +234,18 @@ __device__ __forceinline__ void epilogue_tile_sum(uint32_t t_acc, uint8_t* __res
   __syncwarp();
 }
 
+// Epilogue of one accumulator (128 TMEM lanes x BN columns at `t_acc`), run by the eight epilogue
+// warps; each owns the lane quarter warp % 4 and the column half `half`.  `m0` is the first output
+// row of THIS CTA's 128 rows.
+//
+// FLAGS >= 0 fixes the epilogue at compile time (the combinations the model uses); FLAGS < 0 takes
+// the run-time `flags`.  A thread reads one accumulator ROW from TMEM, but 32 threads storing to 32
+// different rows touch 32 cache lines per instruction, so each warp transposes 32-column chunks
+// through its own 2 KB of shared memory: phase 1, thread = row, writes 16-byte pieces at a swizzled
+// position (conflict-free); phase 2, consecutive lanes cover consecutive bytes of a row, so global
+// stores are full-sector, row-contiguous accesses.  Bias and column scale of the tile are staged
+// in shared memory once per tile.  A residual (fp32 mode; the 16-bit modes add theirs in the LayerNorm
+// kernel) is read by the row's own thread in phase 1.
 template <int BN, int FLAGS>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_acc, uint8_t* __restrict__ stage, const float* __restrict__ sbias,
                                               const float* __restrict__ sscale, int warp, int half, int lane, int m0, int n0,
